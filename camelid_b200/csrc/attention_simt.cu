@@ -1,0 +1,247 @@
+// Attention over the paged cache for any head size, head count and grouping, in float
+// arithmetic on the CUDA cores: the kernel of the true 32-bit path, and the path that
+// takes every shape the tensor-core kernels refuse. Prefill and decode are the same kernel
+// with different tilings.
+//
+// It replaces attention_decode (src/cuda_resident.rs:1587), attention_batched (:1994) and
+// the split-K family attn_sk_* (:2332-2487). The arithmetic follows the reference's
+// per-head routine (src/inference.rs:23945-24025): score = (q . k) * scale, running
+// maximum, exp(score - max), and probabilities times values; query head h reads kv head
+// h / (heads / kv_heads) (src/inference/diagnostic_config.rs:300-317). A query at absolute
+// position p sees keys lo..p with lo = max(0, p - window + 1) when a window is set, else 0.
+//
+// Work split: one block handles `rows_per_tile` consecutive new tokens of one sequence,
+// `heads_per_cta` query heads of one kv head, and one contiguous range of key pages
+// (`n_splits` ranges; partial results are merged by attn_combine_kernel). One warp owns one
+// (token, head) pair; the block shares each key/value page through shared memory.
+#include "common.cuh"
+#include <math_constants.h>
+
+struct AttnParams {
+    const void* q;
+    int q_stride;
+    void* out;
+    int out_stride;
+    const void* k_pages;
+    const void* v_pages;
+    const int* block_table;
+    int max_blocks;
+    const int* tile_seq;
+    const int* tile_q0;
+    const int* seq_row0;
+    const int* seq_start;
+    const int* seq_new;
+    int n_heads, n_kv_heads, head_dim;
+    int rows_per_tile, heads_per_cta, head_chunks;
+    int n_splits, window;
+    float scale;
+    float* partial;
+};
+
+template <typename T, int NACC>
+__global__ void attn_paged_simt_kernel(AttnParams p) {
+    extern __shared__ float smem[];
+    const int hd = p.head_dim;
+    const int kstride = hd + 1;
+    const int n_warps = blockDim.x >> 5;
+    float* Ks = smem;                          // [PAGE][hd + 1]
+    float* Vs = Ks + CML_PAGE * kstride;       // [PAGE][hd]
+    float* Qs = Vs + CML_PAGE * hd;            // [warps][hd]
+    float* Ps = Qs + n_warps * hd;             // [warps][PAGE]
+
+    const int tile = blockIdx.x;
+    const int seq = p.tile_seq[tile];
+    const int q0 = p.tile_q0[tile];
+    const int kvh = blockIdx.y / p.head_chunks;
+    const int chunk = blockIdx.y - kvh * p.head_chunks;
+    const int split = blockIdx.z;
+    const int start = p.seq_start[seq];
+    const int n_new = p.seq_new[seq];
+    const int row0 = p.seq_row0[seq];
+    const int group = p.n_heads / p.n_kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r_local = warp / p.heads_per_cta;
+    const int hg = chunk * p.heads_per_cta + (warp - r_local * p.heads_per_cta);
+    const bool valid = (r_local < p.rows_per_tile) && (q0 + r_local < n_new) && (hg < group);
+    const int head = kvh * group + hg;
+    const int row = row0 + q0 + r_local;
+    const int pos = start + q0 + r_local;
+    const int rows_in_tile = min(p.rows_per_tile, n_new - q0);
+    const int kend = start + q0 + rows_in_tile;                       // exclusive
+    const int kbeg = p.window > 0 ? max(0, start + q0 - p.window + 1) : 0;
+    const int b_first = kbeg / CML_PAGE;
+    const int b_last = (kend + CML_PAGE - 1) / CML_PAGE;              // exclusive
+    const int per = (b_last - b_first + p.n_splits - 1) / p.n_splits;
+    const int sb = b_first + split * per;
+    const int se = min(b_last, sb + per);
+    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+
+    const T* q = (const T*)p.q;
+    if (valid)
+        for (int d = lane; d < hd; d += 32) Qs[warp * hd + d] = to_f32(q[(size_t)row * p.q_stride + head * hd + d]);
+
+    float m = -CUDART_INF_F, l = 0.f;
+    float acc[NACC];
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
+
+    const T* kp = (const T*)p.k_pages;
+    const T* vp = (const T*)p.v_pages;
+    for (int b = sb; b < se; ++b) {
+        const int page = p.block_table[(size_t)seq * p.max_blocks + b];
+        const size_t base = ((size_t)page * p.n_kv_heads + kvh) * CML_PAGE * hd;
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < CML_PAGE * hd; idx += blockDim.x) {
+            const int j = idx / hd, d = idx - j * hd;
+            const bool live = (b * CML_PAGE + j) < kend;          // rows past the end may hold anything
+            Ks[j * kstride + d] = live ? to_f32(kp[base + idx]) : 0.f;
+            Vs[idx] = live ? to_f32(vp[base + idx]) : 0.f;
+        }
+        __syncthreads();
+        if (!valid) continue;
+        const int k0 = b * CML_PAGE + lane, k1 = k0 + 32;
+        const float* qv = Qs + warp * hd;
+        const float* ka = Ks + lane * kstride;
+        const float* kb = Ks + (lane + 32) * kstride;
+        float s0 = 0.f, s1 = 0.f;
+        for (int d = 0; d < hd; ++d) {
+            const float qd = qv[d];
+            s0 = fmaf(qd, ka[d], s0);
+            s1 = fmaf(qd, kb[d], s1);
+        }
+        const bool in0 = (k0 >= lo) && (k0 <= pos), in1 = (k1 >= lo) && (k1 <= pos);
+        s0 = in0 ? s0 * p.scale : -CUDART_INF_F;
+        s1 = in1 ? s1 * p.scale : -CUDART_INF_F;
+        const float bm = warp_max(fmaxf(s0, s1));
+        if (bm == -CUDART_INF_F) continue;                         // no visible key in this page
+        const float mn = fmaxf(m, bm);
+        const float corr = (m == -CUDART_INF_F) ? 0.f : expf(m - mn);
+        const float p0 = in0 ? expf(s0 - mn) : 0.f;
+        const float p1 = in1 ? expf(s1 - mn) : 0.f;
+        l = l * corr + warp_sum(p0 + p1);
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) acc[i] *= corr;
+        float* pw = Ps + warp * CML_PAGE;
+        pw[lane] = p0;
+        pw[lane + 32] = p1;
+        __syncwarp();
+        for (int j = 0; j < CML_PAGE; ++j) {
+            const float pj = pw[j];
+            const float* vr = Vs + j * hd;
+#pragma unroll
+            for (int i = 0; i < NACC; ++i) {
+                const int d = lane + 32 * i;
+                if (d < hd) acc[i] = fmaf(pj, vr[d], acc[i]);
+            }
+        }
+        __syncwarp();
+        m = mn;
+    }
+    if (!valid) return;
+    if (p.n_splits == 1) {
+        T* o = (T*)p.out + (size_t)row * p.out_stride + head * hd;
+        const float inv = 1.0f / l;
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) {
+            const int d = lane + 32 * i;
+            if (d < hd) o[d] = from_f32<T>(acc[i] * inv);
+        }
+    } else {
+        float* o = p.partial + (((size_t)row * p.n_heads + head) * p.n_splits + split) * (hd + 2);
+        if (lane == 0) {
+            o[0] = m;
+            o[1] = l;
+        }
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) {
+            const int d = lane + 32 * i;
+            if (d < hd) o[2 + d] = acc[i];
+        }
+    }
+}
+
+// Merge of the key ranges: out = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s, the
+// ranges taken in index order. A range without visible keys has m = -inf and weight 0.
+template <typename T>
+__global__ void attn_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, int out_stride,
+                                    int n_heads, int head_dim, int n_splits) {
+    const int row = blockIdx.x / n_heads, head = blockIdx.x - row * n_heads;
+    const float* base = partial + (size_t)blockIdx.x * n_splits * (head_dim + 2);
+    float M = -CUDART_INF_F;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, base[(size_t)s * (head_dim + 2)]);
+    float L = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = base[(size_t)s * (head_dim + 2)];
+        const float w = (ms == -CUDART_INF_F) ? 0.f : expf(ms - M);
+        L += w * base[(size_t)s * (head_dim + 2) + 1];
+    }
+    const float inv = 1.0f / L;
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float a = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = base[(size_t)s * (head_dim + 2)];
+            const float w = (ms == -CUDART_INF_F) ? 0.f : expf(ms - M);
+            a += w * base[(size_t)s * (head_dim + 2) + 2 + d];
+        }
+        out[(size_t)row * out_stride + head * head_dim + d] = from_f32<T>(a * inv);
+    }
+}
+
+template <typename T>
+static int launch_attn(const AttnParams& p, int n_tiles, int n_rows, cudaStream_t s) {
+    const int hd = p.head_dim;
+    const int warps = p.rows_per_tile * p.heads_per_cta;
+    if (warps < 1 || warps > 32) return CML_ERR_BAD_SIZE;
+    const size_t smem = ((size_t)CML_PAGE * (hd + 1) + (size_t)CML_PAGE * hd + (size_t)warps * hd +
+                         (size_t)warps * CML_PAGE) * sizeof(float);
+    if (smem > 227 * 1024) return CML_ERR_BAD_SIZE;
+    const int nacc = (hd + 31) / 32;
+    dim3 grid(n_tiles, p.n_kv_heads * p.head_chunks, p.n_splits);
+    dim3 block(warps * 32);
+    cudaError_t e = cudaSuccess;
+#define CML_ATTN(N)                                                                                        \
+    do {                                                                                                   \
+        e = cudaFuncSetAttribute(attn_paged_simt_kernel<T, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)smem);                                                               \
+        if (e != cudaSuccess) return (int)e;                                                               \
+        attn_paged_simt_kernel<T, N><<<grid, block, smem, s>>>(p);                                         \
+    } while (0)
+    if (nacc <= 1) CML_ATTN(1);
+    else if (nacc <= 2) CML_ATTN(2);
+    else if (nacc <= 4) CML_ATTN(4);
+    else if (nacc <= 8) CML_ATTN(8);
+    else return CML_ERR_BAD_SIZE;
+#undef CML_ATTN
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    if (p.n_splits > 1) {
+        attn_combine_kernel<T><<<n_rows * p.n_heads, hd >= 128 ? 128 : 64, 0, s>>>(p.partial, (T*)p.out, p.out_stride,
+                                                                                  p.n_heads, hd, p.n_splits);
+        e = cudaGetLastError();
+    }
+    return (int)e;
+}
+
+// `partial` must hold n_rows * n_heads * n_splits * (head_dim + 2) floats when n_splits > 1.
+extern "C" int cml_attn_paged_simt(const void* q, int q_stride, void* out, int out_stride, int dtype,
+                                   const void* k_pages, const void* v_pages, const int* block_table, int max_blocks,
+                                   const int* tile_seq, const int* tile_q0, int n_tiles, const int* seq_row0,
+                                   const int* seq_start, const int* seq_new, int n_rows, int n_heads, int n_kv_heads,
+                                   int head_dim, int rows_per_tile, int heads_per_cta, int head_chunks, int n_splits,
+                                   int window, float scale, float* partial, void* stream) {
+    if (n_tiles <= 0 || n_rows <= 0) return 0;
+    if (head_dim <= 0 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return CML_ERR_BAD_SIZE;
+    if (n_splits < 1 || (n_splits > 1 && partial == nullptr)) return CML_ERR_BAD_SIZE;
+    if (heads_per_cta * head_chunks < n_heads / n_kv_heads) return CML_ERR_BAD_SIZE;
+    AttnParams p;
+    p.q = q; p.q_stride = q_stride; p.out = out; p.out_stride = out_stride;
+    p.k_pages = k_pages; p.v_pages = v_pages; p.block_table = block_table; p.max_blocks = max_blocks;
+    p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.seq_row0 = seq_row0; p.seq_start = seq_start; p.seq_new = seq_new;
+    p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
+    p.rows_per_tile = rows_per_tile; p.heads_per_cta = heads_per_cta; p.head_chunks = head_chunks;
+    p.n_splits = n_splits; p.window = window; p.scale = scale; p.partial = partial;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CML_DTYPE_F32) return launch_attn<float>(p, n_tiles, n_rows, s);
+    if (dtype == CML_DTYPE_BF16) return launch_attn<bf16>(p, n_tiles, n_rows, s);
+    return CML_ERR_BAD_DTYPE;
+}

@@ -1,0 +1,128 @@
+// C[M, N] = A[M, K] * W[N, K]^T on the CUDA cores with float accumulation, for any M, N, K.
+//
+// This is the matrix product of the true 32-bit path (plain FMA, no reduced-precision
+// tensor mode) and the one that takes every shape the tensor-core kernel refuses. It stands
+// where the reference runs q8_gemv / q8_gemm_batched (src/cuda_resident.rs:230, :1494) with
+// their fused residual add (:304-307). Each output element sums k = 0..K-1 in order, in
+// chunks of 16, whatever M is and wherever the element lies in its tile: the value of a
+// row does not depend on which other rows are in the batch.
+//
+// Epilogues: store in the input type; store float; add into a float matrix (the residual
+// stream); SwiGLU, where output column j takes weight rows gate(j) and up(j) of a packed
+// [2*N, K] matrix interleaved in groups of `group` rows and stores silu(g) * u.
+#include "common.cuh"
+
+#define GEMM_BM 64
+#define GEMM_BN 64
+#define GEMM_BK 16
+#define GEMM_PAD 4
+
+enum { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3 };
+
+template <typename T, int EPI>
+__global__ void __launch_bounds__(256)
+gemm_tn_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int ldw, void* __restrict__ Cv,
+                    int ldc, int M, int N, int K, int group) {
+    __shared__ __align__(16) float As[GEMM_BK][GEMM_BM + GEMM_PAD];
+    __shared__ __align__(16) float Ws[GEMM_BK][GEMM_BN + GEMM_PAD];
+    __shared__ __align__(16) float Us[EPI == EPI_SWIGLU ? GEMM_BK : 1][GEMM_BN + GEMM_PAD];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * GEMM_BM, n0 = blockIdx.x * GEMM_BN;
+    const int lr = tid >> 2;            // 0..63: tile row loaded by this thread
+    const int lk = (tid & 3) * 4;       // first of its 4 consecutive k
+
+    float acc[4][4], acc2[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f, acc2[i][j] = 0.f;
+
+    const int arow = m0 + lr;
+    const int wcol = n0 + lr;
+    long wrow = wcol, urow = 0;
+    if (EPI == EPI_SWIGLU) {
+        wrow = (long)(wcol / group) * 2 * group + wcol % group;
+        urow = wrow + group;
+    }
+    for (int k0 = 0; k0 < K; k0 += GEMM_BK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int k = k0 + lk + i;
+            const bool kin = k < K;
+            As[lk + i][lr] = (kin && arow < M) ? to_f32(A[(size_t)arow * lda + k]) : 0.f;
+            Ws[lk + i][lr] = (kin && wcol < N) ? to_f32(W[(size_t)wrow * ldw + k]) : 0.f;
+            if (EPI == EPI_SWIGLU) Us[lk + i][lr] = (kin && wcol < N) ? to_f32(W[(size_t)urow * ldw + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < GEMM_BK; ++k) {
+            const float4 a = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+            const float4 b = *reinterpret_cast<const float4*>(&Ws[k][tx * 4]);
+            const float av[4] = {a.x, a.y, a.z, a.w};
+            const float bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+            if (EPI == EPI_SWIGLU) {
+                const float4 u = *reinterpret_cast<const float4*>(&Us[k][tx * 4]);
+                const float uv[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc2[i][j] = fmaf(av[i], uv[j], acc2[i][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = m0 + ty * 4 + i;
+        if (r >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = n0 + tx * 4 + j;
+            if (c >= N) continue;
+            const size_t o = (size_t)r * ldc + c;
+            if (EPI == EPI_STORE) ((T*)Cv)[o] = from_f32<T>(acc[i][j]);
+            else if (EPI == EPI_STORE_F32) ((float*)Cv)[o] = acc[i][j];
+            else if (EPI == EPI_ADD_F32) ((float*)Cv)[o] += acc[i][j];
+            else {
+                const float g = acc[i][j];
+                ((T*)Cv)[o] = from_f32<T>((g / (1.0f + expf(-g))) * acc2[i][j]);
+            }
+        }
+    }
+}
+
+template <typename T>
+static int launch_gemm(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
+                       int epilogue, int group, cudaStream_t s) {
+    dim3 grid((N + GEMM_BN - 1) / GEMM_BN, (M + GEMM_BM - 1) / GEMM_BM);
+    if (grid.y > 65535) return CML_ERR_BAD_SIZE;
+#define CML_GEMM(E) gemm_tn_simt_kernel<T, E><<<grid, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, C, ldc, M, N, K, group)
+    switch (epilogue) {
+        case EPI_STORE: CML_GEMM(EPI_STORE); break;
+        case EPI_STORE_F32: CML_GEMM(EPI_STORE_F32); break;
+        case EPI_ADD_F32: CML_GEMM(EPI_ADD_F32); break;
+        case EPI_SWIGLU:
+            if (group <= 0 || N % group != 0) return CML_ERR_BAD_SIZE;
+            CML_GEMM(EPI_SWIGLU);
+            break;
+        default: return CML_ERR_BAD_SIZE;
+    }
+#undef CML_GEMM
+    return cml_launch_status();
+}
+
+// A: [M, K] (row stride lda), W: [N, K] (or [2N, K] for SwiGLU; row stride ldw), C: [M, N] (ldc).
+extern "C" int cml_gemm_tn_simt(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
+                                int dtype, int epilogue, int group, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0) return CML_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CML_DTYPE_F32) return launch_gemm<float>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, group, s);
+    if (dtype == CML_DTYPE_BF16) return launch_gemm<bf16>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, group, s);
+    return CML_ERR_BAD_DTYPE;
+}

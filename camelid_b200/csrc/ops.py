@@ -1,0 +1,210 @@
+"""Python faces of the CUDA launchers: argument checks, then one ctypes call on torch's
+current stream. Tensors must live on a CUDA device; a CPU tensor or a missing extension is
+an error, never a detour through library code."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from ..errors import KernelError
+from . import build
+
+PAGE = 64                      # tokens of a cache page; CML_PAGE in common.cuh
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU = 0, 1, 2, 3
+
+_ERRORS = {-2: "unsupported element type", -3: "a size is outside what the kernel takes",
+           -4: "a pointer or stride is not aligned as the kernel needs"}
+
+_SIGNATURES = {
+    ("rowwise", "cml_embed_gather"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    ("rowwise", "cml_rmsnorm"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
+    ("rowwise", "cml_swiglu_packed"): [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    ("rope_kv", "cml_rope_kv_write"): [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ("attention_simt", "cml_attn_paged_simt"): [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                c_void_p, c_void_p],
+    ("gemm_simt", "cml_gemm_tn_simt"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                        c_int, c_int, c_void_p],
+    ("sampling", "cml_argmax_rows"): [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    ("sampling", "cml_adjust_logits"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_float,
+                                        c_void_p],
+    ("sampling", "cml_sample_rows"): [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_void_p,
+                                      c_void_p, c_void_p, c_void_p],
+}
+_fns: dict = {}
+
+
+def _fn(module: str, name: str):
+    f = _fns.get(name)
+    if f is None:
+        lib = build.load(module)
+        f = getattr(lib, name)
+        f.argtypes = _SIGNATURES[(module, name)]
+        f.restype = c_int
+        _fns[name] = f
+    return f
+
+
+def _check(code: int, what: str):
+    if code != 0:
+        if code in _ERRORS:
+            raise KernelError(f"{what}: {_ERRORS[code]}")
+        raise KernelError(f"{what}: CUDA error {code} ({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
+
+
+def _dev(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("camelid_b200 kernels run on CUDA tensors only; there is no CPU path")
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DT[dt]
+    except KeyError:
+        raise KernelError(f"element type {dt} is not supported (float32 and bfloat16 are)") from None
+
+
+# ---------------------------------------------------------------------------------------
+
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err: torch.Tensor):
+    """out[r] = table[tokens[r]] as float32. ``err`` (int32[1]) gets bit 1 on a bad id."""
+    _dev(table, tokens, out, err)
+    rows, hidden = out.shape
+    assert table.shape[1] == hidden and tokens.dtype == torch.int32 and out.dtype == torch.float32
+    assert table.is_contiguous() and out.is_contiguous() and tokens.numel() >= rows
+    _check(_fn("rowwise", "cml_embed_gather")(_p(table), dtype_code(table.dtype), _p(tokens), _p(out), rows, hidden,
+                                             table.shape[0], _p(err), _stream()), "embed_gather")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, rows_index: torch.Tensor | None = None):
+    """out[r] = rmsnorm(x[rows_index[r] or r]) * weight; x float32, out float32 or bfloat16."""
+    _dev(x, weight, out, rows_index)
+    rows, hidden = out.shape
+    assert x.dtype == torch.float32 and x.shape[1] == hidden and weight.shape[0] == hidden
+    assert x.is_contiguous() and out.is_contiguous()
+    if rows_index is not None:
+        assert rows_index.dtype == torch.int32 and rows_index.numel() >= rows
+    _check(_fn("rowwise", "cml_rmsnorm")(_p(x), _p(weight), dtype_code(weight.dtype), _p(out), dtype_code(out.dtype),
+                                        _p(rows_index), rows, hidden, float(eps), _stream()), "rmsnorm")
+
+
+def swiglu_packed(gu: torch.Tensor, act: torch.Tensor, group: int):
+    _dev(gu, act)
+    rows, inter = act.shape
+    assert gu.shape == (rows, 2 * inter) and gu.dtype == act.dtype and gu.is_contiguous() and act.is_contiguous()
+    _check(_fn("rowwise", "cml_swiglu_packed")(_p(gu), _p(act), dtype_code(act.dtype), rows, inter, group, _stream()),
+           "swiglu_packed")
+
+
+def rope_kv_write(qkv: torch.Tensor, row_pos, row_seq, block_table, k_pages, v_pages, inv_freq, rotary_dim: int,
+                  n_heads: int, n_kv_heads: int, head_dim: int, write_kv: bool):
+    """Rotate q (and k) of packed rows in place; write k and v into their cache pages."""
+    _dev(qkv, row_pos, row_seq, block_table, k_pages, v_pages, inv_freq)
+    rows = qkv.shape[0]
+    assert qkv.stride(1) == 1 and inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rotary_dim
+    need = (n_heads + (2 * n_kv_heads if write_kv else 0)) * head_dim
+    assert qkv.shape[1] >= need, (qkv.shape, need)
+    if write_kv:
+        assert k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype
+        assert k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim) and k_pages.is_contiguous() and v_pages.is_contiguous()
+        max_blocks = block_table.shape[1]
+    else:
+        max_blocks = 0
+    _check(_fn("rope_kv", "cml_rope_kv_write")(
+        _p(qkv), dtype_code(qkv.dtype), rows, qkv.stride(0), _p(row_pos), _p(row_seq), _p(block_table), max_blocks,
+        _p(k_pages), _p(v_pages), _p(inv_freq), rotary_dim, n_heads, n_kv_heads, head_dim, 1 if write_kv else 0,
+        _stream()), "rope_kv_write")
+
+
+def attn_tiling(n_heads: int, n_kv_heads: int, decode: bool) -> tuple[int, int, int]:
+    """(rows_per_tile, heads_per_cta, head_chunks) of the float attention kernel: at most 16
+    warps, one per (row, head) pair; the heads of a kv group are cut in chunks if above 16."""
+    group = n_heads // n_kv_heads
+    chunks = (group + 15) // 16
+    hpc = (group + chunks - 1) // chunks
+    rows = 1 if decode else max(1, 16 // hpc)
+    return rows, hpc, chunks
+
+
+def attn_partial_floats(n_rows: int, n_heads: int, head_dim: int, n_splits: int) -> int:
+    return n_rows * n_heads * n_splits * (head_dim + 2) if n_splits > 1 else 0
+
+
+def attn_paged_simt(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_tiles, seq_row0, seq_start, seq_new,
+                    n_rows, n_heads, n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, n_splits,
+                    window, scale, partial):
+    """Attention of packed query rows over the paged cache (float arithmetic). ``q`` may be a
+    column slice of a wider matrix (its row stride is used)."""
+    _dev(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, seq_row0, seq_start, seq_new, partial)
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == v_pages.dtype
+    assert k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim) and k_pages.is_contiguous() and v_pages.is_contiguous()
+    if n_splits > 1:
+        assert partial is not None and partial.dtype == torch.float32
+        assert partial.numel() >= attn_partial_floats(n_rows, n_heads, head_dim, n_splits)
+    _check(_fn("attention_simt", "cml_attn_paged_simt")(
+        _p(q), q.stride(0), _p(out), out.stride(0), dtype_code(q.dtype), _p(k_pages), _p(v_pages), _p(block_table),
+        block_table.shape[1], _p(tile_seq), _p(tile_q0), n_tiles, _p(seq_row0), _p(seq_start), _p(seq_new), n_rows,
+        n_heads, n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, n_splits, int(window or 0),
+        float(scale), _p(partial), _stream()), "attn_paged_simt")
+
+
+def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, group: int = 0):
+    """c[M, N] (op)= a[M, K] @ w[N, K]^T with float accumulation on the CUDA cores.
+    EPI_SWIGLU reads w as packed [2N, K] gate/up rows interleaved in groups of ``group``."""
+    _dev(a, w, c)
+    M, K = a.shape
+    N = c.shape[1]
+    assert c.shape[0] == M and w.shape[1] == K and a.dtype == w.dtype
+    assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+    if epilogue == EPI_SWIGLU:
+        assert w.shape[0] == 2 * N and c.dtype == a.dtype
+    else:
+        assert w.shape[0] == N
+        assert c.dtype == (a.dtype if epilogue == EPI_STORE else torch.float32)
+    _check(_fn("gemm_simt", "cml_gemm_tn_simt")(_p(a), a.stride(0), _p(w), w.stride(0), _p(c), c.stride(0), M, N, K,
+                                                dtype_code(a.dtype), epilogue, group, _stream()), "gemm_tn_simt")
+
+
+def argmax_rows(logits: torch.Tensor, out: torch.Tensor, err: torch.Tensor):
+    _dev(logits, out, err)
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32 and out.numel() >= rows
+    _check(_fn("sampling", "cml_argmax_rows")(_p(logits), logits.stride(0), rows, vocab, _p(out), _p(err), _stream()),
+           "argmax_rows")
+
+
+def adjust_logits(logits: torch.Tensor, entries: torch.Tensor, biases: torch.Tensor, repeat_penalty: float,
+                  presence_penalty: float, frequency_penalty: float):
+    """entries: int32 [n, 3] of (row, token, count in history); biases: float32 [n]."""
+    _dev(logits, entries, biases)
+    n = entries.shape[0]
+    assert entries.dtype == torch.int32 and entries.is_contiguous() and biases.dtype == torch.float32 and biases.numel() == n
+    _check(_fn("sampling", "cml_adjust_logits")(_p(logits), logits.stride(0), logits.shape[1], _p(entries), _p(biases),
+                                               n, float(repeat_penalty), float(presence_penalty),
+                                               float(frequency_penalty), _stream()), "adjust_logits")
+
+
+def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float,
+                draws: torch.Tensor, out: torch.Tensor, err: torch.Tensor):
+    _dev(logits, draws, out, err)
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and draws.dtype == torch.float32
+    assert draws.numel() >= rows and out.dtype == torch.int32 and out.numel() >= rows
+    _check(_fn("sampling", "cml_sample_rows")(_p(logits), logits.stride(0), rows, vocab, float(temperature),
+                                             int(top_k or 0), float(top_p if top_p is not None else 1.0),
+                                             float(min_p or 0.0), _p(draws), _p(out), _p(err), _stream()), "sample_rows")

@@ -1,0 +1,98 @@
+// Rotary position encoding of q and k, fused with the write of k and v into the paged cache.
+//
+// Replaces rope_rotate / rope_batched (src/cuda_resident.rs:1545, :1949) and kv_scatter /
+// kv_scatter_batched (:1569, :1975). The angle is position * frequency in float, its sine
+// and cosine come from sincosf (no fast-math), and pairs are (i, i + rotary_dim/2): the
+// split-half pairing of un-permuted weights (src/inference/rope.rs:489-524, pairing at
+// :501-509). Dimensions at and beyond rotary_dim pass through unchanged.
+//
+// One block per token row. The row's position is absolute; its page is looked up in the
+// block table of its sequence.
+#include "common.cuh"
+
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ row_pos,
+                                     const int* __restrict__ row_seq, const int* __restrict__ block_table,
+                                     int max_blocks, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                     const float* __restrict__ inv_freq, int rotary_dim, int n_heads,
+                                     int n_kv_heads, int head_dim, int write_kv) {
+    extern __shared__ float sc[];              // cos[half], sin[half]
+    const int half = rotary_dim >> 1;
+    float* cs = sc;
+    float* sn = sc + half;
+    const int r = blockIdx.x;
+    const int pos = row_pos[r];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float angle = (float)pos * inv_freq[i];
+        float s, c;
+        sincosf(angle, &s, &c);
+        cs[i] = c;
+        sn[i] = s;
+    }
+    __syncthreads();
+    T* row = qkv + (size_t)r * row_stride;
+
+    // q: rotate in place
+    const int q_pairs = n_heads * half;
+    for (int w = threadIdx.x; w < q_pairs; w += blockDim.x) {
+        const int h = w / half, i = w - h * half;
+        T* p = row + h * head_dim;
+        const float x0 = to_f32(p[i]), x1 = to_f32(p[i + half]);
+        p[i] = from_f32<T>(x0 * cs[i] - x1 * sn[i]);
+        p[i + half] = from_f32<T>(x0 * sn[i] + x1 * cs[i]);
+    }
+    if (!write_kv) return;
+
+    const int seq = row_seq[r];
+    const int page = block_table[(size_t)seq * max_blocks + pos / CML_PAGE];
+    const int in_page = pos % CML_PAGE;
+    const T* ksrc = row + n_heads * head_dim;
+    const T* vsrc = ksrc + n_kv_heads * head_dim;
+    const size_t page_base = (size_t)page * n_kv_heads * CML_PAGE * head_dim;
+
+    // k: rotate, then store; the pass-through dimensions are copied
+    const int k_pairs = n_kv_heads * half;
+    for (int w = threadIdx.x; w < k_pairs; w += blockDim.x) {
+        const int h = w / half, i = w - h * half;
+        const T* p = ksrc + h * head_dim;
+        T* dst = k_pages + page_base + ((size_t)h * CML_PAGE + in_page) * head_dim;
+        const float x0 = to_f32(p[i]), x1 = to_f32(p[i + half]);
+        dst[i] = from_f32<T>(x0 * cs[i] - x1 * sn[i]);
+        dst[i + half] = from_f32<T>(x0 * sn[i] + x1 * cs[i]);
+    }
+    const int tail = head_dim - rotary_dim;
+    if (tail > 0) {
+        for (int w = threadIdx.x; w < n_kv_heads * tail; w += blockDim.x) {
+            const int h = w / tail, i = rotary_dim + (w - h * tail);
+            k_pages[page_base + ((size_t)h * CML_PAGE + in_page) * head_dim + i] = ksrc[h * head_dim + i];
+        }
+    }
+    // v: copy
+    for (int w = threadIdx.x; w < n_kv_heads * head_dim; w += blockDim.x) {
+        const int h = w / head_dim, i = w - h * head_dim;
+        v_pages[page_base + ((size_t)h * CML_PAGE + in_page) * head_dim + i] = vsrc[w];
+    }
+}
+
+extern "C" int cml_rope_kv_write(void* qkv, int dtype, int rows, int row_stride, const int* row_pos,
+                                 const int* row_seq, const int* block_table, int max_blocks, void* k_pages,
+                                 void* v_pages, const float* inv_freq, int rotary_dim, int n_heads,
+                                 int n_kv_heads, int head_dim, int write_kv, void* stream) {
+    if (rows <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return CML_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = (size_t)rotary_dim * sizeof(float);
+    if (smem > 48 * 1024) return CML_ERR_BAD_SIZE;
+    const int block = 128;
+    if (dtype == CML_DTYPE_F32)
+        rope_kv_write_kernel<float><<<rows, block, smem, s>>>((float*)qkv, row_stride, row_pos, row_seq, block_table,
+                                                              max_blocks, (float*)k_pages, (float*)v_pages, inv_freq,
+                                                              rotary_dim, n_heads, n_kv_heads, head_dim, write_kv);
+    else if (dtype == CML_DTYPE_BF16)
+        rope_kv_write_kernel<bf16><<<rows, block, smem, s>>>((bf16*)qkv, row_stride, row_pos, row_seq, block_table,
+                                                             max_blocks, (bf16*)k_pages, (bf16*)v_pages, inv_freq,
+                                                             rotary_dim, n_heads, n_kv_heads, head_dim, write_kv);
+    else
+        return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}

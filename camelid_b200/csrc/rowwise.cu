@@ -1,0 +1,107 @@
+// Row-wise kernels: embedding gather, RMSNorm (optionally of gathered rows), SwiGLU on a
+// packed gate/up matrix. One block per row; all arithmetic in float.
+//
+// What they replace in the reference: the host-side embedding_lookup
+// (src/tensor/mod.rs:2253-2283) and embed_gather_* (src/cuda_resident.rs:2889-2995);
+// rms_norm_f32 / rms_norm_batched (src/cuda_resident.rs:89, :1925), which sum with one
+// thread to keep the CPU's order; silu_mul (src/cuda_resident.rs:1769).
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------
+// out[r, :] = table[tokens[r], :]  (float residual stream). An id outside the vocabulary
+// sets *err and writes zeros; the host checks ids before the launch, this is the net.
+template <typename T>
+__global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                                    float* __restrict__ out, int hidden, int vocab, int* err) {
+    const int r = blockIdx.x;
+    const int tok = tokens[r];
+    float* o = out + (size_t)r * hidden;
+    if (tok < 0 || tok >= vocab) {
+        if (threadIdx.x == 0) atomicOr(err, 1);
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = 0.f;
+        return;
+    }
+    const T* src = table + (size_t)tok * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = to_f32(src[c]);
+}
+
+extern "C" int cml_embed_gather(const void* table, int dtype, const int* tokens, float* out, int rows,
+                                int hidden, int vocab, int* err, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int block = hidden >= 1024 ? 256 : 128;
+    if (dtype == CML_DTYPE_F32)
+        embed_gather_kernel<float><<<rows, block, 0, s>>>((const float*)table, tokens, out, hidden, vocab, err);
+    else if (dtype == CML_DTYPE_BF16)
+        embed_gather_kernel<bf16><<<rows, block, 0, s>>>((const bf16*)table, tokens, out, hidden, vocab, err);
+    else
+        return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}
+
+// ------------------------------------------------------------------------------------
+// y = x * rsqrt(mean(x^2) + eps) * w, multiplied in that order (src/tensor/mod.rs:2086-2096).
+// `rows_index` (may be null) picks the input row of each output row, so that the final norm
+// runs only on the rows whose logits are wanted.
+template <typename TW, typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
+                               const int* __restrict__ rows_index, int hidden, float eps) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const int src = rows_index ? rows_index[r] : r;
+    const float* xr = x + (size_t)src * hidden;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = xr[c];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+    TO* o = out + (size_t)r * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f32<TO>(xr[c] * scale * to_f32(w[c]));
+}
+
+extern "C" int cml_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype,
+                           const int* rows_index, int rows, int hidden, float eps, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int block = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+#define CML_RMS(TW, TO) rmsnorm_kernel<TW, TO><<<rows, block, 0, s>>>(x, (const TW*)w, (TO*)out, rows_index, hidden, eps)
+    if (w_dtype == CML_DTYPE_F32 && out_dtype == CML_DTYPE_F32) CML_RMS(float, float);
+    else if (w_dtype == CML_DTYPE_F32 && out_dtype == CML_DTYPE_BF16) CML_RMS(float, bf16);
+    else if (w_dtype == CML_DTYPE_BF16 && out_dtype == CML_DTYPE_F32) CML_RMS(bf16, float);
+    else if (w_dtype == CML_DTYPE_BF16 && out_dtype == CML_DTYPE_BF16) CML_RMS(bf16, bf16);
+    else return CML_ERR_BAD_DTYPE;
+#undef CML_RMS
+    return cml_launch_status();
+}
+
+// ------------------------------------------------------------------------------------
+// act[r, j] = silu(g) * u with g / (1 + exp(-g)) (src/inference.rs:9657-9664), on a packed
+// matrix gu[r, 2*inter] whose rows of weights were interleaved in groups of `group`:
+// gate j sits at column (j / group) * 2 * group + j % group, up j `group` columns later.
+template <typename T>
+__global__ void swiglu_packed_kernel(const T* __restrict__ gu, T* __restrict__ act, int inter, int group) {
+    const int r = blockIdx.x;
+    const T* row = gu + (size_t)r * 2 * inter;
+    T* o = act + (size_t)r * inter;
+    for (int j = threadIdx.x; j < inter; j += blockDim.x) {
+        const int col = (j / group) * 2 * group + j % group;
+        const float g = to_f32(row[col]);
+        const float u = to_f32(row[col + group]);
+        o[j] = from_f32<T>((g / (1.0f + expf(-g))) * u);
+    }
+}
+
+extern "C" int cml_swiglu_packed(const void* gu, void* act, int dtype, int rows, int inter, int group, void* stream) {
+    if (rows <= 0) return 0;
+    if (group <= 0 || inter % group != 0) return CML_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CML_DTYPE_F32)
+        swiglu_packed_kernel<float><<<rows, 256, 0, s>>>((const float*)gu, (float*)act, inter, group);
+    else if (dtype == CML_DTYPE_BF16)
+        swiglu_packed_kernel<bf16><<<rows, 256, 0, s>>>((const bf16*)gu, (bf16*)act, inter, group);
+    else
+        return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}

@@ -1,0 +1,310 @@
+// Sampling on the device: greedy argmax and the reference's stochastic sampler
+// (temperature, top-k, min-p, top-p), one block per row of logits.
+//
+// Greedy follows greedy_sample (src/inference.rs:5890-5925; device twin argmax_f32 at
+// src/cuda_resident.rs:1847): strict '>', so the lowest index among equal maxima wins, and
+// non-finite logits are an error. The stochastic sampler follows sample_with_config
+// (src/inference.rs:5991-6091): candidates ordered by logit descending with ties by index
+// ascending; top_k keeps a prefix; softmax of logit/T minus its maximum; min_p keeps
+// p >= min_p * p_max and renormalises; top_p keeps the shortest prefix whose cumulative
+// probability reaches top_p and renormalises; the token is the first whose cumulative
+// probability exceeds the draw. The reference sorts; here every stage is a selection in the
+// same total order, found by descending the bits of a 64-bit key (orderable logit bits,
+// then inverted index) with per-digit histograms of weight, so no sort is needed. Sums are
+// kept in double; the reference's sequential float sums can differ from them in the last
+// bits, which moves a decision only when the draw or top_p lies on a boundary.
+#include "common.cuh"
+#include <math_constants.h>
+
+#define SAMPLE_THREADS 1024
+#define SAMPLE_ERR_NONFINITE 1
+#define SAMPLE_ERR_EMPTY 2
+
+__device__ __forceinline__ unsigned int orderable_bits(float v) {
+    const unsigned int u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);       // larger float -> larger unsigned
+}
+__device__ __forceinline__ unsigned long long composite_key(float v, int idx) {
+    return ((unsigned long long)orderable_bits(v) << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)idx);
+}
+
+// ------------------------------------------------------------------------------------
+__global__ void argmax_rows_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out,
+                                   int* __restrict__ err) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    float best = -CUDART_INF_F;
+    int best_i = 0x7fffffff;
+    bool bad = false;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (!isfinite(v)) bad = true;
+        if (v > best) best = v, best_i = i;          // ascending i per thread: first maximum kept
+    }
+    if (bad) atomicOr(err, SAMPLE_ERR_NONFINITE);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) best = ov, best_i = oi;
+    }
+    if (lane == 0) sv[warp] = best, si[warp] = best_i;
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = blockDim.x >> 5;
+        best = lane < nw ? sv[lane] : -CUDART_INF_F;
+        best_i = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ov > best || (ov == best && oi < best_i)) best = ov, best_i = oi;
+        }
+        if (lane == 0) out[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
+    }
+}
+
+extern "C" int cml_argmax_rows(const float* logits, int ld, int rows, int vocab, int* out, int* err, void* stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0) return CML_ERR_BAD_SIZE;
+    argmax_rows_kernel<<<rows, vocab >= 4096 ? 1024 : 256, 0, (cudaStream_t)stream>>>(logits, ld, vocab, out, err);
+    return cml_launch_status();
+}
+
+// ------------------------------------------------------------------------------------
+// Adjustments before sampling (src/inference.rs:6093-6157): for each listed (row, token,
+// count, bias) entry, logit += bias; then, if count > 0: repeat penalty (divide a positive
+// logit, multiply a negative one), minus presence, minus frequency * count. The host builds
+// the list from the history (one entry per distinct token) and the bias table.
+__global__ void adjust_logits_kernel(float* __restrict__ logits, int ld, int vocab, const int* __restrict__ entries,
+                                     const float* __restrict__ biases, int n_entries, float repeat_penalty,
+                                     float presence_penalty, float frequency_penalty) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n_entries) return;
+    const int row = entries[3 * e], tok = entries[3 * e + 1], count = entries[3 * e + 2];
+    if (tok < 0 || tok >= vocab) return;
+    float v = logits[(size_t)row * ld + tok] + biases[e];
+    if (count > 0) {
+        if (repeat_penalty != 1.0f) v = v > 0.f ? v / repeat_penalty : v * repeat_penalty;
+        if (presence_penalty != 0.0f) v -= presence_penalty;
+        if (frequency_penalty != 0.0f) v -= frequency_penalty * (float)count;
+    }
+    logits[(size_t)row * ld + tok] = v;
+}
+
+extern "C" int cml_adjust_logits(float* logits, int ld, int vocab, const int* entries, const float* biases,
+                                 int n_entries, float repeat_penalty, float presence_penalty,
+                                 float frequency_penalty, void* stream) {
+    if (n_entries <= 0) return 0;
+    adjust_logits_kernel<<<(n_entries + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+        logits, ld, vocab, entries, biases, n_entries, repeat_penalty, presence_penalty, frequency_penalty);
+    return cml_launch_status();
+}
+
+// ------------------------------------------------------------------------------------
+// Selection in the total order (key descending). The weight of element i is given by the
+// functor; elements with key < floor_key are not candidates. Finds the first candidate at
+// which the inclusive cumulative weight reaches (`strict` 0: >=, 1: >) the target, and
+// returns its key and that inclusive sum. If the total never reaches the target the last
+// candidate (floor) is returned with the total.
+struct SelectShared {
+    double mass[256];
+    unsigned int count[256];
+    unsigned long long prefix;
+    double before;
+    int chosen;
+    int found;
+};
+
+template <typename WeightFn>
+__device__ void select_by_mass(const float* row, int vocab, unsigned long long floor_key, double target, int strict,
+                               WeightFn weight, SelectShared* sh, unsigned long long* out_key, double* out_cum) {
+    unsigned long long prefix = 0;      // digits chosen so far, in place
+    double before = 0.0;                // mass of candidates ordered before the chosen prefix
+    for (int shift = 56; shift >= 0; shift -= 8) {
+        for (int b = threadIdx.x; b < 256; b += blockDim.x) sh->mass[b] = 0.0, sh->count[b] = 0u;
+        __syncthreads();
+        const unsigned long long hi_mask = shift == 56 ? 0ull : (~0ull << (shift + 8));
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float v = row[i];
+            const unsigned long long key = composite_key(v, i);
+            if (key < floor_key || (key & hi_mask) != prefix) continue;
+            const int bin = (int)((key >> shift) & 0xFFull);
+            atomicAdd(&sh->mass[bin], (double)weight(v, i));
+            atomicAdd(&sh->count[bin], 1u);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double acc = before;
+            int chosen = -1, last = -1;
+            for (int b = 255; b >= 0; --b) {
+                if (sh->count[b] == 0u) continue;
+                last = b;
+                const double inc = acc + sh->mass[b];
+                if (strict ? (inc > target) : (inc >= target)) { chosen = b; break; }
+                acc = inc;
+            }
+            if (chosen < 0) {           // never reached: settle on the last candidate
+                chosen = last;
+                acc -= sh->mass[last];
+            }
+            sh->chosen = chosen;
+            sh->before = acc;
+        }
+        __syncthreads();
+        if (sh->chosen < 0) {           // no candidate at all
+            *out_key = floor_key;
+            *out_cum = before;
+            return;
+        }
+        prefix |= ((unsigned long long)sh->chosen) << shift;
+        before = sh->before;
+        __syncthreads();
+    }
+    // prefix is now the full key of one element
+    if (threadIdx.x == 0) sh->found = 0;
+    __syncthreads();
+    *out_key = prefix;
+    const int idx = (int)(0xFFFFFFFFu - (unsigned int)(prefix & 0xFFFFFFFFull));
+    double w = 0.0;
+    if (idx >= 0 && idx < vocab) w = (double)weight(row[idx], idx);
+    *out_cum = before + w;
+}
+
+struct SampleParams {
+    float temperature;
+    int top_k;          // 0: off
+    float top_p;        // >= 1: off
+    float min_p;        // <= 0: off
+};
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SampleParams sp,
+                   const float* __restrict__ draws, int* __restrict__ out, int* __restrict__ err) {
+    __shared__ SelectShared sh;
+    __shared__ float red[33];
+    __shared__ double dred[33];
+    __shared__ unsigned long long kred[33];
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+
+    // maximum logit and finiteness
+    float mx = -CUDART_INF_F;
+    bool bad = false;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (!isfinite(v)) bad = true;
+        mx = fmaxf(mx, v);
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    if (bad) atomicOr(err, SAMPLE_ERR_NONFINITE);
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? red[lane] : -CUDART_INF_F;
+        t = warp_max(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    mx = red[32];
+    const float T = sp.temperature;
+    const float max_scaled = mx / T;
+
+    unsigned long long floor_key = 0ull;
+    unsigned long long key;
+    double cum;
+    // top_k: the k-th candidate in order becomes the floor
+    if (sp.top_k > 0 && sp.top_k < vocab) {
+        select_by_mass(row, vocab, 0ull, (double)sp.top_k, 0, [](float, int) { return 1.0f; }, &sh, &key, &cum);
+        floor_key = key;
+        __syncthreads();
+    }
+    // softmax weights and their sum over the candidates
+    auto raw_weight = [=](float v, int) { return expf(v / T - max_scaled); };
+    double part = 0.0;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (composite_key(v, i) >= floor_key) part += (double)raw_weight(v, i);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (lane == 0) dred[warp] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int i = 0; i < nw; ++i) t += dred[i];
+        dred[32] = t;
+    }
+    __syncthreads();
+    const float total = (float)dred[32];
+    if (!(total > 0.f) || !isfinite(total)) {
+        if (threadIdx.x == 0) { atomicOr(err, SAMPLE_ERR_EMPTY); out[blockIdx.x] = 0; }
+        return;
+    }
+    float renorm = 1.0f;                 // successive renormalisations: p = w / total / renorm...
+    float renorm2 = 1.0f;
+    // min_p: keep p >= min_p * p_max, p_max being the first candidate's probability
+    if (sp.min_p > 0.f) {
+        const float pmax = 1.0f / total;             // weight of the maximum is exp(0) = 1
+        const float thr = sp.min_p * pmax;
+        unsigned long long kmin = ~0ull;
+        double s = 0.0;
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float v = row[i];
+            const unsigned long long ck = composite_key(v, i);
+            if (ck < floor_key) continue;
+            const float p = raw_weight(v, i) / total;
+            if (p >= thr) { s += (double)p; kmin = ck < kmin ? ck : kmin; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            s += __shfl_xor_sync(0xffffffffu, s, o);
+            const unsigned long long ok = __shfl_xor_sync(0xffffffffu, kmin, o);
+            kmin = ok < kmin ? ok : kmin;
+        }
+        __syncthreads();
+        if (lane == 0) dred[warp] = s, kred[warp] = kmin;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0.0;
+            unsigned long long k = ~0ull;
+            for (int i = 0; i < nw; ++i) { t += dred[i]; k = kred[i] < k ? kred[i] : k; }
+            dred[32] = t;
+            kred[32] = k;
+        }
+        __syncthreads();
+        if (kred[32] != ~0ull && dred[32] > 0.0) {
+            floor_key = kred[32];
+            renorm = (float)dred[32];
+        }
+        __syncthreads();
+    }
+    // top_p: shortest prefix whose cumulative probability reaches top_p
+    if (sp.top_p < 1.0f) {
+        auto p1 = [=](float v, int) { return raw_weight(v, 0) / total / renorm; };
+        select_by_mass(row, vocab, floor_key, (double)sp.top_p, 0, p1, &sh, &key, &cum);
+        floor_key = key;
+        renorm2 = (float)cum;
+        __syncthreads();
+    }
+    // the draw
+    auto p2 = [=](float v, int) { return raw_weight(v, 0) / total / renorm / renorm2; };
+    select_by_mass(row, vocab, floor_key, (double)draws[blockIdx.x], 1, p2, &sh, &key, &cum);
+    if (threadIdx.x == 0) out[blockIdx.x] = (int)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull));
+}
+
+// draws[r] in [0, 1) is computed by the host from the seed and the length of the history.
+extern "C" int cml_sample_rows(const float* logits, int ld, int rows, int vocab, float temperature, int top_k,
+                               float top_p, float min_p, const float* draws, int* out, int* err, void* stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0 || !(temperature > 0.f)) return CML_ERR_BAD_SIZE;
+    SampleParams sp;
+    sp.temperature = temperature;
+    sp.top_k = top_k;
+    sp.top_p = top_p;
+    sp.min_p = min_p;
+    sample_rows_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, ld, vocab, sp, draws, out, err);
+    return cml_launch_status();
+}

@@ -1,0 +1,190 @@
+"""The model as the engine sees it: parts built from a plan, and one step function.
+
+``step`` takes a batch of sequences with unequal numbers of new tokens (whole prompts in
+one step, then one token each; any mix works, since every row carries its own position),
+runs exactly those tokens as one packed batch against the cache, and returns the float32
+logits at the wanted places. Every check happens before any device work, so a refused
+step leaves the cache as it was (the reference's precedent: tests/inference_session.rs:409-543).
+
+The reference's counterparts are the session's ``generate_next_token`` path
+(src/inference.rs:4383-4548) with ``forward_prefill_chunk_timed_fast`` (:3657-3751) and
+the resident engine's ``forward_pass_inner`` / ``run_batched_layer_stack``
+(src/cuda_resident.rs:6445-7426, :7975-8289); logits only where asked follows
+``forward_final_norm_and_logits`` (src/inference.rs:3638-3651).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..cache.sequence_cache import SequenceCache
+from ..config.plan import ModelPlan
+from ..config.registry import load_config
+from ..errors import KernelError, StepError
+from ..parts import build_block, build_part
+from ..weights.loader import check_tensors
+from ..weights.safetensors_io import ModelFiles
+from .context import StepContext, Workspace
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"compute type must be bfloat16 or float32, got {dtype}")
+        return dtype
+    try:
+        return _DTYPES[str(dtype)]
+    except KeyError:
+        raise ValueError(f"compute type must be 'bfloat16' or 'float32', got {dtype!r}") from None
+
+
+@dataclass
+class StepEntry:
+    """One sequence of a step: its slot, its next tokens, and the places among these tokens
+    (0-based) whose logits are wanted."""
+    slot: int
+    tokens: list
+    want: list = field(default_factory=list)
+
+
+class DecoderModel:
+    def __init__(self, plan: ModelPlan, *, dtype=torch.bfloat16, device="cuda", typed_config=None):
+        self.plan = plan
+        self.typed_config = typed_config
+        self.dtype = parse_dtype(dtype)
+        self.device = torch.device(device)
+        self.embedding = build_part("embedding", plan.embedding)
+        self.blocks = [build_block(layer) for layer in plan.layers]
+        self.final_norm = build_part("norm", plan.final_norm)
+        self.head = build_part("head", plan.head)
+        self.schedule = list(plan.schedule)
+        self.hidden_size = plan.hidden_size
+        self.vocab_size = plan.vocab_size
+        self.loaded = False
+        self.workspace = Workspace(self.device)
+        self._err = None
+        self.last_h2d_bytes = 0
+
+    # ---- construction ----
+    @classmethod
+    def from_config(cls, config, *, dtype=torch.bfloat16, device="cuda") -> "DecoderModel":
+        """``config``: a config.json dict or a model folder. Builds the parts; no weights yet."""
+        _arch, typed, plan = load_config(config)
+        return cls(plan, dtype=dtype, device=device, typed_config=typed)
+
+    @classmethod
+    def from_folder(cls, folder: str, *, dtype=torch.bfloat16, device="cuda") -> "DecoderModel":
+        model = cls.from_config(folder, dtype=dtype, device=device)
+        files = ModelFiles(folder)
+        try:
+            model.load_tensors(files)
+        finally:
+            files.close()
+        return model
+
+    def tensor_specs(self) -> dict:
+        specs = dict(self.embedding.tensor_specs())
+        for b in self.blocks:
+            specs.update(b.tensor_specs())
+        specs.update(self.final_norm.tensor_specs())
+        specs.update(self.head.tensor_specs())
+        return specs
+
+    def load_tensors(self, source) -> None:
+        """``source``: ``ModelFiles`` or a dict name -> tensor. Checks names and shapes first."""
+        specs = self.tensor_specs()
+        if isinstance(source, dict):
+            found = {n: (tuple(t.shape), t.dtype) for n, t in source.items()}
+            get = source.__getitem__
+        else:
+            found = {n: (tuple(source.shape(n)), source.dtype(n)) for n in source.names()}
+            get = source.tensor
+        tied = getattr(self.head, "tied_to", None)
+        tolerated = (self.head.prefix + "weight",) if tied else ()
+        check_tensors(specs, found, tolerated=tolerated)
+
+        class _Lazy(dict):
+            def __missing__(self, name):
+                return get(name)
+        tensors = _Lazy()
+        self.embedding.load(tensors, self.device, self.dtype)
+        for b in self.blocks:
+            b.load(tensors, self.device, self.dtype)
+        self.final_norm.load(tensors, self.device, self.dtype)
+        if tied:
+            self.head.load(tensors, self.device, self.dtype, tied_weight=self.embedding.weight)
+        else:
+            self.head.load(tensors, self.device, self.dtype)
+        self.loaded = True
+
+    # ---- cache ----
+    def entry_cache_specs(self) -> list:
+        return [self.blocks[e.layer].cache_spec() for e in self.schedule]
+
+    def new_cache(self, max_tokens: int, max_slots: int | None = None) -> SequenceCache:
+        """A cache for at most ``max_tokens`` live tokens (each sequence's count rounded up to
+        a multiple of 64) and ``max_slots`` live sequences (default: one per page)."""
+        return SequenceCache(self.entry_cache_specs(), [e.cache_source for e in self.schedule],
+                             max_tokens=max_tokens, max_position=self.plan.max_position, dtype=self.dtype,
+                             device=self.device, max_slots=max_slots)
+
+    # ---- the step ----
+    def _validate(self, cache: SequenceCache, entries: list) -> None:
+        if not self.loaded:
+            raise StepError("the model has no weights yet")
+        if self.device.type != "cuda":
+            raise KernelError("steps run on a CUDA device only; there is no CPU path")
+        if not entries:
+            raise StepError("a step needs at least one sequence")
+        for e in entries:
+            if len(e.tokens) == 0:
+                raise StepError(f"slot {e.slot}: a step must bring at least one token")
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab_size:
+                    raise StepError(f"slot {e.slot}: token id {t} is outside the vocabulary of {self.vocab_size}")
+            for w in e.want:
+                if not 0 <= int(w) < len(e.tokens):
+                    raise StepError(f"slot {e.slot}: wanted place {w} is outside the step's {len(e.tokens)} tokens")
+        cache.book.check_extend([(e.slot, len(e.tokens)) for e in entries])
+
+    def step(self, cache: SequenceCache, entries: list) -> torch.Tensor:
+        """Run the given tokens; returns float32 logits [wanted places, vocabulary] in the order
+        of the entries and of their ``want`` lists (an empty tensor if nothing is wanted)."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        self._validate(cache, entries)
+        starts = [cache.book.extend(e.slot, len(e.tokens)) for e in entries]
+        ctx = StepContext(cache=cache, workspace=self.workspace, dtype=self.dtype, device=self.device,
+                          slots=[e.slot for e in entries], starts=starts,
+                          tokens=[[int(t) for t in e.tokens] for e in entries],
+                          want=[[int(w) for w in e.want] for e in entries])
+        logits = self.run(ctx)
+        for e in entries:
+            cache.book.commit(e.slot, len(e.tokens))
+        self.last_h2d_bytes = ctx.h2d_bytes
+        return logits
+
+    def run(self, ctx: StepContext) -> torch.Tensor:
+        """The forward pass of one step on a prepared context."""
+        if self._err is None:
+            self._err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        h = ctx.buffer("hidden", (ctx.n_rows, self.hidden_size), torch.float32)
+        self.embedding.forward(ctx, ctx.tokens, h, self._err)
+        for i, e in enumerate(self.schedule):
+            ctx.entry = i
+            ctx.cache_source = e.cache_source
+            self.blocks[e.layer].forward(ctx, h)
+        logits = torch.empty((ctx.n_want, self.vocab_size), dtype=torch.float32, device=self.device)
+        if ctx.n_want:
+            x = self.final_norm.forward(ctx, h, rows_index=ctx.want_rows, n_rows=ctx.n_want, name="final_normed")
+            self.head.forward(ctx, x, logits)
+        return logits
+
+    def check_device_errors(self) -> None:
+        """Reads the device-side error word (a synchronising copy) and raises if a kernel saw
+        a token id outside the vocabulary."""
+        if self._err is not None and int(self._err.item()) != 0:
+            self._err.zero_()
+            raise StepError("a kernel met a token id outside the vocabulary")

@@ -1,0 +1,108 @@
+"""Grouped-query attention over the paged cache, as a mixer.
+
+q, k, v = x Wq^T, x Wk^T, x Wv^T without bias (src/inference.rs:6301-6336), here one
+product with the three matrices stacked; rotary encoding of q and k before the keys are
+kept (src/inference.rs:23244-23281); attention of every new row over the keys of its own
+sequence, causal, head h reading kv head h / (heads / kv_heads), scale 1/sqrt(head_dim)
+(src/inference.rs:23945-24025, src/inference/diagnostic_config.rs:300-317); output
+projection added into the residual stream (src/inference.rs:6487-6522).
+
+An entry of the schedule that reads another entry's cache projects only q and writes
+nothing. ``window`` (None for Llama) limits every query to the last ``window`` keys.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache.book import PAGE, KVSpec
+from ..config.plan import PartSpec
+from ..csrc import ops
+from . import linear
+from .base import Part, TensorSpec, build_part, register_part, to_device
+
+_attention_tc = None          # set by camelid_b200.parts.attention_tc when its kernels are available
+
+
+def set_tensor_core_path(fn) -> None:
+    global _attention_tc
+    _attention_tc = fn
+
+
+@register_part("mixer", "attention")
+class GroupedQueryAttention(Part):
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.hidden_size = int(params["hidden_size"])
+        self.num_heads = int(params["num_heads"])
+        self.num_kv_heads = int(params["num_kv_heads"])
+        self.head_dim = int(params["head_dim"])
+        self.window = params.get("window")
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"{self.num_kv_heads} kv heads do not divide {self.num_heads} heads")
+        if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
+            raise ValueError(f"the attention kernels take head sizes 16..256 in steps of 16, got {self.head_dim}")
+        pos = params.get("position") or PartSpec("none")
+        self.position = build_part("position", pos)
+        if self.position.rotary_dim > self.head_dim:
+            raise ValueError(f"rotary_dim {self.position.rotary_dim} exceeds head_dim {self.head_dim}")
+        self.q_width = self.num_heads * self.head_dim
+        self.kv_width = self.num_kv_heads * self.head_dim
+        self.scale = 1.0 / math.sqrt(self.head_dim)
+        self.w_qkv = None
+        self.w_o = None
+
+    def tensor_specs(self):
+        p = self.prefix
+        return {
+            p + "q_proj.weight": TensorSpec((self.q_width, self.hidden_size)),
+            p + "k_proj.weight": TensorSpec((self.kv_width, self.hidden_size)),
+            p + "v_proj.weight": TensorSpec((self.kv_width, self.hidden_size)),
+            p + "o_proj.weight": TensorSpec((self.hidden_size, self.q_width)),
+        }
+
+    def load(self, tensors, device, dtype):
+        p = self.prefix
+        parts = [to_device(tensors[p + n], device, dtype) for n in ("q_proj.weight", "k_proj.weight", "v_proj.weight")]
+        self.w_qkv = torch.cat(parts, dim=0).contiguous()
+        self.w_o = to_device(tensors[p + "o_proj.weight"], device, dtype)
+        self.position.load(tensors, device, dtype)
+
+    def cache_spec(self):
+        return KVSpec(self.num_kv_heads, self.head_dim, self.window)
+
+    # ------------------------------------------------------------------------------
+    def forward(self, ctx, x, residual):
+        n = ctx.n_rows
+        borrow = ctx.cache_source is not None
+        group, k_pages, v_pages = ctx.kv()
+        table = ctx.block_table(group)
+        width = self.q_width if borrow else self.q_width + 2 * self.kv_width
+        qkv = ctx.buffer("qkv", (n, width))
+        linear.linear(ctx, x, self.w_qkv[:width], qkv, linear.STORE)
+        ops.rope_kv_write(qkv, ctx.row_pos, ctx.row_seq, table, k_pages, v_pages, self.position.inv_freq,
+                          self.position.rotary_dim, self.num_heads, self.num_kv_heads, self.head_dim,
+                          write_kv=not borrow)
+        out = ctx.buffer("attn_out", (n, self.q_width))
+        q = qkv[:, :self.q_width]
+        if not (_attention_tc is not None and _attention_tc(self, ctx, q, out, k_pages, v_pages, table)):
+            self._attend_simt(ctx, q, out, k_pages, v_pages, table)
+        linear.linear(ctx, out, self.w_o, residual, linear.ADD_F32)
+
+    def _attend_simt(self, ctx, q, out, k_pages, v_pages, table):
+        rows, hpc, chunks = ops.attn_tiling(self.num_heads, self.num_kv_heads, ctx.decode)
+        tile_seq, tile_q0, n_tiles = ctx.query_tiles(rows)
+        n_splits, partial = 1, None
+        if ctx.decode:
+            blocks = ctx.max_blocks_in_use
+            if self.window:
+                blocks = min(blocks, (self.window + PAGE - 1) // PAGE + 1)
+            ctas = n_tiles * self.num_kv_heads * chunks
+            n_splits = max(1, min(blocks, (2 * 148 + ctas - 1) // ctas, 64))
+            if n_splits > 1:
+                partial = ctx.buffer("attn_partial", (ops.attn_partial_floats(ctx.n_rows, self.num_heads, self.head_dim,
+                                                                             n_splits),), torch.float32)
+        ops.attn_paged_simt(q, out, k_pages, v_pages, table, tile_seq, tile_q0, n_tiles, ctx.seq_row0, ctx.seq_start,
+                            ctx.seq_new, ctx.n_rows, self.num_heads, self.num_kv_heads, self.head_dim, rows, hpc,
+                            chunks, n_splits, self.window or 0, self.scale, partial)

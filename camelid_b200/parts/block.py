@@ -1,0 +1,38 @@
+"""Arrangements of a layer's parts. ``prenorm`` is the reference's decoder layer
+(src/inference.rs:6228-6804): r = x + mixer(norm1(x)); out = r + ffn(norm2(r)). The
+residual stream stays float32; mixer and feed-forward add into it in place."""
+from __future__ import annotations
+
+from .base import Part, build_part, register_part
+
+
+@register_part("block", "prenorm")
+class PreNormBlock(Part):
+    def __init__(self, layer_spec):
+        super().__init__({}, "")
+        self.norm1 = build_part("norm", layer_spec.norm1)
+        self.mixer = build_part("mixer", layer_spec.mixer)
+        self.norm2 = build_part("norm", layer_spec.norm2)
+        self.ffn = build_part("ffn", layer_spec.ffn)
+
+    def parts(self):
+        return (self.norm1, self.mixer, self.norm2, self.ffn)
+
+    def tensor_specs(self):
+        out = {}
+        for p in self.parts():
+            out.update(p.tensor_specs())
+        return out
+
+    def load(self, tensors, device, dtype):
+        for p in self.parts():
+            p.load(tensors, device, dtype)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, ctx, h):
+        x = self.norm1.forward(ctx, h)
+        self.mixer.forward(ctx, x, h)
+        x = self.norm2.forward(ctx, h)
+        self.ffn.forward(ctx, x, h)

@@ -1,0 +1,33 @@
+"""RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w in float32 (src/tensor/mod.rs:2086-2096;
+device twins rms_norm_f32 and rms_norm_batched at src/cuda_resident.rs:89, :1925). The
+input is the float32 residual stream; the output has the compute type."""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .base import Part, TensorSpec, register_part, to_device
+
+
+@register_part("norm", "rmsnorm")
+class RMSNorm(Part):
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.hidden_size = int(params["hidden_size"])
+        self.eps = float(params["eps"])
+        self.weight = None
+
+    def tensor_specs(self):
+        return {self.prefix + "weight": TensorSpec((self.hidden_size,), "norm")}
+
+    def load(self, tensors, device, dtype):
+        w = tensors[self.prefix + "weight"]
+        # a weight stored in 32-bit stays so; a 16-bit one becomes float32 only on the float32 path
+        keep = None if w.dtype == torch.float32 else dtype
+        self.weight = to_device(w, device, keep)
+
+    def forward(self, ctx, h, rows_index=None, n_rows=None, name="normed"):
+        rows = h.shape[0] if n_rows is None else n_rows
+        out = ctx.buffer(name, (rows, self.hidden_size))
+        ops.rmsnorm(h, self.weight, self.eps, out, rows_index)
+        return out
