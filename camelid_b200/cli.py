@@ -1,0 +1,162 @@
+"""The ``camelid`` command line.
+
+    camelid generate MODEL [--prompt "5 17 3" | --prompt-file F] [--max-tokens 128]
+                     [--temperature 0] [--top-k K] [--top-p P] [--min-p P] [--seed S] ...
+    camelid bench-generate ...   the same, one JSON object per iteration on stdout
+    camelid replay --model DIR --dtype T --out DIR --max-tokens N     (bin/trace_run)
+    camelid bench [--batch 8] [--prompt-tokens 2048] [--decode-steps 256] ...
+    camelid random-model CONFIG.json OUT --seed S
+
+Option names and meanings are the reference's where it has them: ``bench-generate MODEL
+--prompt-file --prompt --max-tokens (128) --temperature (0.0) --iterations (1) --warmup
+--json --deterministic`` (src/main.rs:956-990), ``--top-p --top-k --seed``
+(src/main.rs:401-417); the JSON record has its fields (src/main.rs:3216-3240), with
+tokens_per_second = (generated - 1) / decode seconds (src/main.rs:4229-4235). Prompts are
+token ids, since tokenizers are outside this library: ``--prompt`` takes ids separated by
+blanks or commas, ``--prompt-file`` a JSON array of ids (or of several such arrays), or one
+id per line (the format of the reference's ``--force-tokens``, src/main.rs:667-681).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+
+
+def read_prompts(args) -> list:
+    if args.prompt_file:
+        text = open(args.prompt_file).read().strip()
+        try:
+            data = json.loads(text)
+        except json.JSONDecodeError:
+            data = [int(x) for x in text.replace(",", " ").split()]
+        if data and isinstance(data[0], list):
+            return [[int(t) for t in p] for p in data]
+        return [[int(t) for t in data]]
+    if args.prompt:
+        return [[int(x) for x in args.prompt.replace(",", " ").split()]]
+    raise SystemExit("give --prompt or --prompt-file (token ids)")
+
+
+def _generate_args(ap):
+    ap.add_argument("model", help="model folder (config.json, model.safetensors)")
+    ap.add_argument("--prompt-file", help="token ids: a JSON array (or array of arrays), or one id per line; wins over --prompt")
+    ap.add_argument("--prompt", help="token ids separated by blanks or commas")
+    ap.add_argument("--max-tokens", type=int, default=128, help="maximum tokens to generate per iteration")
+    ap.add_argument("--temperature", type=float, default=0.0, help="sampling temperature (0 = greedy/argmax, deterministic)")
+    ap.add_argument("--top-p", type=float, default=None, help="nucleus sampling top-p (omit to leave unset)")
+    ap.add_argument("--top-k", type=int, default=None, help="top-k sampling (omit to leave unset)")
+    ap.add_argument("--min-p", type=float, default=None, help="keep tokens with p >= min_p * p_max")
+    ap.add_argument("--seed", type=int, default=None, help="sampling seed (omit for the engine default, 0)")
+    ap.add_argument("--repeat-penalty", type=float, default=1.0)
+    ap.add_argument("--presence-penalty", type=float, default=0.0)
+    ap.add_argument("--frequency-penalty", type=float, default=0.0)
+    ap.add_argument("--stop-ids", default=None, help="stop token ids, comma separated (default: the model's eos ids)")
+    ap.add_argument("--iterations", type=int, default=1, help="number of measured iterations (one JSON object each)")
+    ap.add_argument("--warmup", action="store_true", help="run one unmeasured generation before the measured ones")
+    ap.add_argument("--json", action="store_true", help="print the JSON record instead of the bare token ids")
+    ap.add_argument("--deterministic", action="store_true",
+                    help="run the true 32-bit path (the same as --dtype float32)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+
+
+def cmd_generate(args, always_json=False) -> int:
+    import torch
+    from . import api
+    t0 = time.perf_counter()
+    dtype = "float32" if args.deterministic else args.dtype
+    lm = api.load(args.model, dtype=dtype)
+    torch.cuda.synchronize()
+    load_ms = (time.perf_counter() - t0) * 1e3
+    prompts = read_prompts(args)
+    stops = None if args.stop_ids is None else tuple(int(x) for x in args.stop_ids.split(",") if x.strip())
+    opts = dict(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p, seed=args.seed,
+                repeat_penalty=args.repeat_penalty, presence_penalty=args.presence_penalty,
+                frequency_penalty=args.frequency_penalty, stop_token_ids=stops)
+    if args.warmup:
+        lm.generate(prompts, max_tokens=args.max_tokens, **opts)
+    for _ in range(args.iterations):
+        torch.cuda.reset_peak_memory_stats()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        first = lm.generate(prompts, max_tokens=min(1, args.max_tokens), **opts)          # prefill + first token
+        torch.cuda.synchronize()
+        ttft_ms = (time.perf_counter() - t1) * 1e3
+        t2 = time.perf_counter()
+        out = lm.generate(prompts, max_tokens=args.max_tokens, **opts)
+        torch.cuda.synchronize()
+        total_ms = (time.perf_counter() - t2) * 1e3
+        generated = sum(len(o) for o in out)
+        decode_ms = max(total_ms - ttft_ms, 0.0)
+        rec = {
+            "prompt_tokens": sum(len(p) for p in prompts), "generated_tokens": generated,
+            "load_ms": load_ms, "prefill_ms": ttft_ms, "ttft_ms": ttft_ms, "decode_ms": decode_ms,
+            "tokens_per_second": (generated - len(out)) / (decode_ms / 1e3) if decode_ms > 0 and generated > len(out) else 0.0,
+            "peak_memory_bytes": torch.cuda.max_memory_allocated(),
+            "output_token_ids": out[0] if len(out) == 1 else out, "dtype": dtype,
+        }
+        del first
+        if args.json or always_json:
+            print(json.dumps(rec), flush=True)
+        else:
+            for o in out:
+                print(" ".join(str(t) for t in o), flush=True)
+    return 0
+
+
+def cmd_random_model(args) -> int:
+    import torch
+    from .weights.random_init import write_random_model
+    with open(args.config) as f:
+        cfg = json.load(f)
+    dt = {"bfloat16": torch.bfloat16, "float32": torch.float32}[args.dtype]
+    write_random_model(args.out, cfg, args.seed, dt)
+    print(args.out)
+    return 0
+
+
+def cmd_bench(args) -> int:
+    from . import benchmark
+    rec = benchmark.run(batch=args.batch, prompt_tokens=args.prompt_tokens, decode_steps=args.decode_steps,
+                        warmup=args.warmup, dtype=args.dtype, layers=args.layers, config_index=args.config)
+    print(json.dumps(rec), flush=True)
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="camelid", description="generation for the dense Llama decoder on one B200")
+    sub = ap.add_subparsers(dest="command", required=True)
+    _generate_args(sub.add_parser("generate", help="generate token ids for a prompt of token ids"))
+    _generate_args(sub.add_parser("bench-generate", help="generate and print one JSON record per iteration"))
+    from . import replay
+    replay.add_arguments(sub.add_parser("replay", help="feed given tokens step by step and write logits"))
+    rm = sub.add_parser("random-model", help="write a model folder with random weights")
+    rm.add_argument("config", help="a config.json")
+    rm.add_argument("out", help="folder to write")
+    rm.add_argument("--seed", type=int, default=0)
+    rm.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    be = sub.add_parser("bench", help="decode and prefill throughput with random weights")
+    be.add_argument("--batch", type=int, default=8)
+    be.add_argument("--prompt-tokens", type=int, default=2048)
+    be.add_argument("--decode-steps", type=int, default=64)
+    be.add_argument("--warmup", type=int, default=3)
+    be.add_argument("--layers", type=int, default=None)
+    be.add_argument("--config", type=int, default=2, help="index into the benchmark shapes (2: Llama 3.2 1B)")
+    be.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    args = ap.parse_args(argv)
+    if args.command == "generate":
+        return cmd_generate(args)
+    if args.command == "bench-generate":
+        return cmd_generate(args, always_json=True)
+    if args.command == "replay":
+        return replay.run(args)
+    if args.command == "random-model":
+        return cmd_random_model(args)
+    if args.command == "bench":
+        return cmd_bench(args)
+    return 2
+
+
+if __name__ == "__main__":
+    sys.exit(main())

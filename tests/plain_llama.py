@@ -47,6 +47,9 @@ def read_safetensors(path: str) -> dict[str, torch.Tensor]:
             continue
         dt, _size = _ST_DTYPES[info["dtype"]]
         b, e = info["data_offsets"]
+        if e == b:
+            out[name] = torch.empty(info["shape"], dtype=dt)
+            continue
         t = torch.frombuffer(bytearray(payload[b:e]), dtype=dt)
         out[name] = t.reshape(info["shape"]).clone()
     return out

@@ -1,0 +1,97 @@
+"""Generation through the Python entry point and the command line against the plain loop."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_llama as pl
+from conftest import CONFIGS
+from helpers import tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_greedy_generation_float32(cuda, model_folders):
+    """tiny_b, prompts of 17, 2, 40 and 9 tokens, 12 greedy steps: token for token."""
+    import camelid_b200
+    name = "tiny_b"
+    lm = camelid_b200.load(model_folders[name], dtype="float32")
+    prompts = [tokens(50 + i, n, CONFIGS[name]["vocab_size"]) for i, n in enumerate([17, 2, 40, 9])]
+    cfg, w = pl.read_model(model_folders[name])
+    want = pl.generate(cfg, w, prompts, 12, dtype=torch.float64)
+    got = lm.generate(prompts, max_tokens=12, stop_token_ids=())
+    assert got == want
+    assert len({tuple(g) for g in got}) > 1 and any(len(set(g)) > 2 for g in got)      # not a trivial repeat
+    one = lm.generate(prompts[2], max_tokens=12, stop_token_ids=())                   # a single prompt, alone
+    assert one == want[2]
+    two = lm.generate(prompts, max_tokens=12, stop_token_ids=(), max_batch=2)         # two batches, slots reused
+    assert two == want
+
+
+def test_stop_tokens_and_details(cuda, model_folders):
+    import camelid_b200
+    name = "tiny_b"
+    lm = camelid_b200.load(model_folders[name], dtype="float32")
+    assert lm.stop_token_ids == (3, 11)
+    prompts = [tokens(60 + i, n, CONFIGS[name]["vocab_size"]) for i, n in enumerate([5, 11, 1])]
+    free = lm.generate(prompts, max_tokens=8, stop_token_ids=())
+    stop = free[1][3]
+    res = lm.generate(prompts, max_tokens=8, stop_token_ids=(stop,), details=True)
+    cfg, w = pl.read_model(model_folders[name])
+    want = pl.generate(cfg, w, prompts, 8, stop_ids=(stop,), dtype=torch.float64)
+    assert [r.tokens for r in res] == want
+    assert res[1].finish_reason == "stop" and res[1].tokens[-1] == stop and len(res[1].tokens) <= 4
+    assert all(r.finish_reason in ("stop", "length") for r in res)
+
+
+def test_temperature_generation_matches_plain(cuda, model_folders):
+    """tiny_a in float32 with temperature 0.8 and a fixed seed. A sampled token can differ
+    from the plain loop only where the draw falls within rounding of a boundary of the
+    cumulative distribution, so nearly all of the 4 x 12 tokens agree; the first ones must."""
+    import camelid_b200
+    name = "tiny_a"
+    lm = camelid_b200.load(model_folders[name], dtype="float32")
+    prompts = [tokens(70 + i, n, CONFIGS[name]["vocab_size"]) for i, n in enumerate([17, 2, 40, 9])]
+    cfg, w = pl.read_model(model_folders[name])
+    want = pl.generate(cfg, w, prompts, 12, temperature=0.8, seed=1234, dtype=torch.float64)
+    got = lm.generate(prompts, max_tokens=12, temperature=0.8, seed=1234, stop_token_ids=())
+    assert [g[0] for g in got] == [x[0] for x in want]
+    assert got == want
+    again = lm.generate(prompts[::-1], max_tokens=12, temperature=0.8, seed=1234, stop_token_ids=())
+    assert again == got[::-1]                           # a request's tokens do not depend on its batch
+
+
+def test_bfloat16_generation_is_close(cuda, model_folders):
+    import camelid_b200
+    name = "tiny_b"
+    lm = camelid_b200.load(model_folders[name], dtype="bfloat16")
+    prompts = [tokens(50 + i, n, CONFIGS[name]["vocab_size"]) for i, n in enumerate([17, 2, 40, 9])]
+    cfg, w = pl.read_model(model_folders[name])
+    got = lm.generate(prompts, max_tokens=4, stop_token_ids=())
+    # teacher-forced check: every generated token is the argmax of the plain logits, or within
+    # the bfloat16 tolerance of it
+    for p, g in zip(prompts, got):
+        seq = list(p)
+        for t in g:
+            ref = pl.forward(cfg, w, seq, dtype=torch.float64)[-1]
+            assert float(ref.max() - ref[t]) <= 2 * 3e-2 * float(ref.abs().max())
+            seq.append(t)
+
+
+def test_command_line(cuda, model_folders, tmp_path):
+    prompt_file = tmp_path / "prompt.json"
+    prompt_file.write_text(json.dumps([5, 17, 3, 200, 9]))
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "camelid"), "generate", model_folders["tiny_b"],
+                          "--prompt-file", str(prompt_file), "--max-tokens", "6", "--dtype", "float32", "--json"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    rec = json.loads(out.stdout.strip().splitlines()[-1])
+    cfg, w = pl.read_model(model_folders["tiny_b"])
+    want = pl.generate(cfg, w, [[5, 17, 3, 200, 9]], 6, stop_ids=(3, 11), dtype=torch.float64)[0]
+    assert rec["output_token_ids"] == want and rec["prompt_tokens"] == 5 and rec["generated_tokens"] == len(want)
+    for key in ("load_ms", "prefill_ms", "ttft_ms", "decode_ms", "tokens_per_second"):
+        assert key in rec

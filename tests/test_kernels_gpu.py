@@ -1,0 +1,242 @@
+"""Each kernel alone against its plain reference, at other sizes than the engine's tests,
+with inputs made so that an addressing fault shows (a far key that dominates, a window's
+edge, stale and non-finite contents in unused cache rows)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+from helpers import TOL, rel_err
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def _i32(x, dev):
+    return torch.tensor(x, dtype=torch.int32, device=dev)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows,hidden,vocab", [(7, 72, 101), (3, 2048, 50)])
+def test_embed_gather(cuda, dtype, rows, hidden, vocab):
+    from camelid_b200.csrc import ops
+    table = torch.randn(vocab, hidden).to(DT[dtype]).to(cuda)
+    toks = torch.randint(0, vocab, (rows,), dtype=torch.int32, device=cuda)
+    out = torch.empty(rows, hidden, device=cuda)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    ops.embed_gather(table, toks, out, err)
+    assert torch.equal(out, table.float()[toks.long()]) and int(err) == 0
+    toks[1] = vocab
+    ops.embed_gather(table, toks, out, err)
+    assert int(err) == 1 and float(out[1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("w_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows,hidden,eps", [(5, 72, 1e-5), (2, 3000, 1e-6), (1, 16, 1e-2)])
+def test_rmsnorm(cuda, out_dtype, w_dtype, rows, hidden, eps):
+    from camelid_b200.csrc import ops
+    x = (torch.randn(rows + 3, hidden) * 3).to(cuda)
+    w = (1 + 0.1 * torch.randn(hidden)).to(DT[w_dtype]).to(cuda)
+    idx = _i32([(r * 2) % (rows + 3) for r in range(rows)], cuda)
+    out = torch.empty(rows, hidden, dtype=DT[out_dtype], device=cuda)
+    ops.rmsnorm(x, w, eps, out, idx)
+    ref = pl.rms_norm(x.cpu().double()[idx.cpu().long()], w.cpu().double(), eps)
+    tol = 1e-5 if out_dtype == "float32" else 2 ** -8
+    assert rel_err(out.cpu(), ref) <= tol
+    ops.rmsnorm(x, w, eps, out[:1], None)
+    assert rel_err(out[:1].cpu(), pl.rms_norm(x[:1].cpu().double(), w.cpu().double(), eps)) <= tol
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(1, 40, 24), (70, 130, 200), (129, 64, 1030), (5, 517, 96)])
+def test_gemm_simt_epilogues(cuda, dtype, M, N, K):
+    from camelid_b200.csrc import ops
+    a = torch.randn(M, K).to(DT[dtype]).to(cuda)
+    w = (torch.randn(N, K) / math.sqrt(K)).to(DT[dtype]).to(cuda)
+    ref = a.cpu().double() @ w.cpu().double().T
+    tol = 1e-5 if dtype == "float32" else 2 ** -8
+    c = torch.empty(M, N, dtype=DT[dtype], device=cuda)
+    ops.gemm_tn_simt(a, w, c, ops.EPI_STORE)
+    assert rel_err(c.cpu(), ref) <= tol
+    c32 = torch.empty(M, N, device=cuda)
+    ops.gemm_tn_simt(a, w, c32, ops.EPI_STORE_F32)
+    assert rel_err(c32.cpu(), ref) <= 1e-5
+    res = torch.randn(M, N, device=cuda)
+    want = res.cpu().double() + ref
+    ops.gemm_tn_simt(a, w, res, ops.EPI_ADD_F32)
+    assert rel_err(res.cpu(), want) <= 1e-5
+    # rows of a wider matrix (strided views), as the attention mixer uses
+    wide = torch.randn(M, K + 8).to(DT[dtype]).to(cuda)
+    ops.gemm_tn_simt(wide[:, 8:], w, c32, ops.EPI_STORE_F32)
+    assert rel_err(c32.cpu(), wide[:, 8:].cpu().double() @ w.cpu().double().T) <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,inter,K,group", [(3, 48, 40, 16), (66, 136, 72, 136), (9, 160, 64, 16)])
+def test_gemm_swiglu_and_packing(cuda, dtype, M, inter, K, group):
+    from camelid_b200.csrc import ops
+    from camelid_b200.parts.linear import pack_gate_up
+    x = torch.randn(M, K).to(DT[dtype]).to(cuda)
+    wg = (torch.randn(inter, K) / math.sqrt(K)).to(DT[dtype]).to(cuda)
+    wu = (torch.randn(inter, K) / math.sqrt(K)).to(DT[dtype]).to(cuda)
+    packed = pack_gate_up(wg, wu, group)
+    g = x.cpu().double() @ wg.cpu().double().T
+    u = x.cpu().double() @ wu.cpu().double().T
+    ref = (g / (1 + torch.exp(-g))) * u
+    act = torch.empty(M, inter, dtype=DT[dtype], device=cuda)
+    ops.gemm_tn_simt(x, packed, act, ops.EPI_SWIGLU, group)
+    tol = 1e-5 if dtype == "float32" else 2 ** -7
+    assert rel_err(act.cpu(), ref) <= tol
+    gu = torch.empty(M, 2 * inter, dtype=DT[dtype], device=cuda)
+    ops.gemm_tn_simt(x, packed, gu, ops.EPI_STORE)
+    act2 = torch.empty_like(act)
+    ops.swiglu_packed(gu, act2, group)
+    assert rel_err(act2.cpu(), ref) <= (1e-5 if dtype == "float32" else 2 ** -6)
+
+
+def _paged(seq_lens, n_kv, hd, dtype, dev, n_pages=64, seed=0):
+    """Random keys and values for sequences of the given lengths, scattered over shuffled
+    pages; unused rows hold NaN."""
+    g = torch.Generator().manual_seed(seed)
+    k_pages = torch.full((n_pages, n_kv, 64, hd), float("nan")).to(dtype)
+    v_pages = torch.full((n_pages, n_kv, 64, hd), float("nan")).to(dtype)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    tables, ks, vs = [], [], []
+    for n in seq_lens:
+        k = torch.randn(n, n_kv, hd, generator=g).to(dtype)
+        v = torch.randn(n, n_kv, hd, generator=g).to(dtype)
+        blocks = [perm.pop() for _ in range((n + 63) // 64)]
+        for p in range(n):
+            k_pages[blocks[p // 64], :, p % 64] = k[p]
+            v_pages[blocks[p // 64], :, p % 64] = v[p]
+        tables.append(blocks)
+        ks.append(k)
+        vs.append(v)
+    width = max(len(t) for t in tables)
+    table = torch.tensor([t + [-1] * (width - len(t)) for t in tables], dtype=torch.int32)
+    return k_pages.to(dev), v_pages.to(dev), table.to(dev), ks, vs
+
+
+def _attn_case(cuda, dtype, n_heads, n_kv, hd, starts, news, window, decode, n_splits=1, spike=None):
+    from camelid_b200.csrc import ops
+    dt = DT[dtype]
+    totals = [s + n for s, n in zip(starts, news)]
+    k_pages, v_pages, table, ks, vs = _paged(totals, n_kv, hd, dt, cuda)
+    g = torch.Generator().manual_seed(1)
+    n_rows = sum(news)
+    q = torch.randn(n_rows, n_heads, hd, generator=g).to(dt)
+    row0 = [sum(news[:i]) for i in range(len(news))]
+    if spike is not None:            # one far key gets a score that stands out for one query
+        seq, key = spike
+        r = row0[seq] + news[seq] - 1
+        ks[seq][key] *= 0
+        ks[seq][key, :, 0] = 8.0
+        q[r, :, 0] = 8.0 * math.sqrt(hd) / 4
+        k_pages[int(table[seq, key // 64]), :, key % 64] = ks[seq][key].to(cuda)
+    rows, hpc, chunks = ops.attn_tiling(n_heads, n_kv, decode)
+    tile_seq, tile_q0 = [], []
+    for i, n in enumerate(news):
+        for q0 in range(0, n, rows):
+            tile_seq.append(i)
+            tile_q0.append(q0)
+    out = torch.empty(n_rows, n_heads * hd, dtype=dt, device=cuda)
+    partial = torch.empty(max(1, ops.attn_partial_floats(n_rows, n_heads, hd, n_splits)), device=cuda)
+    ops.attn_paged_simt(q.view(n_rows, -1).to(cuda), out, k_pages, v_pages, table, _i32(tile_seq, cuda),
+                        _i32(tile_q0, cuda), len(tile_seq), _i32(row0, cuda), _i32(starts, cuda), _i32(news, cuda),
+                        n_rows, n_heads, n_kv, hd, rows, hpc, chunks, n_splits, window or 0, 1 / math.sqrt(hd), partial)
+    out = out.cpu().view(n_rows, n_heads, hd)
+    for i, (s, n) in enumerate(zip(starts, news)):
+        qfull = torch.zeros(s + n, n_heads, hd, dtype=torch.float64)
+        qfull[s:] = q[row0[i]:row0[i] + n].double()
+        ref = pl.attention(qfull, ks[i].double(), vs[i].double(), window)[s:]
+        e = rel_err(out[row0[i]:row0[i] + n], ref)
+        assert e <= (1e-5 if dtype == "float32" else 2 ** -7), f"sequence {i}: {e}"
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_heads,n_kv,hd", [(4, 2, 16), (6, 1, 32), (5, 5, 48), (8, 2, 128), (34, 1, 64), (2, 1, 256)])
+def test_attention_prefill_shapes(cuda, dtype, n_heads, n_kv, hd):
+    _attn_case(cuda, dtype, n_heads, n_kv, hd, starts=[0, 0, 0], news=[1, 70, 129], window=None, decode=False)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_continues_from_cache_and_far_key(cuda, dtype):
+    """New rows on top of cached positions; one key hundreds of positions back dominates the
+    last query of the second sequence: if a page were addressed wrongly it would show."""
+    out = _attn_case(cuda, dtype, 4, 2, 32, starts=[64, 300, 5], news=[3, 20, 64], window=None, decode=False,
+                     spike=(1, 7))
+    assert out is not None
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_splits", [1, 2, 5, 16])
+def test_attention_decode_splits(cuda, dtype, n_splits):
+    """One new row per sequence, keys split over several blocks (also more splits than pages)."""
+    _attn_case(cuda, dtype, 8, 2, 64, starts=[0, 63, 64, 700], news=[1, 1, 1, 1], window=None, decode=True,
+               n_splits=n_splits, spike=(3, 130))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [1, 64, 70, 200])
+def test_attention_window_edges(cuda, dtype, window):
+    """A key just outside the window must not count: put the spike there and compare."""
+    _attn_case(cuda, dtype, 4, 2, 32, starts=[0, 190], news=[150, 10], window=window, decode=False,
+               spike=(1, max(0, 199 - window)))
+    _attn_case(cuda, dtype, 4, 2, 32, starts=[199, 80], news=[1, 1], window=window, decode=True, n_splits=3,
+               spike=(0, max(0, 199 - window)))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_heads,n_kv,hd,rot", [(4, 2, 16, 16), (3, 1, 48, 32), (2, 2, 64, 0)])
+def test_rope_kv_write(cuda, dtype, n_heads, n_kv, hd, rot):
+    from camelid_b200.csrc import ops
+    from camelid_b200.parts.position import rotary_frequencies
+    dt = DT[dtype]
+    cfg = {"hidden_size": rot, "num_attention_heads": 1, "head_dim": rot, "rope_theta": 10000.0}
+    freqs = rotary_frequencies(rot, 10000.0, None) if rot else np.zeros(0, dtype=np.float32)
+    if rot:
+        assert np.array_equal(freqs, pl.rope_frequencies(cfg))
+    positions = [0, 1, 63, 64, 130, 5]
+    seqs = [0, 0, 0, 0, 0, 1]
+    table = _i32([[9, 2, 4], [7, -1, -1]], cuda)
+    width = (n_heads + 2 * n_kv) * hd
+    qkv = torch.randn(len(positions), width + 5).to(dt)
+    k_pages = torch.zeros(12, n_kv, 64, hd, dtype=dt, device=cuda)
+    v_pages = torch.zeros_like(k_pages)
+    dev = qkv.to(cuda)[:, :width]
+    ops.rope_kv_write(dev, _i32(positions, cuda), _i32(seqs, cuda), table, k_pages, v_pages,
+                      torch.from_numpy(freqs).to(cuda), rot, n_heads, n_kv, hd, True)
+    q = qkv[:, :n_heads * hd].double().view(-1, n_heads, hd)
+    k = qkv[:, n_heads * hd:(n_heads + n_kv) * hd].double().view(-1, n_kv, hd)
+    v = qkv[:, (n_heads + n_kv) * hd:width].view(-1, n_kv, hd)
+    pos = torch.tensor(positions)
+    q_ref = pl.rope(q, pos, freqs) if rot else q
+    k_ref = pl.rope(k, pos, freqs) if rot else k
+    tol = 1e-6 if dtype == "float32" else 2 ** -8
+    assert rel_err(dev.cpu()[:, :n_heads * hd].view(-1, n_heads, hd), q_ref) <= tol
+    tab = table.cpu()
+    for r, (p, s) in enumerate(zip(positions, seqs)):
+        page = int(tab[s, p // 64])
+        assert rel_err(k_pages[page, :, p % 64].cpu(), k_ref[r]) <= tol
+        assert torch.equal(v_pages[page, :, p % 64].cpu(), v[r])
+    assert int((k_pages != 0).any(dim=-1).sum()) <= len(positions) * n_kv     # nothing else was written
+    before = k_pages.clone()
+    ops.rope_kv_write(dev, _i32(positions, cuda), _i32(seqs, cuda), table, k_pages, v_pages,
+                      torch.from_numpy(freqs).to(cuda), rot, n_heads, n_kv, hd, False)
+    assert torch.equal(before, k_pages)
+
+
+def test_kernels_refuse_what_they_cannot_do(cuda):
+    from camelid_b200 import KernelError
+    from camelid_b200.csrc import ops
+    with pytest.raises(KernelError):
+        ops.rmsnorm(torch.zeros(2, 8), torch.ones(8), 1e-5, torch.zeros(2, 8))          # CPU tensors
+    with pytest.raises(KernelError):
+        ops.dtype_code(torch.float16)
+    a = torch.zeros(4, 8, device=cuda)
+    with pytest.raises(KernelError):
+        ops.gemm_tn_simt(a, torch.zeros(6, 8, device=cuda), torch.zeros(4, 3, device=cuda), ops.EPI_SWIGLU, 2)

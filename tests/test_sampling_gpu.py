@@ -1,0 +1,97 @@
+"""The device sampler against the plain sampler, fed the same logits."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+
+
+def _sample(cuda, logits, histories, **opts):
+    from camelid_b200.sampling import Sampler, SamplingOptions
+    s = Sampler(SamplingOptions(**opts), logits.shape[1], cuda)
+    out = s.sample(torch.tensor(logits, dtype=torch.float32, device=cuda), histories)
+    s.check()
+    return out.cpu().tolist()
+
+
+def test_greedy_ties_and_many_rows(cuda):
+    rng = np.random.default_rng(0)
+    logits = rng.normal(size=(9, 5003)).astype(np.float32)
+    logits[2, 77] = logits[2, 4000] = 9.0            # equal maxima: the lower index wins
+    logits[5, :] = 1.0
+    got = _sample(cuda, logits, [[]] * 9)
+    assert got == [pl.greedy(r) for r in logits] and got[2] == 77 and got[5] == 0
+    assert _sample(cuda, np.array([[0.5, 2.0, 2.0, -1.0]], dtype=np.float32), [[]]) == [1]
+
+
+def test_non_finite_logits_are_an_error(cuda):
+    from camelid_b200 import SamplingError
+    bad = np.zeros((2, 300), dtype=np.float32)
+    bad[1, 5] = np.nan
+    with pytest.raises(SamplingError):
+        _sample(cuda, bad, [[], []])
+    with pytest.raises(SamplingError):
+        _sample(cuda, bad, [[], []], temperature=1.0)
+
+
+@pytest.mark.parametrize("opts", [
+    dict(temperature=1.0), dict(temperature=0.7, seed=3), dict(temperature=1.5, top_k=5, seed=1),
+    dict(temperature=1.0, top_p=0.8, seed=0), dict(temperature=1.0, min_p=0.1, seed=9),
+    dict(temperature=0.9, top_k=50, top_p=0.9, min_p=0.02, seed=123456789),
+    dict(temperature=1.0, top_k=1, seed=7), dict(temperature=1.0, min_p=1.0, seed=5),
+    dict(temperature=2.0, top_k=1000000, seed=2),
+])
+def test_stochastic_sampler_matches_plain(cuda, opts):
+    rng = np.random.default_rng(42)
+    vocab = 1531
+    logits = (rng.normal(size=(40, vocab)) * 2.5).astype(np.float32)
+    logits[3, 10] = logits[3, 900] = logits[3].max() + 1.0          # ties at the top
+    histories = [[1] * (r % 13) for r in range(40)]                 # different stream positions
+    got = _sample(cuda, logits, histories, **opts)
+    want = [pl.sample(logits[r], histories[r], **opts) for r in range(40)]
+    assert got == want
+
+
+def test_reference_expectations_on_the_device(cuda):
+    """tests/inference_session.rs:172-198, :216-240."""
+    l3 = np.array([[3.0, 2.0, 1.0]], dtype=np.float32)
+    assert _sample(cuda, l3, [[]], temperature=1.0, top_k=1, seed=0) == [0]
+    assert _sample(cuda, l3, [[]], temperature=1.0, top_p=0.8, seed=0) == [1]
+    assert _sample(cuda, np.array([[0.0, 0.5, 0.4]], dtype=np.float32), [[]], logit_bias=[(2, 0.2)]) == [2]
+    assert _sample(cuda, np.array([[1.0, 0.9, 0.0]], dtype=np.float32), [[0, 0]], presence_penalty=0.5,
+                   frequency_penalty=0.25) == [1]
+
+
+def test_adjustments_match_plain(cuda):
+    rng = np.random.default_rng(5)
+    logits = rng.normal(size=(6, 400)).astype(np.float32)
+    histories = [[int(x) for x in rng.integers(0, 400, size=20 + r)] for r in range(6)]
+    opts = dict(temperature=0.8, seed=4, repeat_penalty=1.3, presence_penalty=0.4, frequency_penalty=0.2,
+                logit_bias=[(7, 5.0), (8, -3.0)])
+    got = _sample(cuda, logits, histories, **opts)
+    assert got == [pl.sample(logits[r], histories[r], **opts) for r in range(6)]
+    from camelid_b200.sampling import Sampler, SamplingOptions
+    s = Sampler(SamplingOptions(**opts), 400, cuda)
+    dev = torch.tensor(logits, device=cuda)
+    s.sample(dev, histories)
+    adj = {k: v for k, v in opts.items() if k not in ("temperature", "seed")}
+    want = np.stack([pl.adjust_logits(logits[r], histories[r], **adj) for r in range(6)])
+    assert np.allclose(dev.cpu().numpy(), want, atol=1e-6)
+
+
+def test_large_vocabulary_frequencies(cuda):
+    """At the real vocabulary size the draws follow the softmax (a few heavy tokens)."""
+    vocab = 128256
+    logits = np.full((1, vocab), -20.0, dtype=np.float32)
+    logits[0, [5, 70000, 128255]] = [2.0, 1.0, 0.0]
+    p = np.exp([2.0, 1.0, 0.0]) / np.exp([2.0, 1.0, 0.0]).sum()
+    rows = np.repeat(logits, 64, axis=0)
+    counts = {5: 0, 70000: 0, 128255: 0}
+    for rep in range(8):
+        got = _sample(cuda, rows, [[0] * (rep * 64 + r) for r in range(64)], temperature=1.0, seed=11)
+        for t in got:
+            counts[t] = counts.get(t, 0) + 1
+    freq = np.array([counts[5], counts[70000], counts[128255]]) / 512
+    assert np.abs(freq - p).max() < 0.07 and sum(counts.values()) == 512

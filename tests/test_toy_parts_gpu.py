@@ -1,0 +1,186 @@
+"""Generality of the parts, shown with toy parts that exist only here: a mixer with state of
+its own (no keys and values), registered, built and stepped without a change to the
+library's files; a schedule that names layers twice and lets an entry read another entry's
+cache; a layer with a window next to layers without one (two cache groups)."""
+import dataclasses
+
+import pytest
+import torch
+
+import plain_llama as pl
+from conftest import TINY_A
+from helpers import assert_close, tokens
+
+pytestmark = pytest.mark.gpu
+
+
+def _register_toys():
+    from camelid_b200.cache import StateSpec
+    from camelid_b200.config import LlamaConfig, ScheduleEntry, llama_plan, register_architecture
+    from camelid_b200.config.plan import LayerSpec, PartSpec
+    from camelid_b200.parts import Part, TensorSpec, register_part
+
+    @register_part("mixer", "toy_running_sum")
+    class RunningSum(Part):
+        """y_t = (sum of x_0..x_t) * w: the sum so far is the state, one vector per sequence."""
+
+        def __init__(self, params, prefix=""):
+            super().__init__(params, prefix)
+            self.hidden = params["hidden_size"]
+
+        def tensor_specs(self):
+            return {self.prefix + "w": TensorSpec((self.hidden,), "norm")}
+
+        def load(self, tensors, device, dtype):
+            self.w = tensors[self.prefix + "w"].to(device=device, dtype=torch.float32)
+
+        def cache_spec(self):
+            return StateSpec((self.hidden,), "float32")
+
+        def forward(self, ctx, x, residual):
+            state = ctx.state()                                   # [slots, hidden]
+            for slot, r0, n in zip(ctx.h_slots, ctx.h_row0, ctx.h_new):
+                sums = torch.cumsum(x[r0:r0 + n].float(), 0) + state[slot]
+                residual[r0:r0 + n] += sums * self.w
+                state[slot] = sums[-1]
+
+    def toy_plan(cfg):
+        base = llama_plan(cfg)
+        layers = list(base.layers)
+        layers[1] = dataclasses.replace(layers[1], mixer=PartSpec("toy_running_sum", {"hidden_size": cfg.hidden_size},
+                                                                  "model.layers.1.toy."))
+        return dataclasses.replace(base, layers=tuple(layers))
+
+    def twice_plan(cfg):
+        base = llama_plan(cfg)
+        return dataclasses.replace(base, schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0),
+                                                   ScheduleEntry(1, cache_source=1)))
+
+    def window_plan(cfg):
+        base = llama_plan(cfg)
+        layers = list(base.layers)
+        mixer = layers[1].mixer
+        layers[1] = dataclasses.replace(layers[1], mixer=PartSpec(mixer.kind, {**mixer.params, "window": 70}, mixer.prefix))
+        return dataclasses.replace(base, layers=tuple(layers))
+
+    register_architecture("ToyStateForCausalLM", LlamaConfig.from_dict, toy_plan)
+    register_architecture("ToyTwiceForCausalLM", LlamaConfig.from_dict, twice_plan)
+    register_architecture("ToyWindowForCausalLM", LlamaConfig.from_dict, window_plan)
+
+
+def _model(arch, dtype, seed=3, **over):
+    from camelid_b200.engine.model import DecoderModel
+    from camelid_b200.weights import random_tensors
+    cfg = {**TINY_A, "architectures": [arch], "max_position_embeddings": 512, **over}
+    model = DecoderModel.from_config(cfg, dtype=dtype, device="cuda")
+    tensors = random_tensors(model.tensor_specs(), seed)
+    model.load_tensors(tensors)
+    return cfg, model, tensors
+
+
+def _drive(model, seqs, cut):
+    """Two requests in one batch: prompts of ``cut`` tokens, then token by token until the
+    shorter one ends; then a third request in the freed slot."""
+    from camelid_b200 import StepEntry
+    cache = model.new_cache(1024, max_slots=2)
+    outs = [[], [], []]
+    a, b = cache.alloc_slot(), cache.alloc_slot()
+    lg = model.step(cache, [StepEntry(a, seqs[0][:cut[0]], list(range(cut[0]))),
+                            StepEntry(b, seqs[1][:cut[1]], list(range(cut[1])))]).cpu()
+    outs[0].append(lg[:cut[0]])
+    outs[1].append(lg[cut[0]:])
+    pos = list(cut)
+    while pos[0] < len(seqs[0]) or pos[1] < len(seqs[1]):
+        entries, who = [], []
+        for i, slot in ((0, a), (1, b)):
+            if pos[i] < len(seqs[i]):
+                entries.append(StepEntry(slot, [seqs[i][pos[i]]], [0]))
+                who.append(i)
+            elif slot is not None and cache.book.slots.is_held(slot):
+                cache.free_slot(slot)
+        lg = model.step(cache, entries).cpu()
+        for r, i in enumerate(who):
+            outs[i].append(lg[r:r + 1])
+            pos[i] += 1
+    for slot in (a, b):
+        if cache.book.slots.is_held(slot):
+            cache.free_slot(slot)
+    c = cache.alloc_slot()
+    assert c == 0
+    outs[2].append(model.step(cache, [StepEntry(c, seqs[2], list(range(len(seqs[2]))))]).cpu())
+    cache.free_slot(c)
+    cache.book.audit()
+    return [torch.cat(o) for o in outs]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state(cuda, dtype):
+    _register_toys()
+    cfg, model, w = _model("ToyStateForCausalLM", dtype)
+    assert "model.layers.1.toy.w" in w and "model.layers.1.self_attn.q_proj.weight" not in w
+    from camelid_b200.cache import KVSpec, StateSpec
+    specs = model.entry_cache_specs()
+    assert isinstance(specs[0], KVSpec) and isinstance(specs[1], StateSpec)
+
+    def plain(ids):
+        ids = torch.as_tensor(ids)
+        pos = torch.arange(len(ids))
+        fr = pl.rope_frequencies(cfg)
+        h = pl.embedding(ids, w["model.embed_tokens.weight"], torch.float64)
+        h, _ = pl.decoder_layer(h, w, 0, cfg, pos, fr)
+        p = "model.layers.1."
+        n = pl.rms_norm(h, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        if dtype == "bfloat16":
+            n = n.to(torch.bfloat16).double()          # the toy reads the normed rows in the compute type
+        r = h + torch.cumsum(n, 0) * w[p + "toy.w"].double()
+        n2 = pl.rms_norm(r, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+        r = r + pl.swiglu(n2, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+        return pl.rms_norm(r, w["model.norm.weight"], cfg["rms_norm_eps"]) @ pl.output_weight(cfg, w).double().T
+
+    seqs = [tokens(1, 40, 256), tokens(2, 23, 256), tokens(3, 30, 256)]
+    got = _drive(model, seqs, cut=[17, 20])
+    for i in range(3):
+        assert_close(got[i], plain(seqs[i]), dtype, f"toy state, request {i}")      # request 2: a used slot starts from zero
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_schedule_names_layers_twice_and_shares_a_cache(cuda, dtype):
+    _register_toys()
+    cfg, model, w = _model("ToyTwiceForCausalLM", dtype)
+    cache = model.new_cache(256)
+    assert cache.k[0].shape[0] == 3 and cache.entry_kv[3] == cache.entry_kv[1]      # four runs, three caches
+    seqs = [tokens(4, 70, 256), tokens(5, 33, 256), tokens(6, 66, 256)]
+    got = _drive(model, seqs, cut=[64, 3])
+    sched = [(0, None), (1, None), (0, None), (1, 1)]
+    for i in range(3):
+        assert_close(got[i], pl.forward(cfg, w, seqs[i], dtype=torch.float64, schedule=sched), dtype, f"request {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_window_layer_has_storage_of_its_own(cuda, dtype):
+    _register_toys()
+    cfg, model, w = _model("ToyWindowForCausalLM", dtype)
+    cache = model.new_cache(1024, max_slots=2)
+    assert len(cache.k) == 2 and cache.book.kv_specs[1].window == 70
+
+    def plain(ids):
+        ids = torch.as_tensor(ids)
+        pos = torch.arange(len(ids))
+        fr = pl.rope_frequencies(cfg)
+        h = pl.embedding(ids, w["model.embed_tokens.weight"], torch.float64)
+        h, _ = pl.decoder_layer(h, w, 0, cfg, pos, fr)
+        p = "model.layers.1."
+        n = pl.rms_norm(h, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        T, nH, nKV, hd = len(ids), 4, 2, 16
+        q = pl.rope((n @ w[p + "self_attn.q_proj.weight"].double().T).view(T, nH, hd), pos, fr)
+        k = pl.rope((n @ w[p + "self_attn.k_proj.weight"].double().T).view(T, nKV, hd), pos, fr)
+        v = (n @ w[p + "self_attn.v_proj.weight"].double().T).view(T, nKV, hd)
+        r = h + pl.attention(q, k, v, window=70).reshape(T, -1) @ w[p + "self_attn.o_proj.weight"].double().T
+        n2 = pl.rms_norm(r, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+        r = r + pl.swiglu(n2, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+        return pl.rms_norm(r, w["model.norm.weight"], cfg["rms_norm_eps"]) @ pl.output_weight(cfg, w).double().T
+
+    seqs = [tokens(7, 300, 256), tokens(8, 150, 256), tokens(9, 200, 256)]
+    got = _drive(model, seqs, cut=[200, 140])
+    for i in range(3):
+        assert_close(got[i], plain(seqs[i]), dtype, f"window, request {i}")
