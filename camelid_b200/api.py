@@ -47,6 +47,8 @@ class LanguageModel:
         width = min(len(need), max_batch or len(need))
         tokens = max(64, sum(need[:width]))
         if self._cache is None or self._cache_tokens < tokens:
+            if self._cache is not None:
+                self.model.drop_graphs(self._cache)
             self._cache = None
             self._cache = self.model.new_cache(tokens)
             self._cache_tokens = tokens
@@ -55,7 +57,7 @@ class LanguageModel:
     def generate(self, prompts, max_tokens: int = 128, *, temperature: float = 0.0, top_k=None, top_p=None,
                  min_p=None, seed=None, presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
                  repeat_penalty: float = 1.0, logit_bias=(), stop_token_ids=None, max_batch: int | None = None,
-                 cache=None, details: bool = False):
+                 cache=None, details: bool = False, on_step=None):
         """Generate for a list of prompts (lists of token ids). Returns the generated ids per
         prompt (the stop token included), or ``GenerationResult`` objects with ``details``."""
         single = bool(prompts) and isinstance(prompts[0], int)
@@ -67,7 +69,8 @@ class LanguageModel:
         sampler = Sampler(options, self.model.vocab_size, self.model.device)
         stops = self.stop_token_ids if stop_token_ids is None else tuple(stop_token_ids)
         cache = cache if cache is not None else self._cache_for(prompts, max_tokens, max_batch)
-        results = _generate(self.model, cache, sampler, prompts, max_tokens, stop_ids=stops, max_batch=max_batch)
+        results = _generate(self.model, cache, sampler, prompts, max_tokens, stop_ids=stops, max_batch=max_batch,
+                            on_step=on_step)
         sampler.check()
         self.model.check_device_errors()
         out = results if details else [r.tokens for r in results]

@@ -1,0 +1,286 @@
+"""Measurement: decode tokens a second at a batch size, prefill tokens a second, the same
+end to end through the Python entry point, and the fractions of the roofline.
+
+Shapes are those of the benchmark configurations (Llama 3.2 1B, 3.2 3B, 3.1 8B) with random
+weights drawn on the device; prompts are seeded uniform token ids. The reference's own
+bench loads a model once and times generate runs (src/main.rs:4152-4274); its decode rate
+leaves out the first token (src/main.rs:4229-4235), as the decode numbers here do.
+
+Timing: CUDA events on the launching stream around exactly K decode steps after W warm-up
+steps; every step reads all weights (gigabytes, far more than the 126 MB of L2), so the
+inputs themselves are larger than L2. Clocks are sampled with nvidia-smi meanwhile.
+"""
+from __future__ import annotations
+
+import json
+import os
+import statistics
+import subprocess
+import threading
+import time
+
+import numpy as np
+import torch
+
+_ROPE_32 = {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+            "original_max_position_embeddings": 8192}
+SHAPES = {
+    2: dict(name="llama-3.2-1b", num_hidden_layers=16, hidden_size=2048, num_attention_heads=32, num_key_value_heads=8,
+            head_dim=64, intermediate_size=8192, vocab_size=128256, rope_theta=500000.0, rope_scaling=_ROPE_32,
+            rms_norm_eps=1e-5, tie_word_embeddings=True, seed=2, context=4096),
+    3: dict(name="llama-3.2-3b", num_hidden_layers=28, hidden_size=3072, num_attention_heads=24, num_key_value_heads=8,
+            head_dim=128, intermediate_size=8192, vocab_size=128256, rope_theta=500000.0, rope_scaling=_ROPE_32,
+            rms_norm_eps=1e-5, tie_word_embeddings=True, seed=3, context=4096),
+    4: dict(name="llama-3.1-8b", num_hidden_layers=32, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+            head_dim=128, intermediate_size=14336, vocab_size=128256, rope_theta=500000.0,
+            rope_scaling={**_ROPE_32, "factor": 8.0}, rms_norm_eps=1e-5, tie_word_embeddings=False, seed=4, context=8192),
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def config_for(index: int, layers: int | None = None) -> dict:
+    s = dict(SHAPES[index])
+    cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "max_position_embeddings": 131072,
+           **{k: v for k, v in s.items() if k not in ("name", "seed", "context")}}
+    if layers:
+        cfg["num_hidden_layers"] = layers
+    return cfg
+
+
+def peaks(repo_root: str | None = None) -> dict:
+    root = repo_root or os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+                if isinstance(d.get(k), (int, float)) and d[k] > 0:
+                    out[k] = float(d[k])
+            out["source"] = "measured"
+            return out
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int = 0):
+        self.samples: list = []
+        self.proc = None
+        self.thread = None
+        self.device_index = device_index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        for p in self.samples:
+            try:
+                sm.append(float(p[0]))
+                mx.append(float(p[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def _prompts(rng, n: int, length: int, vocab: int) -> list:
+    return [rng.integers(0, vocab, size=length).tolist() for _ in range(n)]
+
+
+def linear_params(cfg: dict) -> int:
+    h, i, l = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    return l * (h * (q + 2 * kv) + q * h + 3 * h * i)
+
+
+def prefill_flops(cfg: dict, tokens: int, wanted: int = 1) -> float:
+    attn = 2.0 * tokens * tokens * cfg["num_attention_heads"] * cfg["head_dim"] * cfg["num_hidden_layers"]   # causal: half of 4 T^2
+    return 2.0 * tokens * linear_params(cfg) + attn + 2.0 * wanted * cfg["hidden_size"] * cfg["vocab_size"]
+
+
+def decode_bytes(cfg: dict, batch: int, context: float, elem: int) -> float:
+    """Bytes a decode step has to read: every weight it uses once, and the cache of the live requests."""
+    weights = (linear_params(cfg) + cfg["hidden_size"] * cfg["vocab_size"]
+               + (2 * cfg["num_hidden_layers"] + 1) * cfg["hidden_size"]) * elem
+    kv = 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"] * elem * context * batch
+    return weights + kv
+
+
+def measure_prefill(lm, cfg, tokens: int, rng, reps: int = 5, warmup: int = 3) -> dict:
+    from .engine.model import StepEntry
+    cache = lm.new_cache(((tokens + 63) // 64) * 64, max_slots=1)
+    prompt = _prompts(rng, 1, tokens, cfg["vocab_size"])[0]
+    times = []
+    for r in range(warmup + reps):
+        slot = cache.alloc_slot()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        lm.step(cache, [StepEntry(slot, prompt, [tokens - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        cache.free_slot(slot)
+        if r >= warmup:
+            times.append(a.elapsed_time(b))
+    ms = statistics.median(times)
+    del cache
+    return {"ms": ms, "tokens": tokens, "value": tokens / (ms / 1e3)}
+
+
+def _prefill_batch(lm, cache, prompts, chunk: int = 8):
+    """Prefill all prompts (a few per step, to bound the workspace); returns slots and the
+    greedy first token of each."""
+    from .engine.model import StepEntry
+    slots, firsts = [], []
+    for i in range(0, len(prompts), chunk):
+        part = prompts[i:i + chunk]
+        s = [cache.alloc_slot() for _ in part]
+        logits = lm.step(cache, [StepEntry(sl, p, [len(p) - 1]) for sl, p in zip(s, part)])
+        firsts += logits.argmax(dim=-1).to(torch.int32).tolist()
+        slots += s
+    return slots, firsts
+
+
+def measure_decode_device(lm, cfg, batch: int, prompt_tokens: int, steps: int, warmup: int, rng) -> dict:
+    """K decode steps timed on the device: the captured step graph with the greedy token fed
+    back on the device; the host only sends each step's positions."""
+    from .csrc import ops
+    total = prompt_tokens + steps + warmup + 1
+    cache = lm.new_cache(batch * ((total + 63) // 64) * 64, max_slots=batch)
+    slots, firsts = _prefill_batch(lm, cache, _prompts(rng, batch, prompt_tokens, cfg["vocab_size"]))
+    book = cache.book
+    horizon = warmup + steps
+    book.check_extend([(s, horizon) for s in slots])
+    starts = np.array([book.extend(s, horizon) for s in slots], dtype=np.int32)
+    graph = lm.model.decode_graph(cache, slots, feed=True)
+    i = graph.fill(slots, starts, firsts)
+    graph.send(i, with_tokens=True)
+    if graph.graph is None:
+        graph.capture()
+    h2d = 0
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = 0
+    with ClockSampler() as clocks:
+        for step in range(horizon):
+            if step == warmup:
+                torch.cuda.synchronize()
+                launches0 = ops.launch_count()
+                ev0.record()
+            if step > 0:
+                i = graph.fill(slots, starts + step, None)
+                h2d = graph.send(i, with_tokens=False)
+            graph.replay()
+        ev1.record()
+        torch.cuda.synchronize()
+    launches = ops.launch_count() - launches0
+    for s in slots:
+        book.commit(s, horizon)
+    lm.model.check_device_errors()
+    ms = ev0.elapsed_time(ev1)
+    lm.model.drop_graphs(cache)
+    for s in slots:
+        cache.free_slot(s)
+    return {"ms_total": ms, "ms_per_step": ms / steps, "value": batch * steps / (ms / 1e3), "launches": launches,
+            "h2d_bytes_per_step": h2d, "clocks": clocks.summary(),
+            "context": prompt_tokens + warmup + steps / 2.0}
+
+
+def measure_decode_e2e(lm, cfg, batch: int, prompt_tokens: int, steps: int, warmup: int, rng) -> dict:
+    """The same through ``LanguageModel.generate``: every step sends its tokens and positions
+    from pinned host memory and reads the sampled tokens back."""
+    prompts = _prompts(rng, batch, prompt_tokens, cfg["vocab_size"])
+    stamps = []
+
+    def on_step(_live):
+        stamps.append(time.perf_counter())
+    lm.generate(prompts, max_tokens=warmup + steps + 1, stop_token_ids=(), on_step=on_step)
+    torch.cuda.synchronize()
+    # stamps[0]: prompts done and first token on the host; stamps[j]: j decode steps done
+    dt = stamps[warmup + steps] - stamps[warmup]
+    return {"value": batch * steps / dt, "ms_per_step": dt / steps * 1e3, "h2d_bytes_per_step": lm.model.last_h2d_bytes,
+            "d2h_bytes_per_step": batch * 4}
+
+
+def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warmup: int = 8, dtype: str = "bfloat16",
+        layers: int | None = None, config_index: int = 2, points: bool = True, e2e: bool = True,
+        prefill_tokens: int = 2048) -> dict:
+    from . import api
+    shape = SHAPES[config_index]
+    cfg = config_for(config_index, layers)
+    pk = peaks()
+    lm = api.from_random(cfg, seed=shape["seed"], dtype=dtype)
+    rng = np.random.default_rng(shape["seed"])
+    elem = 2 if dtype == "bfloat16" else 4
+    pre = measure_prefill(lm, cfg, prefill_tokens, rng)
+    flop_peak = (pk["bf16_tflops"] if dtype == "bfloat16" else 75.0) * 1e12
+    pre["frac"] = prefill_flops(cfg, prefill_tokens) / (pre["ms"] / 1e3) / flop_peak
+    dec = measure_decode_device(lm, cfg, batch, prompt_tokens, decode_steps, warmup, rng)
+    bytes_step = decode_bytes(cfg, batch, dec["context"], elem)
+    achieved = bytes_step / (dec["ms_per_step"] / 1e3) / 1e9
+    rec = {
+        "metric": "decode tokens/s, Llama 3.2 1B shape, batch 8 (2048-token prompts)" if (config_index, batch) == (2, 8)
+                  else f"decode tokens/s, {shape['name']} shape, batch {batch}",
+        "value": dec["value"], "unit": "tokens/s", "n_gpus": 1, "steps": decode_steps, "warmup": warmup,
+        "ms_per_step": dec["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if dtype == "bfloat16" else "fp32", "data": "synthetic (seeded uniform token ids, random weights)",
+        "config": {"model": shape["name"], "global_batch": batch, "seq_len": shape["context"],
+                   "prompt_tokens": prompt_tokens, "decode_steps": decode_steps, "parallelism": "single-gpu",
+                   "layers": cfg["num_hidden_layers"], "layers_of_model": shape["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "tied": cfg["tie_word_embeddings"], "weights": f"random, seed {shape['seed']}",
+                   "l2": "inputs larger than L2 (every step reads all weights)", "peaks": pk["source"]},
+        "prefill": {"value": pre["value"], "tokens": pre["tokens"], "ms": pre["ms"], "frac": pre["frac"]},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"]},
+        "clocks": dec["clocks"], "gpu_launches": dec["launches"],
+    }
+    if e2e:
+        e = measure_decode_e2e(lm, cfg, batch, prompt_tokens, decode_steps, warmup, rng)
+        rec["e2e"] = {"value": e["value"], "unit": "tokens/s", "h2d_bytes_per_step": e["h2d_bytes_per_step"],
+                      "d2h_bytes_per_step": e["d2h_bytes_per_step"], "ms_per_step": e["ms_per_step"]}
+    if points:
+        pts = {}
+        for b in (1, 64):
+            if b == batch:
+                pts[f"decode_b{b}"] = dec["value"]
+                continue
+            d = measure_decode_device(lm, cfg, b, prompt_tokens, min(decode_steps, 64), min(warmup, 4), rng)
+            pts[f"decode_b{b}"] = d["value"]
+        rec["points"] = pts
+    return rec

@@ -38,6 +38,17 @@ _SIGNATURES = {
                                       c_void_p, c_void_p, c_void_p],
 }
 _fns: dict = {}
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far by this process (graph replays included)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
 
 
 def _fn(module: str, name: str):
@@ -51,7 +62,9 @@ def _fn(module: str, name: str):
     return f
 
 
-def _check(code: int, what: str):
+def _check(code: int, what: str, launches: int = 1):
+    global _launches
+    _launches += launches
     if code != 0:
         if code in _ERRORS:
             raise KernelError(f"{what}: {_ERRORS[code]}")
@@ -160,7 +173,7 @@ def attn_paged_simt(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_
         _p(q), q.stride(0), _p(out), out.stride(0), dtype_code(q.dtype), _p(k_pages), _p(v_pages), _p(block_table),
         block_table.shape[1], _p(tile_seq), _p(tile_q0), n_tiles, _p(seq_row0), _p(seq_start), _p(seq_new), n_rows,
         n_heads, n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, n_splits, int(window or 0),
-        float(scale), _p(partial), _stream()), "attn_paged_simt")
+        float(scale), _p(partial), _stream()), "attn_paged_simt", 2 if n_splits > 1 else 1)
 
 
 def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, group: int = 0):

@@ -4,10 +4,13 @@ All sequences of a step are packed row after row: sequence ``i`` owns rows
 ``seq_row0[i] .. seq_row0[i] + seq_new[i]``; row ``r`` has token ``tokens[r]``, belongs to
 sequence ``row_seq[r]`` and sits at absolute position ``row_pos[r]`` (the sequence's
 length before the step plus its offset). There is no padding, so there is nothing that
-padding could change. The integer arrays reach the device in one copy.
+padding could change. All integer arrays of a step lie in one buffer and reach the device
+in one copy; a decode step of a fixed batch size always has the same layout, which is what
+lets it run as a captured CUDA graph on a static buffer.
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..cache.book import PAGE
@@ -32,54 +35,125 @@ class Workspace:
         return buf[:n].view(shape)
 
 
+class StepLayout:
+    """Offsets of a step's integer arrays in its one buffer: tokens first (so that a decode
+    loop that keeps its tokens on the device can copy everything but them), then rows,
+    sequences, wanted rows, one block table per cache group, and the query tiles."""
+
+    def __init__(self, n_rows: int, n_seqs: int, n_want: int, table_widths: list, n_tiles: dict):
+        self.n_rows, self.n_seqs, self.n_want = n_rows, n_seqs, n_want
+        self.n_tiles = dict(n_tiles)                   # rows per tile -> number of tiles
+        self.table_widths = list(table_widths)
+        names = [("tokens", n_rows), ("row_seq", n_rows), ("row_pos", n_rows), ("seq_slot", n_seqs),
+                 ("seq_start", n_seqs), ("seq_new", n_seqs), ("seq_row0", n_seqs), ("want_rows", n_want)]
+        names += [(f"table{g}", n_seqs * w) for g, w in enumerate(table_widths)]
+        for r, n in self.n_tiles.items():
+            names += [(f"tile_seq{r}", n), (f"tile_q0{r}", n)]
+        self.offsets, off = {}, 0
+        for name, n in names:
+            self.offsets[name] = (off, n)
+            off += n
+        self.total = off
+
+    def view(self, buf, name):
+        off, n = self.offsets[name]
+        return buf[off:off + n]
+
+
 class StepContext:
-    def __init__(self, *, cache, workspace: Workspace, dtype: torch.dtype, device, slots: list, starts: list,
-                 tokens: list, want: list):
+    """Built per step by the engine (``for_step``) or once for a captured decode graph
+    (``static``); parts read it and never change it."""
+
+    # ---- construction ----
+    def __init__(self, *, cache, workspace: Workspace, dtype: torch.dtype, device, layout: StepLayout,
+                 meta_dev: torch.Tensor):
         self.cache = cache
         self.ws = workspace
         self.dtype = dtype
         self.device = device
-        self.h_slots = list(slots)
-        self.h_start = list(starts)
-        self.h_new = [len(t) for t in tokens]
-        self.n_seqs = len(slots)
-        self.n_rows = sum(self.h_new)
-        self.max_new = max(self.h_new)
-        self.max_len = max(s + n for s, n in zip(self.h_start, self.h_new))
-        self.decode = self.max_new == 1
+        self.layout = layout
+        self.meta_dev = meta_dev
+        self.n_rows, self.n_seqs, self.n_want = layout.n_rows, layout.n_seqs, layout.n_want
+        v = lambda name: layout.view(meta_dev, name)        # noqa: E731
+        self.tokens, self.row_seq, self.row_pos = v("tokens"), v("row_seq"), v("row_pos")
+        self.seq_slot, self.seq_start, self.seq_new = v("seq_slot"), v("seq_start"), v("seq_new")
+        self.seq_row0, self.want_rows = v("seq_row0"), v("want_rows")
+        self._tables = [v(f"table{g}").view(layout.n_seqs, w) for g, w in enumerate(layout.table_widths)]
+        self._tiles = {r: (v(f"tile_seq{r}"), v(f"tile_q0{r}"), n) for r, n in layout.n_tiles.items()}
         self.entry = -1                 # schedule entry that is running
         self.cache_source = None        # entry whose keys and values the running entry reads
-        row0, acc = [], 0
-        for n in self.h_new:
-            row0.append(acc)
-            acc += n
-        self.h_row0 = row0
-        want_rows = [row0[i] + w for i, ws in enumerate(want) for w in ws]
-        self.n_want = len(want_rows)
-        flat_tokens = [t for ts in tokens for t in ts]
-        row_seq = [i for i, n in enumerate(self.h_new) for _ in range(n)]
-        row_pos = [self.h_start[i] + j for i, n in enumerate(self.h_new) for j in range(n)]
+        # host-side knowledge (filled by the constructors below)
+        self.h_slots: list = []
+        self.h_start: list = []
+        self.h_new: list = []
+        self.h_row0: list = []
+        self.max_new = 1
+        self.max_len = 1
+        self.decode = True
+        self.h2d_bytes = 0
+
+    @staticmethod
+    def host_arrays(slots, starts, tokens, want, tables, tile_sizes):
+        """The step's integer arrays as one int32 numpy vector, with its layout."""
+        news = [len(t) for t in tokens]
+        row0 = np.zeros(len(news), dtype=np.int64)
+        if len(news) > 1:
+            row0[1:] = np.cumsum(news[:-1])
+        n_rows = int(sum(news))
+        flat = np.fromiter((t for ts in tokens for t in ts), dtype=np.int32, count=n_rows)
+        row_seq = np.repeat(np.arange(len(news), dtype=np.int32), news)
+        row_pos = (np.arange(n_rows, dtype=np.int64) - np.repeat(row0, news) + np.repeat(np.asarray(starts), news))
+        want_rows = [int(row0[i]) + w for i, ws in enumerate(want) for w in ws]
+        tiles = {}
+        for r in (tile_sizes if max(news) > 1 else [1]):
+            tile_seq, tile_q0 = [], []
+            for i, n in enumerate(news):
+                for q0 in range(0, n, r):
+                    tile_seq.append(i)
+                    tile_q0.append(q0)
+            tiles[r] = (tile_seq, tile_q0)
+        layout = StepLayout(n_rows, len(news), len(want_rows), [len(t[0]) for t in tables],
+                            {r: len(t[0]) for r, t in tiles.items()})
+        parts = [flat, row_seq, row_pos.astype(np.int32), np.asarray(slots, dtype=np.int32),
+                 np.asarray(starts, dtype=np.int32), np.asarray(news, dtype=np.int32), row0.astype(np.int32),
+                 np.asarray(want_rows, dtype=np.int32)]
+        parts += [np.asarray(t, dtype=np.int32).reshape(-1) for t in tables]
+        for tile_seq, tile_q0 in tiles.values():
+            parts += [np.asarray(tile_seq, dtype=np.int32), np.asarray(tile_q0, dtype=np.int32)]
+        return layout, np.concatenate(parts), news, row0.tolist()
+
+    @classmethod
+    def for_step(cls, *, cache, workspace, dtype, device, slots, starts, tokens, want, tile_sizes=(1,)):
+        """A context for one eager step: arrays built on the host and sent in one copy."""
         n_groups = len(cache.book.kv_specs) if cache is not None else 0
-        tables = [cache.book.block_table(g, self.h_slots) for g in range(n_groups)]
-        self._table_width = [len(t[0]) for t in tables]
-        parts = [flat_tokens, row_seq, row_pos, self.h_slots, self.h_start, self.h_new, row0, want_rows]
-        for t in tables:
-            parts.append([p for row in t for p in row])
-        sizes = [len(p) for p in parts]
-        host = torch.tensor([x for p in parts for x in p], dtype=torch.int32)
+        tables = [cache.book.block_table(g, list(slots)) for g in range(n_groups)]
+        layout, host, news, row0 = cls.host_arrays(slots, starts, tokens, want, tables, list(tile_sizes))
+        t = torch.from_numpy(host)
         if torch.device(device).type == "cuda":
-            host = host.pin_memory()
-        dev = host.to(device, non_blocking=True)
-        self._host_meta = host            # keep the pinned buffer alive until the copy ran
-        views, off = [], 0
-        for n in sizes:
-            views.append(dev[off:off + n])
-            off += n
-        (self.tokens, self.row_seq, self.row_pos, self.seq_slot, self.seq_start, self.seq_new, self.seq_row0,
-         self.want_rows) = views[:8]
-        self._tables = [views[8 + g].view(self.n_seqs, self._table_width[g]) for g in range(n_groups)]
-        self._tiles: dict = {}
-        self.h2d_bytes = host.numel() * 4
+            t = t.pin_memory()
+        ctx = cls(cache=cache, workspace=workspace, dtype=dtype, device=device, layout=layout,
+                  meta_dev=t.to(device, non_blocking=True))
+        ctx._host_meta = t                # keep the pinned buffer alive until the copy ran
+        ctx._set_host(slots, starts, news, row0)
+        ctx.h2d_bytes = host.nbytes
+        return ctx
+
+    @classmethod
+    def static(cls, *, cache, workspace, dtype, device, n_seqs, table_widths):
+        """A context on a fixed buffer for decode steps of ``n_seqs`` sequences (one token each,
+        every sequence's logits wanted); ``meta_dev`` is refilled before every replay."""
+        layout = StepLayout(n_seqs, n_seqs, n_seqs, table_widths, {1: n_seqs})
+        meta = torch.zeros(layout.total, dtype=torch.int32, device=device)
+        ctx = cls(cache=cache, workspace=workspace, dtype=dtype, device=device, layout=layout, meta_dev=meta)
+        ctx._set_host([0] * n_seqs, [0] * n_seqs, [1] * n_seqs, list(range(n_seqs)))
+        ctx.max_len = max(table_widths) * PAGE if table_widths else 1
+        return ctx
+
+    def _set_host(self, slots, starts, news, row0):
+        self.h_slots, self.h_start, self.h_new, self.h_row0 = list(slots), list(starts), list(news), list(row0)
+        self.max_new = max(news)
+        self.max_len = max(s + n for s, n in zip(starts, news))
+        self.decode = self.max_new == 1
 
     # ---- helpers for parts ----
     def buffer(self, name: str, shape: tuple, dtype: torch.dtype | None = None) -> torch.Tensor:
@@ -102,21 +176,13 @@ class StepContext:
     def query_tiles(self, rows_per_tile: int):
         """Tiles of at most ``rows_per_tile`` consecutive new rows of one sequence:
         (tile_seq, tile_q0, n_tiles) on the device."""
-        got = self._tiles.get(rows_per_tile)
-        if got is None:
-            seqs, q0s = [], []
-            for i, n in enumerate(self.h_new):
-                for q0 in range(0, n, rows_per_tile):
-                    seqs.append(i)
-                    q0s.append(q0)
-            t = torch.tensor(seqs + q0s, dtype=torch.int32)
-            if torch.device(self.device).type == "cuda":
-                t = t.pin_memory()
-            d = t.to(self.device, non_blocking=True)
-            got = (d[:len(seqs)], d[len(seqs):], len(seqs), t)
-            self._tiles[rows_per_tile] = got
-            self.h2d_bytes += t.numel() * 4
-        return got[0], got[1], got[2]
+        if self.decode:                       # one row per sequence: every tiling is the same
+            return self._tiles[1]
+        try:
+            return self._tiles[rows_per_tile]
+        except KeyError:
+            raise ValueError(f"this step has tiles of {sorted(self._tiles)} rows, not of {rows_per_tile}; the "
+                             f"mixer's query_tile_sizes() must name every size it uses") from None
 
     @property
     def max_blocks_in_use(self) -> int:

@@ -1,0 +1,106 @@
+"""Decode steps as captured CUDA graphs.
+
+A decode step of a fixed number of sequences always launches the same kernels on the same
+buffers; only the integer arrays of the step change. So the step is captured once per
+(batch size, block-table widths) on a static context and replayed: per step the host fills
+a pinned copy of the arrays, sends it in one copy, and launches the graph. With ``feed`` the
+graph also picks the next token greedily and writes it where the next step reads its
+tokens, so a decode loop can run without any traffic to the host.
+
+The reference measured CUDA graphs as a loss on its 7.9 ms/token regime
+(src/cuda_resident.rs:5558-5571); at a few hundred microseconds per step on a B200 the
+launch gaps are most of the step without them.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..csrc import ops
+from .context import StepContext, Workspace
+
+_RING = 4
+
+
+def bucket_width(blocks: int) -> int:
+    """Block-table width a graph is captured for: the next power of two, at least 4."""
+    w = 4
+    while w < blocks:
+        w *= 2
+    return w
+
+
+class DecodeGraph:
+    def __init__(self, model, cache, n_seqs: int, widths: list, feed: bool):
+        self.model, self.cache, self.n_seqs, self.widths, self.feed = model, cache, n_seqs, list(widths), feed
+        dev = model.device
+        self.ctx = StepContext.static(cache=cache, workspace=Workspace(dev), dtype=model.dtype, device=dev,
+                                      n_seqs=n_seqs, table_widths=self.widths)
+        lay = self.ctx.layout
+        self.host = [torch.zeros(lay.total, dtype=torch.int32).pin_memory() for _ in range(_RING)]
+        self.host_np = [h.numpy() for h in self.host]
+        self.events = [None] * _RING
+        self.turn = 0
+        ar = np.arange(n_seqs, dtype=np.int32)
+        for h in self.host_np:
+            for name, val in (("row_seq", ar), ("seq_new", 1), ("seq_row0", ar), ("want_rows", ar), ("tile_seq1", ar),
+                              ("tile_q01", 0)):
+                lay.view(h, name)[:] = val
+        self.graph = None
+        self.logits = None
+        self.next_tokens = None
+        self.launches = 0
+        self._table_key = [None] * _RING
+
+    def fill(self, slots: list, starts: list, tokens) -> int:
+        """Write the step's arrays into the next pinned buffer; returns its index."""
+        i = self.turn
+        self.turn = (self.turn + 1) % _RING
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        lay, h = self.ctx.layout, self.host_np[i]
+        if tokens is not None:
+            lay.view(h, "tokens")[:] = tokens
+        lay.view(h, "row_pos")[:] = starts
+        lay.view(h, "seq_start")[:] = starts
+        lay.view(h, "seq_slot")[:] = slots
+        book = self.cache.book
+        key = tuple((s, book.generation[s]) for s in slots)
+        if self._table_key[i] != key:
+            for g, w in enumerate(self.widths):
+                lay.view(h, f"table{g}")[:] = np.asarray(book.block_table(g, slots, width=w), dtype=np.int32).reshape(-1)
+            self._table_key[i] = key
+        return i
+
+    def send(self, i: int, with_tokens: bool) -> int:
+        """One copy of the arrays to the device (without the tokens when the device has them)."""
+        skip = 0 if with_tokens else self.n_seqs
+        self.ctx.meta_dev[skip:].copy_(self.host[i][skip:], non_blocking=True)
+        ev = self.events[i] or torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+        return (self.ctx.layout.total - skip) * 4
+
+    def _forward(self):
+        logits = self.model.run(self.ctx)
+        if self.feed:
+            ops.argmax_rows(logits, self.ctx.tokens, self.model._err)
+        return logits
+
+    def capture(self):
+        """Warm up eagerly on the buffer's present contents, then capture."""
+        tokens_before = self.ctx.tokens.clone()
+        self._forward()
+        self.ctx.tokens.copy_(tokens_before)
+        torch.cuda.synchronize()
+        before = ops.launch_count()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.logits = self._forward()
+        self.launches = ops.launch_count() - before
+        self.graph = g
+
+    def replay(self):
+        self.graph.replay()
+        ops.add_launches(self.launches)
+        return self.logits

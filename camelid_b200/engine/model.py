@@ -67,6 +67,11 @@ class DecoderModel:
         self.workspace = Workspace(self.device)
         self._err = None
         self.last_h2d_bytes = 0
+        self.tile_sizes = sorted({r for b in self.blocks for r in b.query_tile_sizes()}) or [1]
+        # decode steps replay captured CUDA graphs when every part can run inside one
+        self.use_graphs = all(b.graph_safe for b in self.blocks) and all(
+            p.graph_safe for p in (self.embedding, self.final_norm, self.head))
+        self._graphs: dict = {}
 
     # ---- construction ----
     @classmethod
@@ -155,15 +160,47 @@ class DecoderModel:
         of the entries and of their ``want`` lists (an empty tensor if nothing is wanted)."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._validate(cache, entries)
+        if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            return self._graph_step(cache, entries)
         starts = [cache.book.extend(e.slot, len(e.tokens)) for e in entries]
-        ctx = StepContext(cache=cache, workspace=self.workspace, dtype=self.dtype, device=self.device,
-                          slots=[e.slot for e in entries], starts=starts,
-                          tokens=[[int(t) for t in e.tokens] for e in entries],
-                          want=[[int(w) for w in e.want] for e in entries])
+        ctx = StepContext.for_step(cache=cache, workspace=self.workspace, dtype=self.dtype, device=self.device,
+                                   slots=[e.slot for e in entries], starts=starts,
+                                   tokens=[[int(t) for t in e.tokens] for e in entries],
+                                   want=[[int(w) for w in e.want] for e in entries], tile_sizes=self.tile_sizes)
         logits = self.run(ctx)
         for e in entries:
             cache.book.commit(e.slot, len(e.tokens))
         self.last_h2d_bytes = ctx.h2d_bytes
+        return logits
+
+    def decode_graph(self, cache: SequenceCache, slots: list, feed: bool = False):
+        """The captured graph for one-token steps of these slots (made at its first use)."""
+        from .graphs import DecodeGraph, bucket_width
+        book = cache.book
+        widths = [bucket_width(max(len(book.pages[g][s]) for s in slots)) for g in range(len(book.kv_specs))]
+        key = (id(cache), len(slots), tuple(widths), feed)
+        graph = self._graphs.get(key)
+        if graph is None:
+            graph = DecodeGraph(self, cache, len(slots), widths, feed)
+            self._graphs[key] = graph
+        return graph
+
+    def drop_graphs(self, cache=None) -> None:
+        """Forget the captured graphs (of one cache, or all): they keep their cache alive."""
+        for key in [k for k, g in self._graphs.items() if cache is None or g.cache is cache]:
+            del self._graphs[key]
+
+    def _graph_step(self, cache: SequenceCache, entries: list) -> torch.Tensor:
+        slots = [e.slot for e in entries]
+        starts = [cache.book.extend(s, 1) for s in slots]
+        graph = self.decode_graph(cache, slots)
+        i = graph.fill(slots, starts, [int(e.tokens[0]) for e in entries])
+        self.last_h2d_bytes = graph.send(i, with_tokens=True)
+        if graph.graph is None:
+            graph.capture()
+        logits = graph.replay()
+        for s in slots:
+            cache.book.commit(s, 1)
         return logits
 
     def run(self, ctx: StepContext) -> torch.Tensor:

@@ -32,6 +32,8 @@ def set_tensor_core_path(fn) -> None:
 
 @register_part("mixer", "attention")
 class GroupedQueryAttention(Part):
+    graph_safe = True
+
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         self.hidden_size = int(params["hidden_size"])
@@ -71,6 +73,9 @@ class GroupedQueryAttention(Part):
 
     def cache_spec(self):
         return KVSpec(self.num_kv_heads, self.head_dim, self.window)
+
+    def query_tile_sizes(self):
+        return [ops.attn_tiling(self.num_heads, self.num_kv_heads, False)[0]]
 
     # ------------------------------------------------------------------------------
     def forward(self, ctx, x, residual):

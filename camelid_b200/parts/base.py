@@ -40,6 +40,10 @@ class TensorSpec:
 class Part:
     role: str = ""
     kind: str = ""
+    # True if ``forward`` only launches work on the device arrays of the context (no host-side
+    # reads of the step, no allocation that must outlive the call): such a part can run
+    # inside a captured CUDA graph. Parts that do not say so make the model step eagerly.
+    graph_safe: bool = False
 
     def __init__(self, params: dict, prefix: str = ""):
         self.params = dict(params)
@@ -54,6 +58,11 @@ class Part:
 
     def cache_spec(self):
         return None
+
+    def query_tile_sizes(self) -> list:
+        """Mixers: the sizes of query tiles (rows per tile) their prefill kernels ask the
+        step context for."""
+        return []
 
 
 _REGISTRY: dict = {role: {} for role in ROLES}

@@ -28,8 +28,15 @@ class PreNormBlock(Part):
         for p in self.parts():
             p.load(tensors, device, dtype)
 
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts())
+
     def cache_spec(self):
         return self.mixer.cache_spec()
+
+    def query_tile_sizes(self):
+        return self.mixer.query_tile_sizes()
 
     def forward(self, ctx, h):
         x = self.norm1.forward(ctx, h)

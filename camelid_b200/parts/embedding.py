@@ -12,6 +12,8 @@ from .base import Part, TensorSpec, register_part, to_device
 
 @register_part("embedding", "embedding")
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         self.vocab_size = int(params["vocab_size"])
@@ -31,6 +33,7 @@ class TokenEmbedding(Part):
 @register_part("head", "lm_head")
 class OutputProjection(Part):
     """logits = x W^T in float32, without bias, soft-cap or scale (src/inference.rs:4284-4290)."""
+    graph_safe = True
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)

@@ -10,6 +10,8 @@ from .base import Part, TensorSpec, register_part, to_device
 
 @register_part("ffn", "swiglu")
 class SwiGLU(Part):
+    graph_safe = True
+
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         self.hidden_size = int(params["hidden_size"])

@@ -11,6 +11,8 @@ from .base import Part, TensorSpec, register_part, to_device
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
+    graph_safe = True
+
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         self.hidden_size = int(params["hidden_size"])

@@ -40,6 +40,8 @@ def rotary_frequencies(rotary_dim: int, theta: float, scaling: dict | None) -> n
 
 @register_part("position", "rope")
 class RotaryEncoding(Part):
+    graph_safe = True
+
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         self.rotary_dim = int(params["rotary_dim"])
@@ -56,6 +58,7 @@ class RotaryEncoding(Part):
 @register_part("position", "none")
 class NoPositionEncoding(Part):
     """Leaves q and k as they are: a rotary encoding of zero dimensions."""
+    graph_safe = True
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)

@@ -12,10 +12,11 @@ pytestmark = pytest.mark.gpu
 DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
-def _ctx(cache, dtype, slots, starts, token_lists, want=None):
+def _ctx(cache, dtype, slots, starts, token_lists, want=None, tile_sizes=(1,)):
     from camelid_b200.engine.context import StepContext, Workspace
-    return StepContext(cache=cache, workspace=Workspace("cuda"), dtype=DT[dtype], device="cuda", slots=slots,
-                       starts=starts, tokens=token_lists, want=want or [[] for _ in slots])
+    return StepContext.for_step(cache=cache, workspace=Workspace("cuda"), dtype=DT[dtype], device="cuda", slots=slots,
+                                starts=starts, tokens=token_lists, want=want or [[] for _ in slots],
+                                tile_sizes=tile_sizes)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -129,7 +130,7 @@ def test_attention_part(cuda, dtype, heads, kv_heads, hd, rot):
     for step, news in enumerate([[l - 3 for l in lens], [1, 1], [1, 1], [1, 1]]):
         for s, n in zip(slots, news):
             cache.book.extend(s, n)
-        ctx = _ctx(cache, dtype, slots, list(done), [[0] * n for n in news])
+        ctx = _ctx(cache, dtype, slots, list(done), [[0] * n for n in news], tile_sizes=mixer.query_tile_sizes())
         ctx.entry = 0
         x = torch.cat([xs[i][done[i]:done[i] + n] for i, n in enumerate(news)]).cuda()
         res = torch.zeros(sum(news), hidden, device="cuda")
