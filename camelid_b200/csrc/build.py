@@ -29,6 +29,7 @@ MODULES = {
     "attention_simt": ["attention_simt.cu"],
     "gemm_simt": ["gemm_simt.cu"],
     "sampling": ["sampling.cu"],
+    "gemm_tc": ["gemm_tc.cu"],
 }
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]

@@ -1,0 +1,387 @@
+// bfloat16 matrix products on the fifth-generation tensor cores: TMA loads into swizzled
+// shared memory, tcgen05.mma issued by one thread with the accumulator in tensor memory,
+// tcgen05.ld in the epilogue. One kernel serves prefill and decode:
+//
+//   D[128 x BN] tile = Arows[128, K] * Brows[BN, K]^T        (both operands K-major)
+//
+// * prefill: Arows = activations [tokens, K], Brows = weights [out, K]; BN = 128 or 256;
+//   epilogues: store bfloat16, store float, add into the float residual stream, SwiGLU on
+//   packed gate/up rows (interleaved in groups of 16 output columns).
+// * decode ("transposed"): Arows = weights [out, K], Brows = activations [batch, K] with
+//   BN = 16..64 >= batch, so every weight byte crosses the memory bus once and no tensor-core
+//   row is wasted on padding; K may be split over gridDim.z, each split writing a float
+//   partial [split][batch][out] that the consumer sums in order (no atomics: the result does
+//   not depend on timing); epilogues: float partial, SwiGLU to bfloat16 (no split).
+//
+// It stands where the reference runs q8_gemv / q8_gemm_batched
+// (src/cuda_resident.rs:230, :1494), whose batched form re-reads the weights once per 8
+// tokens (src/cuda_resident.rs:8824-8847).
+//
+// Warp roles (192 threads): warp 0 lane 0 issues TMA loads through a ring of stages, warp 1
+// allocates tensor memory and lane 0 issues the MMAs, warps 2-5 read the accumulator (each
+// its own quarter of the 128 lanes) and write the result. Every wait on an mbarrier is
+// bounded: when a bound is hit the kernel sets *err, lets its copies land, frees its tensor
+// memory and returns. No load uses cluster multicast.
+#include "common.cuh"
+#include <cuda.h>
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define TC_WAIT_CYCLES 2000000000ll
+
+enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_SWIGLU = 3, TC_T_PARTIAL = 4, TC_T_SWIGLU = 5 };
+
+struct TcParams {
+    void* C;            // output (type by epilogue)
+    long ldc;           // row stride of C in elements
+    int rowsA, rowsB;   // valid rows of the two operands
+    int num_kb;         // k-blocks of 64 in total
+    int kb_per_split;
+    int* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false (and *abort set) when the bound is hit or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > TC_WAIT_CYCLES) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16),
+// 128-byte swizzled as TMA writes it: start address, leading offset 1 (unused for swizzled
+// K-major), stride 1024 bytes between groups of 8 rows, version 1, layout SWIZZLE_128B.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__host__ __device__ constexpr int tc_stages(int bn) {
+    return bn >= 256 ? 4 : (bn >= 128 ? 6 : 8);
+}
+__host__ __device__ constexpr int tc_tmem_cols(int bn) { return bn <= 32 ? 32 : (bn <= 64 ? 64 : (bn <= 128 ? 128 : 256)); }
+__host__ __device__ constexpr size_t tc_smem_bytes(int bn) {
+    return 1024 /*alignment slack*/ + (size_t)tc_stages(bn) * (TC_BM * 128 + bn * 128) + 256 /*barriers*/;
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, TcParams p) {
+    constexpr int STAGES = tc_stages(BN);
+    constexpr uint32_t A_BYTES = TC_BM * 128, B_BYTES = BN * 128;
+    constexpr uint32_t TMEM_COLS = tc_tmem_cols(BN);
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t smemA = base, smemB = base + STAGES * A_BYTES;
+    const uint32_t bars = smemB + STAGES * B_BYTES;            // full[S], empty[S], accum, then tmem slot + abort
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + STAGES * (A_BYTES + B_BYTES) + (2 * STAGES + 1) * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int a0 = blockIdx.x * TC_BM, b0 = blockIdx.y * BN, split = blockIdx.z;
+    const int kb_begin = split * p.kb_per_split;
+    const int kb_end = min(p.num_kb, kb_begin + p.kb_per_split);
+    const int n_kb = max(0, kb_end - kb_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_d = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+                if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) break;
+                mbar_expect_tx(full_bar(s), A_BYTES + B_BYTES);
+                const int k = (kb_begin + i) * TC_BK;
+                tma_load_2d(smemA + s * A_BYTES, &mapA, full_bar(s), k, a0);
+                tma_load_2d(smemB + s * B_BYTES, &mapB, full_bar(s), k, b0);
+                issued = i + 1;
+            }
+            if (*abort_flag) {
+                // let the copies that are in flight land before the block leaves
+                for (int i = max(0, issued - STAGES); i < issued; ++i) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(full_bar(i % STAGES), (uint32_t)(i / STAGES) & 1u) &&
+                           clock64() - t0 < 20000000ll) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                       ((uint32_t)(TC_BM >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+                ok = mbar_wait(full_bar(s), ph, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t adesc = smem_desc_sw128(smemA + s * A_BYTES);
+                const uint64_t bdesc = smem_desc_sw128(smemB + s * B_BYTES);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)
+                    tc_mma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (i | k) ? 1u : 0u);
+                tc_commit(empty_bar(s));         // the stage is free once these MMAs have read it
+            }
+            if (ok) tc_commit(accum_bar);        // the accumulator is complete
+        }
+    } else {
+        const int q = warp & 3;                  // the quarter of tensor-memory lanes this warp may read
+        const int rowA = a0 + q * 32 + lane;
+        bool ok = true;
+        if (n_kb > 0) ok = mbar_wait(accum_bar, 0, abort_flag);
+        tc_fence_after();
+        if (ok) {
+            const uint32_t taddr = tmem_d + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t r[16];
+                if (n_kb > 0) {
+                    tc_ld16(taddr + c, r);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) r[i] = 0u;
+                }
+                const int colB = b0 + c;
+                if (EPI == TC_STORE || EPI == TC_STORE_F32 || EPI == TC_ADD_F32) {
+                    if (rowA < p.rowsA && colB < p.rowsB) {
+                        const int n_ok = min(16, p.rowsB - colB);
+                        if (EPI == TC_STORE) {
+                            bf16* dst = (bf16*)p.C + (size_t)rowA * p.ldc + colB;
+                            if (n_ok == 16 && (((uintptr_t)dst & 15) == 0)) {
+                                uint32_t w[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                                    w[i] = *reinterpret_cast<uint32_t*>(&h);
+                                }
+                                reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                                reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                            } else {
+                                for (int i = 0; i < n_ok; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+                            }
+                        } else {
+                            float* dst = (float*)p.C + (size_t)rowA * p.ldc + colB;
+                            const bool vec = n_ok == 16 && (((uintptr_t)dst & 15) == 0);
+                            if (vec) {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                                           __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                                    if (EPI == TC_ADD_F32) {
+                                        const float4 o = reinterpret_cast<float4*>(dst)[i];
+                                        v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                                    }
+                                    reinterpret_cast<float4*>(dst)[i] = v;
+                                }
+                            } else {
+                                for (int i = 0; i < n_ok; ++i) {
+                                    const float v = __uint_as_float(r[i]);
+                                    dst[i] = (EPI == TC_ADD_F32) ? dst[i] + v : v;
+                                }
+                            }
+                        }
+                    }
+                } else if (EPI == TC_SWIGLU) {
+                    // columns come in groups of 32: 16 gate columns, then the 16 up columns of the same outputs
+                    uint32_t u[16];
+                    tc_ld16(taddr + c + 16, u);
+                    const int out_col = colB / 2;
+                    const int inter = p.rowsB / 2;
+                    if (rowA < p.rowsA && out_col < inter) {
+                        bf16* dst = (bf16*)p.C + (size_t)rowA * p.ldc + out_col;
+                        const int n_ok = min(16, inter - out_col);
+                        for (int i = 0; i < n_ok; ++i) {
+                            const float g = __uint_as_float(r[i]);
+                            dst[i] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * __uint_as_float(u[i]));
+                        }
+                    }
+                    c += 16;
+                } else if (EPI == TC_T_PARTIAL) {
+                    // transposed: this thread owns output feature rowA for 16 batch rows
+                    if (rowA < p.rowsA) {
+                        float* dst = (float*)p.C + ((size_t)split * p.rowsB) * p.ldc + rowA;
+                        const int n_ok = min(16, p.rowsB - colB);
+                        for (int i = 0; i < n_ok; ++i) dst[(size_t)(colB + i) * p.ldc] = __uint_as_float(r[i]);
+                    }
+                } else {   // TC_T_SWIGLU: lanes 0-15 hold gate rows, lanes 16-31 the up rows of the same outputs
+                    const int inter = p.rowsA / 2;
+                    const int out_j = (a0 + q * 32) / 2 + (lane & 15);
+                    const int n_ok = min(16, p.rowsB - colB);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float mine = __uint_as_float(r[i]);
+                        const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+                        if (lane < 16 && i < n_ok && out_j < inter) {
+                            ((bf16*)p.C)[(size_t)(colB + i) * p.ldc + out_j] =
+                                __float2bfloat16_rn((mine / (1.0f + expf(-mine))) * other);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 2);
+}
+
+// ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A 2-D map over a row-major bfloat16 matrix [rows, K] with row stride ld (elements):
+// boxes of 64 columns (128 bytes, swizzled) by box_rows rows; out-of-range parts read zero.
+static int make_map(CUtensorMap* map, const void* base, long rows, long K, long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return CML_ERR_BAD_SIZE;
+    if (((uintptr_t)base & 15) || ((ld * 2) & 15)) return CML_ERR_BAD_ALIGN;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : CML_ERR_BAD_SIZE;
+}
+
+template <int BN, int EPI>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t s) {
+    const size_t smem = tc_smem_bytes(BN);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    gemm_tc_kernel<BN, EPI><<<grid, TC_THREADS, smem, s>>>(ma, mb, p);
+    return (int)cudaGetLastError();
+}
+
+// A: [rowsA, K] bfloat16 (ld lda), B: [rowsB, K] bfloat16 (ld ldb).
+// Normal epilogues (0..3) write C[rowA][rowB]; transposed ones (4, 5) write C[..][rowA] per rowB.
+// bn: tile over B rows (16, 32, 64, 128 or 256). splits > 1 only with TC_T_PARTIAL.
+extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, long ldb, int rowsB, int K, void* C,
+                           long ldc, int epilogue, int bn, int splits, int* err, void* stream) {
+    if (rowsA <= 0 || rowsB <= 0) return 0;
+    if (K <= 0 || (K & 7)) return CML_ERR_BAD_SIZE;
+    if (splits < 1 || (splits > 1 && epilogue != TC_T_PARTIAL)) return CML_ERR_BAD_SIZE;
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, A, rowsA, K, lda, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mb, B, rowsB, K, ldb, bn);
+    if (rc) return rc;
+    TcParams p;
+    p.C = C; p.ldc = ldc; p.rowsA = rowsA; p.rowsB = rowsB;
+    p.num_kb = (K + TC_BK - 1) / TC_BK;
+    if (splits > p.num_kb) splits = p.num_kb;
+    p.kb_per_split = (p.num_kb + splits - 1) / splits;
+    p.err = err;
+    dim3 grid((rowsA + TC_BM - 1) / TC_BM, (rowsB + bn - 1) / bn, splits);
+    if (grid.y > 65535 || grid.z > 65535) return CML_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+#define TC_CASE(BN_, EPI_) if (bn == BN_ && epilogue == EPI_) return launch_tc<BN_, EPI_>(ma, mb, p, grid, s)
+    TC_CASE(128, TC_STORE); TC_CASE(128, TC_STORE_F32); TC_CASE(128, TC_ADD_F32); TC_CASE(128, TC_SWIGLU);
+    TC_CASE(256, TC_STORE); TC_CASE(256, TC_STORE_F32); TC_CASE(256, TC_ADD_F32); TC_CASE(256, TC_SWIGLU);
+    TC_CASE(64, TC_STORE); TC_CASE(64, TC_STORE_F32); TC_CASE(64, TC_ADD_F32); TC_CASE(64, TC_SWIGLU);
+    TC_CASE(16, TC_T_PARTIAL); TC_CASE(32, TC_T_PARTIAL); TC_CASE(64, TC_T_PARTIAL);
+    TC_CASE(16, TC_T_SWIGLU); TC_CASE(32, TC_T_SWIGLU); TC_CASE(64, TC_T_SWIGLU);
+#undef TC_CASE
+    return CML_ERR_BAD_SIZE;
+}

@@ -4,7 +4,7 @@ an error, never a detour through library code."""
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_float, c_int, c_long, c_void_p
 
 import torch
 
@@ -21,10 +21,17 @@ _ERRORS = {-2: "unsupported element type", -3: "a size is outside what the kerne
 
 _SIGNATURES = {
     ("rowwise", "cml_embed_gather"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
-    ("rowwise", "cml_rmsnorm"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
+    ("rowwise", "cml_rmsnorm"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p,
+                                 c_int, c_long, c_void_p],
+    ("rowwise", "cml_add_partials"): [c_void_p, c_void_p, c_int, c_long, c_void_p],
     ("rowwise", "cml_swiglu_packed"): [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("rope_kv", "cml_rope_kv_write"): [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ("rope_kv", "cml_rope_kv_from_partials"): [c_void_p, c_int, c_long, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
+                                               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                               c_int, c_int, c_int, c_void_p],
+    ("gemm_tc", "cml_gemm_tc"): [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_void_p, c_long, c_int, c_int,
+                                 c_int, c_void_p, c_void_p],
     ("attention_simt", "cml_attn_paged_simt"): [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                                 c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -104,16 +111,32 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, e
                                              table.shape[0], _p(err), _stream()), "embed_gather")
 
 
-def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, rows_index: torch.Tensor | None = None):
-    """out[r] = rmsnorm(x[rows_index[r] or r]) * weight; x float32, out float32 or bfloat16."""
-    _dev(x, weight, out, rows_index)
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, rows_index: torch.Tensor | None = None,
+            partial: torch.Tensor | None = None):
+    """out[r] = rmsnorm(x[rows_index[r] or r]) * weight; x float32, out float32 or bfloat16.
+    ``partial`` (float32 [splits, x rows, hidden]) is first added to x, split by split; without
+    ``rows_index`` the sum is written back to x."""
+    _dev(x, weight, out, rows_index, partial)
     rows, hidden = out.shape
     assert x.dtype == torch.float32 and x.shape[1] == hidden and weight.shape[0] == hidden
     assert x.is_contiguous() and out.is_contiguous()
     if rows_index is not None:
         assert rows_index.dtype == torch.int32 and rows_index.numel() >= rows
+    n_splits, stride = 0, 0
+    if partial is not None:
+        assert partial.dtype == torch.float32 and partial.is_contiguous() and partial.shape[1:] == x.shape
+        n_splits, stride = partial.shape[0], partial.stride(0)
     _check(_fn("rowwise", "cml_rmsnorm")(_p(x), _p(weight), dtype_code(weight.dtype), _p(out), dtype_code(out.dtype),
-                                        _p(rows_index), rows, hidden, float(eps), _stream()), "rmsnorm")
+                                        _p(rows_index), rows, hidden, float(eps), _p(partial), n_splits, stride,
+                                        _stream()), "rmsnorm")
+
+
+def add_partials(x: torch.Tensor, partial: torch.Tensor):
+    """x += sum over splits of partial[split] (float32), splits in index order."""
+    _dev(x, partial)
+    assert x.dtype == torch.float32 and partial.dtype == torch.float32 and partial.shape[1:] == x.shape
+    assert x.is_contiguous() and partial.is_contiguous()
+    _check(_fn("rowwise", "cml_add_partials")(_p(x), _p(partial), partial.shape[0], x.numel(), _stream()), "add_partials")
 
 
 def swiglu_packed(gu: torch.Tensor, act: torch.Tensor, group: int):
@@ -142,6 +165,48 @@ def rope_kv_write(qkv: torch.Tensor, row_pos, row_seq, block_table, k_pages, v_p
         _p(qkv), dtype_code(qkv.dtype), rows, qkv.stride(0), _p(row_pos), _p(row_seq), _p(block_table), max_blocks,
         _p(k_pages), _p(v_pages), _p(inv_freq), rotary_dim, n_heads, n_kv_heads, head_dim, 1 if write_kv else 0,
         _stream()), "rope_kv_write")
+
+
+def rope_kv_from_partials(partial: torch.Tensor, q_out: torch.Tensor, row_pos, row_seq, block_table, k_pages, v_pages,
+                          inv_freq, rotary_dim: int, n_heads: int, n_kv_heads: int, head_dim: int, write_kv: bool):
+    """The same as rope_kv_write on the split sums ``partial`` (float32 [splits, rows, width]) of
+    the q/k/v product; the rotated q goes to ``q_out`` in the compute type."""
+    _dev(partial, q_out, row_pos, row_seq, block_table, k_pages, v_pages, inv_freq)
+    n_splits, rows, width = partial.shape
+    assert partial.dtype == torch.float32 and partial.is_contiguous() and q_out.stride(1) == 1
+    assert q_out.shape == (rows, n_heads * head_dim) and inv_freq.numel() * 2 == rotary_dim
+    if write_kv:
+        assert k_pages.dtype == q_out.dtype and k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim)
+        assert k_pages.is_contiguous() and v_pages.is_contiguous()
+    _check(_fn("rope_kv", "cml_rope_kv_from_partials")(
+        _p(partial), n_splits, partial.stride(0), width, _p(q_out), q_out.stride(0), dtype_code(q_out.dtype), rows,
+        _p(row_pos), _p(row_seq), _p(block_table), block_table.shape[1] if write_kv else 0, _p(k_pages), _p(v_pages),
+        _p(inv_freq), rotary_dim, n_heads, n_kv_heads, head_dim, 1 if write_kv else 0, _stream()),
+        "rope_kv_from_partials")
+
+
+TC_STORE, TC_STORE_F32, TC_ADD_F32, TC_SWIGLU, TC_T_PARTIAL, TC_T_SWIGLU = 0, 1, 2, 3, 4, 5
+
+
+def gemm_tc_usable(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel takes these operands ([rows, K] bfloat16, K-major): TMA
+    needs 16-byte aligned bases and row strides, so K and the strides must be multiples of 8."""
+    return (a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.shape[1] == b.shape[1]
+            and a.shape[1] % 8 == 0 and a.stride(1) == 1 and b.stride(1) == 1 and a.stride(0) % 8 == 0
+            and b.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0)
+
+
+def gemm_tc(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, epilogue: int, bn: int, splits: int, err: torch.Tensor):
+    """D = a @ b.T on the tensor cores (see gemm_tc.cu). Epilogues 0..3 write c[row of a][row of b];
+    4 and 5 are transposed: c[split][row of b][row of a] partial sums, or SwiGLU of packed a rows."""
+    _dev(a, b, c, err)
+    if not gemm_tc_usable(a, b):
+        raise KernelError("gemm_tc: operands must be bfloat16 [rows, K] with K and the row strides multiples of 8 "
+                          "and 16-byte aligned bases")
+    assert c.stride(-1) == 1
+    ldc = c.stride(-2)
+    _check(_fn("gemm_tc", "cml_gemm_tc")(_p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], a.shape[1],
+                                        _p(c), ldc, epilogue, bn, splits, _p(err), _stream()), "gemm_tc")
 
 
 def attn_tiling(n_heads: int, n_kv_heads: int, decode: bool) -> tuple[int, int, int]:

@@ -74,6 +74,99 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
     }
 }
 
+// The same on the split sums of the q/k/v product: row r of the product is the sum over s of
+// partial[s][r][:] (float, `width` columns, summed in index order). The rotated q goes to
+// q_out in the compute type; k and v go to the cache.
+template <typename T>
+__global__ void rope_kv_from_partials_kernel(const float* __restrict__ partial, int n_splits, size_t split_stride,
+                                             int width, T* __restrict__ q_out, int q_stride,
+                                             const int* __restrict__ row_pos, const int* __restrict__ row_seq,
+                                             const int* __restrict__ block_table, int max_blocks,
+                                             T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                             const float* __restrict__ inv_freq, int rotary_dim, int n_heads,
+                                             int n_kv_heads, int head_dim, int write_kv) {
+    extern __shared__ float sh[];              // cos[half], sin[half], row[width]
+    const int half = rotary_dim >> 1;
+    float* cs = sh;
+    float* sn = sh + half;
+    float* row = sh + rotary_dim;
+    const int r = blockIdx.x;
+    const int pos = row_pos[r];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float angle = (float)pos * inv_freq[i];
+        float s, c;
+        sincosf(angle, &s, &c);
+        cs[i] = c;
+        sn[i] = s;
+    }
+    const float* src = partial + (size_t)r * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < n_splits; ++s) v += src[s * split_stride + c];
+        // the product's own epilogue would have rounded to the compute type here
+        row[c] = to_f32(from_f32<T>(v));
+    }
+    __syncthreads();
+    const int q_pairs = n_heads * half;
+    T* qo = q_out + (size_t)r * q_stride;
+    for (int w = threadIdx.x; w < n_heads * head_dim; w += blockDim.x) {
+        const int h = w / head_dim, d = w - h * head_dim;
+        const float* p = row + h * head_dim;
+        float v;
+        if (d < half) v = p[d] * cs[d] - p[d + half] * sn[d];
+        else if (d < rotary_dim) v = p[d - half] * sn[d - half] + p[d] * cs[d - half];
+        else v = p[d];
+        qo[w] = from_f32<T>(v);
+    }
+    (void)q_pairs;
+    if (!write_kv) return;
+    const int seq = row_seq[r];
+    const int page = block_table[(size_t)seq * max_blocks + pos / CML_PAGE];
+    const int in_page = pos % CML_PAGE;
+    const float* ksrc = row + n_heads * head_dim;
+    const float* vsrc = ksrc + n_kv_heads * head_dim;
+    const size_t page_base = (size_t)page * n_kv_heads * CML_PAGE * head_dim;
+    for (int w = threadIdx.x; w < n_kv_heads * head_dim; w += blockDim.x) {
+        const int h = w / head_dim, d = w - h * head_dim;
+        const float* p = ksrc + h * head_dim;
+        float v;
+        if (d < half) v = p[d] * cs[d] - p[d + half] * sn[d];
+        else if (d < rotary_dim) v = p[d - half] * sn[d - half] + p[d] * cs[d - half];
+        else v = p[d];
+        const size_t o = page_base + ((size_t)h * CML_PAGE + in_page) * head_dim + d;
+        k_pages[o] = from_f32<T>(v);
+        v_pages[o] = from_f32<T>(vsrc[w]);
+    }
+}
+
+extern "C" int cml_rope_kv_from_partials(const float* partial, int n_splits, long split_stride, int width, void* q_out,
+                                         int q_stride, int dtype, int rows, const int* row_pos, const int* row_seq,
+                                         const int* block_table, int max_blocks, void* k_pages, void* v_pages,
+                                         const float* inv_freq, int rotary_dim, int n_heads, int n_kv_heads,
+                                         int head_dim, int write_kv, void* stream) {
+    if (rows <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return CML_ERR_BAD_SIZE;
+    if (width < (n_heads + (write_kv ? 2 * n_kv_heads : 0)) * head_dim) return CML_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = ((size_t)rotary_dim + width) * sizeof(float);
+    if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
+    cudaError_t e;
+#define CML_RKP(T)                                                                                                     \
+    do {                                                                                                               \
+        e = cudaFuncSetAttribute(rope_kv_from_partials_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return (int)e;                                                                           \
+        rope_kv_from_partials_kernel<T><<<rows, 256, smem, s>>>(partial, n_splits, (size_t)split_stride, width, (T*)q_out, \
+                                                               q_stride, row_pos, row_seq, block_table, max_blocks,    \
+                                                               (T*)k_pages, (T*)v_pages, inv_freq, rotary_dim, n_heads, \
+                                                               n_kv_heads, head_dim, write_kv);                        \
+    } while (0)
+    if (dtype == CML_DTYPE_F32) CML_RKP(float);
+    else if (dtype == CML_DTYPE_BF16) CML_RKP(bf16);
+    else return CML_ERR_BAD_DTYPE;
+#undef CML_RKP
+    return cml_launch_status();
+}
+
 extern "C" int cml_rope_kv_write(void* qkv, int dtype, int rows, int row_stride, const int* row_pos,
                                  const int* row_seq, const int* block_table, int max_blocks, void* k_pages,
                                  void* v_pages, const float* inv_freq, int rotary_dim, int n_heads,

@@ -43,30 +43,47 @@ extern "C" int cml_embed_gather(const void* table, int dtype, const int* tokens,
 // y = x * rsqrt(mean(x^2) + eps) * w, multiplied in that order (src/tensor/mod.rs:2086-2096).
 // `rows_index` (may be null) picks the input row of each output row, so that the final norm
 // runs only on the rows whose logits are wanted.
+// `partial` (may be null) holds `n_splits` float matrices [x_rows, hidden] that are still to
+// be added to x (the split sums of the product before): they are added in index order, and
+// without `rows_index` the sum is written back to x, which settles the residual stream.
 template <typename TW, typename TO>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
-                               const int* __restrict__ rows_index, int hidden, float eps) {
+__global__ void rmsnorm_kernel(float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
+                               const int* __restrict__ rows_index, int hidden, float eps,
+                               const float* __restrict__ partial, int n_splits, size_t split_stride) {
     __shared__ float red[33];
+    extern __shared__ float rowbuf[];
     const int r = blockIdx.x;
     const int src = rows_index ? rows_index[r] : r;
-    const float* xr = x + (size_t)src * hidden;
+    float* xr = x + (size_t)src * hidden;
     float ss = 0.f;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float v = xr[c];
+        float v = xr[c];
+        if (partial) {
+            const float* pp = partial + (size_t)src * hidden + c;
+            for (int s = 0; s < n_splits; ++s) v += pp[s * split_stride];
+            rowbuf[c] = v;
+            if (!rows_index) xr[c] = v;
+        }
         ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, red);
     const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
     TO* o = out + (size_t)r * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f32<TO>(xr[c] * scale * to_f32(w[c]));
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = partial ? rowbuf[c] : xr[c];
+        o[c] = from_f32<TO>(v * scale * to_f32(w[c]));
+    }
 }
 
-extern "C" int cml_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype,
-                           const int* rows_index, int rows, int hidden, float eps, void* stream) {
+extern "C" int cml_rmsnorm(float* x, const void* w, int w_dtype, void* out, int out_dtype,
+                           const int* rows_index, int rows, int hidden, float eps, const float* partial,
+                           int n_splits, long split_stride, void* stream) {
     if (rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int block = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-#define CML_RMS(TW, TO) rmsnorm_kernel<TW, TO><<<rows, block, 0, s>>>(x, (const TW*)w, (TO*)out, rows_index, hidden, eps)
+    const size_t smem = partial ? (size_t)hidden * sizeof(float) : 0;
+    if (smem > 48 * 1024) return CML_ERR_BAD_SIZE;
+#define CML_RMS(TW, TO) rmsnorm_kernel<TW, TO><<<rows, block, smem, s>>>(x, (const TW*)w, (TO*)out, rows_index, hidden, eps, partial, n_splits, (size_t)split_stride)
     if (w_dtype == CML_DTYPE_F32 && out_dtype == CML_DTYPE_F32) CML_RMS(float, float);
     else if (w_dtype == CML_DTYPE_F32 && out_dtype == CML_DTYPE_BF16) CML_RMS(float, bf16);
     else if (w_dtype == CML_DTYPE_BF16 && out_dtype == CML_DTYPE_F32) CML_RMS(bf16, float);
@@ -103,5 +120,22 @@ extern "C" int cml_swiglu_packed(const void* gu, void* act, int dtype, int rows,
         swiglu_packed_kernel<bf16><<<rows, 256, 0, s>>>((const bf16*)gu, (bf16*)act, inter, group);
     else
         return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}
+
+// ------------------------------------------------------------------------------------
+// x += sum_s partial[s] (float), splits in index order: settles split sums that no norm
+// kernel picked up.
+__global__ void add_partials_kernel(float* __restrict__ x, const float* __restrict__ partial, int n_splits, long n) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = x[i];
+    for (int s = 0; s < n_splits; ++s) v += partial[(size_t)s * n + i];
+    x[i] = v;
+}
+
+extern "C" int cml_add_partials(float* x, const float* partial, int n_splits, long n, void* stream) {
+    if (n <= 0 || n_splits <= 0) return 0;
+    add_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, partial, n_splits, n);
     return cml_launch_status();
 }

@@ -14,6 +14,7 @@ import numpy as np
 import torch
 
 from ..cache.book import PAGE
+from ..csrc import ops
 
 
 class Workspace:
@@ -82,6 +83,7 @@ class StepContext:
         self._tiles = {r: (v(f"tile_seq{r}"), v(f"tile_q0{r}"), n) for r, n in layout.n_tiles.items()}
         self.entry = -1                 # schedule entry that is running
         self.cache_source = None        # entry whose keys and values the running entry reads
+        self.pending = None             # float32 [splits, rows, hidden] still to be added to the residual stream
         # host-side knowledge (filled by the constructors below)
         self.h_slots: list = []
         self.h_start: list = []
@@ -156,6 +158,13 @@ class StepContext:
         self.decode = self.max_new == 1
 
     # ---- helpers for parts ----
+    def settle(self, residual: torch.Tensor) -> None:
+        """Add what is pending to the residual stream now. A norm that reads the stream next does
+        this itself in its own kernel; parts that touch the stream otherwise call this first."""
+        if self.pending is not None:
+            part, self.pending = self.pending, None
+            ops.add_partials(residual, part)
+
     def buffer(self, name: str, shape: tuple, dtype: torch.dtype | None = None) -> torch.Tensor:
         return self.ws.get(name, shape, dtype or self.dtype)
 

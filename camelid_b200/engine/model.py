@@ -207,6 +207,7 @@ class DecoderModel:
         """The forward pass of one step on a prepared context."""
         if self._err is None:
             self._err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        ctx.pending = None
         h = ctx.buffer("hidden", (ctx.n_rows, self.hidden_size), torch.float32)
         self.embedding.forward(ctx, ctx.tokens, h, self._err)
         for i, e in enumerate(self.schedule):
@@ -217,6 +218,7 @@ class DecoderModel:
         if ctx.n_want:
             x = self.final_norm.forward(ctx, h, rows_index=ctx.want_rows, n_rows=ctx.n_want, name="final_normed")
             self.head.forward(ctx, x, logits)
+        ctx.pending = None
         return logits
 
     def check_device_errors(self) -> None:
@@ -225,3 +227,5 @@ class DecoderModel:
         if self._err is not None and int(self._err.item()) != 0:
             self._err.zero_()
             raise StepError("a kernel met a token id outside the vocabulary")
+        from ..parts import linear
+        linear.check_errors()

@@ -84,16 +84,23 @@ class GroupedQueryAttention(Part):
         group, k_pages, v_pages = ctx.kv()
         table = ctx.block_table(group)
         width = self.q_width if borrow else self.q_width + 2 * self.kv_width
-        qkv = ctx.buffer("qkv", (n, width))
-        linear.linear(ctx, x, self.w_qkv[:width], qkv, linear.STORE)
-        ops.rope_kv_write(qkv, ctx.row_pos, ctx.row_seq, table, k_pages, v_pages, self.position.inv_freq,
-                          self.position.rotary_dim, self.num_heads, self.num_kv_heads, self.head_dim,
-                          write_kv=not borrow)
+        pos = self.position
+        part = linear.partial_sums(ctx, x, self.w_qkv[:width], "qkv_partial")
+        if part is not None:          # decode: the rotary kernel sums the splits of the product
+            q = ctx.buffer("q_rot", (n, self.q_width))
+            ops.rope_kv_from_partials(part, q, ctx.row_pos, ctx.row_seq, table, k_pages, v_pages, pos.inv_freq,
+                                      pos.rotary_dim, self.num_heads, self.num_kv_heads, self.head_dim,
+                                      write_kv=not borrow)
+        else:
+            qkv = ctx.buffer("qkv", (n, width))
+            linear.linear(ctx, x, self.w_qkv[:width], qkv, linear.STORE)
+            ops.rope_kv_write(qkv, ctx.row_pos, ctx.row_seq, table, k_pages, v_pages, pos.inv_freq, pos.rotary_dim,
+                              self.num_heads, self.num_kv_heads, self.head_dim, write_kv=not borrow)
+            q = qkv[:, :self.q_width]
         out = ctx.buffer("attn_out", (n, self.q_width))
-        q = qkv[:, :self.q_width]
         if not (_attention_tc is not None and _attention_tc(self, ctx, q, out, k_pages, v_pages, table)):
             self._attend_simt(ctx, q, out, k_pages, v_pages, table)
-        linear.linear(ctx, out, self.w_o, residual, linear.ADD_F32)
+        linear.add_into_residual(ctx, out, self.w_o, residual, "o_partial")
 
     def _attend_simt(self, ctx, q, out, k_pages, v_pages, table):
         rows, hpc, chunks = ops.attn_tiling(self.num_heads, self.num_kv_heads, ctx.decode)

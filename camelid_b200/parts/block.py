@@ -39,7 +39,14 @@ class PreNormBlock(Part):
         return self.mixer.query_tile_sizes()
 
     def forward(self, ctx, h):
+        # A built-in mixer or feed-forward may leave split sums pending on the context; the
+        # norm that reads the stream next adds them. Parts from outside the library get a
+        # settled stream.
         x = self.norm1.forward(ctx, h)
+        if not self.mixer.graph_safe:
+            ctx.settle(h)
         self.mixer.forward(ctx, x, h)
         x = self.norm2.forward(ctx, h)
+        if not self.ffn.graph_safe:
+            ctx.settle(h)
         self.ffn.forward(ctx, x, h)

@@ -38,4 +38,4 @@ class SwiGLU(Part):
     def forward(self, ctx, x, residual):
         act = ctx.buffer("ffn_act", (ctx.n_rows, self.intermediate_size))
         linear.linear(ctx, x, self.w_gate_up, act, linear.SWIGLU, self.group)
-        linear.linear(ctx, act, self.w_down, residual, linear.ADD_F32)
+        linear.add_into_residual(ctx, act, self.w_down, residual, "down_partial")

@@ -5,6 +5,12 @@ bfloat16 operands whose sizes the tensor-core kernel takes go there; everything 
 to the CUDA-core kernel. Both accumulate in float32 and share the epilogues: store in the
 compute type, store float32, add into the float32 residual stream, or SwiGLU on packed
 gate/up rows.
+
+Steps of at most 64 rows (decode) run the tensor-core kernel transposed, with the weights as
+the 128-row operand and K split over several blocks so that every SM streams weights. The
+split sums stay in float32 and are added, in split order, by the kernel that reads the
+result next: the rotary kernel for q/k/v (``partial_sums``), the next norm for products that
+go into the residual stream (``add_into_residual`` leaves them *pending* on the context).
 """
 from __future__ import annotations
 
@@ -14,19 +20,86 @@ from ..csrc import ops
 
 STORE, STORE_F32, ADD_F32, SWIGLU = ops.EPI_STORE, ops.EPI_STORE_F32, ops.EPI_ADD_F32, ops.EPI_SWIGLU
 
-_tensor_core = None           # set by camelid_b200.parts.linear_tc when its kernel is available
+SM_COUNT = 148
+DECODE_ROWS = 64              # up to here a step runs the transposed kernel
+_err: dict = {}
 
 
-def set_tensor_core_path(fn) -> None:
-    global _tensor_core
-    _tensor_core = fn
+def _err_word(device) -> torch.Tensor:
+    e = _err.get(device)
+    if e is None:
+        e = torch.zeros(1, dtype=torch.int32, device=device)
+        _err[device] = e
+    return e
+
+
+def check_errors() -> None:
+    """Synchronising read of the tensor-core kernel's error word (a wait that ran out)."""
+    from ..errors import KernelError
+    for e in _err.values():
+        if int(e.item()):
+            e.zero_()
+            raise KernelError("the tensor-core matrix product gave up waiting on a barrier")
+
+
+def _bn_decode(rows: int) -> int:
+    return 16 if rows <= 16 else (32 if rows <= 32 else 64)
+
+
+def _splits(out_features: int, k: int) -> int:
+    tiles = (out_features + 127) // 128
+    return max(1, min((k + 63) // 64, round(SM_COUNT / tiles))) if tiles < SM_COUNT else 1
 
 
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, group: int = 0) -> None:
-    """out (op)= x @ w.T. For SWIGLU ``w`` is the packed [2N, K] matrix and ``out`` [M, N]."""
-    if _tensor_core is not None and x.dtype == torch.bfloat16 and _tensor_core(ctx, x, w, out, epilogue, group):
-        return
+    """out (op)= x @ w.T, complete on return. For SWIGLU ``w`` is the packed [2N, K] matrix
+    and ``out`` is [M, N]."""
+    if ops.gemm_tc_usable(x, w):
+        rows = x.shape[0]
+        err = _err_word(x.device)
+        if rows <= DECODE_ROWS:
+            bn = _bn_decode(rows)
+            if epilogue == SWIGLU and group == 16 and w.shape[0] % 32 == 0:
+                ops.gemm_tc(w, x, out, ops.TC_T_SWIGLU, bn, 1, err)
+                return
+            if epilogue == STORE_F32:
+                ops.gemm_tc(w, x, out.unsqueeze(0), ops.TC_T_PARTIAL, bn, 1, err)
+                return
+        else:
+            bn = 256 if w.shape[0] >= 1024 else 128
+            if epilogue == SWIGLU:
+                if group == 16 and w.shape[0] % 32 == 0:
+                    ops.gemm_tc(x, w, out, ops.TC_SWIGLU, bn, 1, err)
+                    return
+            else:
+                ops.gemm_tc(x, w, out, {STORE: ops.TC_STORE, STORE_F32: ops.TC_STORE_F32, ADD_F32: ops.TC_ADD_F32}[epilogue],
+                            bn, 1, err)
+                return
     ops.gemm_tn_simt(x, w, out, epilogue, group)
+
+
+def partial_sums(ctx, x: torch.Tensor, w: torch.Tensor, name: str):
+    """For a decode-sized step on the tensor-core path: float32 [splits, rows, out] whose sum
+    over splits is x @ w.T. None when the operands do not take that path."""
+    rows = x.shape[0]
+    if rows > DECODE_ROWS or not ops.gemm_tc_usable(x, w):
+        return None
+    n, k = w.shape
+    splits = min(_splits(n, k), (k + 63) // 64)
+    part = ctx.buffer(name, (splits, rows, n), torch.float32)
+    ops.gemm_tc(w, x, part, ops.TC_T_PARTIAL, _bn_decode(rows), splits, _err_word(x.device))
+    return part
+
+
+def add_into_residual(ctx, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, name: str) -> None:
+    """residual += x @ w.T. On the decode path the split sums are left pending on the context
+    and the next norm adds them; otherwise the product's epilogue adds."""
+    ctx.settle(residual)
+    part = partial_sums(ctx, x, w, name)
+    if part is not None:
+        ctx.pending = part
+    else:
+        linear(ctx, x, w, residual, ADD_F32)
 
 
 def pack_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int) -> torch.Tensor:

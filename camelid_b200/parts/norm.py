@@ -31,5 +31,6 @@ class RMSNorm(Part):
     def forward(self, ctx, h, rows_index=None, n_rows=None, name="normed"):
         rows = h.shape[0] if n_rows is None else n_rows
         out = ctx.buffer(name, (rows, self.hidden_size))
-        ops.rmsnorm(h, self.weight, self.eps, out, rows_index)
+        pending, ctx.pending = ctx.pending, None            # split sums still to be added to h: added here
+        ops.rmsnorm(h, self.weight, self.eps, out, rows_index, pending)
         return out

@@ -1,0 +1,123 @@
+"""The tensor-core matrix product (TMA + tcgen05) alone against float64 products, in both
+orientations, with ragged edges in every dimension and split K."""
+import math
+
+import pytest
+import torch
+
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def _ops():
+    from camelid_b200.csrc import ops
+    return ops
+
+
+def _operands(m, n, k, cuda, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(m, k, generator=g).to(BF).to(cuda)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(BF).to(cuda)
+    return a, w, a.cpu().double() @ w.cpu().double().T
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (200, 300, 136), (1000, 520, 192), (65, 517, 72), (2048, 1024, 2048)])
+def test_normal_orientation(cuda, m, n, k, bn):
+    ops = _ops()
+    a, w, ref = _operands(m, n, k, cuda)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    c = torch.full((m, n), float("nan"), dtype=BF, device=cuda)
+    ops.gemm_tc(a, w, c, ops.TC_STORE, bn, 1, err)
+    assert rel_err(c.cpu(), ref) <= 2 ** -8
+    c32 = torch.full((m, n), float("nan"), device=cuda)
+    ops.gemm_tc(a, w, c32, ops.TC_STORE_F32, bn, 1, err)
+    assert rel_err(c32.cpu(), ref) <= 1e-5
+    res = torch.randn(m, n, device=cuda)
+    want = res.cpu().double() + ref
+    ops.gemm_tc(a, w, res, ops.TC_ADD_F32, bn, 1, err)
+    assert rel_err(res.cpu(), want) <= 1e-5
+    assert int(err) == 0
+
+
+def test_strided_operands_and_output(cuda):
+    ops = _ops()
+    a, w, _ = _operands(300, 200, 128, cuda)
+    wide = torch.randn(300, 136).to(BF).to(cuda)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    c = torch.full((300, 208), float("nan"), device=cuda)
+    ops.gemm_tc(wide[:, 8:], w, c[:, :200], ops.TC_STORE_F32, 128, 1, err)
+    assert rel_err(c[:, :200].cpu(), wide[:, 8:].cpu().double() @ w.cpu().double().T) <= 1e-5
+    assert torch.isnan(c[:, 200:]).all()
+    assert not ops.gemm_tc_usable(wide[:, 4:], w[:, :132])          # K and strides must be multiples of 8
+
+
+@pytest.mark.parametrize("m,inter,k", [(300, 160, 64), (130, 528, 200), (1024, 2048, 512)])
+def test_swiglu_normal(cuda, m, inter, k):
+    ops = _ops()
+    from camelid_b200.parts.linear import pack_gate_up
+    x, wg, g = _operands(m, inter, k, cuda, 1)
+    _, wu, _ = _operands(m, inter, k, cuda, 2)
+    u = x.cpu().double() @ wu.cpu().double().T
+    ref = (g / (1 + torch.exp(-g))) * u
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    for bn in (64, 128, 256):
+        act = torch.full((m, inter), float("nan"), dtype=BF, device=cuda)
+        ops.gemm_tc(x, pack_gate_up(wg, wu, 16), act, ops.TC_SWIGLU, bn, 1, err)
+        assert rel_err(act.cpu(), ref) <= 2 ** -7, bn
+
+
+@pytest.mark.parametrize("rows", [1, 8, 17, 64])
+@pytest.mark.parametrize("n,k,splits", [(100, 64, 1), (384, 200, 3), (3072, 2048, 6), (2048, 8192, 9), (517, 136, 7)])
+def test_transposed_partials(cuda, rows, n, k, splits):
+    ops = _ops()
+    x, w, ref = _operands(rows, n, k, cuda, 3)
+    bn = 16 if rows <= 16 else (32 if rows <= 32 else 64)
+    splits = min(splits, (k + 63) // 64)
+    part = torch.full((splits, rows, n), float("nan"), device=cuda)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    ops.gemm_tc(w, x, part, ops.TC_T_PARTIAL, bn, splits, err)
+    assert rel_err(part.sum(0).cpu(), ref) <= 1e-5
+    assert int(err) == 0
+
+
+@pytest.mark.parametrize("rows", [1, 8, 33])
+@pytest.mark.parametrize("inter,k", [(160, 64), (528, 200), (8192, 2048)])
+def test_swiglu_transposed(cuda, rows, inter, k):
+    ops = _ops()
+    from camelid_b200.parts.linear import pack_gate_up
+    x, wg, g = _operands(rows, inter, k, cuda, 4)
+    _, wu, _ = _operands(rows, inter, k, cuda, 5)
+    u = x.cpu().double() @ wu.cpu().double().T
+    ref = (g / (1 + torch.exp(-g))) * u
+    bn = 16 if rows <= 16 else (32 if rows <= 32 else 64)
+    act = torch.full((rows, inter), float("nan"), dtype=BF, device=cuda)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    ops.gemm_tc(pack_gate_up(wg, wu, 16), x, act, ops.TC_T_SWIGLU, bn, 1, err)
+    assert rel_err(act.cpu(), ref) <= 2 ** -7
+
+
+def test_consumers_of_split_sums(cuda):
+    """The norm and the rotary kernel add the split sums themselves."""
+    ops = _ops()
+    import plain_llama as pl
+    g = torch.Generator().manual_seed(0)
+    h = torch.randn(5, 96, generator=g).to(cuda)
+    part = torch.randn(3, 5, 96, generator=g).to(cuda)
+    w = (1 + 0.1 * torch.randn(96, generator=g)).to(cuda)
+    total = h.cpu().double() + part.cpu().double().sum(0)
+    out = torch.empty(5, 96, device=cuda)
+    h2 = h.clone()
+    ops.rmsnorm(h2, w, 1e-5, out, None, part)
+    assert rel_err(h2.cpu(), total) <= 1e-6 and rel_err(out.cpu(), pl.rms_norm(total, w.cpu().double(), 1e-5)) <= 1e-5
+    idx = torch.tensor([4, 4, 1], dtype=torch.int32, device=cuda)
+    h3 = h.clone()
+    out3 = torch.empty(3, 96, device=cuda)
+    ops.rmsnorm(h3, w, 1e-5, out3, idx, part)
+    assert torch.equal(h3, h)                                           # gathered rows: nothing is written back
+    assert rel_err(out3.cpu(), pl.rms_norm(total[[4, 4, 1]], w.cpu().double(), 1e-5)) <= 1e-5
+    h4 = h.clone()
+    ops.add_partials(h4, part)
+    assert rel_err(h4.cpu(), total) <= 1e-6
