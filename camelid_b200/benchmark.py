@@ -237,7 +237,7 @@ def measure_decode_e2e(lm, cfg, batch: int, prompt_tokens: int, steps: int, warm
 
 def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warmup: int = 8, dtype: str = "bfloat16",
         layers: int | None = None, config_index: int = 2, points: bool = True, e2e: bool = True,
-        prefill_tokens: int = 2048) -> dict:
+        prefill_tokens: int = 2048, prefill: bool = True, decode: bool = True) -> dict:
     from . import api
     shape = SHAPES[config_index]
     cfg = config_for(config_index, layers)
@@ -245,9 +245,14 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
     lm = api.from_random(cfg, seed=shape["seed"], dtype=dtype)
     rng = np.random.default_rng(shape["seed"])
     elem = 2 if dtype == "bfloat16" else 4
-    pre = measure_prefill(lm, cfg, prefill_tokens, rng)
     flop_peak = (pk["bf16_tflops"] if dtype == "bfloat16" else 75.0) * 1e12
-    pre["frac"] = prefill_flops(cfg, prefill_tokens) / (pre["ms"] / 1e3) / flop_peak
+    if prefill:
+        pre = measure_prefill(lm, cfg, prefill_tokens, rng)
+        pre["frac"] = prefill_flops(cfg, prefill_tokens) / (pre["ms"] / 1e3) / flop_peak
+    else:
+        pre = {"value": None, "tokens": prefill_tokens, "ms": None, "frac": None}
+    if not decode:
+        return {"prefill": pre, "dtype": dtype, "config": {"model": shape["name"], "layers": cfg["num_hidden_layers"]}}
     dec = measure_decode_device(lm, cfg, batch, prompt_tokens, decode_steps, warmup, rng)
     bytes_step = decode_bytes(cfg, batch, dec["context"], elem)
     achieved = bytes_step / (dec["ms_per_step"] / 1e3) / 1e9

@@ -68,9 +68,10 @@ class SequenceCache:
             free, _total = torch.cuda.mem_get_info(self.device)
             if need > free:
                 raise CacheError(f"the cache needs {need} bytes ({n_pages} pages of {PAGE} tokens) but only {free} are free on {self.device}")
-        self.k = [torch.empty((counts_kv[g], n_pages, s.n_kv_heads, PAGE, s.head_dim), dtype=dtype, device=self.device)
+        # zero-filled once; kernels never count rows beyond a sequence's length
+        self.k = [torch.zeros((counts_kv[g], n_pages, s.n_kv_heads, PAGE, s.head_dim), dtype=dtype, device=self.device)
                   for g, s in enumerate(kv_specs)]
-        self.v = [torch.empty_like(t) for t in self.k]
+        self.v = [torch.zeros_like(t) for t in self.k]
         self.state = [torch.zeros((counts_state[g], n_slots) + tuple(s.shape), dtype=_STATE_DTYPES[s.dtype],
                                   device=self.device) for g, s in enumerate(state_specs)]
         self.bytes = need

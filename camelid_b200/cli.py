@@ -119,7 +119,9 @@ def cmd_random_model(args) -> int:
 def cmd_bench(args) -> int:
     from . import benchmark
     rec = benchmark.run(batch=args.batch, prompt_tokens=args.prompt_tokens, decode_steps=args.decode_steps,
-                        warmup=args.warmup, dtype=args.dtype, layers=args.layers, config_index=args.config)
+                        warmup=args.warmup, dtype=args.dtype, layers=args.layers, config_index=args.config,
+                        points=args.points, e2e=args.e2e, prefill=not args.no_prefill, decode=not args.no_decode,
+                        prefill_tokens=args.prefill_tokens)
     print(json.dumps(rec), flush=True)
     return 0
 
@@ -144,6 +146,11 @@ def main(argv=None) -> int:
     be.add_argument("--layers", type=int, default=None)
     be.add_argument("--config", type=int, default=2, help="index into the benchmark shapes (2: Llama 3.2 1B)")
     be.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    be.add_argument("--prefill-tokens", type=int, default=2048)
+    be.add_argument("--points", action="store_true", help="also decode at batch 1 and 64")
+    be.add_argument("--e2e", action="store_true", help="also time the loop through the Python entry point")
+    be.add_argument("--no-prefill", action="store_true")
+    be.add_argument("--no-decode", action="store_true")
     args = ap.parse_args(argv)
     if args.command == "generate":
         return cmd_generate(args)

@@ -1,0 +1,348 @@
+// bfloat16 attention over the paged cache on the tensor cores, for prefill tiles and for
+// decode, with float softmax and float accumulation.
+//
+// One block handles up to 16 (token, head) pairs that share one kv head: `rows_per_tile`
+// consecutive new tokens of one sequence times `heads_per_cta` query heads, which fill the
+// 16 rows of an m16n8k16 MMA, so the grouped heads (and in prefill a few neighbouring
+// tokens) reuse every key and value that is read. Keys are walked in tiles of 32; the four
+// warps of a block take tiles round-robin, each with its own cp.async pipeline into padded
+// shared memory, and merge their running (max, sum, output) at the end. A range of keys
+// can also be split over gridDim.z; the partial results are merged by attn_combine_kernel.
+//
+// It replaces attention_decode / attn_sk_* and attention_batched / flash_pref_*
+// (src/cuda_resident.rs:1587, :2332-2487, :1994, :2523-2705); the arithmetic is the
+// reference's (src/inference.rs:23945-24025): (q . k) * scale, running maximum,
+// exp(score - max), probabilities times values.
+//
+// Values of cache rows beyond a sequence's length never count: their probability is exactly
+// zero, and the kernel zeroes those rows of its shared-memory tile before multiplying.
+#include "attention_common.cuh"
+
+#define AM_WARPS 4
+#define AM_TILE 32
+#define AM_STAGES 3
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(AM_WARPS * 32)
+attn_paged_mma_kernel(AttnParams p) {
+    constexpr int LDS = HD + 8;                              // padded row: conflict-free ldmatrix
+    constexpr int TILE_ELEMS = AM_TILE * LDS;
+    constexpr int STAGE_ELEMS = 2 * TILE_ELEMS;              // keys, then values
+    constexpr int KSTEPS = HD / 16, DTILES = HD / 8;
+    constexpr int CHUNKS = HD / 8;                           // 16-byte chunks of a row
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+
+    const int tile = blockIdx.x;
+    const int seq = p.tile_seq[tile];
+    const int q0 = p.tile_q0[tile];
+    const int kvh = blockIdx.y / p.head_chunks;
+    const int chunk = blockIdx.y - kvh * p.head_chunks;
+    const int split = blockIdx.z;
+    const int start = p.seq_start[seq];
+    const int n_new = p.seq_new[seq];
+    const int row0 = p.seq_row0[seq];
+    const int group = p.n_heads / p.n_kv_heads;
+    const int hpc = p.heads_per_cta;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rows_in_tile = min(p.rows_per_tile, n_new - q0);
+    const int kend = start + q0 + rows_in_tile;                          // exclusive
+    const int kbeg = p.window > 0 ? max(0, start + q0 - p.window + 1) : 0;
+    const int t_first = kbeg / AM_TILE;
+    const int t_last = (kend + AM_TILE - 1) / AM_TILE;                   // exclusive
+    const int per = (t_last - t_first + p.n_splits - 1) / p.n_splits;
+    const int t_beg = t_first + split * per;
+    const int t_end = min(t_last, t_beg + per);
+
+    // the two MMA rows of this thread: i = lane/4 and i + 8
+    int pos_r[2], lo_r[2];
+    bool valid_r[2];
+    const bf16* q_r[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int i = (lane >> 2) + 8 * h;
+        const int r_local = i / hpc;
+        const int hg = chunk * hpc + (i - r_local * hpc);
+        valid_r[h] = (r_local < rows_in_tile) && (hg < group);
+        pos_r[h] = start + q0 + r_local;
+        lo_r[h] = p.window > 0 ? max(0, pos_r[h] - p.window + 1) : 0;
+        q_r[h] = (const bf16*)p.q + (size_t)(row0 + q0 + r_local) * p.q_stride + (size_t)(kvh * group + hg) * HD;
+    }
+    // A fragments of Q (zero rows where there is no query)
+    uint32_t qa[KSTEPS][4];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+        const int c = ks * 16 + 2 * (lane & 3);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            qa[ks][h] = valid_r[h] ? *reinterpret_cast<const uint32_t*>(q_r[h] + c) : 0u;
+            qa[ks][h + 2] = valid_r[h] ? *reinterpret_cast<const uint32_t*>(q_r[h] + c + 8) : 0u;
+        }
+    }
+
+    float m_r[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_r[2] = {0.f, 0.f};
+    float o[DTILES][4];
+#pragma unroll
+    for (int dt = 0; dt < DTILES; ++dt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[dt][i] = 0.f;
+
+    const bf16* kp = (const bf16*)p.k_pages;
+    const bf16* vp = (const bf16*)p.v_pages;
+    bf16* my_smem = smem + (size_t)warp * AM_STAGES * STAGE_ELEMS;
+    const uint32_t my_smem_u32 = (uint32_t)__cvta_generic_to_shared(my_smem);
+
+    auto issue = [&](int t, int stage) {
+        const int page = p.block_table[(size_t)seq * p.max_blocks + (t * AM_TILE) / CML_PAGE];
+        const size_t base = (((size_t)page * p.n_kv_heads + kvh) * CML_PAGE + (t * AM_TILE) % CML_PAGE) * HD;
+        const uint32_t dst = my_smem_u32 + (uint32_t)stage * STAGE_ELEMS * 2;
+        for (int c = lane; c < AM_TILE * CHUNKS; c += 32) {
+            const int r = c / CHUNKS, cc = c - r * CHUNKS;
+            cp_async16(dst + (uint32_t)(r * LDS + cc * 8) * 2, kp + base + (size_t)r * HD + cc * 8);
+            cp_async16(dst + (uint32_t)(TILE_ELEMS + r * LDS + cc * 8) * 2, vp + base + (size_t)r * HD + cc * 8);
+        }
+    };
+
+    // this warp's tiles: t_beg + warp, + 4, + 8, ...
+    const int n_mine = (t_end - t_beg - warp + AM_WARPS - 1) / AM_WARPS;
+#pragma unroll
+    for (int s = 0; s < AM_STAGES - 1; ++s) {
+        if (s < n_mine) issue(t_beg + warp + s * AM_WARPS, s);
+        cp_async_commit();
+    }
+    const float scale = p.scale;
+    for (int it = 0; it < n_mine; ++it) {
+        const int t = t_beg + warp + it * AM_WARPS;
+        cp_async_wait<AM_STAGES - 2>();
+        __syncwarp();
+        {   // keep the pipeline full
+            const int nxt = it + AM_STAGES - 1;
+            if (nxt < n_mine) issue(t_beg + warp + nxt * AM_WARPS, nxt % AM_STAGES);
+            cp_async_commit();
+        }
+        const uint32_t ks_u32 = my_smem_u32 + (uint32_t)(it % AM_STAGES) * STAGE_ELEMS * 2;
+        const uint32_t vs_u32 = ks_u32 + TILE_ELEMS * 2;
+        if ((t + 1) * AM_TILE > kend) {
+            // value rows past the end of the sequence: their probability is zero, make the
+            // product zero too whatever the page holds
+            bf16* vs = my_smem + (size_t)(it % AM_STAGES) * STAGE_ELEMS + TILE_ELEMS;
+            const int first = kend - t * AM_TILE;
+            for (int c = lane; c < (AM_TILE - first) * (HD / 2); c += 32) {
+                const int r = first + c / (HD / 2), d = (c % (HD / 2)) * 2;
+                *reinterpret_cast<uint32_t*>(vs + r * LDS + d) = 0u;
+            }
+            __syncwarp();
+        }
+
+        // S = Q K^T : 16 x 32
+        float s[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+            for (int np = 0; np < 2; ++np) {          // pairs of 8-key tiles
+                const int mat = lane >> 3, rr = lane & 7;
+                const int key = np * 16 + (mat >> 1) * 8 + rr;
+                const int d = ks * 16 + (mat & 1) * 8;
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(ks_u32 + (uint32_t)(key * LDS + d) * 2, b0, b1, b2, b3);
+                mma_bf16(s[np * 2], qa[ks], b0, b1);
+                mma_bf16(s[np * 2 + 1], qa[ks], b2, b3);
+            }
+        }
+        // scale, mask, running maximum
+        const int key_base = t * AM_TILE + 2 * (lane & 3);
+        float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int h = i >> 1;
+                const int key = key_base + nt * 8 + (i & 1);
+                const bool in = valid_r[h] && key <= pos_r[h] && key >= lo_r[h];
+                s[nt][i] = in ? s[nt][i] * scale : -CUDART_INF_F;
+                mx[h] = fmaxf(mx[h], s[nt][i]);
+            }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            const float mn = fmaxf(m_r[h], mx[h]);
+            m_use[h] = (mn == -CUDART_INF_F) ? 0.f : mn;
+            corr[h] = (m_r[h] == -CUDART_INF_F) ? 0.f : __expf(m_r[h] - m_use[h]);
+            m_r[h] = mn;
+            l_r[h] *= corr[h];
+        }
+#pragma unroll
+        for (int dt = 0; dt < DTILES; ++dt) {
+            o[dt][0] *= corr[0]; o[dt][1] *= corr[0];
+            o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+        }
+        // probabilities as A fragments (two k-steps of 16 keys)
+        uint32_t pa[2][4];
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            float e[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    e[j][i] = __expf(s[kk * 2 + j][i] - m_use[i >> 1]);
+                    l_r[i >> 1] += e[j][i];
+                }
+            pa[kk][0] = pack_bf16(e[0][0], e[0][1]);
+            pa[kk][1] = pack_bf16(e[0][2], e[0][3]);
+            pa[kk][2] = pack_bf16(e[1][0], e[1][1]);
+            pa[kk][3] = pack_bf16(e[1][2], e[1][3]);
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+            for (int dp = 0; dp < DTILES / 2; ++dp) {
+                const int mat = lane >> 3, rr = lane & 7;
+                const int key = kk * 16 + (mat & 1) * 8 + rr;
+                const int d = dp * 16 + (mat >> 1) * 8;
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_t(vs_u32 + (uint32_t)(key * LDS + d) * 2, b0, b1, b2, b3);
+                mma_bf16(o[dp * 2], pa[kk], b0, b1);
+                mma_bf16(o[dp * 2 + 1], pa[kk], b2, b3);
+            }
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_r[h] += __shfl_xor_sync(0xffffffffu, l_r[h], 1);
+        l_r[h] += __shfl_xor_sync(0xffffffffu, l_r[h], 2);
+    }
+    __syncthreads();                       // every warp is done with its stage buffers
+
+    // merge the four warps: [warp][16 rows][HD + 2] floats in shared memory
+    float* red = reinterpret_cast<float*>(smem_raw);
+    constexpr int RW = HD + 2;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float* dst = red + ((size_t)warp * 16 + (lane >> 2) + 8 * h) * RW;
+        if ((lane & 3) == 0) {
+            dst[0] = m_r[h];
+            dst[1] = l_r[h];
+        }
+#pragma unroll
+        for (int dt = 0; dt < DTILES; ++dt) {
+            dst[2 + dt * 8 + 2 * (lane & 3)] = o[dt][2 * h];
+            dst[2 + dt * 8 + 2 * (lane & 3) + 1] = o[dt][2 * h + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 16 * (HD / 2); idx += blockDim.x) {
+        const int i = idx / (HD / 2), d = (idx - i * (HD / 2)) * 2;
+        const int r_local = i / hpc;
+        const int hg = chunk * hpc + (i - r_local * hpc);
+        if (r_local >= rows_in_tile || hg >= group) continue;
+        float M = -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < AM_WARPS; ++w) M = fmaxf(M, red[((size_t)w * 16 + i) * RW]);
+        float L = 0.f, a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int w = 0; w < AM_WARPS; ++w) {
+            const float* src = red + ((size_t)w * 16 + i) * RW;
+            const float wgt = (src[0] == -CUDART_INF_F) ? 0.f : __expf(src[0] - M);
+            L += wgt * src[1];
+            a0 += wgt * src[2 + d];
+            a1 += wgt * src[2 + d + 1];
+        }
+        const int row = row0 + q0 + r_local;
+        const int head = kvh * group + hg;
+        if (p.n_splits == 1) {
+            const float inv = 1.0f / L;
+            bf16* dst = (bf16*)p.out + (size_t)row * p.out_stride + (size_t)head * HD + d;
+            *reinterpret_cast<uint32_t*>(dst) = pack_bf16(a0 * inv, a1 * inv);
+        } else {
+            float* dst = p.partial + (((size_t)row * p.n_heads + head) * p.n_splits + split) * RW;
+            if (d == 0) {
+                dst[0] = M;
+                dst[1] = L;
+            }
+            dst[2 + d] = a0;
+            dst[2 + d + 1] = a1;
+        }
+    }
+}
+
+template <int HD>
+static int launch_mma(const AttnParams& p, int n_tiles, int n_rows, cudaStream_t s) {
+    constexpr size_t stage_bytes = (size_t)AM_WARPS * AM_STAGES * 2 * AM_TILE * (HD + 8) * sizeof(bf16);
+    constexpr size_t red_bytes = (size_t)AM_WARPS * 16 * (HD + 2) * sizeof(float);
+    constexpr size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
+    dim3 grid(n_tiles, p.n_kv_heads * p.head_chunks, p.n_splits);
+    cudaError_t e = cudaFuncSetAttribute(attn_paged_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attn_paged_mma_kernel<HD><<<grid, AM_WARPS * 32, smem, s>>>(p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    if (p.n_splits > 1) {
+        attn_combine_kernel<bf16><<<n_rows * p.n_heads, HD >= 128 ? 128 : 64, 0, s>>>(p.partial, (bf16*)p.out, p.out_stride,
+                                                                                    p.n_heads, HD, p.n_splits);
+        e = cudaGetLastError();
+    }
+    return (int)e;
+}
+
+// bfloat16 only; head_dim 64 or 128 (others take the float kernel); rows_per_tile * heads_per_cta <= 16.
+// q rows and the output must be 4-byte aligned (even strides).
+extern "C" int cml_attn_paged_mma(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                  const void* v_pages, const int* block_table, int max_blocks, const int* tile_seq,
+                                  const int* tile_q0, int n_tiles, const int* seq_row0, const int* seq_start,
+                                  const int* seq_new, int n_rows, int n_heads, int n_kv_heads, int head_dim,
+                                  int rows_per_tile, int heads_per_cta, int head_chunks, int n_splits, int window,
+                                  float scale, float* partial, void* stream) {
+    if (n_tiles <= 0 || n_rows <= 0) return 0;
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return CML_ERR_BAD_SIZE;
+    if (rows_per_tile * heads_per_cta > 16 || rows_per_tile < 1 || heads_per_cta < 1) return CML_ERR_BAD_SIZE;
+    if (heads_per_cta * head_chunks < n_heads / n_kv_heads) return CML_ERR_BAD_SIZE;
+    if (n_splits < 1 || (n_splits > 1 && partial == nullptr)) return CML_ERR_BAD_SIZE;
+    if ((q_stride & 1) || (out_stride & 1) || ((uintptr_t)q & 3) || ((uintptr_t)out & 3)) return CML_ERR_BAD_ALIGN;
+    if (((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15)) return CML_ERR_BAD_ALIGN;
+    AttnParams p;
+    p.q = q; p.q_stride = q_stride; p.out = out; p.out_stride = out_stride;
+    p.k_pages = k_pages; p.v_pages = v_pages; p.block_table = block_table; p.max_blocks = max_blocks;
+    p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.seq_row0 = seq_row0; p.seq_start = seq_start; p.seq_new = seq_new;
+    p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
+    p.rows_per_tile = rows_per_tile; p.heads_per_cta = heads_per_cta; p.head_chunks = head_chunks;
+    p.n_splits = n_splits; p.window = window; p.scale = scale; p.partial = partial;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (head_dim == 64) return launch_mma<64>(p, n_tiles, n_rows, s);
+    if (head_dim == 128) return launch_mma<128>(p, n_tiles, n_rows, s);
+    return CML_ERR_BAD_SIZE;
+}

@@ -14,29 +14,7 @@
 // `heads_per_cta` query heads of one kv head, and one contiguous range of key pages
 // (`n_splits` ranges; partial results are merged by attn_combine_kernel). One warp owns one
 // (token, head) pair; the block shares each key/value page through shared memory.
-#include "common.cuh"
-#include <math_constants.h>
-
-struct AttnParams {
-    const void* q;
-    int q_stride;
-    void* out;
-    int out_stride;
-    const void* k_pages;
-    const void* v_pages;
-    const int* block_table;
-    int max_blocks;
-    const int* tile_seq;
-    const int* tile_q0;
-    const int* seq_row0;
-    const int* seq_start;
-    const int* seq_new;
-    int n_heads, n_kv_heads, head_dim;
-    int rows_per_tile, heads_per_cta, head_chunks;
-    int n_splits, window;
-    float scale;
-    float* partial;
-};
+#include "attention_common.cuh"
 
 template <typename T, int NACC>
 __global__ void attn_paged_simt_kernel(AttnParams p) {
@@ -157,33 +135,6 @@ __global__ void attn_paged_simt_kernel(AttnParams p) {
             const int d = lane + 32 * i;
             if (d < hd) o[2 + d] = acc[i];
         }
-    }
-}
-
-// Merge of the key ranges: out = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s, the
-// ranges taken in index order. A range without visible keys has m = -inf and weight 0.
-template <typename T>
-__global__ void attn_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, int out_stride,
-                                    int n_heads, int head_dim, int n_splits) {
-    const int row = blockIdx.x / n_heads, head = blockIdx.x - row * n_heads;
-    const float* base = partial + (size_t)blockIdx.x * n_splits * (head_dim + 2);
-    float M = -CUDART_INF_F;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, base[(size_t)s * (head_dim + 2)]);
-    float L = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float ms = base[(size_t)s * (head_dim + 2)];
-        const float w = (ms == -CUDART_INF_F) ? 0.f : expf(ms - M);
-        L += w * base[(size_t)s * (head_dim + 2) + 1];
-    }
-    const float inv = 1.0f / L;
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-        float a = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = base[(size_t)s * (head_dim + 2)];
-            const float w = (ms == -CUDART_INF_F) ? 0.f : expf(ms - M);
-            a += w * base[(size_t)s * (head_dim + 2) + 2 + d];
-        }
-        out[(size_t)row * out_stride + head * head_dim + d] = from_f32<T>(a * inv);
     }
 }
 

@@ -22,11 +22,12 @@ import time
 from ..errors import KernelError
 
 CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "attention_common.cuh"]
 MODULES = {
     "rowwise": ["rowwise.cu"],
     "rope_kv": ["rope_kv.cu"],
     "attention_simt": ["attention_simt.cu"],
+    "attention_mma": ["attention_mma.cu"],
     "gemm_simt": ["gemm_simt.cu"],
     "sampling": ["sampling.cu"],
     "gemm_tc": ["gemm_tc.cu"],

@@ -36,6 +36,10 @@ _SIGNATURES = {
                                                 c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                                 c_void_p, c_void_p],
+    ("attention_mma", "cml_attn_paged_mma"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                              c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                              c_void_p],
     ("gemm_simt", "cml_gemm_tn_simt"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_void_p],
     ("sampling", "cml_argmax_rows"): [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
@@ -239,6 +243,37 @@ def attn_paged_simt(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_
         block_table.shape[1], _p(tile_seq), _p(tile_q0), n_tiles, _p(seq_row0), _p(seq_start), _p(seq_new), n_rows,
         n_heads, n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, n_splits, int(window or 0),
         float(scale), _p(partial), _stream()), "attn_paged_simt", 2 if n_splits > 1 else 1)
+
+
+def attn_mma_tiling(n_heads: int, n_kv_heads: int, decode: bool) -> tuple[int, int, int]:
+    """(rows_per_tile, heads_per_cta, head_chunks) of the tensor-core attention kernel: the 16
+    rows of an MMA hold the grouped heads of one kv head times a few consecutive tokens."""
+    group = n_heads // n_kv_heads
+    chunks = (group + 15) // 16
+    hpc = (group + chunks - 1) // chunks
+    rows = 1 if decode else max(1, 16 // hpc)
+    return rows, hpc, chunks
+
+
+def attn_mma_usable(q: torch.Tensor, head_dim: int) -> bool:
+    return q.dtype == torch.bfloat16 and head_dim in (64, 128) and q.stride(0) % 2 == 0
+
+
+def attn_paged_mma(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_tiles, seq_row0, seq_start, seq_new,
+                   n_rows, n_heads, n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, n_splits,
+                   window, scale, partial):
+    """bfloat16 attention of packed query rows over the paged cache on the tensor cores."""
+    _dev(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, seq_row0, seq_start, seq_new, partial)
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == torch.bfloat16
+    assert k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim) and k_pages.is_contiguous() and v_pages.is_contiguous()
+    if n_splits > 1:
+        assert partial is not None and partial.dtype == torch.float32
+        assert partial.numel() >= attn_partial_floats(n_rows, n_heads, head_dim, n_splits)
+    _check(_fn("attention_mma", "cml_attn_paged_mma")(
+        _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1],
+        _p(tile_seq), _p(tile_q0), n_tiles, _p(seq_row0), _p(seq_start), _p(seq_new), n_rows, n_heads, n_kv_heads,
+        head_dim, rows_per_tile, heads_per_cta, head_chunks, n_splits, int(window or 0), float(scale), _p(partial),
+        _stream()), "attn_paged_mma", 2 if n_splits > 1 else 1)
 
 
 def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, group: int = 0):

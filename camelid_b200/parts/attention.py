@@ -22,14 +22,6 @@ from ..csrc import ops
 from . import linear
 from .base import Part, TensorSpec, build_part, register_part, to_device
 
-_attention_tc = None          # set by camelid_b200.parts.attention_tc when its kernels are available
-
-
-def set_tensor_core_path(fn) -> None:
-    global _attention_tc
-    _attention_tc = fn
-
-
 @register_part("mixer", "attention")
 class GroupedQueryAttention(Part):
     graph_safe = True
@@ -75,7 +67,8 @@ class GroupedQueryAttention(Part):
         return KVSpec(self.num_kv_heads, self.head_dim, self.window)
 
     def query_tile_sizes(self):
-        return [ops.attn_tiling(self.num_heads, self.num_kv_heads, False)[0]]
+        return [ops.attn_tiling(self.num_heads, self.num_kv_heads, False)[0],
+                ops.attn_mma_tiling(self.num_heads, self.num_kv_heads, False)[0]]
 
     # ------------------------------------------------------------------------------
     def forward(self, ctx, x, residual):
@@ -98,23 +91,29 @@ class GroupedQueryAttention(Part):
                               self.num_heads, self.num_kv_heads, self.head_dim, write_kv=not borrow)
             q = qkv[:, :self.q_width]
         out = ctx.buffer("attn_out", (n, self.q_width))
-        if not (_attention_tc is not None and _attention_tc(self, ctx, q, out, k_pages, v_pages, table)):
-            self._attend_simt(ctx, q, out, k_pages, v_pages, table)
+        if ops.attn_mma_usable(q, self.head_dim):
+            self._attend(ctx, q, out, k_pages, v_pages, table, tensor_cores=True)
+        else:
+            self._attend(ctx, q, out, k_pages, v_pages, table, tensor_cores=False)
         linear.add_into_residual(ctx, out, self.w_o, residual, "o_partial")
 
-    def _attend_simt(self, ctx, q, out, k_pages, v_pages, table):
-        rows, hpc, chunks = ops.attn_tiling(self.num_heads, self.num_kv_heads, ctx.decode)
+    def _attend(self, ctx, q, out, k_pages, v_pages, table, tensor_cores: bool):
+        """Attention of the step's rows over the cache. bfloat16 with a head size of 64 or 128
+        runs on the tensor cores, everything else in float on the CUDA cores. A decode step
+        splits each sequence's keys over several blocks so that all SMs stream the cache."""
+        tiling = ops.attn_mma_tiling if tensor_cores else ops.attn_tiling
+        rows, hpc, chunks = tiling(self.num_heads, self.num_kv_heads, ctx.decode)
         tile_seq, tile_q0, n_tiles = ctx.query_tiles(rows)
         n_splits, partial = 1, None
         if ctx.decode:
-            blocks = ctx.max_blocks_in_use
-            if self.window:
-                blocks = min(blocks, (self.window + PAGE - 1) // PAGE + 1)
+            keys = ctx.max_len if not self.window else min(ctx.max_len, self.window + PAGE)
             ctas = n_tiles * self.num_kv_heads * chunks
-            n_splits = max(1, min(blocks, (2 * 148 + ctas - 1) // ctas, 64))
+            unit = 8 * 32 if tensor_cores else PAGE               # keys a block should at least have
+            n_splits = max(1, min((keys + unit - 1) // unit, (2 * linear.SM_COUNT + ctas - 1) // ctas, 64))
             if n_splits > 1:
                 partial = ctx.buffer("attn_partial", (ops.attn_partial_floats(ctx.n_rows, self.num_heads, self.head_dim,
                                                                              n_splits),), torch.float32)
-        ops.attn_paged_simt(q, out, k_pages, v_pages, table, tile_seq, tile_q0, n_tiles, ctx.seq_row0, ctx.seq_start,
-                            ctx.seq_new, ctx.n_rows, self.num_heads, self.num_kv_heads, self.head_dim, rows, hpc,
-                            chunks, n_splits, self.window or 0, self.scale, partial)
+        fn = ops.attn_paged_mma if tensor_cores else ops.attn_paged_simt
+        fn(q, out, k_pages, v_pages, table, tile_seq, tile_q0, n_tiles, ctx.seq_row0, ctx.seq_start, ctx.seq_new,
+           ctx.n_rows, self.num_heads, self.num_kv_heads, self.head_dim, rows, hpc, chunks, n_splits,
+           self.window or 0, self.scale, partial)
