@@ -22,6 +22,7 @@ struct AttnParams {
     int n_splits, window;
     float scale;
     float* partial;
+    int* tickets;       // one zeroed counter per block column (tile, kv head chunk), or null
 };
 
 // Merge of the key ranges: out = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s, the
@@ -29,6 +30,8 @@ struct AttnParams {
 template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, int out_stride,
                                     int n_heads, int head_dim, int n_splits) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int row = blockIdx.x / n_heads, head = blockIdx.x - row * n_heads;
     const float* base = partial + (size_t)blockIdx.x * n_splits * (head_dim + 2);
     float M = -CUDART_INF_F;

@@ -58,6 +58,8 @@ attn_paged_mma_kernel(AttnParams p) {
     constexpr int CHUNKS = HD / 8;                           // 16-byte chunks of a row
     extern __shared__ __align__(16) uint8_t smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    pdl_wait();
+    pdl_launch_dependents();
 
     const int tile = blockIdx.x;
     const int seq = p.tile_seq[tile];
@@ -298,6 +300,42 @@ attn_paged_mma_kernel(AttnParams p) {
             dst[2 + d + 1] = a1;
         }
     }
+    if (p.n_splits == 1 || p.tickets == nullptr) return;
+
+    // The block that finishes last among the splits of this (tile, kv head chunk) merges
+    // their partial results, in split order, and writes the output: no second kernel.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    int* ticket = p.tickets + (size_t)tile * gridDim.y + blockIdx.y;
+    if (threadIdx.x == 0) is_last = (atomicAdd(ticket, 1) == p.n_splits - 1);
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < 16 * (HD / 2); idx += blockDim.x) {
+        const int i = idx / (HD / 2), d = (idx - i * (HD / 2)) * 2;
+        const int r_local = i / hpc;
+        const int hg = chunk * hpc + (i - r_local * hpc);
+        if (r_local >= rows_in_tile || hg >= group) continue;
+        const int row = row0 + q0 + r_local;
+        const int head = kvh * group + hg;
+        const float* base = p.partial + ((size_t)row * p.n_heads + head) * p.n_splits * RW;
+        float M = -CUDART_INF_F;
+        for (int s = 0; s < p.n_splits; ++s) M = fmaxf(M, __ldcg(base + (size_t)s * RW));
+        float L = 0.f, a0 = 0.f, a1 = 0.f;
+        for (int s = 0; s < p.n_splits; ++s) {
+            const float* src = base + (size_t)s * RW;
+            const float ms = __ldcg(src);
+            const float wgt = (ms == -CUDART_INF_F) ? 0.f : __expf(ms - M);
+            L += wgt * __ldcg(src + 1);
+            a0 += wgt * __ldcg(src + 2 + d);
+            a1 += wgt * __ldcg(src + 2 + d + 1);
+        }
+        const float inv = 1.0f / L;
+        bf16* dst = (bf16*)p.out + (size_t)row * p.out_stride + (size_t)head * HD + d;
+        *reinterpret_cast<uint32_t*>(dst) = pack_bf16(a0 * inv, a1 * inv);
+    }
+    if (threadIdx.x == 0) *ticket = 0;         // ready for the next launch
 }
 
 template <int HD>
@@ -308,17 +346,19 @@ static int launch_mma(const AttnParams& p, int n_tiles, int n_rows, cudaStream_t
     dim3 grid(n_tiles, p.n_kv_heads * p.head_chunks, p.n_splits);
     cudaError_t e = cudaFuncSetAttribute(attn_paged_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attn_paged_mma_kernel<HD><<<grid, AM_WARPS * 32, smem, s>>>(p);
-    e = cudaGetLastError();
+    e = launch_pdl(attn_paged_mma_kernel<HD>, grid, dim3(AM_WARPS * 32), smem, s, p);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    if (p.n_splits > 1) {
-        attn_combine_kernel<bf16><<<n_rows * p.n_heads, HD >= 128 ? 128 : 64, 0, s>>>(p.partial, (bf16*)p.out, p.out_stride,
-                                                                                    p.n_heads, HD, p.n_splits);
+    if (p.n_splits > 1 && p.tickets == nullptr) {
+        launch_pdl(attn_combine_kernel<bf16>, dim3(n_rows * p.n_heads), dim3(HD >= 128 ? 128 : 64), 0, s,
+                   (const float*)p.partial, (bf16*)p.out, p.out_stride, p.n_heads, HD, p.n_splits);
         e = cudaGetLastError();
     }
     return (int)e;
 }
 
+// `tickets` (may be null): n_tiles * n_kv_heads * head_chunks ints, zero before the first call and left zero;
+// with it the last block of each column merges the splits itself, without it a second kernel does.
 // bfloat16 only; head_dim 64 or 128 (others take the float kernel); rows_per_tile * heads_per_cta <= 16.
 // q rows and the output must be 4-byte aligned (even strides).
 extern "C" int cml_attn_paged_mma(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
@@ -326,7 +366,7 @@ extern "C" int cml_attn_paged_mma(const void* q, int q_stride, void* out, int ou
                                   const int* tile_q0, int n_tiles, const int* seq_row0, const int* seq_start,
                                   const int* seq_new, int n_rows, int n_heads, int n_kv_heads, int head_dim,
                                   int rows_per_tile, int heads_per_cta, int head_chunks, int n_splits, int window,
-                                  float scale, float* partial, void* stream) {
+                                  float scale, float* partial, int* tickets, void* stream) {
     if (n_tiles <= 0 || n_rows <= 0) return 0;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return CML_ERR_BAD_SIZE;
     if (rows_per_tile * heads_per_cta > 16 || rows_per_tile < 1 || heads_per_cta < 1) return CML_ERR_BAD_SIZE;
@@ -340,7 +380,7 @@ extern "C" int cml_attn_paged_mma(const void* q, int q_stride, void* out, int ou
     p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.seq_row0 = seq_row0; p.seq_start = seq_start; p.seq_new = seq_new;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
     p.rows_per_tile = rows_per_tile; p.heads_per_cta = heads_per_cta; p.head_chunks = head_chunks;
-    p.n_splits = n_splits; p.window = window; p.scale = scale; p.partial = partial;
+    p.n_splits = n_splits; p.window = window; p.scale = scale; p.partial = partial; p.tickets = tickets;
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 64) return launch_mma<64>(p, n_tiles, n_rows, s);
     if (head_dim == 128) return launch_mma<128>(p, n_tiles, n_rows, s);

@@ -19,6 +19,8 @@
 template <typename T, int NACC>
 __global__ void attn_paged_simt_kernel(AttnParams p) {
     extern __shared__ float smem[];
+    pdl_wait();
+    pdl_launch_dependents();
     const int hd = p.head_dim;
     const int kstride = hd + 1;
     const int n_warps = blockDim.x >> 5;
@@ -155,7 +157,7 @@ static int launch_attn(const AttnParams& p, int n_tiles, int n_rows, cudaStream_
         e = cudaFuncSetAttribute(attn_paged_simt_kernel<T, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                  (int)smem);                                                               \
         if (e != cudaSuccess) return (int)e;                                                               \
-        attn_paged_simt_kernel<T, N><<<grid, block, smem, s>>>(p);                                         \
+        launch_pdl(attn_paged_simt_kernel<T, N>, grid, block, smem, s, p);                                 \
     } while (0)
     if (nacc <= 1) CML_ATTN(1);
     else if (nacc <= 2) CML_ATTN(2);
@@ -166,8 +168,8 @@ static int launch_attn(const AttnParams& p, int n_tiles, int n_rows, cudaStream_
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (p.n_splits > 1) {
-        attn_combine_kernel<T><<<n_rows * p.n_heads, hd >= 128 ? 128 : 64, 0, s>>>(p.partial, (T*)p.out, p.out_stride,
-                                                                                  p.n_heads, hd, p.n_splits);
+        launch_pdl(attn_combine_kernel<T>, dim3(n_rows * p.n_heads), dim3(hd >= 128 ? 128 : 64), 0, s,
+                   (const float*)p.partial, (T*)p.out, p.out_stride, p.n_heads, hd, p.n_splits);
         e = cudaGetLastError();
     }
     return (int)e;
@@ -190,7 +192,7 @@ extern "C" int cml_attn_paged_simt(const void* q, int q_stride, void* out, int o
     p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.seq_row0 = seq_row0; p.seq_start = seq_start; p.seq_new = seq_new;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
     p.rows_per_tile = rows_per_tile; p.heads_per_cta = heads_per_cta; p.head_chunks = head_chunks;
-    p.n_splits = n_splits; p.window = window; p.scale = scale; p.partial = partial;
+    p.n_splits = n_splits; p.window = window; p.scale = scale; p.partial = partial; p.tickets = nullptr;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == CML_DTYPE_F32) return launch_attn<float>(p, n_tiles, n_rows, s);
     if (dtype == CML_DTYPE_BF16) return launch_attn<bf16>(p, n_tiles, n_rows, s);

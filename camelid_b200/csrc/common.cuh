@@ -57,6 +57,41 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return out;
 }
 
+// Programmatic dependent launch: a kernel launched with `launch_pdl` may begin while the
+// kernel before it in the stream is still running; `pdl_wait()` holds a thread until every
+// earlier kernel has completed and its writes are visible, so it comes before the first
+// access to anything an earlier kernel wrote (or still reads). `pdl_launch_dependents()`
+// lets the next kernel start its own prologue early. Without the launch attribute both are
+// no-ops. Set CAMELID_NO_PDL=1 to launch plainly.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+static inline bool cml_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("CAMELID_NO_PDL");
+        on = (e && e[0] && e[0] != '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = cml_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 static inline int cml_launch_status() {
     cudaError_t e = cudaGetLastError();
     return (int)e;

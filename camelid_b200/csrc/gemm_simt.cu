@@ -26,6 +26,8 @@ gemm_tn_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, i
     __shared__ __align__(16) float As[GEMM_BK][GEMM_BM + GEMM_PAD];
     __shared__ __align__(16) float Ws[GEMM_BK][GEMM_BN + GEMM_PAD];
     __shared__ __align__(16) float Us[EPI == EPI_SWIGLU ? GEMM_BK : 1][GEMM_BN + GEMM_PAD];
+    pdl_wait();
+    pdl_launch_dependents();
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * GEMM_BM, n0 = blockIdx.x * GEMM_BN;
@@ -101,7 +103,7 @@ static int launch_gemm(const void* A, int lda, const void* W, int ldw, void* C, 
                        int epilogue, int group, cudaStream_t s) {
     dim3 grid((N + GEMM_BN - 1) / GEMM_BN, (M + GEMM_BM - 1) / GEMM_BM);
     if (grid.y > 65535) return CML_ERR_BAD_SIZE;
-#define CML_GEMM(E) gemm_tn_simt_kernel<T, E><<<grid, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, C, ldc, M, N, K, group)
+#define CML_GEMM(E) launch_pdl(gemm_tn_simt_kernel<T, E>, grid, dim3(256), 0, s, (const T*)A, lda, (const T*)W, ldw, C, ldc, M, N, K, group)
     switch (epilogue) {
         case EPI_STORE: CML_GEMM(EPI_STORE); break;
         case EPI_STORE_F32: CML_GEMM(EPI_STORE_F32); break;

@@ -38,6 +38,7 @@ struct TcParams {
     int rowsA, rowsB;   // valid rows of the two operands
     int num_kb;         // k-blocks of 64 in total
     int kb_per_split;
+    int independent;    // operand that no earlier kernel writes (weights): 0 = A, 1 = B
     int* err;
 };
 
@@ -165,10 +166,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_d = *tmem_slot;
 
+    pdl_launch_dependents();
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
-            for (int i = 0; i < n_kb; ++i) {
+            // The weights do not depend on the kernel before: their first tiles are on their
+            // way before this kernel waits for that kernel's results (the other operand).
+            const int pre = min(n_kb, STAGES);
+            for (int i = 0; i < pre; ++i) {
+                mbar_expect_tx(full_bar(i), A_BYTES + B_BYTES);
+                const int k = (kb_begin + i) * TC_BK;
+                if (p.independent == 0) tma_load_2d(smemA + i * A_BYTES, &mapA, full_bar(i), k, a0);
+                else tma_load_2d(smemB + i * B_BYTES, &mapB, full_bar(i), k, b0);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                const int k = (kb_begin + i) * TC_BK;
+                if (p.independent == 0) tma_load_2d(smemB + i * B_BYTES, &mapB, full_bar(i), k, b0);
+                else tma_load_2d(smemA + i * A_BYTES, &mapA, full_bar(i), k, a0);
+            }
+            int issued = pre;
+            for (int i = pre; i < n_kb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
                 if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) break;
@@ -210,6 +227,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     } else {
         const int q = warp & 3;                  // the quarter of tensor-memory lanes this warp may read
         const int rowA = a0 + q * 32 + lane;
+        pdl_wait();                              // the output may still be read by a kernel before
         bool ok = true;
         if (n_kb > 0) ok = mbar_wait(accum_bar, 0, abort_flag);
         tc_fence_after();
@@ -350,8 +368,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
     const size_t smem = tc_smem_bytes(BN);
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    gemm_tc_kernel<BN, EPI><<<grid, TC_THREADS, smem, s>>>(ma, mb, p);
-    return (int)cudaGetLastError();
+    e = launch_pdl(gemm_tc_kernel<BN, EPI>, grid, dim3(TC_THREADS), smem, s, ma, mb, p);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 // A: [rowsA, K] bfloat16 (ld lda), B: [rowsB, K] bfloat16 (ld ldb).
@@ -373,6 +391,7 @@ extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, lo
     if (splits > p.num_kb) splits = p.num_kb;
     p.kb_per_split = (p.num_kb + splits - 1) / splits;
     p.err = err;
+    p.independent = (epilogue == TC_T_PARTIAL || epilogue == TC_T_SWIGLU) ? 0 : 1;
     dim3 grid((rowsA + TC_BM - 1) / TC_BM, (rowsB + bn - 1) / bn, splits);
     if (grid.y > 65535 || grid.z > 65535) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;

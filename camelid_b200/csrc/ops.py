@@ -39,10 +39,10 @@ _SIGNATURES = {
     ("attention_mma", "cml_attn_paged_mma"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                                              c_void_p],
+                                              c_void_p, c_void_p],
     ("gemm_simt", "cml_gemm_tn_simt"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_void_p],
-    ("sampling", "cml_argmax_rows"): [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    ("sampling", "cml_argmax_rows"): [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     ("sampling", "cml_adjust_logits"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_float,
                                         c_void_p],
     ("sampling", "cml_sample_rows"): [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_void_p,
@@ -266,14 +266,16 @@ def attn_paged_mma(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_t
     _dev(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, seq_row0, seq_start, seq_new, partial)
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == torch.bfloat16
     assert k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim) and k_pages.is_contiguous() and v_pages.is_contiguous()
+    tickets = None
     if n_splits > 1:
         assert partial is not None and partial.dtype == torch.float32
         assert partial.numel() >= attn_partial_floats(n_rows, n_heads, head_dim, n_splits)
+        tickets = zeroed_scratch(q.device, "attention_tickets", 4 * n_tiles * n_kv_heads * head_chunks)
     _check(_fn("attention_mma", "cml_attn_paged_mma")(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1],
         _p(tile_seq), _p(tile_q0), n_tiles, _p(seq_row0), _p(seq_start), _p(seq_new), n_rows, n_heads, n_kv_heads,
         head_dim, rows_per_tile, heads_per_cta, head_chunks, n_splits, int(window or 0), float(scale), _p(partial),
-        _stream()), "attn_paged_mma", 2 if n_splits > 1 else 1)
+        _p(tickets), _stream()), "attn_paged_mma")
 
 
 def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, group: int = 0):
@@ -293,12 +295,32 @@ def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
                                                 dtype_code(a.dtype), epilogue, group, _stream()), "gemm_tn_simt")
 
 
+_scratch: dict = {}
+_retired: list = []
+
+
+def zeroed_scratch(device, name: str, n_bytes: int) -> torch.Tensor:
+    """Device memory that kernels of this library leave zeroed between calls (tickets of
+    the blocks of a kernel and the like); it only ever grows. Not to be made while a CUDA
+    graph is being captured: the first call of a kernel that needs it should come before."""
+    key = (torch.device(device), name)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < n_bytes:
+        if buf is not None:
+            _retired.append(buf)               # captured graphs may still point at it
+        buf = torch.zeros(max(n_bytes, 4096), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
 def argmax_rows(logits: torch.Tensor, out: torch.Tensor, err: torch.Tensor):
+    """out[r] = index of the largest logit of row r, the lowest index among equals."""
     _dev(logits, out, err)
     rows, vocab = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32 and out.numel() >= rows
-    _check(_fn("sampling", "cml_argmax_rows")(_p(logits), logits.stride(0), rows, vocab, _p(out), _p(err), _stream()),
-           "argmax_rows")
+    scratch = zeroed_scratch(logits.device, "argmax", 16 * max(rows, 64))
+    _check(_fn("sampling", "cml_argmax_rows")(_p(logits), logits.stride(0), rows, vocab, _p(out), _p(err), _p(scratch),
+                                             _stream()), "argmax_rows")
 
 
 def adjust_logits(logits: torch.Tensor, entries: torch.Tensor, biases: torch.Tensor, repeat_penalty: float,

@@ -17,6 +17,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
                                      const float* __restrict__ inv_freq, int rotary_dim, int n_heads,
                                      int n_kv_heads, int head_dim, int write_kv) {
     extern __shared__ float sc[];              // cos[half], sin[half]
+    pdl_wait();
+    pdl_launch_dependents();
     const int half = rotary_dim >> 1;
     float* cs = sc;
     float* sn = sc + half;
@@ -75,8 +77,10 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
 }
 
 // The same on the split sums of the q/k/v product: row r of the product is the sum over s of
-// partial[s][r][:] (float, `width` columns, summed in index order). The rotated q goes to
-// q_out in the compute type; k and v go to the cache.
+// partial[s][r][:] (float, `width` columns, summed in index order) rounded to the compute
+// type as the product's own epilogue would have. The rotated q goes to q_out in the compute
+// type; k and v go to the cache. One warp per (row, head) so that a decode step of a few rows
+// still spreads over many blocks.
 template <typename T>
 __global__ void rope_kv_from_partials_kernel(const float* __restrict__ partial, int n_splits, size_t split_stride,
                                              int width, T* __restrict__ q_out, int q_stride,
@@ -85,57 +89,44 @@ __global__ void rope_kv_from_partials_kernel(const float* __restrict__ partial, 
                                              T* __restrict__ k_pages, T* __restrict__ v_pages,
                                              const float* __restrict__ inv_freq, int rotary_dim, int n_heads,
                                              int n_kv_heads, int head_dim, int write_kv) {
-    extern __shared__ float sh[];              // cos[half], sin[half], row[width]
-    const int half = rotary_dim >> 1;
-    float* cs = sh;
-    float* sn = sh + half;
-    float* row = sh + rotary_dim;
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);    // q heads, then k heads, then v heads
+    const int n_units = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+    if (unit >= n_units) return;
+    const int half = rotary_dim >> 1;
     const int pos = row_pos[r];
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        const float angle = (float)pos * inv_freq[i];
-        float s, c;
-        sincosf(angle, &s, &c);
-        cs[i] = c;
-        sn[i] = s;
-    }
-    const float* src = partial + (size_t)r * width;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float* src = partial + (size_t)r * width + (size_t)unit * head_dim;
+    auto value = [&](int d) {
         float v = 0.f;
-        for (int s = 0; s < n_splits; ++s) v += src[s * split_stride + c];
-        // the product's own epilogue would have rounded to the compute type here
-        row[c] = to_f32(from_f32<T>(v));
+        for (int s = 0; s < n_splits; ++s) v += src[s * split_stride + d];
+        return to_f32(from_f32<T>(v));
+    };
+    T* dst;
+    bool rotate = true;
+    if (unit < n_heads) {
+        dst = q_out + (size_t)r * q_stride + (size_t)unit * head_dim;
+    } else {
+        const int seq = row_seq[r];
+        const int page = block_table[(size_t)seq * max_blocks + pos / CML_PAGE];
+        const int kv = unit - n_heads;
+        const int h = kv < n_kv_heads ? kv : kv - n_kv_heads;
+        rotate = kv < n_kv_heads;
+        dst = (rotate ? k_pages : v_pages) + (((size_t)page * n_kv_heads + h) * CML_PAGE + pos % CML_PAGE) * head_dim;
     }
-    __syncthreads();
-    const int q_pairs = n_heads * half;
-    T* qo = q_out + (size_t)r * q_stride;
-    for (int w = threadIdx.x; w < n_heads * head_dim; w += blockDim.x) {
-        const int h = w / head_dim, d = w - h * head_dim;
-        const float* p = row + h * head_dim;
-        float v;
-        if (d < half) v = p[d] * cs[d] - p[d + half] * sn[d];
-        else if (d < rotary_dim) v = p[d - half] * sn[d - half] + p[d] * cs[d - half];
-        else v = p[d];
-        qo[w] = from_f32<T>(v);
-    }
-    (void)q_pairs;
-    if (!write_kv) return;
-    const int seq = row_seq[r];
-    const int page = block_table[(size_t)seq * max_blocks + pos / CML_PAGE];
-    const int in_page = pos % CML_PAGE;
-    const float* ksrc = row + n_heads * head_dim;
-    const float* vsrc = ksrc + n_kv_heads * head_dim;
-    const size_t page_base = (size_t)page * n_kv_heads * CML_PAGE * head_dim;
-    for (int w = threadIdx.x; w < n_kv_heads * head_dim; w += blockDim.x) {
-        const int h = w / head_dim, d = w - h * head_dim;
-        const float* p = ksrc + h * head_dim;
-        float v;
-        if (d < half) v = p[d] * cs[d] - p[d + half] * sn[d];
-        else if (d < rotary_dim) v = p[d - half] * sn[d - half] + p[d] * cs[d - half];
-        else v = p[d];
-        const size_t o = page_base + ((size_t)h * CML_PAGE + in_page) * head_dim + d;
-        k_pages[o] = from_f32<T>(v);
-        v_pages[o] = from_f32<T>(vsrc[w]);
+    if (rotate) {
+        for (int i = lane; i < half; i += 32) {
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            const float x0 = value(i), x1 = value(i + half);
+            dst[i] = from_f32<T>(x0 * cs - x1 * sn);
+            dst[i + half] = from_f32<T>(x0 * sn + x1 * cs);
+        }
+        for (int d = rotary_dim + lane; d < head_dim; d += 32) dst[d] = from_f32<T>(value(d));
+    } else {
+        for (int d = lane; d < head_dim; d += 32) dst[d] = from_f32<T>(value(d));
     }
 }
 
@@ -146,20 +137,16 @@ extern "C" int cml_rope_kv_from_partials(const float* partial, int n_splits, lon
                                          int head_dim, int write_kv, void* stream) {
     if (rows <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return CML_ERR_BAD_SIZE;
-    if (width < (n_heads + (write_kv ? 2 * n_kv_heads : 0)) * head_dim) return CML_ERR_BAD_SIZE;
+    const int n_units = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+    if (width < n_units * head_dim) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem = ((size_t)rotary_dim + width) * sizeof(float);
-    if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
-    cudaError_t e;
-#define CML_RKP(T)                                                                                                     \
-    do {                                                                                                               \
-        e = cudaFuncSetAttribute(rope_kv_from_partials_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        if (e != cudaSuccess) return (int)e;                                                                           \
-        rope_kv_from_partials_kernel<T><<<rows, 256, smem, s>>>(partial, n_splits, (size_t)split_stride, width, (T*)q_out, \
-                                                               q_stride, row_pos, row_seq, block_table, max_blocks,    \
-                                                               (T*)k_pages, (T*)v_pages, inv_freq, rotary_dim, n_heads, \
-                                                               n_kv_heads, head_dim, write_kv);                        \
-    } while (0)
+    dim3 grid(rows, (n_units + 3) / 4);
+    if (grid.y > 65535) return CML_ERR_BAD_SIZE;
+#define CML_RKP(T)                                                                                                    \
+    launch_pdl(rope_kv_from_partials_kernel<T>, grid, dim3(128), 0, s, partial, n_splits, (size_t)split_stride, width, (T*)q_out,   \
+                                                         q_stride, row_pos, row_seq, block_table, max_blocks,         \
+                                                         (T*)k_pages, (T*)v_pages, inv_freq, rotary_dim, n_heads,     \
+                                                         n_kv_heads, head_dim, write_kv)
     if (dtype == CML_DTYPE_F32) CML_RKP(float);
     else if (dtype == CML_DTYPE_BF16) CML_RKP(bf16);
     else return CML_ERR_BAD_DTYPE;
@@ -178,11 +165,11 @@ extern "C" int cml_rope_kv_write(void* qkv, int dtype, int rows, int row_stride,
     if (smem > 48 * 1024) return CML_ERR_BAD_SIZE;
     const int block = 128;
     if (dtype == CML_DTYPE_F32)
-        rope_kv_write_kernel<float><<<rows, block, smem, s>>>((float*)qkv, row_stride, row_pos, row_seq, block_table,
+        launch_pdl(rope_kv_write_kernel<float>, dim3(rows), dim3(block), smem, s, (float*)qkv, row_stride, row_pos, row_seq, block_table,
                                                               max_blocks, (float*)k_pages, (float*)v_pages, inv_freq,
                                                               rotary_dim, n_heads, n_kv_heads, head_dim, write_kv);
     else if (dtype == CML_DTYPE_BF16)
-        rope_kv_write_kernel<bf16><<<rows, block, smem, s>>>((bf16*)qkv, row_stride, row_pos, row_seq, block_table,
+        launch_pdl(rope_kv_write_kernel<bf16>, dim3(rows), dim3(block), smem, s, (bf16*)qkv, row_stride, row_pos, row_seq, block_table,
                                                              max_blocks, (bf16*)k_pages, (bf16*)v_pages, inv_freq,
                                                              rotary_dim, n_heads, n_kv_heads, head_dim, write_kv);
     else

@@ -13,6 +13,8 @@
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                                     float* __restrict__ out, int hidden, int vocab, int* err) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.x;
     const int tok = tokens[r];
     float* o = out + (size_t)r * hidden;
@@ -31,9 +33,9 @@ extern "C" int cml_embed_gather(const void* table, int dtype, const int* tokens,
     cudaStream_t s = (cudaStream_t)stream;
     const int block = hidden >= 1024 ? 256 : 128;
     if (dtype == CML_DTYPE_F32)
-        embed_gather_kernel<float><<<rows, block, 0, s>>>((const float*)table, tokens, out, hidden, vocab, err);
+        launch_pdl(embed_gather_kernel<float>, dim3(rows), dim3(block), 0, s, (const float*)table, tokens, out, hidden, vocab, err);
     else if (dtype == CML_DTYPE_BF16)
-        embed_gather_kernel<bf16><<<rows, block, 0, s>>>((const bf16*)table, tokens, out, hidden, vocab, err);
+        launch_pdl(embed_gather_kernel<bf16>, dim3(rows), dim3(block), 0, s, (const bf16*)table, tokens, out, hidden, vocab, err);
     else
         return CML_ERR_BAD_DTYPE;
     return cml_launch_status();
@@ -52,6 +54,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TW* __restrict__ w, 
                                const float* __restrict__ partial, int n_splits, size_t split_stride) {
     __shared__ float red[33];
     extern __shared__ float rowbuf[];
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.x;
     const int src = rows_index ? rows_index[r] : r;
     float* xr = x + (size_t)src * hidden;
@@ -83,7 +87,7 @@ extern "C" int cml_rmsnorm(float* x, const void* w, int w_dtype, void* out, int 
     const int block = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     const size_t smem = partial ? (size_t)hidden * sizeof(float) : 0;
     if (smem > 48 * 1024) return CML_ERR_BAD_SIZE;
-#define CML_RMS(TW, TO) rmsnorm_kernel<TW, TO><<<rows, block, smem, s>>>(x, (const TW*)w, (TO*)out, rows_index, hidden, eps, partial, n_splits, (size_t)split_stride)
+#define CML_RMS(TW, TO) launch_pdl(rmsnorm_kernel<TW, TO>, dim3(rows), dim3(block), smem, s, x, (const TW*)w, (TO*)out, rows_index, hidden, eps, partial, n_splits, (size_t)split_stride)
     if (w_dtype == CML_DTYPE_F32 && out_dtype == CML_DTYPE_F32) CML_RMS(float, float);
     else if (w_dtype == CML_DTYPE_F32 && out_dtype == CML_DTYPE_BF16) CML_RMS(float, bf16);
     else if (w_dtype == CML_DTYPE_BF16 && out_dtype == CML_DTYPE_F32) CML_RMS(bf16, float);
@@ -99,6 +103,8 @@ extern "C" int cml_rmsnorm(float* x, const void* w, int w_dtype, void* out, int 
 // gate j sits at column (j / group) * 2 * group + j % group, up j `group` columns later.
 template <typename T>
 __global__ void swiglu_packed_kernel(const T* __restrict__ gu, T* __restrict__ act, int inter, int group) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.x;
     const T* row = gu + (size_t)r * 2 * inter;
     T* o = act + (size_t)r * inter;
@@ -115,9 +121,9 @@ extern "C" int cml_swiglu_packed(const void* gu, void* act, int dtype, int rows,
     if (group <= 0 || inter % group != 0) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == CML_DTYPE_F32)
-        swiglu_packed_kernel<float><<<rows, 256, 0, s>>>((const float*)gu, (float*)act, inter, group);
+        launch_pdl(swiglu_packed_kernel<float>, dim3(rows), dim3(256), 0, s, (const float*)gu, (float*)act, inter, group);
     else if (dtype == CML_DTYPE_BF16)
-        swiglu_packed_kernel<bf16><<<rows, 256, 0, s>>>((const bf16*)gu, (bf16*)act, inter, group);
+        launch_pdl(swiglu_packed_kernel<bf16>, dim3(rows), dim3(256), 0, s, (const bf16*)gu, (bf16*)act, inter, group);
     else
         return CML_ERR_BAD_DTYPE;
     return cml_launch_status();
@@ -127,6 +133,8 @@ extern "C" int cml_swiglu_packed(const void* gu, void* act, int dtype, int rows,
 // x += sum_s partial[s] (float), splits in index order: settles split sums that no norm
 // kernel picked up.
 __global__ void add_partials_kernel(float* __restrict__ x, const float* __restrict__ partial, int n_splits, long n) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     float v = x[i];
@@ -136,6 +144,6 @@ __global__ void add_partials_kernel(float* __restrict__ x, const float* __restri
 
 extern "C" int cml_add_partials(float* x, const float* partial, int n_splits, long n, void* stream) {
     if (n <= 0 || n_splits <= 0) return 0;
-    add_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, partial, n_splits, n);
+    launch_pdl(add_partials_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, x, partial, n_splits, n);
     return cml_launch_status();
 }

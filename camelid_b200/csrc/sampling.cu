@@ -29,47 +29,59 @@ __device__ __forceinline__ unsigned long long composite_key(float v, int idx) {
 }
 
 // ------------------------------------------------------------------------------------
+// Greedy choice per row, spread over several blocks per row so that a large vocabulary is
+// read at memory speed. Every block folds its part into one 64-bit word per row with
+// atomicMax: the orderable bits of the logit above, the inverted index below, so that the
+// largest logit wins and among equals the lowest index. The block that arrives last (a
+// counter per row) writes the token and clears the row's two words for the next call.
+// `scratch` holds 2 * rows unsigned 64-bit words, zero before the first call.
 __global__ void argmax_rows_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out,
-                                   int* __restrict__ err) {
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    const float* row = logits + (size_t)blockIdx.x * ld;
-    float best = -CUDART_INF_F;
-    int best_i = 0x7fffffff;
+                                   int* __restrict__ err, unsigned long long* __restrict__ scratch) {
+    __shared__ unsigned long long red[32];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int row = blockIdx.y;
+    const float* r = logits + (size_t)row * ld;
+    const int per = (vocab + gridDim.x - 1) / gridDim.x;
+    const int begin = blockIdx.x * per, end = min(vocab, begin + per);
+    unsigned long long best = 0ull;
     bool bad = false;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = r[i];
         if (!isfinite(v)) bad = true;
-        if (v > best) best = v, best_i = i;          // ascending i per thread: first maximum kept
+        const unsigned long long key = composite_key(v, i);
+        best = key > best ? key : best;
     }
     if (bad) atomicOr(err, SAMPLE_ERR_NONFINITE);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-        if (ov > best || (ov == best && oi < best_i)) best = ov, best_i = oi;
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
     }
-    if (lane == 0) sv[warp] = best, si[warp] = best_i;
+    if (lane == 0) red[warp] = best;
     __syncthreads();
-    if (warp == 0) {
-        const int nw = blockDim.x >> 5;
-        best = lane < nw ? sv[lane] : -CUDART_INF_F;
-        best_i = lane < nw ? si[lane] : 0x7fffffff;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-            if (ov > best || (ov == best && oi < best_i)) best = ov, best_i = oi;
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) best = red[w] > best ? red[w] : best;
+        unsigned long long* cell = scratch + 2 * (size_t)row;
+        if (best) atomicMax(cell, best);
+        __threadfence();
+        const unsigned long long ticket = atomicAdd(cell + 1, 1ull);
+        if (ticket == gridDim.x - 1) {
+            __threadfence();
+            const unsigned long long win = atomicExch(cell, 0ull);
+            out[row] = win ? (int)(0xFFFFFFFFu - (unsigned int)(win & 0xFFFFFFFFull)) : 0;
+            cell[1] = 0ull;
         }
-        if (lane == 0) out[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
     }
 }
 
-extern "C" int cml_argmax_rows(const float* logits, int ld, int rows, int vocab, int* out, int* err, void* stream) {
+extern "C" int cml_argmax_rows(const float* logits, int ld, int rows, int vocab, int* out, int* err,
+                               unsigned long long* scratch, void* stream) {
     if (rows <= 0) return 0;
-    if (vocab <= 0) return CML_ERR_BAD_SIZE;
-    argmax_rows_kernel<<<rows, vocab >= 4096 ? 1024 : 256, 0, (cudaStream_t)stream>>>(logits, ld, vocab, out, err);
+    if (vocab <= 0 || rows > 65535) return CML_ERR_BAD_SIZE;
+    const int blocks = max(1, min(64, vocab / 2048));
+    launch_pdl(argmax_rows_kernel, dim3(blocks, rows), dim3(256), 0, (cudaStream_t)stream, logits, ld, vocab, out, err, scratch);
     return cml_launch_status();
 }
 
