@@ -58,8 +58,10 @@ attn_paged_mma_kernel(AttnParams p) {
     constexpr int CHUNKS = HD / 8;                           // 16-byte chunks of a row
     extern __shared__ __align__(16) uint8_t smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
-    pdl_wait();
     pdl_launch_dependents();
+    // The step's integer arrays and the keys and values of earlier steps do not depend on the
+    // kernels just before this one: everything up to the first read of q or of a freshly
+    // written cache row runs ahead of pdl_wait().
 
     const int tile = blockIdx.x;
     const int seq = p.tile_seq[tile];
@@ -96,18 +98,6 @@ attn_paged_mma_kernel(AttnParams p) {
         lo_r[h] = p.window > 0 ? max(0, pos_r[h] - p.window + 1) : 0;
         q_r[h] = (const bf16*)p.q + (size_t)(row0 + q0 + r_local) * p.q_stride + (size_t)(kvh * group + hg) * HD;
     }
-    // A fragments of Q (zero rows where there is no query)
-    uint32_t qa[KSTEPS][4];
-#pragma unroll
-    for (int ks = 0; ks < KSTEPS; ++ks) {
-        const int c = ks * 16 + 2 * (lane & 3);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            qa[ks][h] = valid_r[h] ? *reinterpret_cast<const uint32_t*>(q_r[h] + c) : 0u;
-            qa[ks][h + 2] = valid_r[h] ? *reinterpret_cast<const uint32_t*>(q_r[h] + c + 8) : 0u;
-        }
-    }
-
     float m_r[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_r[2] = {0.f, 0.f};
     float o[DTILES][4];
 #pragma unroll
@@ -120,8 +110,16 @@ attn_paged_mma_kernel(AttnParams p) {
     bf16* my_smem = smem + (size_t)warp * AM_STAGES * STAGE_ELEMS;
     const uint32_t my_smem_u32 = (uint32_t)__cvta_generic_to_shared(my_smem);
 
-    auto issue = [&](int t, int stage) {
-        const int page = p.block_table[(size_t)seq * p.max_blocks + (t * AM_TILE) / CML_PAGE];
+    // this warp's tiles: t_beg + warp, + 4, + 8, ...
+    const int n_mine = (t_end - t_beg - warp + AM_WARPS - 1) / AM_WARPS;
+    // page of each of this warp's tiles, looked up once: lane i keeps the page of tile i (mod 32)
+    const int* table_row = p.block_table + (size_t)seq * p.max_blocks;
+    int my_page = 0;
+    if (lane < n_mine) my_page = table_row[((t_beg + warp + lane * AM_WARPS) * AM_TILE) / CML_PAGE];
+
+    auto issue = [&](int t, int stage, int it_index) {
+        int page = __shfl_sync(0xffffffffu, my_page, it_index & 31);
+        if (it_index >= 32) page = table_row[(t * AM_TILE) / CML_PAGE];
         const size_t base = (((size_t)page * p.n_kv_heads + kvh) * CML_PAGE + (t * AM_TILE) % CML_PAGE) * HD;
         const uint32_t dst = my_smem_u32 + (uint32_t)stage * STAGE_ELEMS * 2;
         for (int c = lane; c < AM_TILE * CHUNKS; c += 32) {
@@ -131,12 +129,30 @@ attn_paged_mma_kernel(AttnParams p) {
         }
     };
 
-    // this warp's tiles: t_beg + warp, + 4, + 8, ...
-    const int n_mine = (t_end - t_beg - warp + AM_WARPS - 1) / AM_WARPS;
+    // tiles that lie wholly in what the cache held before this step are fetched at once
+    bool early[AM_STAGES - 1];
 #pragma unroll
     for (int s = 0; s < AM_STAGES - 1; ++s) {
-        if (s < n_mine) issue(t_beg + warp + s * AM_WARPS, s);
+        const int t = t_beg + warp + s * AM_WARPS;
+        early[s] = s < n_mine && (t + 1) * AM_TILE <= start;
+        if (early[s]) issue(t, s, s);
+    }
+    pdl_wait();
+#pragma unroll
+    for (int s = 0; s < AM_STAGES - 1; ++s) {
+        if (s < n_mine && !early[s]) issue(t_beg + warp + s * AM_WARPS, s, s);
         cp_async_commit();
+    }
+    // A fragments of Q (zero rows where there is no query)
+    uint32_t qa[KSTEPS][4];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+        const int c = ks * 16 + 2 * (lane & 3);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            qa[ks][h] = valid_r[h] ? *reinterpret_cast<const uint32_t*>(q_r[h] + c) : 0u;
+            qa[ks][h + 2] = valid_r[h] ? *reinterpret_cast<const uint32_t*>(q_r[h] + c + 8) : 0u;
+        }
     }
     const float scale = p.scale;
     for (int it = 0; it < n_mine; ++it) {
@@ -145,7 +161,7 @@ attn_paged_mma_kernel(AttnParams p) {
         __syncwarp();
         {   // keep the pipeline full
             const int nxt = it + AM_STAGES - 1;
-            if (nxt < n_mine) issue(t_beg + warp + nxt * AM_WARPS, nxt % AM_STAGES);
+            if (nxt < n_mine) issue(t_beg + warp + nxt * AM_WARPS, nxt % AM_STAGES, nxt);
             cp_async_commit();
         }
         const uint32_t ks_u32 = my_smem_u32 + (uint32_t)(it % AM_STAGES) * STAGE_ELEMS * 2;

@@ -114,18 +114,22 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return d;
 }
 
-__host__ __device__ constexpr int tc_stages(int bn) {
-    return bn >= 256 ? 4 : (bn >= 128 ? 6 : 8);
+// Stages of the ring. Decode tiles (bn <= 64) with little work per block keep a small ring so
+// that several blocks fit an SM: the blocks of the next kernel then become resident while
+// this one still runs and prefetch their weights. Blocks that stream many k-blocks take a
+// deep ring: the bytes in flight per SM are what bounds their bandwidth.
+__host__ __device__ constexpr int tc_stages(int bn, bool deep) {
+    return bn >= 256 ? 4 : (bn >= 128 ? 6 : (deep ? (bn >= 64 ? 8 : 10) : 4));
 }
 __host__ __device__ constexpr int tc_tmem_cols(int bn) { return bn <= 32 ? 32 : (bn <= 64 ? 64 : (bn <= 128 ? 128 : 256)); }
-__host__ __device__ constexpr size_t tc_smem_bytes(int bn) {
-    return 1024 /*alignment slack*/ + (size_t)tc_stages(bn) * (TC_BM * 128 + bn * 128) + 256 /*barriers*/;
+__host__ __device__ constexpr size_t tc_smem_bytes(int bn, bool deep) {
+    return 1024 /*alignment slack*/ + (size_t)tc_stages(bn, deep) * (TC_BM * 128 + bn * 128) + 256 /*barriers*/;
 }
 
-template <int BN, int EPI>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+template <int BN, int EPI, bool DEEP>
+__global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, TcParams p) {
-    constexpr int STAGES = tc_stages(BN);
+    constexpr int STAGES = tc_stages(BN, DEEP);
     constexpr uint32_t A_BYTES = TC_BM * 128, B_BYTES = BN * 128;
     constexpr uint32_t TMEM_COLS = tc_tmem_cols(BN);
     extern __shared__ uint8_t smem_raw[];
@@ -363,13 +367,19 @@ static int make_map(CUtensorMap* map, const void* base, long rows, long K, long 
     return r == CUDA_SUCCESS ? 0 : CML_ERR_BAD_SIZE;
 }
 
+template <int BN, int EPI, bool DEEP>
+static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t s) {
+    const size_t smem = tc_smem_bytes(BN, DEEP);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    e = launch_pdl(gemm_tc_kernel<BN, EPI, DEEP>, grid, dim3(TC_THREADS), smem, s, ma, mb, p);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
 template <int BN, int EPI>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t s) {
-    const size_t smem = tc_smem_bytes(BN);
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    e = launch_pdl(gemm_tc_kernel<BN, EPI>, grid, dim3(TC_THREADS), smem, s, ma, mb, p);
-    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+    if (BN <= 64 && p.kb_per_split >= 12) return launch_tc2<BN, EPI, true>(ma, mb, p, grid, s);
+    return launch_tc2<BN, EPI, false>(ma, mb, p, grid, s);
 }
 
 // A: [rowsA, K] bfloat16 (ld lda), B: [rowsB, K] bfloat16 (ld ldb).

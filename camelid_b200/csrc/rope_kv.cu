@@ -99,9 +99,15 @@ __global__ void rope_kv_from_partials_kernel(const float* __restrict__ partial, 
     const int half = rotary_dim >> 1;
     const int pos = row_pos[r];
     const float* src = partial + (size_t)r * width + (size_t)unit * head_dim;
-    auto value = [&](int d) {
+    auto value = [&](int d) {          // loads of a group first, then the adds in split order
         float v = 0.f;
-        for (int s = 0; s < n_splits; ++s) v += src[s * split_stride + d];
+        for (int s0 = 0; s0 < n_splits; s0 += 8) {
+            float t[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t[i] = (s0 + i < n_splits) ? src[(size_t)(s0 + i) * split_stride + d] : 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v += t[i];
+        }
         return to_f32(from_f32<T>(v));
     };
     T* dst;

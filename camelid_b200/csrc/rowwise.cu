@@ -64,7 +64,14 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TW* __restrict__ w, 
         float v = xr[c];
         if (partial) {
             const float* pp = partial + (size_t)src * hidden + c;
-            for (int s = 0; s < n_splits; ++s) v += pp[s * split_stride];
+            // all loads of a group are issued before the first add, the adds stay in split order
+            for (int s0 = 0; s0 < n_splits; s0 += 8) {
+                float t[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) t[i] = (s0 + i < n_splits) ? pp[(size_t)(s0 + i) * split_stride] : 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v += t[i];
+            }
             rowbuf[c] = v;
             if (!rows_index) xr[c] = v;
         }
@@ -84,7 +91,7 @@ extern "C" int cml_rmsnorm(float* x, const void* w, int w_dtype, void* out, int 
                            int n_splits, long split_stride, void* stream) {
     if (rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int block = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    const int block = hidden >= 1024 ? 1024 : (hidden >= 512 ? 256 : 128);
     const size_t smem = partial ? (size_t)hidden * sizeof(float) : 0;
     if (smem > 48 * 1024) return CML_ERR_BAD_SIZE;
 #define CML_RMS(TW, TO) launch_pdl(rmsnorm_kernel<TW, TO>, dim3(rows), dim3(block), smem, s, x, (const TW*)w, (TO*)out, rows_index, hidden, eps, partial, n_splits, (size_t)split_stride)

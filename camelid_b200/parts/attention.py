@@ -109,7 +109,8 @@ class GroupedQueryAttention(Part):
             keys = ctx.max_len if not self.window else min(ctx.max_len, self.window + PAGE)
             ctas = n_tiles * self.num_kv_heads * chunks
             unit = 8 * 32 if tensor_cores else PAGE               # keys a block should at least have
-            n_splits = max(1, min((keys + unit - 1) // unit, (2 * linear.SM_COUNT + ctas - 1) // ctas, 64))
+            resident = (2 if self.head_dim <= 64 else 1) * linear.SM_COUNT    # blocks that run at the same time
+            n_splits = max(1, min((keys + unit - 1) // unit, resident // ctas, 64))
             if n_splits > 1:
                 partial = ctx.buffer("attn_partial", (ops.attn_partial_floats(ctx.n_rows, self.num_heads, self.head_dim,
                                                                              n_splits),), torch.float32)
