@@ -251,7 +251,7 @@ def attn_mma_tiling(n_heads: int, n_kv_heads: int, decode: bool) -> tuple[int, i
     group = n_heads // n_kv_heads
     chunks = (group + 15) // 16
     hpc = (group + chunks - 1) // chunks
-    rows = 1 if decode else max(1, 16 // hpc)
+    rows = 1 if decode else max(1, 64 // hpc)          # prefill: four MMA row tiles share each key tile
     return rows, hpc, chunks
 
 

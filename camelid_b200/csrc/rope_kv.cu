@@ -169,7 +169,7 @@ extern "C" int cml_rope_kv_write(void* qkv, int dtype, int rows, int row_stride,
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = (size_t)rotary_dim * sizeof(float);
     if (smem > 48 * 1024) return CML_ERR_BAD_SIZE;
-    const int block = 128;
+    const int block = 256;
     if (dtype == CML_DTYPE_F32)
         launch_pdl(rope_kv_write_kernel<float>, dim3(rows), dim3(block), smem, s, (float*)qkv, row_stride, row_pos, row_seq, block_table,
                                                               max_blocks, (float*)k_pages, (float*)v_pages, inv_freq,

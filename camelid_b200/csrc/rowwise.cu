@@ -91,7 +91,8 @@ extern "C" int cml_rmsnorm(float* x, const void* w, int w_dtype, void* out, int 
                            int n_splits, long split_stride, void* stream) {
     if (rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int block = hidden >= 1024 ? 1024 : (hidden >= 512 ? 256 : 128);
+    // few rows (decode): many threads per row shorten the chain; many rows: several blocks per SM
+    const int block = hidden >= 1024 ? (rows <= 256 ? 1024 : 256) : (hidden >= 512 ? 256 : 128);
     const size_t smem = partial ? (size_t)hidden * sizeof(float) : 0;
     if (smem > 48 * 1024) return CML_ERR_BAD_SIZE;
 #define CML_RMS(TW, TO) launch_pdl(rmsnorm_kernel<TW, TO>, dim3(rows), dim3(block), smem, s, x, (const TW*)w, (TO*)out, rows_index, hidden, eps, partial, n_splits, (size_t)split_stride)
