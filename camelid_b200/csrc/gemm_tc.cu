@@ -38,6 +38,7 @@ struct TcParams {
     int rowsA, rowsB;   // valid rows of the two operands
     int num_kb;         // k-blocks of 64 in total
     int kb_per_split;
+    int tiles_a, tiles_b, splits;   // work items
     int independent;    // operand that no earlier kernel writes (weights): 0 = A, 1 = B
     int* err;
 };
@@ -121,40 +122,132 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 __host__ __device__ constexpr int tc_stages(int bn, bool deep) {
     return bn >= 256 ? 4 : (bn >= 128 ? 6 : (deep ? (bn >= 64 ? 8 : 10) : 4));
 }
-__host__ __device__ constexpr int tc_tmem_cols(int bn) { return bn <= 32 ? 32 : (bn <= 64 ? 64 : (bn <= 128 ? 128 : 256)); }
+__host__ __device__ constexpr int tc_tmem_cols(int bn) { return bn <= 16 ? 32 : (bn <= 32 ? 64 : (bn <= 64 ? 128 : (bn <= 128 ? 256 : 512))); }
 __host__ __device__ constexpr size_t tc_smem_bytes(int bn, bool deep) {
-    return 1024 /*alignment slack*/ + (size_t)tc_stages(bn, deep) * (TC_BM * 128 + bn * 128) + 256 /*barriers*/;
+    return 1024 /*alignment slack*/ + (size_t)tc_stages(bn, deep) * (TC_BM * 128 + bn * 128) + 512 /*barriers*/;
 }
 
+// One 16-column chunk of one accumulator row, already in registers, to its place in the output.
+template <int EPI>
+__device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const uint32_t (&r)[16], const uint32_t (&u)[16],
+                                                  int rowA, int colB, int split, int lane, int a_group0) {
+    if (EPI == TC_STORE || EPI == TC_STORE_F32 || EPI == TC_ADD_F32) {
+        if (rowA >= p.rowsA || colB >= p.rowsB) return;
+        const int n_ok = min(16, p.rowsB - colB);
+        if (EPI == TC_STORE) {
+            bf16* dst = (bf16*)p.C + (size_t)rowA * p.ldc + colB;
+            if (n_ok == 16 && (((uintptr_t)dst & 15) == 0)) {
+                uint32_t w[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                    w[i] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+                for (int i = 0; i < n_ok; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+            }
+        } else {
+            float* dst = (float*)p.C + (size_t)rowA * p.ldc + colB;
+            if (n_ok == 16 && (((uintptr_t)dst & 15) == 0)) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                           __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                    if (EPI == TC_ADD_F32) {
+                        const float4 o = reinterpret_cast<float4*>(dst)[i];
+                        v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                    }
+                    reinterpret_cast<float4*>(dst)[i] = v;
+                }
+            } else {
+                for (int i = 0; i < n_ok; ++i) {
+                    const float v = __uint_as_float(r[i]);
+                    dst[i] = (EPI == TC_ADD_F32) ? dst[i] + v : v;
+                }
+            }
+        }
+    } else if (EPI == TC_SWIGLU) {
+        // r: 16 gate columns, u: the 16 up columns of the same outputs
+        const int out_col = colB / 2;
+        const int inter = p.rowsB / 2;
+        if (rowA >= p.rowsA || out_col >= inter) return;
+        bf16* dst = (bf16*)p.C + (size_t)rowA * p.ldc + out_col;
+        const int n_ok = min(16, inter - out_col);
+        float a[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float g = __uint_as_float(r[i]);
+            a[i] = __fdividef(g, 1.0f + __expf(-g)) * __uint_as_float(u[i]);
+        }
+        if (n_ok == 16 && (((uintptr_t)dst & 15) == 0)) {
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
+                w[i] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        } else {
+            for (int i = 0; i < n_ok; ++i) dst[i] = __float2bfloat16_rn(a[i]);
+        }
+    } else if (EPI == TC_T_PARTIAL) {
+        // transposed: this thread owns output feature rowA for 16 batch rows
+        if (rowA >= p.rowsA) return;
+        float* dst = (float*)p.C + ((size_t)split * p.rowsB) * p.ldc + rowA;
+        const int n_ok = min(16, p.rowsB - colB);
+        for (int i = 0; i < n_ok; ++i) dst[(size_t)(colB + i) * p.ldc] = __uint_as_float(r[i]);
+    } else {   // TC_T_SWIGLU: lanes 0-15 hold gate rows, lanes 16-31 the up rows of the same outputs
+        const int inter = p.rowsA / 2;
+        const int out_j = a_group0 / 2 + (lane & 15);
+        const int n_ok = min(16, p.rowsB - colB);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float mine = __uint_as_float(r[i]);
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+            if (lane < 16 && i < n_ok && out_j < inter)
+                ((bf16*)p.C)[(size_t)(colB + i) * p.ldc + out_j] =
+                    __float2bfloat16_rn(__fdividef(mine, 1.0f + __expf(-mine)) * other);
+        }
+    }
+}
+
+// Work items are (tile of A rows, tile of B rows, split of K), numbered with the A tile
+// fastest; a block takes items blockIdx.x, blockIdx.x + gridDim.x, ... The accumulator is
+// double-buffered in tensor memory, so while the epilogue warps drain one item the MMA
+// thread already runs the next one.
 template <int BN, int EPI, bool DEEP>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, TcParams p) {
     constexpr int STAGES = tc_stages(BN, DEEP);
     constexpr uint32_t A_BYTES = TC_BM * 128, B_BYTES = BN * 128;
-    constexpr uint32_t TMEM_COLS = tc_tmem_cols(BN);
+    constexpr uint32_t TMEM_COLS = tc_tmem_cols(BN);          // two accumulators of BN columns
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t smemA = base, smemB = base + STAGES * A_BYTES;
-    const uint32_t bars = smemB + STAGES * B_BYTES;            // full[S], empty[S], accum, then tmem slot + abort
+    const uint32_t bars = smemB + STAGES * B_BYTES;   // full[S], empty[S], acc_full[2], acc_empty[2]; tmem slot; abort
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + STAGES * (A_BYTES + B_BYTES) + (2 * STAGES + 1) * 8);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + STAGES * (A_BYTES + B_BYTES) + (2 * STAGES + 4) * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+    auto acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+    auto acc_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int a0 = blockIdx.x * TC_BM, b0 = blockIdx.y * BN, split = blockIdx.z;
-    const int kb_begin = split * p.kb_per_split;
-    const int kb_end = min(p.num_kb, kb_begin + p.kb_per_split);
-    const int n_kb = max(0, kb_end - kb_begin);
+    const int n_work = p.tiles_a * p.tiles_b * p.splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full(b), 1);
+            mbar_init(acc_empty(b), 128);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -168,40 +261,60 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_d = *tmem_slot;
-
+    const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
+
+    auto item = [&](int w, int& a0, int& b0, int& split, int& kb_begin, int& n_kb) {
+        const int ta = w % p.tiles_a;
+        const int rest = w / p.tiles_a;
+        const int tb = rest % p.tiles_b;
+        split = rest / p.tiles_b;
+        a0 = ta * TC_BM;
+        b0 = tb * BN;
+        kb_begin = split * p.kb_per_split;
+        n_kb = max(0, min(p.num_kb, kb_begin + p.kb_per_split) - kb_begin);
+    };
+
     if (warp == 0) {
         if (lane == 0) {
-            // The weights do not depend on the kernel before: their first tiles are on their
-            // way before this kernel waits for that kernel's results (the other operand).
-            const int pre = min(n_kb, STAGES);
-            for (int i = 0; i < pre; ++i) {
-                mbar_expect_tx(full_bar(i), A_BYTES + B_BYTES);
-                const int k = (kb_begin + i) * TC_BK;
-                if (p.independent == 0) tma_load_2d(smemA + i * A_BYTES, &mapA, full_bar(i), k, a0);
-                else tma_load_2d(smemB + i * B_BYTES, &mapB, full_bar(i), k, b0);
-            }
-            pdl_wait();
-            for (int i = 0; i < pre; ++i) {
-                const int k = (kb_begin + i) * TC_BK;
-                if (p.independent == 0) tma_load_2d(smemB + i * B_BYTES, &mapB, full_bar(i), k, b0);
-                else tma_load_2d(smemA + i * A_BYTES, &mapA, full_bar(i), k, a0);
-            }
-            int issued = pre;
-            for (int i = pre; i < n_kb; ++i) {
-                const int s = i % STAGES;
-                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
-                if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) break;
-                mbar_expect_tx(full_bar(s), A_BYTES + B_BYTES);
-                const int k = (kb_begin + i) * TC_BK;
-                tma_load_2d(smemA + s * A_BYTES, &mapA, full_bar(s), k, a0);
-                tma_load_2d(smemB + s * B_BYTES, &mapB, full_bar(s), k, b0);
-                issued = i + 1;
+            int g = 0;                      // k-blocks issued so far by this block, over all its items
+            bool waited = false, ok = true;
+            for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+                int a0, b0, split, kb_begin, n_kb;
+                item(w, a0, b0, split, kb_begin, n_kb);
+                int i = 0;
+                if (!waited) {
+                    // The weights do not depend on the kernel before: their first tiles are on
+                    // their way before this kernel waits for that kernel's results.
+                    const int pre = min(n_kb, STAGES);
+                    for (; i < pre; ++i) {
+                        mbar_expect_tx(full_bar(i), A_BYTES + B_BYTES);
+                        const int k = (kb_begin + i) * TC_BK;
+                        if (p.independent == 0) tma_load_2d(smemA + i * A_BYTES, &mapA, full_bar(i), k, a0);
+                        else tma_load_2d(smemB + i * B_BYTES, &mapB, full_bar(i), k, b0);
+                    }
+                    pdl_wait();
+                    waited = true;
+                    for (int j = 0; j < pre; ++j) {
+                        const int k = (kb_begin + j) * TC_BK;
+                        if (p.independent == 0) tma_load_2d(smemB + j * B_BYTES, &mapB, full_bar(j), k, b0);
+                        else tma_load_2d(smemA + j * A_BYTES, &mapA, full_bar(j), k, a0);
+                    }
+                    g = pre;
+                }
+                for (; i < n_kb; ++i, ++g) {
+                    const int s = g % STAGES;
+                    const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(full_bar(s), A_BYTES + B_BYTES);
+                    const int k = (kb_begin + i) * TC_BK;
+                    tma_load_2d(smemA + s * A_BYTES, &mapA, full_bar(s), k, a0);
+                    tma_load_2d(smemB + s * B_BYTES, &mapB, full_bar(s), k, b0);
+                }
             }
             if (*abort_flag) {
                 // let the copies that are in flight land before the block leaves
-                for (int i = max(0, issued - STAGES); i < issued; ++i) {
+                for (int i = max(0, g - STAGES); i < g; ++i) {
                     const long long t0 = clock64();
                     while (!mbar_try_wait(full_bar(i % STAGES), (uint32_t)(i / STAGES) & 1u) &&
                            clock64() - t0 < 20000000ll) {}
@@ -212,116 +325,68 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         if (lane == 0) {
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                        ((uint32_t)(TC_BM >> 4) << 24);
+            int g = 0, j = 0;                             // j counts the items that have k-blocks
             bool ok = true;
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % STAGES;
-                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
-                ok = mbar_wait(full_bar(s), ph, abort_flag);
+            for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+                int a0, b0, split, kb_begin, n_kb;
+                item(w, a0, b0, split, kb_begin, n_kb);
+                if (n_kb == 0) continue;                  // the epilogue writes zeros on its own
+                const int buf = j & 1;
+                // the epilogue must have drained this accumulator (two items ago)
+                ok = mbar_wait(acc_empty(buf), (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t adesc = smem_desc_sw128(smemA + s * A_BYTES);
-                const uint64_t bdesc = smem_desc_sw128(smemB + s * B_BYTES);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                for (int i = 0; i < n_kb && ok; ++i, ++g) {
+                    const int s = g % STAGES;
+                    const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+                    ok = mbar_wait(full_bar(s), ph, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t adesc = smem_desc_sw128(smemA + s * A_BYTES);
+                    const uint64_t bdesc = smem_desc_sw128(smemB + s * B_BYTES);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)
-                    tc_mma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (i | k) ? 1u : 0u);
-                tc_commit(empty_bar(s));         // the stage is free once these MMAs have read it
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        tc_mma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (i | k) ? 1u : 0u);
+                    tc_commit(empty_bar(s));         // the stage is free once these MMAs have read it
+                }
+                if (ok) tc_commit(acc_full(buf));    // the accumulator is complete
+                ++j;
             }
-            if (ok) tc_commit(accum_bar);        // the accumulator is complete
         }
     } else {
         const int q = warp & 3;                  // the quarter of tensor-memory lanes this warp may read
-        const int rowA = a0 + q * 32 + lane;
         pdl_wait();                              // the output may still be read by a kernel before
         bool ok = true;
-        if (n_kb > 0) ok = mbar_wait(accum_bar, 0, abort_flag);
-        tc_fence_after();
-        if (ok) {
-            const uint32_t taddr = tmem_d + ((uint32_t)(q * 32) << 16);
+        int j = 0;                               // counts the items that have k-blocks, as the MMA thread does
+        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+            int a0, b0, split, kb_begin, n_kb;
+            item(w, a0, b0, split, kb_begin, n_kb);
+            const int buf = j & 1;
+            const int rowA = a0 + q * 32 + lane;
+            if (n_kb > 0) {
+                ok = mbar_wait(acc_full(buf), ((uint32_t)j >> 1) & 1u, abort_flag);
+                if (!ok) break;
+            }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
+            constexpr int STEP = (EPI == TC_SWIGLU) ? 32 : 16;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                uint32_t r[16];
+            for (int c = 0; c < BN; c += STEP) {
+                uint32_t r[16], u[16];
                 if (n_kb > 0) {
                     tc_ld16(taddr + c, r);
+                    if (EPI == TC_SWIGLU) tc_ld16(taddr + c + 16, u);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) r[i] = 0u;
+                    for (int i = 0; i < 16; ++i) r[i] = 0u, u[i] = 0u;
                 }
-                const int colB = b0 + c;
-                if (EPI == TC_STORE || EPI == TC_STORE_F32 || EPI == TC_ADD_F32) {
-                    if (rowA < p.rowsA && colB < p.rowsB) {
-                        const int n_ok = min(16, p.rowsB - colB);
-                        if (EPI == TC_STORE) {
-                            bf16* dst = (bf16*)p.C + (size_t)rowA * p.ldc + colB;
-                            if (n_ok == 16 && (((uintptr_t)dst & 15) == 0)) {
-                                uint32_t w[8];
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) {
-                                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                                    w[i] = *reinterpret_cast<uint32_t*>(&h);
-                                }
-                                reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                                reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                            } else {
-                                for (int i = 0; i < n_ok; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
-                            }
-                        } else {
-                            float* dst = (float*)p.C + (size_t)rowA * p.ldc + colB;
-                            const bool vec = n_ok == 16 && (((uintptr_t)dst & 15) == 0);
-                            if (vec) {
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                                           __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-                                    if (EPI == TC_ADD_F32) {
-                                        const float4 o = reinterpret_cast<float4*>(dst)[i];
-                                        v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                                    }
-                                    reinterpret_cast<float4*>(dst)[i] = v;
-                                }
-                            } else {
-                                for (int i = 0; i < n_ok; ++i) {
-                                    const float v = __uint_as_float(r[i]);
-                                    dst[i] = (EPI == TC_ADD_F32) ? dst[i] + v : v;
-                                }
-                            }
-                        }
-                    }
-                } else if (EPI == TC_SWIGLU) {
-                    // columns come in groups of 32: 16 gate columns, then the 16 up columns of the same outputs
-                    uint32_t u[16];
-                    tc_ld16(taddr + c + 16, u);
-                    const int out_col = colB / 2;
-                    const int inter = p.rowsB / 2;
-                    if (rowA < p.rowsA && out_col < inter) {
-                        bf16* dst = (bf16*)p.C + (size_t)rowA * p.ldc + out_col;
-                        const int n_ok = min(16, inter - out_col);
-                        for (int i = 0; i < n_ok; ++i) {
-                            const float g = __uint_as_float(r[i]);
-                            dst[i] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * __uint_as_float(u[i]));
-                        }
-                    }
-                    c += 16;
-                } else if (EPI == TC_T_PARTIAL) {
-                    // transposed: this thread owns output feature rowA for 16 batch rows
-                    if (rowA < p.rowsA) {
-                        float* dst = (float*)p.C + ((size_t)split * p.rowsB) * p.ldc + rowA;
-                        const int n_ok = min(16, p.rowsB - colB);
-                        for (int i = 0; i < n_ok; ++i) dst[(size_t)(colB + i) * p.ldc] = __uint_as_float(r[i]);
-                    }
-                } else {   // TC_T_SWIGLU: lanes 0-15 hold gate rows, lanes 16-31 the up rows of the same outputs
-                    const int inter = p.rowsA / 2;
-                    const int out_j = (a0 + q * 32) / 2 + (lane & 15);
-                    const int n_ok = min(16, p.rowsB - colB);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float mine = __uint_as_float(r[i]);
-                        const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
-                        if (lane < 16 && i < n_ok && out_j < inter) {
-                            ((bf16*)p.C)[(size_t)(colB + i) * p.ldc + out_j] =
-                                __float2bfloat16_rn((mine / (1.0f + expf(-mine))) * other);
-                        }
-                    }
-                }
+                tc_epilogue_chunk<EPI>(p, r, u, rowA, b0 + c, split, lane, a0 + q * 32);
+            }
+            if (n_kb > 0) {
+                tc_fence_before();
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(buf)) : "memory");
+                ++j;
             }
         }
     }
@@ -329,7 +394,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 2);
 }
@@ -402,8 +467,16 @@ extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, lo
     p.kb_per_split = (p.num_kb + splits - 1) / splits;
     p.err = err;
     p.independent = (epilogue == TC_T_PARTIAL || epilogue == TC_T_SWIGLU) ? 0 : 1;
-    dim3 grid((rowsA + TC_BM - 1) / TC_BM, (rowsB + bn - 1) / bn, splits);
-    if (grid.y > 65535 || grid.z > 65535) return CML_ERR_BAD_SIZE;
+    p.tiles_a = (rowsA + TC_BM - 1) / TC_BM;
+    p.tiles_b = (rowsB + bn - 1) / bn;
+    p.splits = splits;
+    const long work = (long)p.tiles_a * p.tiles_b * splits;
+    if (work > 0x7fffffffL) return CML_ERR_BAD_SIZE;
+    // Large tiles fill an SM: one persistent block per SM walks the items. Decode tiles are
+    // small: one block per item, several per SM.
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    dim3 grid((unsigned)(bn >= 128 ? (work < sms ? work : sms) : work), 1, 1);
     cudaStream_t s = (cudaStream_t)stream;
 #define TC_CASE(BN_, EPI_) if (bn == BN_ && epilogue == EPI_) return launch_tc<BN_, EPI_>(ma, mb, p, grid, s)
     TC_CASE(128, TC_STORE); TC_CASE(128, TC_STORE_F32); TC_CASE(128, TC_ADD_F32); TC_CASE(128, TC_SWIGLU);
