@@ -22,7 +22,7 @@ import time
 from ..errors import KernelError
 
 CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
-HEADERS = ["common.cuh", "attention_common.cuh"]
+HEADERS = ["common.cuh", "attention_common.cuh", "argmax_static.h"]
 MODULES = {
     "rowwise": ["rowwise.cu"],
     "rope_kv": ["rope_kv.cu"],

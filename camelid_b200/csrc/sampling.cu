@@ -320,3 +320,68 @@ extern "C" int cml_sample_rows(const float* logits, int ld, int rows, int vocab,
     sample_rows_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, ld, vocab, sp, draws, out, err);
     return cml_launch_status();
 }
+
+// ------------------------------------------------------------------------------------
+// The greedy choice again, for callers that cannot allocate: the same kernel with its two
+// words per row in a fixed array of this library instead of a buffer the caller brings.
+// See argmax_static.h for who needs this and for the rules of use.
+#include "argmax_static.h"
+#include <mutex>
+#include <stdio.h>
+
+// 2 words x 8 bytes per row. File-scope device memory: zero when the module is loaded.
+static __device__ __align__(256) unsigned long long g_argmax_static_words[2 * CML_ARGMAX_STATIC_MAX_ROWS];
+
+#define CML_MAX_DEVICES 64
+static unsigned long long* g_argmax_static_ptr[CML_MAX_DEVICES];     // device address per GPU, looked up once
+static std::mutex g_argmax_static_mutex;
+
+static void refuse(char* msg, int msg_len, const char* text) {
+    if (msg && msg_len > 0) snprintf(msg, (size_t)msg_len, "%s", text);
+}
+
+extern "C" int cml_argmax_rows_static(const float* logits, int ld, int rows, int vocab, int* out, int* err,
+                                      void* stream, char* msg, int msg_len) {
+    if (msg && msg_len > 0) msg[0] = 0;
+    if (rows <= 0) return 0;
+    if (rows > CML_ARGMAX_STATIC_MAX_ROWS) {
+        if (msg && msg_len > 0)
+            snprintf(msg, (size_t)msg_len, "cml_argmax_rows_static: %d rows exceed the fixed scratch of %d rows; "
+                     "split the call or use cml_argmax_rows with a buffer of your own", rows, CML_ARGMAX_STATIC_MAX_ROWS);
+        return CML_ARGMAX_STATIC_TOO_MANY_ROWS;
+    }
+    if (!logits || !out || !err || vocab <= 0 || ld < vocab) {
+        refuse(msg, msg_len, "cml_argmax_rows_static: null pointer, vocab <= 0 or ld < vocab");
+        return CML_ARGMAX_STATIC_BAD_ARGUMENT;
+    }
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= CML_MAX_DEVICES) {
+        refuse(msg, msg_len, "cml_argmax_rows_static: device index beyond the table of this library");
+        return CML_ARGMAX_STATIC_BAD_ARGUMENT;
+    }
+    unsigned long long* words;
+    {
+        // Set-up, once per GPU and with that GPU current: in host code the array's name is
+        // only a handle, the kernel needs the address the symbol has on this device.
+        std::lock_guard<std::mutex> lock(g_argmax_static_mutex);
+        if (!g_argmax_static_ptr[dev]) {
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_argmax_static_words);
+            if (e != cudaSuccess) {
+                refuse(msg, msg_len, "cml_argmax_rows_static: cudaGetSymbolAddress failed");
+                return (int)e;
+            }
+            g_argmax_static_ptr[dev] = (unsigned long long*)p;
+        }
+        words = g_argmax_static_ptr[dev];
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    // the words of these rows must start at zero, whatever an earlier call left
+    e = cudaMemsetAsync(words, 0, (size_t)rows * 2 * sizeof(unsigned long long), s);
+    if (e != cudaSuccess) return (int)e;
+    const int blocks = max(1, min(64, vocab / 2048));
+    argmax_rows_kernel<<<dim3(blocks, rows), 256, 0, s>>>(logits, ld, vocab, out, err, words);
+    return (int)cudaGetLastError();
+}
