@@ -289,3 +289,74 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
             pts[f"decode_b{b}"] = d["value"]
         rec["points"] = pts
     return rec
+
+
+def ablate_decode(batch: int = 8, prompt_tokens: int = 2048, dtype: str = "bfloat16", layers: int | None = None,
+                  config_index: int = 2, reps: int = 50) -> dict:
+    """Where a decode step's time goes: the captured step graph is timed whole, and again with
+    one kind of kernel switched off at a time (the results are then wrong, only the time is
+    read). The difference is what that kernel costs in place, inside the chain of dependent
+    launches, which no profiler that serialises kernels can show."""
+    from . import api
+    from .csrc import ops
+    from .engine.graphs import DecodeGraph, bucket_width
+    shape = SHAPES[config_index]
+    cfg = config_for(config_index, layers)
+    lm = api.from_random(cfg, seed=shape["seed"], dtype=dtype)
+    rng = np.random.default_rng(0)
+    cache = lm.new_cache(batch * (((prompt_tokens + 256 + 63) // 64) * 64), max_slots=batch)
+    slots, firsts = _prefill_batch(lm, cache, _prompts(rng, batch, prompt_tokens, cfg["vocab_size"]))
+    book = cache.book
+    book.check_extend([(s, 128) for s in slots])
+    starts = np.array([book.extend(s, 128) for s in slots], dtype=np.int32)
+
+    def time_graph():
+        widths = [bucket_width(max(len(book.pages[g][s]) for s in slots)) for g in range(len(book.kv_specs))]
+        g = DecodeGraph(lm.model, cache, batch, widths, feed=True)
+        i = g.fill(slots, starts, firsts)
+        g.send(i, True)
+        g.capture()
+        for _ in range(5):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return {"us_per_step": a.elapsed_time(b) / reps * 1e3, "launches": g.launches}
+
+    def noop(*_a, **_k):
+        return None
+
+    real_gemm = ops.gemm_tc
+
+    def gemm_without(pred):
+        def f(a, b, c, epi, bn, splits, err):
+            return None if pred(a, epi) else real_gemm(a, b, c, epi, bn, splits, err)
+        return f
+
+    hidden, inter = cfg["hidden_size"], cfg["intermediate_size"]
+    qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
+    out = {"full": time_graph()}
+    for name in ("attn_paged_mma", "attn_paged_simt", "rope_kv_from_partials", "rmsnorm", "argmax_rows"):
+        real = getattr(ops, name)
+        setattr(ops, name, noop)
+        out["without " + name] = time_graph()
+        setattr(ops, name, real)
+    for label, pred in (("qkv product", lambda a, e: a.shape[0] == qkv and e == ops.TC_T_PARTIAL),
+                        ("output product", lambda a, e: tuple(a.shape) == (hidden, cfg["num_attention_heads"] * cfg["head_dim"])),
+                        ("gate-up product", lambda a, e: e == ops.TC_T_SWIGLU),
+                        ("down product", lambda a, e: tuple(a.shape) == (hidden, inter)),
+                        ("output head", lambda a, e: a.shape[0] == cfg["vocab_size"]),
+                        ("any product", lambda a, e: True)):
+        ops.gemm_tc = gemm_without(pred)
+        out["without " + label] = time_graph()
+    ops.gemm_tc = real_gemm
+    full = out["full"]["us_per_step"]
+    for k, v in out.items():
+        v["cost_us"] = round(full - v["us_per_step"], 1)
+        v["us_per_step"] = round(v["us_per_step"], 1)
+    return {"batch": batch, "prompt_tokens": prompt_tokens, "dtype": dtype, "model": shape["name"],
+            "layers": cfg["num_hidden_layers"], "steps": out}

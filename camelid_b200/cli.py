@@ -118,6 +118,11 @@ def cmd_random_model(args) -> int:
 
 def cmd_bench(args) -> int:
     from . import benchmark
+    if args.ablate:
+        rec = benchmark.ablate_decode(batch=args.batch, prompt_tokens=args.prompt_tokens, dtype=args.dtype,
+                                      layers=args.layers, config_index=args.config)
+        print(json.dumps(rec, indent=1), flush=True)
+        return 0
     rec = benchmark.run(batch=args.batch, prompt_tokens=args.prompt_tokens, decode_steps=args.decode_steps,
                         warmup=args.warmup, dtype=args.dtype, layers=args.layers, config_index=args.config,
                         points=args.points, e2e=args.e2e, prefill=not args.no_prefill, decode=not args.no_decode,
@@ -151,6 +156,8 @@ def main(argv=None) -> int:
     be.add_argument("--e2e", action="store_true", help="also time the loop through the Python entry point")
     be.add_argument("--no-prefill", action="store_true")
     be.add_argument("--no-decode", action="store_true")
+    be.add_argument("--ablate", action="store_true",
+                    help="time the decode step with one kind of kernel switched off at a time")
     args = ap.parse_args(argv)
     if args.command == "generate":
         return cmd_generate(args)
