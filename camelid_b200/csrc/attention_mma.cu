@@ -375,7 +375,8 @@ attn_prefill_mma_kernel(AttnParams p) {
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     pdl_launch_dependents();
 
-    const int tile = blockIdx.x;
+    // the last tiles of a sequence see the most keys: they are handed out first
+    const int tile = gridDim.x - 1 - blockIdx.x;
     const int seq = p.tile_seq[tile];
     const int q0 = p.tile_q0[tile];
     const int kvh = blockIdx.y / p.head_chunks;

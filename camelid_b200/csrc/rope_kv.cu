@@ -16,63 +16,39 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
                                      int max_blocks, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                      const float* __restrict__ inv_freq, int rotary_dim, int n_heads,
                                      int n_kv_heads, int head_dim, int write_kv) {
-    extern __shared__ float sc[];              // cos[half], sin[half]
     pdl_wait();
     pdl_launch_dependents();
-    const int half = rotary_dim >> 1;
-    float* cs = sc;
-    float* sn = sc + half;
+    // one warp per (row, head): q heads first, then k heads, then v heads
     const int r = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int n_units = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+    if (unit >= n_units) return;
+    const int half = rotary_dim >> 1;
     const int pos = row_pos[r];
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        const float angle = (float)pos * inv_freq[i];
-        float s, c;
-        sincosf(angle, &s, &c);
-        cs[i] = c;
-        sn[i] = s;
+    T* src = qkv + (size_t)r * row_stride + (size_t)unit * head_dim;
+    T* dst = src;                               // q is rotated in place
+    bool rotate = true;
+    if (unit >= n_heads) {
+        const int seq = row_seq[r];
+        const int page = block_table[(size_t)seq * max_blocks + pos / CML_PAGE];
+        const int kv = unit - n_heads;
+        const int h = kv < n_kv_heads ? kv : kv - n_kv_heads;
+        rotate = kv < n_kv_heads;
+        dst = (rotate ? k_pages : v_pages) + (((size_t)page * n_kv_heads + h) * CML_PAGE + pos % CML_PAGE) * head_dim;
     }
-    __syncthreads();
-    T* row = qkv + (size_t)r * row_stride;
-
-    // q: rotate in place
-    const int q_pairs = n_heads * half;
-    for (int w = threadIdx.x; w < q_pairs; w += blockDim.x) {
-        const int h = w / half, i = w - h * half;
-        T* p = row + h * head_dim;
-        const float x0 = to_f32(p[i]), x1 = to_f32(p[i + half]);
-        p[i] = from_f32<T>(x0 * cs[i] - x1 * sn[i]);
-        p[i + half] = from_f32<T>(x0 * sn[i] + x1 * cs[i]);
-    }
-    if (!write_kv) return;
-
-    const int seq = row_seq[r];
-    const int page = block_table[(size_t)seq * max_blocks + pos / CML_PAGE];
-    const int in_page = pos % CML_PAGE;
-    const T* ksrc = row + n_heads * head_dim;
-    const T* vsrc = ksrc + n_kv_heads * head_dim;
-    const size_t page_base = (size_t)page * n_kv_heads * CML_PAGE * head_dim;
-
-    // k: rotate, then store; the pass-through dimensions are copied
-    const int k_pairs = n_kv_heads * half;
-    for (int w = threadIdx.x; w < k_pairs; w += blockDim.x) {
-        const int h = w / half, i = w - h * half;
-        const T* p = ksrc + h * head_dim;
-        T* dst = k_pages + page_base + ((size_t)h * CML_PAGE + in_page) * head_dim;
-        const float x0 = to_f32(p[i]), x1 = to_f32(p[i + half]);
-        dst[i] = from_f32<T>(x0 * cs[i] - x1 * sn[i]);
-        dst[i + half] = from_f32<T>(x0 * sn[i] + x1 * cs[i]);
-    }
-    const int tail = head_dim - rotary_dim;
-    if (tail > 0) {
-        for (int w = threadIdx.x; w < n_kv_heads * tail; w += blockDim.x) {
-            const int h = w / tail, i = rotary_dim + (w - h * tail);
-            k_pages[page_base + ((size_t)h * CML_PAGE + in_page) * head_dim + i] = ksrc[h * head_dim + i];
+    if (rotate) {
+        for (int i = lane; i < half; i += 32) {
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            const float x0 = to_f32(src[i]), x1 = to_f32(src[i + half]);
+            dst[i] = from_f32<T>(x0 * cs - x1 * sn);
+            dst[i + half] = from_f32<T>(x0 * sn + x1 * cs);
         }
-    }
-    // v: copy
-    for (int w = threadIdx.x; w < n_kv_heads * head_dim; w += blockDim.x) {
-        const int h = w / head_dim, i = w - h * head_dim;
-        v_pages[page_base + ((size_t)h * CML_PAGE + in_page) * head_dim + i] = vsrc[w];
+        if (dst != src)
+            for (int d = rotary_dim + lane; d < head_dim; d += 32) dst[d] = src[d];
+    } else {
+        for (int d = lane; d < head_dim; d += 32) dst[d] = src[d];
     }
 }
 
@@ -167,15 +143,16 @@ extern "C" int cml_rope_kv_write(void* qkv, int dtype, int rows, int row_stride,
     if (rows <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem = (size_t)rotary_dim * sizeof(float);
-    if (smem > 48 * 1024) return CML_ERR_BAD_SIZE;
-    const int block = 256;
+    const int n_units = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+    const dim3 grid(rows, (n_units + 7) / 8), block(256);
+    if (grid.y > 65535) return CML_ERR_BAD_SIZE;
+    const size_t smem = 0;
     if (dtype == CML_DTYPE_F32)
-        launch_pdl(rope_kv_write_kernel<float>, dim3(rows), dim3(block), smem, s, (float*)qkv, row_stride, row_pos, row_seq, block_table,
+        launch_pdl(rope_kv_write_kernel<float>, grid, block, smem, s, (float*)qkv, row_stride, row_pos, row_seq, block_table,
                                                               max_blocks, (float*)k_pages, (float*)v_pages, inv_freq,
                                                               rotary_dim, n_heads, n_kv_heads, head_dim, write_kv);
     else if (dtype == CML_DTYPE_BF16)
-        launch_pdl(rope_kv_write_kernel<bf16>, dim3(rows), dim3(block), smem, s, (bf16*)qkv, row_stride, row_pos, row_seq, block_table,
+        launch_pdl(rope_kv_write_kernel<bf16>, grid, block, smem, s, (bf16*)qkv, row_stride, row_pos, row_seq, block_table,
                                                              max_blocks, (bf16*)k_pages, (bf16*)v_pages, inv_freq,
                                                              rotary_dim, n_heads, n_kv_heads, head_dim, write_kv);
     else

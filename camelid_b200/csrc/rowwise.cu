@@ -86,11 +86,76 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TW* __restrict__ w, 
     }
 }
 
+// Many rows (prefill): one warp per row, the row held in registers, so the row is read once
+// and nothing waits on a block-wide barrier. VPL float4 per lane cover hidden = 128 * VPL.
+template <typename TW, typename TO, int VPL>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
+                    const int* __restrict__ rows_index, int rows, int hidden, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const int src = rows_index ? rows_index[r] : r;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * hidden);
+    float4 v[VPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int c = lane + 32 * i;                         // float4 index
+        v[i] = (c * 4 < hidden) ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        ss = fmaf(v[i].x, v[i].x, ss);
+        ss = fmaf(v[i].y, v[i].y, ss);
+        ss = fmaf(v[i].z, v[i].z, ss);
+        ss = fmaf(v[i].w, v[i].w, ss);
+    }
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+    TO* o = out + (size_t)r * hidden;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int c = (lane + 32 * i) * 4;
+        if (c >= hidden) continue;
+        o[c] = from_f32<TO>(v[i].x * scale * to_f32(w[c]));
+        o[c + 1] = from_f32<TO>(v[i].y * scale * to_f32(w[c + 1]));
+        o[c + 2] = from_f32<TO>(v[i].z * scale * to_f32(w[c + 2]));
+        o[c + 3] = from_f32<TO>(v[i].w * scale * to_f32(w[c + 3]));
+    }
+}
+
+template <typename TW, typename TO>
+static bool launch_rmsnorm_rows(const float* x, const void* w, void* out, const int* rows_index, int rows, int hidden,
+                                float eps, cudaStream_t s) {
+    if (hidden % 4 != 0 || hidden > 4096 || rows < 64) return false;
+    const dim3 grid((rows + 7) / 8), block(256);
+    const int vpl = (hidden / 4 + 31) / 32;
+#define CML_ROWS(V) launch_pdl(rmsnorm_rows_kernel<TW, TO, V>, grid, block, 0, s, x, (const TW*)w, (TO*)out, rows_index, rows, hidden, eps)
+    if (vpl <= 4) CML_ROWS(4);
+    else if (vpl <= 8) CML_ROWS(8);
+    else if (vpl <= 16) CML_ROWS(16);
+    else if (vpl <= 32) CML_ROWS(32);
+    else return false;
+#undef CML_ROWS
+    return true;
+}
+
 extern "C" int cml_rmsnorm(float* x, const void* w, int w_dtype, void* out, int out_dtype,
                            const int* rows_index, int rows, int hidden, float eps, const float* partial,
                            int n_splits, long split_stride, void* stream) {
     if (rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
+    if (!partial) {
+        bool done = false;
+        if (w_dtype == CML_DTYPE_F32 && out_dtype == CML_DTYPE_F32) done = launch_rmsnorm_rows<float, float>(x, w, out, rows_index, rows, hidden, eps, s);
+        else if (w_dtype == CML_DTYPE_F32 && out_dtype == CML_DTYPE_BF16) done = launch_rmsnorm_rows<float, bf16>(x, w, out, rows_index, rows, hidden, eps, s);
+        else if (w_dtype == CML_DTYPE_BF16 && out_dtype == CML_DTYPE_F32) done = launch_rmsnorm_rows<bf16, float>(x, w, out, rows_index, rows, hidden, eps, s);
+        else if (w_dtype == CML_DTYPE_BF16 && out_dtype == CML_DTYPE_BF16) done = launch_rmsnorm_rows<bf16, bf16>(x, w, out, rows_index, rows, hidden, eps, s);
+        if (done) return cml_launch_status();
+    }
     // few rows (decode): many threads per row shorten the chain; many rows: several blocks per SM
     const int block = hidden >= 1024 ? (rows <= 256 ? 1024 : 256) : (hidden >= 512 ? 256 : 128);
     const size_t smem = partial ? (size_t)hidden * sizeof(float) : 0;

@@ -46,6 +46,15 @@ def _bn_decode(rows: int) -> int:
     return 16 if rows <= 16 else (32 if rows <= 32 else 64)
 
 
+def _bn_prefill(rows: int, out_features: int) -> int:
+    """Tile width over the weight rows for a persistent launch: the one that needs fewer
+    rounds of SM_COUNT blocks times its width (wider tiles reuse operands better on a tie)."""
+    def cost(bn):
+        tiles = ((rows + 127) // 128) * ((out_features + bn - 1) // bn)
+        return ((tiles + SM_COUNT - 1) // SM_COUNT) * bn
+    return 256 if cost(256) <= cost(128) else 128
+
+
 def _splits(out_features: int, k: int) -> int:
     tiles = (out_features + 127) // 128
     return max(1, min((k + 63) // 64, round(SM_COUNT / tiles))) if tiles < SM_COUNT else 1
@@ -66,7 +75,7 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
                 ops.gemm_tc(w, x, out.unsqueeze(0), ops.TC_T_PARTIAL, bn, 1, err)
                 return
         else:
-            bn = 256 if w.shape[0] >= 1024 else 128
+            bn = _bn_prefill(rows, w.shape[0])
             if epilogue == SWIGLU:
                 if group == 16 and w.shape[0] % 32 == 0:
                     ops.gemm_tc(x, w, out, ops.TC_SWIGLU, bn, 1, err)
