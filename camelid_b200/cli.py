@@ -79,24 +79,22 @@ def cmd_generate(args, always_json=False) -> int:
     for _ in range(args.iterations):
         torch.cuda.reset_peak_memory_stats()
         torch.cuda.synchronize()
+        stamps = []
         t1 = time.perf_counter()
-        first = lm.generate(prompts, max_tokens=min(1, args.max_tokens), **opts)          # prefill + first token
+        out = lm.generate(prompts, max_tokens=args.max_tokens, on_step=lambda _live: stamps.append(time.perf_counter()),
+                          **opts)
         torch.cuda.synchronize()
-        ttft_ms = (time.perf_counter() - t1) * 1e3
-        t2 = time.perf_counter()
-        out = lm.generate(prompts, max_tokens=args.max_tokens, **opts)
-        torch.cuda.synchronize()
-        total_ms = (time.perf_counter() - t2) * 1e3
+        # the first stamp is taken when the prompts have run and the first tokens are on the host
+        ttft_ms = (stamps[0] - t1) * 1e3 if stamps else 0.0
+        decode_ms = (stamps[-1] - stamps[0]) * 1e3 if len(stamps) > 1 else 0.0
         generated = sum(len(o) for o in out)
-        decode_ms = max(total_ms - ttft_ms, 0.0)
         rec = {
             "prompt_tokens": sum(len(p) for p in prompts), "generated_tokens": generated,
             "load_ms": load_ms, "prefill_ms": ttft_ms, "ttft_ms": ttft_ms, "decode_ms": decode_ms,
-            "tokens_per_second": (generated - len(out)) / (decode_ms / 1e3) if decode_ms > 0 and generated > len(out) else 0.0,
+            "tokens_per_second": (generated - len(out)) / (decode_ms / 1e3) if decode_ms > 0 else 0.0,
             "peak_memory_bytes": torch.cuda.max_memory_allocated(),
             "output_token_ids": out[0] if len(out) == 1 else out, "dtype": dtype,
         }
-        del first
         if args.json or always_json:
             print(json.dumps(rec), flush=True)
         else:

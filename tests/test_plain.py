@@ -160,3 +160,22 @@ def test_generate_stops_and_keeps_the_stop_token(model_folders):
     assert len(free) == 6
     stopped = pl.generate(cfg, w, [[5, 6, 7]], 6, stop_ids=(free[2],))[0]
     assert stopped == free[:free.index(free[2]) + 1]
+
+
+def test_pinned_logits_of_the_micro_model():
+    """tests/golden/plain_micro.json was written by tests/golden/make_golden.py from weights of
+    a generator written out there; the plain implementation must still give those logits."""
+    import importlib.util
+    import json
+    import os
+    here = os.path.dirname(os.path.abspath(__file__))
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(here, "golden", "make_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    with open(os.path.join(here, "golden", "plain_micro.json")) as f:
+        want = json.load(f)
+    got = mod.compute()
+    assert got["argmax_per_position"] == want["argmax_per_position"]
+    assert np.allclose(got["logits_last"], want["logits_last"], atol=1e-9)
+    assert np.allclose(got["logits_first"], want["logits_first"], atol=1e-9)
+    assert abs(got["sum_abs"] - want["sum_abs"]) < 1e-6
