@@ -28,6 +28,7 @@ MODULES = {
     "rope_kv": ["rope_kv.cu"],
     "attention_simt": ["attention_simt.cu"],
     "attention_mma": ["attention_mma.cu"],
+    "attention_tc": ["attention_tc.cu"],
     "gemm_simt": ["gemm_simt.cu"],
     "sampling": ["sampling.cu"],
     "gemm_tc": ["gemm_tc.cu"],

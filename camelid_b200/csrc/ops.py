@@ -40,6 +40,9 @@ _SIGNATURES = {
                                               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                               c_void_p, c_void_p],
+    ("attention_tc", "cml_attn_prefill_tc"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p,
+                                              c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     ("gemm_simt", "cml_gemm_tn_simt"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_void_p],
     ("sampling", "cml_argmax_rows"): [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -276,6 +279,33 @@ def attn_paged_mma(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_t
         _p(tile_seq), _p(tile_q0), n_tiles, _p(seq_row0), _p(seq_start), _p(seq_new), n_rows, n_heads, n_kv_heads,
         head_dim, rows_per_tile, heads_per_cta, head_chunks, n_splits, int(window or 0), float(scale), _p(partial),
         _p(tickets), _stream()), "attn_paged_mma")
+
+
+def attn_tc_tiling(n_heads: int, n_kv_heads: int) -> tuple[int, int, int]:
+    """(rows_per_tile, heads_per_cta, head_chunks) of the tcgen05 prefill attention kernel: the
+    128 lanes of tensor memory hold the grouped heads of one kv head times consecutive tokens."""
+    group = n_heads // n_kv_heads
+    chunks = (group + 15) // 16
+    hpc = (group + chunks - 1) // chunks
+    return max(1, 128 // hpc), hpc, chunks
+
+
+def attn_tc_usable(q: torch.Tensor, out: torch.Tensor, head_dim: int) -> bool:
+    return (q.dtype == torch.bfloat16 and head_dim in (64, 128) and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
+            and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
+
+
+def attn_prefill_tc(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_tiles, seq_row0, seq_start, seq_new,
+                    n_heads, n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, window, scale, err):
+    """bfloat16 prefill attention of packed query rows over the paged cache with tcgen05.mma."""
+    _dev(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, seq_row0, seq_start, seq_new, err)
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == torch.bfloat16
+    assert k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim) and k_pages.is_contiguous() and v_pages.is_contiguous()
+    _check(_fn("attention_tc", "cml_attn_prefill_tc")(
+        _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), k_pages.shape[0], _p(block_table),
+        block_table.shape[1], _p(tile_seq), _p(tile_q0), n_tiles, _p(seq_row0), _p(seq_start), _p(seq_new), n_heads,
+        n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, int(window or 0), float(scale), _p(err),
+        _stream()), "attn_prefill_tc")
 
 
 def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, group: int = 0):

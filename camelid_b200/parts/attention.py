@@ -13,6 +13,7 @@ nothing. ``window`` (None for Llama) limits every query to the last ``window`` k
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -46,6 +47,9 @@ class GroupedQueryAttention(Part):
         self.scale = 1.0 / math.sqrt(self.head_dim)
         self.w_qkv = None
         self.w_o = None
+        # prefill steps of bfloat16 models with head size 64 or 128 use the tcgen05 kernel;
+        # CAMELID_PREFILL_ATTENTION=mma keeps the mma.sync kernel (for comparisons)
+        self.prefill_tcgen05 = os.environ.get("CAMELID_PREFILL_ATTENTION", "tcgen05") != "mma"
 
     def tensor_specs(self):
         p = self.prefix
@@ -68,7 +72,8 @@ class GroupedQueryAttention(Part):
 
     def query_tile_sizes(self):
         return [ops.attn_tiling(self.num_heads, self.num_kv_heads, False)[0],
-                ops.attn_mma_tiling(self.num_heads, self.num_kv_heads, False)[0]]
+                ops.attn_mma_tiling(self.num_heads, self.num_kv_heads, False)[0],
+                ops.attn_tc_tiling(self.num_heads, self.num_kv_heads)[0]]
 
     # ------------------------------------------------------------------------------
     def forward(self, ctx, x, residual):
@@ -91,7 +96,13 @@ class GroupedQueryAttention(Part):
                               self.num_heads, self.num_kv_heads, self.head_dim, write_kv=not borrow)
             q = qkv[:, :self.q_width]
         out = ctx.buffer("attn_out", (n, self.q_width))
-        if ops.attn_mma_usable(q, self.head_dim):
+        if not ctx.decode and self.prefill_tcgen05 and ops.attn_tc_usable(q, out, self.head_dim):
+            rows, hpc, chunks = ops.attn_tc_tiling(self.num_heads, self.num_kv_heads)
+            tile_seq, tile_q0, n_tiles = ctx.query_tiles(rows)
+            ops.attn_prefill_tc(q, out, k_pages, v_pages, table, tile_seq, tile_q0, n_tiles, ctx.seq_row0,
+                                ctx.seq_start, ctx.seq_new, self.num_heads, self.num_kv_heads, self.head_dim, rows,
+                                hpc, chunks, self.window or 0, self.scale, linear._err_word(q.device))
+        elif ops.attn_mma_usable(q, self.head_dim):
             self._attend(ctx, q, out, k_pages, v_pages, table, tensor_cores=True)
         else:
             self._attend(ctx, q, out, k_pages, v_pages, table, tensor_cores=False)

@@ -299,3 +299,57 @@ def test_attention_mma_window_edges(cuda, window):
                    spike=(1, max(0, 199 - window)))
     _attn_mma_case(cuda, 4, 2, 64, starts=[199, 80], news=[1, 1], window=window, decode=True, n_splits=3,
                    spike=(0, max(0, 199 - window)))
+
+
+# ---- the tcgen05 prefill attention kernel ----
+
+def _attn_tc_case(cuda, n_heads, n_kv, hd, starts, news, window, spike=None):
+    from camelid_b200.csrc import ops
+    dt = torch.bfloat16
+    totals = [s + n for s, n in zip(starts, news)]
+    k_pages, v_pages, table, ks, vs = _paged(totals, n_kv, hd, dt, cuda)
+    g = torch.Generator().manual_seed(1)
+    n_rows = sum(news)
+    q = torch.randn(n_rows, n_heads, hd, generator=g).to(dt)
+    row0 = [sum(news[:i]) for i in range(len(news))]
+    if spike is not None:
+        seq, key = spike
+        r = row0[seq] + news[seq] - 1
+        ks[seq][key] *= 0
+        ks[seq][key, :, 0] = 8.0
+        q[r, :, 0] = 8.0 * math.sqrt(hd) / 4
+        k_pages[int(table[seq, key // 64]), :, key % 64] = ks[seq][key].to(cuda)
+    rows, hpc, chunks = ops.attn_tc_tiling(n_heads, n_kv)
+    tile_seq, tile_q0 = [], []
+    for i, n in enumerate(news):
+        for q0 in range(0, n, rows):
+            tile_seq.append(i)
+            tile_q0.append(q0)
+    out = torch.full((n_rows, n_heads * hd), float("nan"), dtype=dt, device=cuda)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    ops.attn_prefill_tc(q.view(n_rows, -1).to(cuda), out, k_pages, v_pages, table, _i32(tile_seq, cuda),
+                        _i32(tile_q0, cuda), len(tile_seq), _i32(row0, cuda), _i32(starts, cuda), _i32(news, cuda),
+                        n_heads, n_kv, hd, rows, hpc, chunks, window or 0, 1 / math.sqrt(hd), err)
+    assert int(err) == 0
+    out = out.cpu().view(n_rows, n_heads, hd)
+    for i, (s, n) in enumerate(zip(starts, news)):
+        qfull = torch.zeros(s + n, n_heads, hd, dtype=torch.float64)
+        qfull[s:] = q[row0[i]:row0[i] + n].double()
+        ref = pl.attention(qfull, ks[i].double(), vs[i].double(), window)[s:]
+        e = rel_err(out[row0[i]:row0[i] + n], ref)
+        assert e <= 2 ** -6, f"sequence {i}: {e}"
+
+
+@pytest.mark.parametrize("n_heads,n_kv,hd", [(4, 1, 64), (32, 8, 64), (6, 2, 128), (5, 5, 64), (34, 1, 128), (12, 2, 64)])
+def test_attention_tc_prefill_shapes(cuda, n_heads, n_kv, hd):
+    _attn_tc_case(cuda, n_heads, n_kv, hd, starts=[0, 0, 0, 64], news=[1, 70, 300, 33], spike=(2, 3), window=None)
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+def test_attention_tc_continues_from_cache(cuda, hd):
+    _attn_tc_case(cuda, 8, 2, hd, starts=[64, 300, 5, 0], news=[3, 200, 64, 129], spike=(1, 7), window=None)
+
+
+@pytest.mark.parametrize("window", [1, 32, 70, 200])
+def test_attention_tc_window_edges(cuda, window):
+    _attn_tc_case(cuda, 4, 2, 64, starts=[0, 190], news=[150, 10], window=window, spike=(1, max(0, 199 - window)))
