@@ -5,8 +5,8 @@
 // Per page of 64 keys: S = Q K^T by tcgen05.mma into tensor memory; the 128 softmax threads
 // each read their own row of S (no shuffles: a thread owns a row), keep the running maximum
 // and sum in float, write the probabilities as bfloat16 into a swizzled shared-memory tile;
-// P V by tcgen05.mma into a second tensor-memory buffer, which the same threads add to their
-// float output row. Keys and values come straight from the cache pages by TMA (128-byte
+// P V by tcgen05.mma accumulates the output rows in a second tensor-memory buffer, which the
+// same threads rescale in place on the rare pages where a row's reference maximum moves. Keys and values come straight from the cache pages by TMA (128-byte
 // swizzle, no multicast); V is used as an MN-major operand, so no transpose is stored.
 // MMA of the next page's S overlaps the softmax of this page; several blocks per SM overlap
 // the rest.
@@ -105,6 +105,18 @@ __device__ __forceinline__ void at_ld32_nowait(uint32_t taddr, float* r) {
           "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
         : "r"(taddr));
 }
+__device__ __forceinline__ void at_st32(uint32_t taddr, const float* r) {
+    const uint32_t* u = reinterpret_cast<const uint32_t*>(r);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]), "r"(u[8]),
+          "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]), "r"(u[16]), "r"(u[17]),
+          "r"(u[18]), "r"(u[19]), "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]), "r"(u[24]), "r"(u[25]), "r"(u[26]),
+          "r"(u[27]), "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31])
+        : "memory");
+}
+__device__ __forceinline__ void at_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void at_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float at_exp2(float x) {
     float y;
@@ -140,7 +152,7 @@ __device__ __forceinline__ uint32_t at_swizzled(int row, int chunk) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(AT_THREADS, HD == 64 ? 2 : 1)
+__global__ void __launch_bounds__(AT_THREADS, HD == 64 ? 3 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, AtParams ap) {
     const AttnParams& p = ap.a;
     constexpr int KB = HD / 64;                               // 64-column blocks of a head
@@ -274,7 +286,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                 const uint64_t vd = at_desc_mnmajor(sV + s * V_BYTES, KV_BLOCK);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)        // 16 keys per MMA: 32 bytes along P's rows, 2 key groups of V
-                    at_mma(tmem_pv, pd + (uint64_t)(k * 2), vd + (uint64_t)(k * 128), idesc_pv, k ? 1u : 0u);
+                    at_mma(tmem_pv, pd + (uint64_t)(k * 2), vd + (uint64_t)(k * 128), idesc_pv, (it | k) ? 1u : 0u);
                 at_commit(pv_full);
                 at_commit(kv_empty(s));
             }
@@ -305,10 +317,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
         const int blk_lo = p.window > 0 ? max(0, start + q0 + rows_in_tile - 1 - p.window + 1) : 0;
         const float sl2 = p.scale * 1.4426950408889634f;       // scores are kept raw; exp2((s - m) * scale * log2 e)
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        // m is the reference the exponentials are taken against. It follows the running maximum
+        // lazily: it moves only when the maximum has grown by more than 8 powers of two, so the
+        // output rows in tensor memory rarely need rescaling (the result is the same: numerator
+        // and denominator share the reference).
         float m = -CUDART_INF_F, l = 0.f;
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.f;
         bool ok = true;
         for (int it = 0; it < n_tiles_k && ok; ++it) {
             const int t = t_first + it;
@@ -336,10 +349,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                     mx = fmaxf(mx, s[c]);
                 }
             }
-            const float mn = fmaxf(m, mx);
-            const float m_use = (mn == -CUDART_INF_F) ? 0.f : mn;
-            const float corr = (m == -CUDART_INF_F) ? 0.f : at_exp2((m - m_use) * sl2);
-            m = mn;
+            float corr = 1.0f;
+            if (mx > m && (m == -CUDART_INF_F || (mx - m) * sl2 > 8.0f)) {
+                corr = (m == -CUDART_INF_F) ? 0.f : at_exp2((m - mx) * sl2);
+                m = mx;
+            }
+            const float m_use = (m == -CUDART_INF_F) ? 0.f : m;
             uint32_t pk[AT_KEYS / 2];
             float sum = 0.f;
             const float neg = -m_use * sl2;
@@ -351,25 +366,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                 pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
             }
             if (it > 0) {
-                // P V of the page before: wait for it, add it, then bring the row to the new maximum
+                // The product of the page before is complete: its P tile is free, and the output
+                // rows in tensor memory can be rescaled if a row of this warp moved its reference.
                 ok = at_mbar_wait(pv_full, (uint32_t)(it - 1) & 1u, abort_flag);
                 if (!ok) break;
                 at_fence_after();
-                // when no row of the warp has a new maximum the rescaling is a multiplication by one
-                const bool rescale = __any_sync(0xffffffffu, corr != 1.0f);
+                if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll
-                for (int c = 0; c < HD; c += 64) {
-                    float pv[64];
-                    at_ld32_nowait(tmem_pv + lane_base + c, pv);
-                    at_ld32_nowait(tmem_pv + lane_base + c + 32, pv + 32);
-                    at_ld_wait();
-                    if (rescale) {
+                    for (int c = 0; c < HD; c += 32) {
+                        float ov[32];
+                        at_ld32_nowait(tmem_pv + lane_base + c, ov);
+                        at_ld_wait();
 #pragma unroll
-                        for (int d = 0; d < 64; ++d) o[c + d] = (o[c + d] + pv[d]) * corr;
-                    } else {
-#pragma unroll
-                        for (int d = 0; d < 64; ++d) o[c + d] += pv[d];
+                        for (int d = 0; d < 32; ++d) ov[d] *= corr;
+                        at_st32(tmem_pv + lane_base + c, ov);
                     }
+                    at_st_wait();
                 }
             }
             l = l * corr + sum;
@@ -401,18 +413,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                 const float inv = valid ? 1.0f / l : 0.f;
                 bf16* dst = (bf16*)p.out + row * p.out_stride + (size_t)head * HD;
 #pragma unroll
-                for (int c = 0; c < HD; c += 16) {
-                    float pv[16];
-                    at_ld16(tmem_pv + lane_base + c, pv);
-                    uint32_t w[8];
+                for (int c = 0; c < HD; c += 32) {
+                    float ov[32];
+                    at_ld32_nowait(tmem_pv + lane_base + c, ov);
+                    at_ld_wait();
+                    uint32_t w[16];
 #pragma unroll
-                    for (int d = 0; d < 8; ++d) {
-                        __nv_bfloat162 h = __floats2bfloat162_rn((o[c + 2 * d] + pv[2 * d]) * inv, (o[c + 2 * d + 1] + pv[2 * d + 1]) * inv);
+                    for (int d = 0; d < 16; ++d) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(ov[2 * d] * inv, ov[2 * d + 1] * inv);
                         w[d] = *reinterpret_cast<uint32_t*>(&h);
                     }
                     if (valid) {
-                        reinterpret_cast<uint4*>(dst + c)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                        reinterpret_cast<uint4*>(dst + c)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            reinterpret_cast<uint4*>(dst + c)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
                     }
                 }
             }
