@@ -54,6 +54,11 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TW* __restrict__ w, 
                                const float* __restrict__ partial, int n_splits, size_t split_stride) {
     __shared__ float red[33];
     extern __shared__ float rowbuf[];
+    // the norm's weight does not depend on the kernels before: its first columns are fetched
+    // ahead of the wait (each thread's first two columns cover hidden <= 2 * blockDim)
+    const int c0 = threadIdx.x, c1 = threadIdx.x + blockDim.x;
+    const float w0 = c0 < hidden ? to_f32(w[c0]) : 0.f;
+    const float w1 = c1 < hidden ? to_f32(w[c1]) : 0.f;
     pdl_wait();
     pdl_launch_dependents();
     const int r = blockIdx.x;
@@ -65,12 +70,12 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TW* __restrict__ w, 
         if (partial) {
             const float* pp = partial + (size_t)src * hidden + c;
             // all loads of a group are issued before the first add, the adds stay in split order
-            for (int s0 = 0; s0 < n_splits; s0 += 8) {
-                float t[8];
+            for (int s0 = 0; s0 < n_splits; s0 += 16) {
+                float t[16];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) t[i] = (s0 + i < n_splits) ? pp[(size_t)(s0 + i) * split_stride] : 0.f;
+                for (int i = 0; i < 16; ++i) t[i] = (s0 + i < n_splits) ? pp[(size_t)(s0 + i) * split_stride] : 0.f;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v += t[i];
+                for (int i = 0; i < 16; ++i) v += t[i];
             }
             rowbuf[c] = v;
             if (!rows_index) xr[c] = v;
@@ -82,7 +87,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TW* __restrict__ w, 
     TO* o = out + (size_t)r * hidden;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         const float v = partial ? rowbuf[c] : xr[c];
-        o[c] = from_f32<TO>(v * scale * to_f32(w[c]));
+        const float wc = c == c0 ? w0 : (c == c1 ? w1 : to_f32(w[c]));
+        o[c] = from_f32<TO>(v * scale * wc);
     }
 }
 
