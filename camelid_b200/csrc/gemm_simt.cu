@@ -98,6 +98,94 @@ gemm_tn_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, i
     }
 }
 
+// Few rows (decode) in float: every output column is one warp's dot products, the weight row
+// read once with 16-byte loads and used for all MB activation rows, which stay in cache.
+// Each lane sums its k's in ascending order, then the lanes are summed in a fixed tree: the
+// value of a row does not depend on the other rows of the step.
+template <int MB, int EPI>
+__global__ void __launch_bounds__(256)
+gemv_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw, float* __restrict__ C,
+                int ldc, int M, int N, int K, int group) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int m0 = blockIdx.y * MB;
+    if (n >= N) return;
+    long wrow = n, urow = 0;
+    if (EPI == EPI_SWIGLU) {
+        wrow = (long)(n / group) * 2 * group + n % group;
+        urow = wrow + group;
+    }
+    const float* wr = W + (size_t)wrow * ldw;
+    const float* ur = W + (size_t)urow * ldw;
+    float acc[MB], acc2[MB];
+#pragma unroll
+    for (int m = 0; m < MB; ++m) acc[m] = 0.f, acc2[m] = 0.f;
+    const bool vec = ((K & 3) == 0) && ((lda & 3) == 0) && ((ldw & 3) == 0) && (((uintptr_t)A & 15) == 0) &&
+                     (((uintptr_t)W & 15) == 0);
+    if (vec) {
+        for (int k = lane * 4; k < K; k += 128) {
+            const float4 w4 = *reinterpret_cast<const float4*>(wr + k);
+            float4 u4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (EPI == EPI_SWIGLU) u4 = *reinterpret_cast<const float4*>(ur + k);
+#pragma unroll
+            for (int m = 0; m < MB; ++m) {
+                if (m0 + m >= M) break;
+                const float4 a4 = *reinterpret_cast<const float4*>(A + (size_t)(m0 + m) * lda + k);
+                acc[m] = fmaf(a4.x, w4.x, acc[m]); acc[m] = fmaf(a4.y, w4.y, acc[m]);
+                acc[m] = fmaf(a4.z, w4.z, acc[m]); acc[m] = fmaf(a4.w, w4.w, acc[m]);
+                if (EPI == EPI_SWIGLU) {
+                    acc2[m] = fmaf(a4.x, u4.x, acc2[m]); acc2[m] = fmaf(a4.y, u4.y, acc2[m]);
+                    acc2[m] = fmaf(a4.z, u4.z, acc2[m]); acc2[m] = fmaf(a4.w, u4.w, acc2[m]);
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) {
+            const float wv = wr[k];
+            const float uv = EPI == EPI_SWIGLU ? ur[k] : 0.f;
+#pragma unroll
+            for (int m = 0; m < MB; ++m) {
+                if (m0 + m >= M) break;
+                const float av = A[(size_t)(m0 + m) * lda + k];
+                acc[m] = fmaf(av, wv, acc[m]);
+                if (EPI == EPI_SWIGLU) acc2[m] = fmaf(av, uv, acc2[m]);
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+        const float v = warp_sum(acc[m]);
+        const float v2 = EPI == EPI_SWIGLU ? warp_sum(acc2[m]) : 0.f;
+        if (lane == 0 && m0 + m < M) {
+            float* o = C + (size_t)(m0 + m) * ldc + n;
+            if (EPI == EPI_ADD_F32) *o += v;
+            else if (EPI == EPI_SWIGLU) *o = (v / (1.0f + expf(-v))) * v2;
+            else *o = v;
+        }
+    }
+}
+
+static int launch_gemv_f32(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
+                           int epilogue, int group, cudaStream_t s) {
+    constexpr int MB = 8;
+    dim3 grid((N + 7) / 8, (M + MB - 1) / MB);
+#define CML_GEMV(E) launch_pdl(gemv_f32_kernel<MB, E>, grid, dim3(256), 0, s, (const float*)A, lda, (const float*)W, ldw, (float*)C, ldc, M, N, K, group)
+    switch (epilogue) {
+        case EPI_STORE:
+        case EPI_STORE_F32: CML_GEMV(EPI_STORE_F32); break;
+        case EPI_ADD_F32: CML_GEMV(EPI_ADD_F32); break;
+        case EPI_SWIGLU:
+            if (group <= 0 || N % group != 0) return CML_ERR_BAD_SIZE;
+            CML_GEMV(EPI_SWIGLU);
+            break;
+        default: return CML_ERR_BAD_SIZE;
+    }
+#undef CML_GEMV
+    return cml_launch_status();
+}
+
 template <typename T>
 static int launch_gemm(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
                        int epilogue, int group, cudaStream_t s) {
@@ -124,6 +212,7 @@ extern "C" int cml_gemm_tn_simt(const void* A, int lda, const void* W, int ldw, 
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CML_DTYPE_F32 && M <= 32) return launch_gemv_f32(A, lda, W, ldw, C, ldc, M, N, K, epilogue, group, s);
     if (dtype == CML_DTYPE_F32) return launch_gemm<float>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, group, s);
     if (dtype == CML_DTYPE_BF16) return launch_gemm<bf16>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, group, s);
     return CML_ERR_BAD_DTYPE;
