@@ -30,7 +30,7 @@ MODULES = {
     "attention_mma": ["attention_mma.cu"],
     "attention_tc": ["attention_tc.cu"],
     "gemm_simt": ["gemm_simt.cu"],
-    "sampling": ["sampling.cu"],
+    "sampling": ["sampling.cu", "decode_loop.cu"],
     "gemm_tc": ["gemm_tc.cu"],
 }
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",

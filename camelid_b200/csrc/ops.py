@@ -48,6 +48,11 @@ _SIGNATURES = {
     ("sampling", "cml_argmax_rows"): [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     ("sampling", "cml_adjust_logits"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_float,
                                         c_void_p],
+    ("sampling", "cml_decode_loop_size"): [],
+    ("sampling", "cml_decode_loop_init"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                          c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    ("sampling", "cml_decode_loop_run"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                         c_int, c_float, c_int, c_float, c_float, ctypes.c_ulonglong, c_void_p, c_void_p],
     ("sampling", "cml_sample_rows"): [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_void_p,
                                       c_void_p, c_void_p, c_void_p],
 }
@@ -373,3 +378,49 @@ def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: flo
     _check(_fn("sampling", "cml_sample_rows")(_p(logits), logits.stride(0), rows, vocab, float(temperature),
                                              int(top_k or 0), float(top_p if top_p is not None else 1.0),
                                              float(min_p or 0.0), _p(draws), _p(out), _p(err), _stream()), "sample_rows")
+
+
+class NativeDecodeLoop:
+    """The C++ decode loop (decode_loop.cu) bound to one captured step graph: ``run`` performs up
+    to ``max_steps`` one-token steps (copy in, graph, sampling kernel, copy out) per call."""
+
+    def __init__(self, n: int, layout, meta_dev: torch.Tensor, head_template, logits: torch.Tensor, err: torch.Tensor):
+        import numpy as np
+        dev = meta_dev.device
+        size = _fn("sampling", "cml_decode_loop_size")()
+        self._state = ctypes.create_string_buffer(size)
+        self.n = n
+        self.head_ints = layout.offsets["seq_start"][0] + n
+        self.meta_host = torch.zeros(self.head_ints, dtype=torch.int32).pin_memory()
+        self.meta_host.numpy()[:] = head_template[:self.head_ints]
+        self.tokens_dev = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.tokens_host = torch.zeros(n, dtype=torch.int32).pin_memory()
+        self.draws_dev = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.draws_host = torch.zeros(n, dtype=torch.float32).pin_memory()
+        self.scratch = zeroed_scratch(dev, "argmax", 16 * max(n, 64))
+        self.logits, self.err, self.meta_dev = logits, err, meta_dev
+        self._np = np
+        _check(_fn("sampling", "cml_decode_loop_init")(
+            ctypes.addressof(self._state), n, layout.offsets["tokens"][0], layout.offsets["row_pos"][0],
+            layout.offsets["seq_start"][0], self.head_ints, _p(meta_dev), _p(self.meta_host), _p(logits),
+            logits.stride(0), logits.shape[1], _p(self.tokens_dev), _p(self.tokens_host), _p(err), _p(self.scratch),
+            _p(self.draws_dev), _p(self.draws_host)), "decode_loop_init", 0)
+        self.h2d_bytes_per_step = self.head_ints * 4
+        self.d2h_bytes_per_step = n * 4
+
+    def run(self, graph_exec: int, tokens, positions, history_lens, max_steps: int, stop_ids, temperature: float,
+            top_k: int, top_p: float, min_p: float, seed: int, launches_per_step: int):
+        np = self._np
+        tok = np.ascontiguousarray(tokens, dtype=np.int32)
+        pos = np.ascontiguousarray(positions, dtype=np.int32)
+        hist = np.ascontiguousarray(history_lens, dtype=np.int32)
+        stops = np.ascontiguousarray(list(stop_ids), dtype=np.int32)
+        out = np.empty((max_steps, self.n), dtype=np.int32)
+        done = ctypes.c_int(0)
+        rc = _fn("sampling", "cml_decode_loop_run")(
+            ctypes.addressof(self._state), graph_exec, _stream(), tok.ctypes.data, pos.ctypes.data, hist.ctypes.data,
+            max_steps, stops.ctypes.data if stops.size else None, int(stops.size), float(temperature), int(top_k or 0),
+            float(top_p if top_p is not None else 1.0), float(min_p or 0.0), int(seed or 0), out.ctypes.data,
+            ctypes.addressof(done))
+        _check(rc, "decode_loop_run", (launches_per_step + 1) * done.value)
+        return out[:done.value], done.value

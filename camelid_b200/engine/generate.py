@@ -81,7 +81,37 @@ def run_batch(model, cache, sampler, prompts: list, budgets: list, requested: li
         if not live:
             return results
         entries = [StepEntry(slots[i], prompts[i], [len(prompts[i]) - 1]) for i in live]
+        # After the prompts, a model that steps through captured graphs and a sampler without
+        # per-history adjustments hand the one-token steps to the C++ loop: many steps per call.
+        native = (getattr(model, "use_graphs", False) and hasattr(model, "decode_natively")
+                  and getattr(sampler, "native_ok", False))
+        first = True
         while live:
+            if native and not first:
+                k = min(budgets[i] - len(results[i].tokens) for i in live)
+                out, steps = model.decode_natively(cache, [slots[i] for i in live], [results[i].tokens[-1] for i in live],
+                                                   [len(histories[i]) for i in live], k, sorted(stop_ids),
+                                                   sampler.options, sampler.error_word)
+                still = []
+                for j, i in enumerate(live):
+                    new = [int(t) for t in out[:steps, j]]
+                    results[i].tokens.extend(new)
+                    histories[i].extend(new)
+                    if new[-1] in stop_ids:
+                        results[i].finish_reason = "stop"
+                    elif len(results[i].tokens) >= budgets[i]:
+                        results[i].finish_reason = "length" if budgets[i] >= requested[i] else "capacity"
+                    if results[i].finish_reason:
+                        cache.free_slot(slots[i])
+                        slots[i] = None
+                    else:
+                        still.append(i)
+                if on_step is not None:
+                    for _ in range(steps):
+                        on_step(len(live))
+                live = still
+                continue
+            first = False
             logits = model.step(cache, entries)
             tokens = _to_list(sampler.sample(logits, [histories[i] for i in live]))
             if on_step is not None:

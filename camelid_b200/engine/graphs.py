@@ -104,3 +104,23 @@ class DecodeGraph:
         self.graph.replay()
         ops.add_launches(self.launches)
         return self.logits
+
+    def native_loop(self, err: torch.Tensor):
+        """The C++ decode loop bound to this graph (made at its first use, after capture).
+        ``err``: the sampler's error word (non-finite logits)."""
+        if getattr(self, "_native", None) is None or self._native.err is not err:
+            self._native = ops.NativeDecodeLoop(self.n_seqs, self.ctx.layout, self.ctx.meta_dev, self.host_np[0],
+                                                self.logits, err)
+        return self._native
+
+    def run_native(self, slots: list, starts: list, tokens: list, history_lens: list, max_steps: int, stop_ids,
+                   temperature: float, top_k, top_p, min_p, seed, err: torch.Tensor):
+        """Up to ``max_steps`` steps in C++ (the cache must already hold pages for them). Returns
+        (tokens [steps, sequences] as a numpy array, steps done)."""
+        i = self.fill(slots, starts, tokens)
+        self.send(i, with_tokens=True)                  # block tables and the static arrays
+        if self.graph is None:
+            self.capture()
+        loop = self.native_loop(err)
+        return loop.run(self.graph.raw_cuda_graph_exec(), tokens, starts, history_lens, max_steps, stop_ids,
+                        temperature, top_k, top_p, min_p, seed, self.launches)

@@ -185,6 +185,30 @@ class DecoderModel:
             self._graphs[key] = graph
         return graph
 
+    def decode_natively(self, cache: SequenceCache, slots: list, tokens: list, history_lens: list, max_steps: int,
+                        stop_ids, options, err: torch.Tensor) -> tuple:
+        """Run up to ``max_steps`` one-token steps of these sequences in the C++ loop: each feeds
+        its token, the sampling kernel picks the next, which is fed in the next step. Stops after
+        the step in which a sequence picks a stop token. Returns (tokens [steps][sequence], steps);
+        the cache's lengths have moved by ``steps``."""
+        if self._err is None:
+            self._err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        if not self.use_graphs:
+            raise StepError("the C++ decode loop needs a model whose parts can run in a captured graph")
+        for t in tokens:
+            if not 0 <= int(t) < self.vocab_size:
+                raise StepError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
+        book = cache.book
+        book.check_extend([(s, max_steps) for s in slots])
+        starts = [book.extend(s, max_steps) for s in slots]
+        graph = self.decode_graph(cache, slots)
+        out, steps = graph.run_native(slots, starts, [int(t) for t in tokens], history_lens, max_steps, stop_ids,
+                                      options.temperature, options.top_k, options.top_p, options.min_p, options.seed, err)
+        for s in slots:
+            book.commit(s, steps)
+        self.last_h2d_bytes = graph.native_loop(err).h2d_bytes_per_step
+        return out, steps
+
     def drop_graphs(self, cache=None) -> None:
         """Forget the captured graphs (of one cache, or all): they keep their cache alive."""
         for key in [k for k, g in self._graphs.items() if cache is None or g.cache is cache]:

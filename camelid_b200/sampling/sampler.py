@@ -21,6 +21,16 @@ class Sampler:
         self.device = torch.device(device)
         self._err = torch.zeros(1, dtype=torch.int32, device=self.device)
 
+    @property
+    def native_ok(self) -> bool:
+        """Whether the C++ decode loop can sample for this sampler: everything but the
+        adjustments that need each request's history on the host (penalties, bias)."""
+        return not self.options.adjusts
+
+    @property
+    def error_word(self) -> torch.Tensor:
+        return self._err
+
     def _adjust_entries(self, histories: list):
         o = self.options
         entries, biases = [], []

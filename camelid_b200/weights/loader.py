@@ -35,8 +35,3 @@ def check_tensors(specs: dict, names_shapes_dtypes: dict, *, tolerated: tuple = 
         raise WeightsError(missing, unexpected, wrong, other)
 
 
-def stored_dtype(dtype: torch.dtype, compute: torch.dtype) -> torch.dtype:
-    """Type a floating-point tensor has on the device: the compute type, except that a
-    tensor stored in 32-bit is not narrowed when it is a vector (norm weights); matrices
-    that feed the matrix products take the compute type."""
-    return compute

@@ -95,3 +95,32 @@ def test_command_line(cuda, model_folders, tmp_path):
     assert rec["output_token_ids"] == want and rec["prompt_tokens"] == 5 and rec["generated_tokens"] == len(want)
     for key in ("load_ms", "prefill_ms", "ttft_ms", "decode_ms", "tokens_per_second"):
         assert key in rec
+
+
+def test_penalties_take_the_python_loop_and_match_plain(cuda, model_folders):
+    """Penalties and bias need each request's history on the host, so these requests run the
+    Python loop instead of the C++ one; both must agree with the plain loop."""
+    import camelid_b200
+    name = "tiny_b"
+    lm = camelid_b200.load(model_folders[name], dtype="float32")
+    prompts = [tokens(80 + i, n, CONFIGS[name]["vocab_size"]) for i, n in enumerate([6, 13])]
+    cfg, w = pl.read_model(model_folders[name])
+    opts = dict(repeat_penalty=1.3, presence_penalty=0.2, frequency_penalty=0.1, logit_bias=[(5, 2.0)])
+    want = pl.generate(cfg, w, prompts, 10, dtype=torch.float64, **opts)
+    got = lm.generate(prompts, max_tokens=10, stop_token_ids=(), **opts)
+    assert got == want
+    plain_loop = lm.generate(prompts, max_tokens=10, stop_token_ids=())          # the C++ loop
+    assert plain_loop == pl.generate(cfg, w, prompts, 10, dtype=torch.float64)
+
+
+def test_long_generation_crosses_pages_in_the_native_loop(cuda, model_folders):
+    """70 + 140 tokens: the C++ loop runs over two page boundaries, for two requests of unequal
+    length that stop at different times."""
+    import camelid_b200
+    name = "tiny_c"
+    lm = camelid_b200.load(model_folders[name], dtype="float32")
+    prompts = [tokens(90, 70, CONFIGS[name]["vocab_size"]), tokens(91, 3, CONFIGS[name]["vocab_size"])]
+    cfg, w = pl.read_model(model_folders[name])
+    want = pl.generate(cfg, w, prompts, 140, dtype=torch.float64)
+    got = lm.generate(prompts, max_tokens=[140, 90])
+    assert got[0] == want[0] and got[1] == want[1][:90]
