@@ -1,6 +1,7 @@
 // bfloat16 matrix products on the fifth-generation tensor cores: TMA loads into swizzled
 // shared memory, tcgen05.mma issued by one thread with the accumulator in tensor memory,
-// tcgen05.ld in the epilogue. One kernel serves prefill and decode:
+// tcgen05.ld in the epilogue. One kernel serves decode and prefill steps of few rows; steps
+// of many rows run its two-block form (gemm_tc_pair_kernel, tcgen05 cta_group::2) below:
 //
 //   D[128 x BN] tile = Arows[128, K] * Brows[BN, K]^T        (both operands K-major)
 //
@@ -101,6 +102,14 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_ld16_nowait(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
 }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16),
@@ -400,6 +409,238 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 }
 
 // ------------------------------------------------------------------------------------
+// Two blocks of a cluster on one tile (tcgen05 cta_group::2): D[256 x 256] = Arows[256, K] *
+// Brows[256, K]^T. Each block of the pair loads its own 128 rows of A and its own 128 rows of B
+// (16 KB + 16 KB a stage instead of 16 KB + 32 KB for a 128 x 256 tile of one block), the
+// leader's MMA thread issues 256 x 256 x 16 MMAs for both, and each block ends up with its 128
+// rows of the tile in its own tensor memory. A third less shared-memory and L2 traffic per
+// flop than the one-block tile, which is what bounds large products.
+//
+// Barriers live at the same offsets in both blocks. full[s] is used in the leader only: its
+// producer expects the bytes of both blocks, and both blocks' TMA loads report to it
+// (cp.async.bulk.tensor with .cta_group::2 and no multicast). empty[s] and acc_full[b] are
+// signalled in both blocks at once by the leader's tcgen05.commit with .multicast::cluster;
+// acc_empty[b] is the leader's, and the epilogue warps of both blocks arrive on it.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(leader_bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
+#define TC_PAIR_STAGES 6
+#define TC_PAIR_BN 256
+__host__ __device__ constexpr size_t tc_pair_smem_bytes() { return 1024 + (size_t)TC_PAIR_STAGES * (2 * TC_BM * 128) + 512; }
+
+// Work items are tiles of 256 A rows by 256 B rows, A tile fastest; cluster c takes items
+// c, c + clusters, ... p.tiles_a and p.tiles_b count those tiles. No split of K.
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, TcParams p) {
+    constexpr int STAGES = TC_PAIR_STAGES, BN = TC_PAIR_BN;
+    constexpr uint32_t A_BYTES = TC_BM * 128, B_BYTES = TC_BM * 128;      // this block's halves of a stage
+    constexpr uint32_t TMEM_COLS = 512;                                    // two accumulators of 256 columns
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t smemA = base, smemB = base + STAGES * A_BYTES;
+    const uint32_t bars = smemB + STAGES * B_BYTES;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + STAGES * (A_BYTES + B_BYTES) + (2 * STAGES + 4) * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+    auto acc_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int cluster = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+    const int n_work = p.tiles_a * p.tiles_b;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full(b), 1);
+            mbar_init(acc_empty(b), 8);          // one lane of each epilogue warp of both blocks
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        // All 512 columns: the allocation only returns once the SM's tensor memory is free of
+        // other blocks, so both blocks of the pair get the same base (the MMA addresses both).
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) {
+        uint32_t other;
+        asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(other) : "r"(map_to_cta(smem_u32(tmem_slot), rank ^ 1u)));
+        if (other != tmem_base) *abort_flag = 1;         // both blocks see the mismatch and give up
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    auto item = [&](int w, int& a0, int& b0) {
+        a0 = (w % p.tiles_a) * 256 + (int)rank * TC_BM;
+        b0 = (w / p.tiles_a) * BN + (int)rank * TC_BM;
+    };
+
+    if (warp == 0) {
+        if (lane == 0 && !*abort_flag) {
+            int g = 0;
+            bool waited = false, ok = true;
+            auto leader_full = [&](int s) { return map_to_cta(full_bar(s), 0); };
+            for (int w = cluster; w < n_work && ok; w += n_clusters) {
+                int a0, b0;
+                item(w, a0, b0);
+                int i = 0;
+                if (!waited) {
+                    const int pre = min(p.num_kb, STAGES);
+                    for (; i < pre; ++i) {
+                        if (leader) mbar_expect_tx(full_bar(i), 2 * (A_BYTES + B_BYTES));
+                        if (p.independent == 0) tma_load_2d_pair(smemA + i * A_BYTES, &mapA, leader_full(i), i * TC_BK, a0);
+                        else tma_load_2d_pair(smemB + i * B_BYTES, &mapB, leader_full(i), i * TC_BK, b0);
+                    }
+                    pdl_wait();
+                    waited = true;
+                    for (int j = 0; j < pre; ++j) {
+                        if (p.independent == 0) tma_load_2d_pair(smemB + j * B_BYTES, &mapB, leader_full(j), j * TC_BK, b0);
+                        else tma_load_2d_pair(smemA + j * A_BYTES, &mapA, leader_full(j), j * TC_BK, a0);
+                    }
+                    g = pre;
+                }
+                for (; i < p.num_kb; ++i, ++g) {
+                    const int s = g % STAGES;
+                    const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    if (leader) mbar_expect_tx(full_bar(s), 2 * (A_BYTES + B_BYTES));
+                    tma_load_2d_pair(smemA + s * A_BYTES, &mapA, leader_full(s), i * TC_BK, a0);
+                    tma_load_2d_pair(smemB + s * B_BYTES, &mapB, leader_full(s), i * TC_BK, b0);
+                }
+            }
+            if (*abort_flag) {
+                // let the copies in flight land before the block leaves (the leader sees them on
+                // its barriers; the other block has none of its own and just gives them time)
+                const long long t0 = clock64();
+                if (leader) {
+                    for (int i = max(0, g - STAGES); i < g; ++i)
+                        while (!mbar_try_wait(full_bar(i % STAGES), (uint32_t)(i / STAGES) & 1u) &&
+                               clock64() - t0 < 20000000ll) {}
+                } else {
+                    while (clock64() - t0 < 20000000ll) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader && !*abort_flag) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                       ((uint32_t)(256 >> 4) << 24);
+            int g = 0, j = 0;
+            bool ok = true;
+            for (int w = cluster; w < n_work && ok; w += n_clusters, ++j) {
+                const int buf = j & 1;
+                ok = mbar_wait(acc_empty(buf), (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                for (int i = 0; i < p.num_kb && ok; ++i, ++g) {
+                    const int s = g % STAGES;
+                    const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+                    ok = mbar_wait(full_bar(s), ph, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t adesc = smem_desc_sw128(smemA + s * A_BYTES);
+                    const uint64_t bdesc = smem_desc_sw128(smemB + s * B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        tc_mma_bf16_pair(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (i | k) ? 1u : 0u);
+                    tc_commit_pair(empty_bar(s));        // frees the stage in both blocks
+                }
+                if (ok) tc_commit_pair(acc_full(buf));   // both blocks' halves of the tile are complete
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        pdl_wait();
+        bool ok = !*abort_flag;
+        int j = 0;
+        for (int w = cluster; w < n_work && ok; w += n_clusters, ++j) {
+            int a0, b0;
+            item(w, a0, b0);
+            b0 -= (int)rank * TC_BM;                     // every block holds all 256 columns of its rows
+            const int buf = j & 1;
+            const int rowA = a0 + q * 32 + lane;
+            ok = mbar_wait(acc_full(buf), ((uint32_t)j >> 1) & 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[16], u[16];
+                tc_ld16_nowait(taddr + c, r);
+                tc_ld16_nowait(taddr + c + 16, u);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (EPI == TC_SWIGLU) {
+                    tc_epilogue_chunk<EPI>(p, r, u, rowA, b0 + c, 0, lane, 0);
+                } else {
+                    tc_epilogue_chunk<EPI>(p, r, r, rowA, b0 + c, 0, lane, 0);
+                    tc_epilogue_chunk<EPI>(p, u, u, rowA, b0 + c + 16, 0, lane, 0);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(map_to_cta(acc_empty(buf), 0)) : "memory");
+        }
+    }
+    tc_fence_before();
+    cluster_sync_all();          // no block leaves while its partner may still signal its barriers
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 2);
+}
+
+// ------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -485,5 +726,50 @@ extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, lo
     TC_CASE(16, TC_T_PARTIAL); TC_CASE(32, TC_T_PARTIAL); TC_CASE(64, TC_T_PARTIAL);
     TC_CASE(16, TC_T_SWIGLU); TC_CASE(32, TC_T_SWIGLU); TC_CASE(64, TC_T_SWIGLU);
 #undef TC_CASE
+    return CML_ERR_BAD_SIZE;
+}
+
+template <int EPI>
+static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t s) {
+    const size_t smem = tc_pair_smem_bytes();
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    e = launch_pdl(gemm_tc_pair_kernel<EPI>, grid, dim3(TC_THREADS), smem, s, ma, mb, p);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
+// The same product as cml_gemm_tc with epilogues 0..3, on tiles of 256 x 256 that two blocks
+// of a cluster share (see gemm_tc_pair_kernel). For many rows of A: a tile covers 256 of them.
+extern "C" int cml_gemm_tc_pair(const void* A, long lda, int rowsA, const void* B, long ldb, int rowsB, int K, void* C,
+                                long ldc, int epilogue, int* err, void* stream) {
+    if (rowsA <= 0 || rowsB <= 0) return 0;
+    if (K <= 0 || (K & 7)) return CML_ERR_BAD_SIZE;
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, A, rowsA, K, lda, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mb, B, rowsB, K, ldb, TC_BM);
+    if (rc) return rc;
+    TcParams p;
+    p.C = C; p.ldc = ldc; p.rowsA = rowsA; p.rowsB = rowsB;
+    p.num_kb = (K + TC_BK - 1) / TC_BK;
+    p.kb_per_split = p.num_kb;
+    p.err = err;
+    p.independent = 1;
+    p.tiles_a = (rowsA + 255) / 256;
+    p.tiles_b = (rowsB + TC_PAIR_BN - 1) / TC_PAIR_BN;
+    p.splits = 1;
+    const long work = (long)p.tiles_a * p.tiles_b;
+    if (work > 0x7fffffffL) return CML_ERR_BAD_SIZE;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    const long clusters = work < sms / 2 ? work : sms / 2;
+    dim3 grid((unsigned)(2 * clusters), 1, 1);
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (epilogue) {
+        case TC_STORE: return launch_tc_pair<TC_STORE>(ma, mb, p, grid, s);
+        case TC_STORE_F32: return launch_tc_pair<TC_STORE_F32>(ma, mb, p, grid, s);
+        case TC_ADD_F32: return launch_tc_pair<TC_ADD_F32>(ma, mb, p, grid, s);
+        case TC_SWIGLU: return launch_tc_pair<TC_SWIGLU>(ma, mb, p, grid, s);
+    }
     return CML_ERR_BAD_SIZE;
 }

@@ -32,6 +32,8 @@ _SIGNATURES = {
                                                c_int, c_int, c_int, c_void_p],
     ("gemm_tc", "cml_gemm_tc"): [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_void_p, c_long, c_int, c_int,
                                  c_int, c_void_p, c_void_p],
+    ("gemm_tc", "cml_gemm_tc_pair"): [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_void_p, c_long, c_int,
+                                      c_void_p, c_void_p],
     ("attention_simt", "cml_attn_paged_simt"): [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                                 c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -219,6 +221,19 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, epilogue: int, bn
     ldc = c.stride(-2)
     _check(_fn("gemm_tc", "cml_gemm_tc")(_p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], a.shape[1],
                                         _p(c), ldc, epilogue, bn, splits, _p(err), _stream()), "gemm_tc")
+
+
+def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, epilogue: int, err: torch.Tensor):
+    """c[row of a][row of b] (op)= a @ b.T with epilogues 0..3 of ``gemm_tc``, on tiles of
+    256 x 256 that the two blocks of a cluster share (tcgen05 cta_group::2): the kernel for
+    products with many rows of ``a``."""
+    _dev(a, b, c, err)
+    if not gemm_tc_usable(a, b):
+        raise KernelError("gemm_tc_pair: operands must be bfloat16 [rows, K] with K and the row strides multiples "
+                          "of 8 and 16-byte aligned bases")
+    assert c.stride(-1) == 1 and epilogue in (TC_STORE, TC_STORE_F32, TC_ADD_F32, TC_SWIGLU)
+    _check(_fn("gemm_tc", "cml_gemm_tc_pair")(_p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], a.shape[1],
+                                             _p(c), c.stride(-2), epilogue, _p(err), _stream()), "gemm_tc_pair")
 
 
 def attn_tiling(n_heads: int, n_kv_heads: int, decode: bool) -> tuple[int, int, int]:

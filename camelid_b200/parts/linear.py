@@ -46,6 +46,9 @@ def _bn_decode(rows: int) -> int:
     return 16 if rows <= 16 else (32 if rows <= 32 else 64)
 
 
+PAIR_ROWS = 128     # above this many rows the product runs on 256 x 256 tiles of two blocks
+
+
 def _bn_prefill(rows: int, out_features: int) -> int:
     """Tile width over the weight rows for a persistent launch: the one that needs fewer
     rounds of SM_COUNT blocks times its width (wider tiles reuse operands better on a tie)."""
@@ -76,13 +79,20 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
                 return
         else:
             bn = _bn_prefill(rows, w.shape[0])
+            pair = rows > PAIR_ROWS          # tiles of 256 x 256 on two blocks: less operand traffic per flop
             if epilogue == SWIGLU:
                 if group == 16 and w.shape[0] % 32 == 0:
-                    ops.gemm_tc(x, w, out, ops.TC_SWIGLU, bn, 1, err)
+                    if pair:
+                        ops.gemm_tc_pair(x, w, out, ops.TC_SWIGLU, err)
+                    else:
+                        ops.gemm_tc(x, w, out, ops.TC_SWIGLU, bn, 1, err)
                     return
             else:
-                ops.gemm_tc(x, w, out, {STORE: ops.TC_STORE, STORE_F32: ops.TC_STORE_F32, ADD_F32: ops.TC_ADD_F32}[epilogue],
-                            bn, 1, err)
+                epi = {STORE: ops.TC_STORE, STORE_F32: ops.TC_STORE_F32, ADD_F32: ops.TC_ADD_F32}[epilogue]
+                if pair:
+                    ops.gemm_tc_pair(x, w, out, epi, err)
+                else:
+                    ops.gemm_tc(x, w, out, epi, bn, 1, err)
                 return
     ops.gemm_tn_simt(x, w, out, epilogue, group)
 

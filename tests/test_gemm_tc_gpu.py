@@ -121,3 +121,43 @@ def test_consumers_of_split_sums(cuda):
     h4 = h.clone()
     ops.add_partials(h4, part)
     assert rel_err(h4.cpu(), total) <= 1e-6
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 300, 136), (1000, 520, 192), (129, 517, 72), (2048, 1024, 2048),
+                                   (513, 2048, 1088), (4096, 768, 4104)])
+def test_pair_tiles(cuda, m, n, k):
+    """Tiles of 256 x 256 shared by two blocks of a cluster: ragged edges in every dimension,
+    row counts that leave the second block of a pair without rows, many k-blocks, several
+    tiles per cluster."""
+    ops = _ops()
+    a, w, ref = _operands(m, n, k, cuda, seed=3)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    c = torch.full((m, n), float("nan"), dtype=BF, device=cuda)
+    ops.gemm_tc_pair(a, w, c, ops.TC_STORE, err)
+    assert rel_err(c.cpu(), ref) <= 2 ** -8
+    c32 = torch.full((m, n), float("nan"), device=cuda)
+    ops.gemm_tc_pair(a, w, c32, ops.TC_STORE_F32, err)
+    assert rel_err(c32.cpu(), ref) <= 1e-5
+    res = torch.randn(m, n, device=cuda)
+    want = res.cpu().double() + ref
+    ops.gemm_tc_pair(a, w, res, ops.TC_ADD_F32, err)
+    assert rel_err(res.cpu(), want) <= 1e-5
+    assert int(err) == 0
+
+
+@pytest.mark.parametrize("m,inter,k", [(300, 160, 64), (130, 528, 200), (1024, 2048, 512), (2048, 8192, 256)])
+def test_pair_tiles_swiglu(cuda, m, inter, k):
+    ops = _ops()
+    from camelid_b200.parts.linear import pack_gate_up
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(m, k, generator=g).to(BF).to(cuda)
+    wg = (torch.randn(inter, k, generator=g) / math.sqrt(k)).to(BF)
+    wu = (torch.randn(inter, k, generator=g) / math.sqrt(k)).to(BF)
+    packed = pack_gate_up(wg, wu, 16).to(cuda)
+    gate = x.cpu().double() @ wg.double().T
+    ref = torch.nn.functional.silu(gate) * (x.cpu().double() @ wu.double().T)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    out = torch.full((m, inter), float("nan"), dtype=BF, device=cuda)
+    ops.gemm_tc_pair(x, packed, out, ops.TC_SWIGLU, err)
+    assert rel_err(out.cpu(), ref) <= 2 ** -7
+    assert int(err) == 0
