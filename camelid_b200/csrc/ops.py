@@ -42,6 +42,9 @@ _SIGNATURES = {
                                               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                               c_void_p, c_void_p],
+    ("attention_mma", "cml_attn_decode_fused"): [c_void_p, c_int, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                 c_float, c_int, c_void_p, c_int, c_void_p],
     ("attention_tc", "cml_attn_prefill_tc"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p,
                                               c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
@@ -299,6 +302,41 @@ def attn_paged_mma(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_t
         _p(tile_seq), _p(tile_q0), n_tiles, _p(seq_row0), _p(seq_start), _p(seq_new), n_rows, n_heads, n_kv_heads,
         head_dim, rows_per_tile, heads_per_cta, head_chunks, n_splits, int(window or 0), float(scale), _p(partial),
         _p(tickets), _stream()), "attn_paged_mma")
+
+
+def attn_decode_fused_usable(partial, out, head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
+    return (partial is not None and partial.dtype == torch.float32 and out.dtype == torch.bfloat16
+            and head_dim in (64, 128) and n_heads // n_kv_heads <= 16 and out.stride(0) % 2 == 0)
+
+
+def attn_decode_fused_splits(n_splits: int, n_heads: int, n_kv_heads: int, head_dim: int) -> int:
+    """The number of blocks per cluster the fused decode kernel can take, at most ``n_splits``:
+    block 0 keeps the ranges of all blocks in shared memory beside its own cache tiles."""
+    group = n_heads // n_kv_heads
+    stages = 4 * 3 * 2 * 32 * head_dim * 2
+    n_splits = max(1, min(8, n_splits))
+    while n_splits > 1 and stages + n_splits * group * (head_dim + 2) * 4 + 8 * 1024 > 227 * 1024:
+        n_splits -= 1
+    return n_splits
+
+
+def attn_decode_fused(partial, out, row_pos, row_seq, block_table, k_pages, v_pages, inv_freq, rotary_dim: int,
+                      n_heads: int, n_kv_heads: int, head_dim: int, write_kv: bool, window: int, scale: float,
+                      n_splits: int):
+    """Decode attention in one launch from the partial sums [splits, rows, width] of the q/k/v
+    product: sums them, rotates q and the new key, writes the new key and value to the cache
+    (``write_kv``) and attends every row (one new token of a sequence each) over its cache,
+    the keys split over the ``n_splits`` (at most 8) blocks of a cluster."""
+    _dev(partial, out, row_pos, row_seq, block_table, k_pages, v_pages, inv_freq)
+    assert partial.dim() == 3 and partial.is_contiguous() and out.stride(1) == 1
+    assert k_pages.dtype == torch.bfloat16 and k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim)
+    assert k_pages.is_contiguous() and v_pages.is_contiguous() and 1 <= n_splits <= 8
+    rows = partial.shape[1]
+    _check(_fn("attention_mma", "cml_attn_decode_fused")(
+        _p(partial), partial.shape[0], partial.stride(0), partial.shape[2], rows, _p(row_pos), _p(row_seq),
+        _p(block_table), block_table.shape[1], _p(k_pages), _p(v_pages), _p(inv_freq), rotary_dim, n_heads, n_kv_heads,
+        head_dim, 1 if write_kv else 0, int(window or 0), float(scale), n_splits, _p(out), out.stride(0), _stream()),
+        "attn_decode_fused")
 
 
 def attn_tc_tiling(n_heads: int, n_kv_heads: int) -> tuple[int, int, int]:

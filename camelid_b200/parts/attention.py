@@ -50,6 +50,8 @@ class GroupedQueryAttention(Part):
         # prefill steps of bfloat16 models with head size 64 or 128 use the tcgen05 kernel;
         # CAMELID_PREFILL_ATTENTION=mma keeps the mma.sync kernel (for comparisons)
         self.prefill_tcgen05 = os.environ.get("CAMELID_PREFILL_ATTENTION", "tcgen05") != "mma"
+        # decode in one launch from the q/k/v product (the default) or as rotary kernel + split attention kernel
+        self.decode_fused = os.environ.get("CAMELID_DECODE_ATTENTION", "fused") != "split"
 
     def tensor_specs(self):
         p = self.prefix
@@ -84,6 +86,17 @@ class GroupedQueryAttention(Part):
         width = self.q_width if borrow else self.q_width + 2 * self.kv_width
         pos = self.position
         part = linear.partial_sums(ctx, x, self.w_qkv[:width], "qkv_partial")
+        out = ctx.buffer("attn_out", (n, self.q_width))
+        splits = self._decode_splits(ctx, n, 1, True) if ctx.decode else 1
+        if (part is not None and ctx.decode and self.decode_fused and (splits <= 8 or ctx.max_len <= 8192)
+                and ops.attn_decode_fused_usable(part, out, self.head_dim, self.num_heads, self.num_kv_heads)):
+            # decode: one launch sums the product's splits, rotates, writes the cache and attends
+            ops.attn_decode_fused(part, out, ctx.row_pos, ctx.row_seq, table, k_pages, v_pages, pos.inv_freq,
+                                  pos.rotary_dim, self.num_heads, self.num_kv_heads, self.head_dim, not borrow,
+                                  self.window or 0, self.scale,
+                                  ops.attn_decode_fused_splits(splits, self.num_heads, self.num_kv_heads, self.head_dim))
+            linear.add_into_residual(ctx, out, self.w_o, residual, "o_partial")
+            return
         if part is not None:          # decode: the rotary kernel sums the splits of the product
             q = ctx.buffer("q_rot", (n, self.q_width))
             ops.rope_kv_from_partials(part, q, ctx.row_pos, ctx.row_seq, table, k_pages, v_pages, pos.inv_freq,
@@ -95,7 +108,6 @@ class GroupedQueryAttention(Part):
             ops.rope_kv_write(qkv, ctx.row_pos, ctx.row_seq, table, k_pages, v_pages, pos.inv_freq, pos.rotary_dim,
                               self.num_heads, self.num_kv_heads, self.head_dim, write_kv=not borrow)
             q = qkv[:, :self.q_width]
-        out = ctx.buffer("attn_out", (n, self.q_width))
         if not ctx.decode and self.prefill_tcgen05 and ops.attn_tc_usable(q, out, self.head_dim):
             rows, hpc, chunks = ops.attn_tc_tiling(self.num_heads, self.num_kv_heads)
             tile_seq, tile_q0, n_tiles = ctx.query_tiles(rows)
@@ -108,6 +120,15 @@ class GroupedQueryAttention(Part):
             self._attend(ctx, q, out, k_pages, v_pages, table, tensor_cores=False)
         linear.add_into_residual(ctx, out, self.w_o, residual, "o_partial")
 
+    def _decode_splits(self, ctx, n_tiles: int, chunks: int, tensor_cores: bool) -> int:
+        """Blocks that share the keys of one (row, kv head) in a decode step: enough for all SMs
+        to stream the cache, but no block with less than a few tiles of keys."""
+        keys = ctx.max_len if not self.window else min(ctx.max_len, self.window + PAGE)
+        ctas = n_tiles * self.num_kv_heads * chunks
+        unit = 8 * 32 if tensor_cores else PAGE               # keys a block should at least have
+        resident = (2 if self.head_dim <= 64 else 1) * linear.SM_COUNT    # blocks that run at the same time
+        return max(1, min((keys + unit - 1) // unit, resident // ctas, 64))
+
     def _attend(self, ctx, q, out, k_pages, v_pages, table, tensor_cores: bool):
         """Attention of the step's rows over the cache. bfloat16 with a head size of 64 or 128
         runs on the tensor cores, everything else in float on the CUDA cores. A decode step
@@ -117,11 +138,7 @@ class GroupedQueryAttention(Part):
         tile_seq, tile_q0, n_tiles = ctx.query_tiles(rows)
         n_splits, partial = 1, None
         if ctx.decode:
-            keys = ctx.max_len if not self.window else min(ctx.max_len, self.window + PAGE)
-            ctas = n_tiles * self.num_kv_heads * chunks
-            unit = 8 * 32 if tensor_cores else PAGE               # keys a block should at least have
-            resident = (2 if self.head_dim <= 64 else 1) * linear.SM_COUNT    # blocks that run at the same time
-            n_splits = max(1, min((keys + unit - 1) // unit, resident // ctas, 64))
+            n_splits = self._decode_splits(ctx, n_tiles, chunks, tensor_cores)
             if n_splits > 1:
                 partial = ctx.buffer("attn_partial", (ops.attn_partial_floats(ctx.n_rows, self.num_heads, self.head_dim,
                                                                              n_splits),), torch.float32)

@@ -353,3 +353,79 @@ def test_attention_tc_continues_from_cache(cuda, hd):
 @pytest.mark.parametrize("window", [1, 32, 70, 200])
 def test_attention_tc_window_edges(cuda, window):
     _attn_tc_case(cuda, 4, 2, 64, starts=[0, 190], news=[150, 10], window=window, spike=(1, max(0, 199 - window)))
+
+
+def _attn_fused_case(cuda, n_heads, n_kv, hd, rot, starts, window, n_splits, gsplits, write_kv=True, spike=None):
+    """Decode attention in one launch from the partial sums of the q/k/v product: against the
+    plain rotary encoding and attention of the whole sequences, and the cache rows it writes."""
+    from camelid_b200.csrc import ops
+    from camelid_b200.parts.position import rotary_frequencies
+    dt = torch.bfloat16
+    n = len(starts)
+    totals = [s + 1 for s in starts]
+    k_pages, v_pages, table, ks, vs = _paged(totals, n_kv, hd, dt, cuda, seed=4)
+    freqs = rotary_frequencies(rot, 10000.0, None) if rot else np.zeros(0, dtype=np.float32)
+    g = torch.Generator().manual_seed(7)
+    width = (n_heads + 2 * n_kv) * hd
+    part = torch.randn(gsplits, n, width, generator=g) / math.sqrt(gsplits)
+    total = torch.zeros(n, width)
+    for s in range(gsplits):
+        total = total + part[s]                       # the kernel's order of adding
+    qkv = total.to(dt)
+    if spike is not None:                             # one far key gets a score that stands out
+        seq, key = spike
+        ks[seq][key] *= 0
+        ks[seq][key, :, hd - 1] = 8.0                 # a dimension the rotation leaves alone when rot < hd
+        k_pages[int(table[seq, key // 64]), :, key % 64] = ks[seq][key].to(cuda)
+    pos = torch.tensor(starts)
+    q = qkv[:, :n_heads * hd].double().view(n, n_heads, hd)
+    k = qkv[:, n_heads * hd:(n_heads + n_kv) * hd].double().view(n, n_kv, hd)
+    v = qkv[:, (n_heads + n_kv) * hd:].view(n, n_kv, hd)
+    q_rot = (pl.rope(q, pos, freqs) if rot else q).to(dt)
+    k_rot = (pl.rope(k, pos, freqs) if rot else k).to(dt)
+    tab = table.cpu()
+    slots = [(int(tab[i, s // 64]), s % 64) for i, s in enumerate(starts)]
+    if write_kv:                                      # the row's own place holds something else until the kernel writes it
+        for page, off in slots:
+            k_pages[page, :, off] = float("nan")
+            v_pages[page, :, off] = float("nan")
+    else:                                             # a borrowed cache already holds the row's key and value
+        for i, (page, off) in enumerate(slots):
+            k_pages[page, :, off] = k_rot[i].to(cuda)
+            v_pages[page, :, off] = v[i].to(cuda)
+    before_k = k_pages.clone()
+    out = torch.full((n, n_heads * hd), float("nan"), dtype=dt, device=cuda)
+    ops.attn_decode_fused(part.to(cuda), out, _i32(starts, cuda), _i32(list(range(n)), cuda), table, k_pages, v_pages,
+                          torch.from_numpy(freqs).to(cuda), rot, n_heads, n_kv, hd, write_kv, window or 0,
+                          1 / math.sqrt(hd), n_splits)
+    out = out.cpu().view(n, n_heads, hd)
+    for i, s in enumerate(starts):
+        page, off = slots[i]
+        if write_kv:
+            assert rel_err(k_pages[page, :, off].cpu(), k_rot[i].double()) <= 2 ** -8
+            assert torch.equal(v_pages[page, :, off].cpu(), v[i])
+        kfull = torch.cat([ks[i][:s].double(), k_rot[i].double()[None]], dim=0)
+        vfull = torch.cat([vs[i][:s].double(), v[i].double()[None]], dim=0)
+        qfull = torch.zeros(s + 1, n_heads, hd, dtype=torch.float64)
+        qfull[s] = q_rot[i].double()
+        ref = pl.attention(qfull, kfull, vfull, window)[s:]
+        e = rel_err(out[i:i + 1], ref)
+        assert e <= 2 ** -6, f"sequence {i} at position {s}: {e}"
+    changed = (before_k != k_pages) & ~(torch.isnan(before_k) & torch.isnan(k_pages))
+    assert int(changed.any(dim=-1).sum()) <= (n * n_kv if write_kv else 0)     # nothing else was written
+
+
+@pytest.mark.parametrize("n_splits", [1, 2, 5, 8])
+@pytest.mark.parametrize("n_heads,n_kv,hd,rot", [(8, 2, 64, 64), (6, 2, 128, 64), (5, 5, 64, 32), (16, 1, 64, 0)])
+def test_attention_decode_fused(cuda, n_heads, n_kv, hd, rot, n_splits):
+    _attn_fused_case(cuda, n_heads, n_kv, hd, rot, starts=[0, 31, 32, 63, 64, 700], window=None, n_splits=n_splits,
+                     gsplits=3, spike=(5, 130))
+
+
+@pytest.mark.parametrize("window", [1, 32, 70, 200])
+def test_attention_decode_fused_window_and_borrowed_cache(cuda, window):
+    _attn_fused_case(cuda, 4, 2, 64, 64, starts=[199, 80, 0], window=window, n_splits=3, gsplits=9,
+                     spike=(0, max(0, 200 - window)))
+    _attn_fused_case(cuda, 4, 2, 64, 64, starts=[199, 80, 0], window=window, n_splits=4, gsplits=1, write_kv=False,
+                     spike=(0, max(0, 200 - window)))
+    _attn_fused_case(cuda, 8, 2, 128, 128, starts=[300, 5], window=None, n_splits=2, gsplits=2, write_kv=False)
