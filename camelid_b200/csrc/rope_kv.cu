@@ -80,7 +80,10 @@ __global__ void rope_kv_from_partials_kernel(const float* __restrict__ partial, 
         for (int s0 = 0; s0 < n_splits; s0 += 8) {
             float t[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) t[i] = (s0 + i < n_splits) ? src[(size_t)(s0 + i) * split_stride + d] : 0.f;
+            for (int i = 0; i < 8; ++i) {       // unconditional loads of valid places: none waits for another
+                const float tv = src[(size_t)min(s0 + i, n_splits - 1) * split_stride + d];
+                t[i] = (s0 + i < n_splits) ? tv : 0.f;
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) v += t[i];
         }

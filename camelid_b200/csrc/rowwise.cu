@@ -65,22 +65,42 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TW* __restrict__ w, 
     const int src = rows_index ? rows_index[r] : r;
     float* xr = x + (size_t)src * hidden;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        float v = xr[c];
+    // Two columns of a thread at a time, and every load of both unconditional (of a valid
+    // place, the value dropped where it does not count): all of them are in flight before the
+    // first add. The adds stay in split order.
+    for (int cb = threadIdx.x; cb < hidden; cb += 2 * blockDim.x) {
+        const int cc[2] = {cb, cb + (int)blockDim.x};
+        const bool in[2] = {true, cc[1] < hidden};
+        float v[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) v[j] = xr[in[j] ? cc[j] : cb];
         if (partial) {
-            const float* pp = partial + (size_t)src * hidden + c;
-            // all loads of a group are issued before the first add, the adds stay in split order
-            for (int s0 = 0; s0 < n_splits; s0 += 16) {
-                float t[16];
+            for (int s0 = 0; s0 < n_splits; s0 += 8) {
+                float t[2][8];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) t[i] = (s0 + i < n_splits) ? pp[(size_t)(s0 + i) * split_stride] : 0.f;
+                for (int j = 0; j < 2; ++j) {
+                    const float* pp = partial + (size_t)src * hidden + (in[j] ? cc[j] : cb);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v += t[i];
+                    for (int i = 0; i < 8; ++i) {
+                        const float tv = pp[(size_t)min(s0 + i, n_splits - 1) * split_stride];
+                        t[j][i] = (s0 + i < n_splits) ? tv : 0.f;
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[j] += t[j][i];
             }
-            rowbuf[c] = v;
-            if (!rows_index) xr[c] = v;
         }
-        ss = fmaf(v, v, ss);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            if (!in[j]) continue;
+            if (partial) {
+                rowbuf[cc[j]] = v[j];
+                if (!rows_index) xr[cc[j]] = v[j];
+            }
+            ss = fmaf(v[j], v[j], ss);
+        }
     }
     ss = block_sum(ss, red);
     const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
