@@ -31,7 +31,7 @@
 #define TC_THREADS 192
 #define TC_WAIT_CYCLES 2000000000ll
 
-enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_SWIGLU = 3, TC_T_PARTIAL = 4, TC_T_SWIGLU = 5 };
+enum { TC_STORE = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_SWIGLU = 3, TC_T_PARTIAL = 4, TC_T_SWIGLU = 5, TC_ADD_NORM = 6 };
 
 struct TcParams {
     void* C;            // output (type by epilogue)
@@ -42,6 +42,20 @@ struct TcParams {
     int tiles_a, tiles_b, splits;   // work items
     int independent;    // operand that no earlier kernel writes (weights): 0 = A, 1 = B
     int* err;
+    // Two-block kernel only. A norm between two products is split over them: the product before
+    // it (TC_ADD_NORM) adds into the residual stream C, writes x_out = bfloat16(C * norm_w) and
+    // the sum of squares of its 256 columns of every row; the product after it reads rows of
+    // x_out and multiplies its own output rows by rsqrt(sum of those sums / in_hidden + in_eps),
+    // which is what the norm's scale would have done to its input rows.
+    const void* norm_w; // [rowsB] weight of the norm after this product
+    int norm_w_dtype;
+    bf16* x_out;        // [rowsA, rowsB] (row stride ldx)
+    long ldx;
+    float* out_sumsq;   // [tiles_b][rowsA]
+    const float* in_sumsq;  // [in_parts][rowsA], or null: the rows of A are complete
+    int in_parts;
+    float in_inv_hidden, in_eps;
+    int staged_ok;      // the outputs are aligned for 16-byte (float) and 8-byte (bfloat16) row pieces
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -408,6 +422,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.err, 2);
 }
 
+// TC_ADD_NORM, 16 columns of one row: C += accumulator; x_out = bfloat16(C * norm_w); returns the
+// sum of squares of the new C values (zero for columns beyond the matrix).
+__device__ __forceinline__ float tc_add_norm_chunk(const TcParams& p, const uint32_t (&r)[16], int rowA, int colB) {
+    if (rowA >= p.rowsA || colB >= p.rowsB) return 0.f;
+    const int n_ok = min(16, p.rowsB - colB);
+    float* dst = (float*)p.C + (size_t)rowA * p.ldc + colB;
+    bf16* xo = p.x_out + (size_t)rowA * p.ldx + colB;
+    float v[16], g[16];
+    const bool vec = n_ok == 16 && (((uintptr_t)dst & 15) == 0) && (((uintptr_t)xo & 15) == 0);
+    if (vec) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 o = reinterpret_cast<const float4*>(dst)[i];
+            v[4 * i] = o.x; v[4 * i + 1] = o.y; v[4 * i + 2] = o.z; v[4 * i + 3] = o.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = i < n_ok ? dst[i] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int col = colB + min(i, n_ok - 1);
+        g[i] = p.norm_w_dtype == CML_DTYPE_F32 ? ((const float*)p.norm_w)[col] : __bfloat162float(((const bf16*)p.norm_w)[col]);
+    }
+    float ssq = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        v[i] = i < n_ok ? v[i] + __uint_as_float(r[i]) : 0.f;
+        ssq = fmaf(v[i], v[i], ssq);
+    }
+    if (vec) {
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i] * g[2 * i], v[2 * i + 1] * g[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        reinterpret_cast<uint4*>(xo)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        reinterpret_cast<uint4*>(xo)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    } else {
+        for (int i = 0; i < n_ok; ++i) {
+            dst[i] = v[i];
+            xo[i] = __float2bfloat16_rn(v[i] * g[i]);
+        }
+    }
+    return ssq;
+}
+
 // ------------------------------------------------------------------------------------
 // Two blocks of a cluster on one tile (tcgen05 cta_group::2): D[256 x 256] = Arows[256, K] *
 // Brows[256, K]^T. Each block of the pair loads its own 128 rows of A and its own 128 rows of B
@@ -456,17 +520,19 @@ __device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t adesc
 }
 
 #define TC_PAIR_STAGES 6
-#define TC_PAIR_BN 256
-__host__ __device__ constexpr size_t tc_pair_smem_bytes() { return 1024 + (size_t)TC_PAIR_STAGES * (2 * TC_BM * 128) + 512; }
+#define TC_STAGE_LD 36       // floats between rows of an epilogue warp's staging tile (conflict-free 16-byte accesses)
+__host__ __device__ constexpr size_t tc_pair_smem_bytes() {
+    return 1024 + (size_t)TC_PAIR_STAGES * (2 * TC_BM * 128) + 512 + 4 * 32 * TC_STAGE_LD * sizeof(float);
+}
 
 // Work items are tiles of 256 A rows by 256 B rows, A tile fastest; cluster c takes items
 // c, c + clusters, ... p.tiles_a and p.tiles_b count those tiles. No split of K.
-template <int EPI>
+template <int EPI, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, TcParams p) {
-    constexpr int STAGES = TC_PAIR_STAGES, BN = TC_PAIR_BN;
-    constexpr uint32_t A_BYTES = TC_BM * 128, B_BYTES = TC_BM * 128;      // this block's halves of a stage
-    constexpr uint32_t TMEM_COLS = 512;                                    // two accumulators of 256 columns
+    constexpr int STAGES = TC_PAIR_STAGES;
+    constexpr uint32_t A_BYTES = TC_BM * 128, B_BYTES = (BN / 2) * 128;   // this block's halves of a stage
+    constexpr uint32_t TMEM_COLS = 512;                                    // two accumulators of BN columns; all of the SM's
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t smemA = base, smemB = base + STAGES * A_BYTES;
@@ -474,6 +540,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + STAGES * (A_BYTES + B_BYTES) + (2 * STAGES + 4) * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* stage = reinterpret_cast<float*>(gen_base + STAGES * (A_BYTES + B_BYTES) + 512);   // [4 warps][32][TC_STAGE_LD]
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     auto acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
@@ -520,7 +587,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
 
     auto item = [&](int w, int& a0, int& b0) {
         a0 = (w % p.tiles_a) * 256 + (int)rank * TC_BM;
-        b0 = (w / p.tiles_a) * BN + (int)rank * TC_BM;
+        b0 = (w / p.tiles_a) * BN + (int)rank * (BN / 2);
     };
 
     if (warp == 0) {
@@ -605,25 +672,107 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         for (int w = cluster; w < n_work && ok; w += n_clusters, ++j) {
             int a0, b0;
             item(w, a0, b0);
-            b0 -= (int)rank * TC_BM;                     // every block holds all 256 columns of its rows
+            b0 -= (int)rank * (BN / 2);                  // every block holds all BN columns of its rows
             const int buf = j & 1;
             const int rowA = a0 + q * 32 + lane;
             ok = mbar_wait(acc_full(buf), ((uint32_t)j >> 1) & 1u, abort_flag);
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
+            float row_scale = 1.f;                   // what the norm before this product left to it
+            if (p.in_sumsq != nullptr && rowA < p.rowsA) {
+                float ssq = 0.f;
+                for (int t = 0; t < p.in_parts; ++t) ssq += p.in_sumsq[(size_t)t * p.rowsA + rowA];
+                row_scale = 1.0f / sqrtf(ssq * p.in_inv_hidden + p.in_eps);
+            }
+            float ssq_out = 0.f;                     // sum of squares of this thread's row (columns that took the plain path)
+            float ssq_st[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // and of rows it * 4 + lane / 8, this lane's 4 columns (staged path)
+            constexpr bool CAN_STAGE = EPI == TC_STORE || EPI == TC_ADD_F32 || EPI == TC_ADD_NORM;
+            float* st = stage + q * 32 * TC_STAGE_LD;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[16], u[16];
                 tc_ld16_nowait(taddr + c, r);
                 tc_ld16_nowait(taddr + c + 16, u);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (EPI == TC_SWIGLU) {
+                if (p.in_sumsq != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        r[i] = __float_as_uint(__uint_as_float(r[i]) * row_scale);
+                        u[i] = __float_as_uint(__uint_as_float(u[i]) * row_scale);
+                    }
+                }
+                if (CAN_STAGE && p.staged_ok && b0 + c + 32 <= p.rowsB) {
+                    // Through shared memory, so that a warp's accesses to the output are whole
+                    // 128-byte pieces of four rows instead of 16 bytes of each of 32 rows.
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        *reinterpret_cast<uint4*>(st + lane * TC_STAGE_LD + 4 * i) = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+                        *reinterpret_cast<uint4*>(st + lane * TC_STAGE_LD + 16 + 4 * i) = make_uint4(u[4 * i], u[4 * i + 1], u[4 * i + 2], u[4 * i + 3]);
+                    }
+                    __syncwarp();
+                    const int cl = (lane & 7) * 4;
+                    const int col = b0 + c + cl;
+                    const int row_base = a0 + q * 32 + (lane >> 3);
+                    float g4[4] = {1.f, 1.f, 1.f, 1.f};
+                    if (EPI == TC_ADD_NORM) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            g4[i] = p.norm_w_dtype == CML_DTYPE_F32 ? ((const float*)p.norm_w)[col + i]
+                                                                    : __bfloat162float(((const bf16*)p.norm_w)[col + i]);
+                    }
+                    float4 o[8];
+                    if (EPI != TC_STORE) {
+#pragma unroll
+                        for (int it = 0; it < 8; ++it) {
+                            const int grow = min(row_base + it * 4, p.rowsA - 1);          // a valid place always
+                            o[it] = *reinterpret_cast<const float4*>((const float*)p.C + (size_t)grow * p.ldc + col);
+                        }
+                    }
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int grow = row_base + it * 4;
+                        float4 v = *reinterpret_cast<const float4*>(st + ((lane >> 3) + it * 4) * TC_STAGE_LD + cl);
+                        if (grow >= p.rowsA) continue;
+                        if (EPI == TC_STORE) {
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                            *reinterpret_cast<uint2*>((bf16*)p.C + (size_t)grow * p.ldc + col) =
+                                make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                        } else {
+                            v.x += o[it].x; v.y += o[it].y; v.z += o[it].z; v.w += o[it].w;
+                            *reinterpret_cast<float4*>((float*)p.C + (size_t)grow * p.ldc + col) = v;
+                            if (EPI == TC_ADD_NORM) {
+                                ssq_st[it] = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ssq_st[it]))));
+                                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * g4[0], v.y * g4[1]);
+                                __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * g4[2], v.w * g4[3]);
+                                *reinterpret_cast<uint2*>(p.x_out + (size_t)grow * p.ldx + col) =
+                                    make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                            }
+                        }
+                    }
+                    __syncwarp();
+                } else if (EPI == TC_SWIGLU) {
                     tc_epilogue_chunk<EPI>(p, r, u, rowA, b0 + c, 0, lane, 0);
+                } else if (EPI == TC_ADD_NORM) {
+                    ssq_out += tc_add_norm_chunk(p, r, rowA, b0 + c);
+                    ssq_out += tc_add_norm_chunk(p, u, rowA, b0 + c + 16);
                 } else {
                     tc_epilogue_chunk<EPI>(p, r, r, rowA, b0 + c, 0, lane, 0);
                     tc_epilogue_chunk<EPI>(p, u, u, rowA, b0 + c + 16, 0, lane, 0);
                 }
+            }
+            if (EPI == TC_ADD_NORM) {
+                // the staged sums: over the 8 lanes that share a row, then to the lane that owns the row
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    float t = ssq_st[it];
+                    t += __shfl_xor_sync(0xffffffffu, t, 1);
+                    t += __shfl_xor_sync(0xffffffffu, t, 2);
+                    t += __shfl_xor_sync(0xffffffffu, t, 4);
+                    t = __shfl_sync(0xffffffffu, t, (lane & 3) * 8);
+                    if ((lane >> 2) == it) ssq_out += t;
+                }
+                if (rowA < p.rowsA) p.out_sumsq[(size_t)(b0 / BN) * p.rowsA + rowA] = ssq_out;
             }
             tc_fence_before();
             __syncwarp();
@@ -707,6 +856,8 @@ extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, lo
     if (splits > p.num_kb) splits = p.num_kb;
     p.kb_per_split = (p.num_kb + splits - 1) / splits;
     p.err = err;
+    p.norm_w = nullptr; p.norm_w_dtype = 0; p.x_out = nullptr; p.ldx = 0; p.out_sumsq = nullptr;
+    p.in_sumsq = nullptr; p.in_parts = 0; p.in_inv_hidden = 0.f; p.in_eps = 0.f; p.staged_ok = 0;
     p.independent = (epilogue == TC_T_PARTIAL || epilogue == TC_T_SWIGLU) ? 0 : 1;
     p.tiles_a = (rowsA + TC_BM - 1) / TC_BM;
     p.tiles_b = (rowsB + bn - 1) / bn;
@@ -729,25 +880,36 @@ extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, lo
     return CML_ERR_BAD_SIZE;
 }
 
-template <int EPI>
-static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t s) {
+template <int EPI, int BN>
+static int launch_tc_pair2(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t s) {
     const size_t smem = tc_pair_smem_bytes();
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    e = launch_pdl(gemm_tc_pair_kernel<EPI>, grid, dim3(TC_THREADS), smem, s, ma, mb, p);
+    e = launch_pdl(gemm_tc_pair_kernel<EPI, BN>, grid, dim3(TC_THREADS), smem, s, ma, mb, p);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
+// Tiles of 256 x 128 were measured too: they move as much operand data per flop as a 128 x 256
+// tile of one block and ran at little more than half the rate of 256 x 256 on every shape tried.
+#define TC_PAIR_BN 256
+template <int EPI>
+static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t s) {
+    return launch_tc_pair2<EPI, TC_PAIR_BN>(ma, mb, p, grid, s);
+}
 
-// The same product as cml_gemm_tc with epilogues 0..3, on tiles of 256 x 256 that two blocks
-// of a cluster share (see gemm_tc_pair_kernel). For many rows of A: a tile covers 256 of them.
-extern "C" int cml_gemm_tc_pair(const void* A, long lda, int rowsA, const void* B, long ldb, int rowsB, int K, void* C,
-                                long ldc, int epilogue, int* err, void* stream) {
+struct TcPairNorm {
+    const void* norm_w; int norm_w_dtype; void* x_out; long ldx; float* out_sumsq;     // TC_ADD_NORM
+    const float* in_sumsq; int in_parts; int in_hidden; float in_eps;                  // rows of A still lack their scale
+};
+
+static int gemm_tc_pair_launch(const void* A, long lda, int rowsA, const void* B, long ldb, int rowsB, int K, void* C,
+                               long ldc, int epilogue, int* err, const TcPairNorm& nm, void* stream) {
     if (rowsA <= 0 || rowsB <= 0) return 0;
     if (K <= 0 || (K & 7)) return CML_ERR_BAD_SIZE;
+    constexpr int bn = TC_PAIR_BN;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, rowsA, K, lda, TC_BM);
     if (rc) return rc;
-    rc = make_map(&mb, B, rowsB, K, ldb, TC_BM);
+    rc = make_map(&mb, B, rowsB, K, ldb, bn / 2);
     if (rc) return rc;
     TcParams p;
     p.C = C; p.ldc = ldc; p.rowsA = rowsA; p.rowsB = rowsB;
@@ -756,8 +918,16 @@ extern "C" int cml_gemm_tc_pair(const void* A, long lda, int rowsA, const void* 
     p.err = err;
     p.independent = 1;
     p.tiles_a = (rowsA + 255) / 256;
-    p.tiles_b = (rowsB + TC_PAIR_BN - 1) / TC_PAIR_BN;
+    p.tiles_b = (rowsB + bn - 1) / bn;
     p.splits = 1;
+    p.norm_w = nm.norm_w; p.norm_w_dtype = nm.norm_w_dtype; p.x_out = (bf16*)nm.x_out; p.ldx = nm.ldx;
+    p.out_sumsq = nm.out_sumsq;
+    p.in_sumsq = nm.in_sumsq; p.in_parts = nm.in_parts;
+    p.in_inv_hidden = nm.in_hidden > 0 ? 1.0f / (float)nm.in_hidden : 0.f;
+    p.in_eps = nm.in_eps;
+    if (epilogue == TC_STORE) p.staged_ok = ((uintptr_t)C % 8 == 0) && (ldc % 4 == 0);
+    else p.staged_ok = ((uintptr_t)C % 16 == 0) && (ldc % 4 == 0) &&
+                       (epilogue != TC_ADD_NORM || (((uintptr_t)nm.x_out % 8 == 0) && (nm.ldx % 4 == 0)));
     const long work = (long)p.tiles_a * p.tiles_b;
     if (work > 0x7fffffffL) return CML_ERR_BAD_SIZE;
     int sms = 148;
@@ -770,6 +940,34 @@ extern "C" int cml_gemm_tc_pair(const void* A, long lda, int rowsA, const void* 
         case TC_STORE_F32: return launch_tc_pair<TC_STORE_F32>(ma, mb, p, grid, s);
         case TC_ADD_F32: return launch_tc_pair<TC_ADD_F32>(ma, mb, p, grid, s);
         case TC_SWIGLU: return launch_tc_pair<TC_SWIGLU>(ma, mb, p, grid, s);
+        case TC_ADD_NORM: return launch_tc_pair<TC_ADD_NORM>(ma, mb, p, grid, s);
     }
     return CML_ERR_BAD_SIZE;
+}
+
+// The same product as cml_gemm_tc with epilogues 0..3, on tiles of 256 x 256 that two blocks
+// of a cluster share (see gemm_tc_pair_kernel). For many rows of A: a tile covers 256 of them.
+// in_sumsq (may be null): float [in_parts][rowsA]; the rows of A came out of a norm without
+// their scale rsqrt(sum_t in_sumsq[t][row] / in_hidden + in_eps), and this product applies it
+// to its output rows instead (before the SwiGLU of that epilogue).
+extern "C" int cml_gemm_tc_pair(const void* A, long lda, int rowsA, const void* B, long ldb, int rowsB, int K, void* C,
+                                long ldc, int epilogue, int* err, const float* in_sumsq, int in_parts, int in_hidden,
+                                float in_eps, void* stream) {
+    if (epilogue < TC_STORE || epilogue > TC_SWIGLU) return CML_ERR_BAD_SIZE;
+    if (in_sumsq && (in_parts < 1 || in_hidden < 1)) return CML_ERR_BAD_SIZE;
+    TcPairNorm nm = {nullptr, 0, nullptr, 0, nullptr, in_sumsq, in_parts, in_hidden, in_eps};
+    return gemm_tc_pair_launch(A, lda, rowsA, B, ldb, rowsB, K, C, ldc, epilogue, err, nm, stream);
+}
+
+// C [rowsA, rowsB] float (the residual stream) += A B^T, and for the norm that reads C next:
+// x_out [rowsA, rowsB] bfloat16 = C * norm_w (without the rows' scale) and out_sumsq
+// [ceil(rowsB / 256)][rowsA] = the sum of squares of each row's 256 columns of a tile. The
+// product that reads x_out passes out_sumsq as its in_sumsq.
+extern "C" int cml_gemm_tc_pair_add_norm(const void* A, long lda, int rowsA, const void* B, long ldb, int rowsB, int K,
+                                         float* C, long ldc, int* err, const void* norm_w, int norm_w_dtype,
+                                         void* x_out, long ldx, float* out_sumsq, void* stream) {
+    if (!norm_w || !x_out || !out_sumsq) return CML_ERR_BAD_SIZE;
+    if (norm_w_dtype != CML_DTYPE_F32 && norm_w_dtype != CML_DTYPE_BF16) return CML_ERR_BAD_DTYPE;
+    TcPairNorm nm = {norm_w, norm_w_dtype, x_out, ldx, out_sumsq, nullptr, 0, 0, 0.f};
+    return gemm_tc_pair_launch(A, lda, rowsA, B, ldb, rowsB, K, C, ldc, TC_ADD_NORM, err, nm, stream);
 }

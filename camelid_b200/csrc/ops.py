@@ -33,7 +33,10 @@ _SIGNATURES = {
     ("gemm_tc", "cml_gemm_tc"): [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_void_p, c_long, c_int, c_int,
                                  c_int, c_void_p, c_void_p],
     ("gemm_tc", "cml_gemm_tc_pair"): [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_void_p, c_long, c_int,
-                                      c_void_p, c_void_p],
+                                      c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+    ("gemm_tc", "cml_gemm_tc_pair_add_norm"): [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_void_p, c_long,
+                                               c_void_p, c_void_p, c_int, c_void_p, c_long, c_void_p, c_void_p],
+    ("rowwise", "cml_scale_rows"): [c_void_p, c_int, c_long, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
     ("attention_simt", "cml_attn_paged_simt"): [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                                 c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -226,17 +229,66 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, epilogue: int, bn
                                         _p(c), ldc, epilogue, bn, splits, _p(err), _stream()), "gemm_tc")
 
 
-def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, epilogue: int, err: torch.Tensor):
+class RowScale:
+    """What a norm left undone when the product before it wrote the norm's output: the rows of
+    that output lack the factor rsqrt(sum over parts of sumsq[part][row] / hidden + eps).
+    The product that reads those rows applies it to its own output rows (a product is linear
+    in its input rows), or ``scale_rows`` applies it in place."""
+
+    def __init__(self, sumsq: torch.Tensor, hidden: int, eps: float):
+        assert sumsq.dim() == 2 and sumsq.dtype == torch.float32 and sumsq.is_contiguous()
+        self.sumsq, self.hidden, self.eps = sumsq, int(hidden), float(eps)
+
+
+def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, epilogue: int, err: torch.Tensor,
+                 row_scale: "RowScale | None" = None):
     """c[row of a][row of b] (op)= a @ b.T with epilogues 0..3 of ``gemm_tc``, on tiles of
     256 x 256 that the two blocks of a cluster share (tcgen05 cta_group::2): the kernel for
-    products with many rows of ``a``."""
+    products with many rows of ``a``. ``row_scale``: the scale the rows of ``a`` still lack."""
     _dev(a, b, c, err)
     if not gemm_tc_usable(a, b):
         raise KernelError("gemm_tc_pair: operands must be bfloat16 [rows, K] with K and the row strides multiples "
                           "of 8 and 16-byte aligned bases")
     assert c.stride(-1) == 1 and epilogue in (TC_STORE, TC_STORE_F32, TC_ADD_F32, TC_SWIGLU)
+    sumsq, parts, hidden, eps = None, 0, 0, 0.0
+    if row_scale is not None:
+        sumsq, hidden, eps = row_scale.sumsq, row_scale.hidden, row_scale.eps
+        _dev(sumsq)
+        parts = sumsq.shape[0]
+        assert sumsq.shape[1] == a.shape[0]
     _check(_fn("gemm_tc", "cml_gemm_tc_pair")(_p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], a.shape[1],
-                                             _p(c), c.stride(-2), epilogue, _p(err), _stream()), "gemm_tc_pair")
+                                             _p(c), c.stride(-2), epilogue, _p(err), _p(sumsq), parts, hidden, eps,
+                                             _stream()), "gemm_tc_pair")
+
+
+def gemm_tc_pair_add_norm(a: torch.Tensor, b: torch.Tensor, h: torch.Tensor, err: torch.Tensor, norm_w: torch.Tensor,
+                          eps: float, x_out: torch.Tensor, sumsq: torch.Tensor) -> RowScale:
+    """h (float32 [rows, out]) += a @ b.T, and the first half of the RMS norm that reads h next:
+    x_out = bfloat16(h * norm_w) and the sums of squares of every row, one per tile of 256
+    columns, in ``sumsq`` (float32 [ceil(out / 256), rows]). Returns the scale the rows of
+    x_out still lack."""
+    _dev(a, b, h, err, norm_w, x_out, sumsq)
+    if not gemm_tc_usable(a, b):
+        raise KernelError("gemm_tc_pair_add_norm: operands must be bfloat16 [rows, K] with K and the row strides "
+                          "multiples of 8 and 16-byte aligned bases")
+    rows, n = a.shape[0], b.shape[0]
+    assert h.dtype == torch.float32 and h.shape == (rows, n) and h.stride(1) == 1
+    assert x_out.dtype == torch.bfloat16 and x_out.shape == (rows, n) and x_out.stride(1) == 1
+    assert norm_w.numel() == n and norm_w.is_contiguous()
+    assert sumsq.dtype == torch.float32 and sumsq.is_contiguous() and sumsq.shape == ((n + 255) // 256, rows)
+    _check(_fn("gemm_tc", "cml_gemm_tc_pair_add_norm")(
+        _p(a), a.stride(0), rows, _p(b), b.stride(0), n, a.shape[1], _p(h), h.stride(0), _p(err), _p(norm_w),
+        dtype_code(norm_w.dtype), _p(x_out), x_out.stride(0), _p(sumsq), _stream()), "gemm_tc_pair_add_norm")
+    return RowScale(sumsq, n, eps)
+
+
+def scale_rows(x: torch.Tensor, row_scale: RowScale):
+    """x[r] *= the scale its rows still lack, in place."""
+    _dev(x, row_scale.sumsq)
+    assert x.dim() == 2 and x.stride(1) == 1 and row_scale.sumsq.shape[1] == x.shape[0]
+    _check(_fn("rowwise", "cml_scale_rows")(_p(x), dtype_code(x.dtype), x.stride(0), x.shape[0], x.shape[1],
+                                           _p(row_scale.sumsq), row_scale.sumsq.shape[0], row_scale.hidden,
+                                           row_scale.eps, _stream()), "scale_rows")
 
 
 def attn_tiling(n_heads: int, n_kv_heads: int, decode: bool) -> tuple[int, int, int]:

@@ -246,3 +246,32 @@ extern "C" int cml_add_partials(float* x, const float* partial, int n_splits, lo
     launch_pdl(add_partials_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, x, partial, n_splits, n);
     return cml_launch_status();
 }
+
+// x[r][:] *= rsqrt(sum_t sumsq[t][r] / hidden + eps): gives rows that came out of a norm without
+// their scale (see cml_gemm_tc_pair_add_norm) that scale, for a consumer that cannot apply it.
+template <typename T>
+__global__ void scale_rows_kernel(T* __restrict__ x, long ldx, int width, const float* __restrict__ sumsq, int parts,
+                                  int rows, float inv_hidden, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    float ssq = 0.f;
+    for (int t = 0; t < parts; ++t) ssq += sumsq[(size_t)t * rows + r];
+    const float scale = 1.0f / sqrtf(ssq * inv_hidden + eps);
+    T* row = x + (size_t)r * ldx;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) row[c] = from_f32<T>(to_f32(row[c]) * scale);
+}
+
+extern "C" int cml_scale_rows(void* x, int dtype, long ldx, int rows, int width, const float* sumsq, int parts, int hidden,
+                              float eps, void* stream) {
+    if (rows <= 0 || width <= 0) return 0;
+    if (parts < 1 || hidden < 1) return CML_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CML_DTYPE_F32)
+        launch_pdl(scale_rows_kernel<float>, dim3(rows), dim3(256), 0, s, (float*)x, ldx, width, sumsq, parts, rows, 1.0f / (float)hidden, eps);
+    else if (dtype == CML_DTYPE_BF16)
+        launch_pdl(scale_rows_kernel<bf16>, dim3(rows), dim3(256), 0, s, (bf16*)x, ldx, width, sumsq, parts, rows, 1.0f / (float)hidden, eps);
+    else
+        return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}

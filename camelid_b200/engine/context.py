@@ -84,6 +84,8 @@ class StepContext:
         self.entry = -1                 # schedule entry that is running
         self.cache_source = None        # entry whose keys and values the running entry reads
         self.pending = None             # float32 [splits, rows, hidden] still to be added to the residual stream
+        self.deferred = None            # (x, w, residual): a product into the residual stream not yet launched
+        self.row_scale = None           # ops.RowScale: what the rows of the last norm's output still lack
         # host-side knowledge (filled by the constructors below)
         self.h_slots: list = []
         self.h_start: list = []
@@ -161,9 +163,18 @@ class StepContext:
     def settle(self, residual: torch.Tensor) -> None:
         """Add what is pending to the residual stream now. A norm that reads the stream next does
         this itself in its own kernel; parts that touch the stream otherwise call this first."""
+        if self.deferred is not None:
+            from ..parts import linear
+            linear.run_deferred(self)
         if self.pending is not None:
             part, self.pending = self.pending, None
             ops.add_partials(residual, part)
+
+    def take_row_scale(self):
+        """The scale the rows of the last norm's output still lack (None if they are complete).
+        Whoever takes it applies it: a product may scale its own output rows instead."""
+        scale, self.row_scale = self.row_scale, None
+        return scale
 
     def buffer(self, name: str, shape: tuple, dtype: torch.dtype | None = None) -> torch.Tensor:
         return self.ws.get(name, shape, dtype or self.dtype)

@@ -232,6 +232,8 @@ class DecoderModel:
         if self._err is None:
             self._err = torch.zeros(1, dtype=torch.int32, device=self.device)
         ctx.pending = None
+        ctx.deferred = None
+        ctx.row_scale = None
         h = ctx.buffer("hidden", (ctx.n_rows, self.hidden_size), torch.float32)
         self.embedding.forward(ctx, ctx.tokens, h, self._err)
         for i, e in enumerate(self.schedule):
@@ -243,6 +245,7 @@ class DecoderModel:
             x = self.final_norm.forward(ctx, h, rows_index=ctx.want_rows, n_rows=ctx.n_want, name="final_normed")
             self.head.forward(ctx, x, logits)
         ctx.pending = None
+        ctx.deferred = None
         return logits
 
     def check_device_errors(self) -> None:

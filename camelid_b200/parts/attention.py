@@ -26,6 +26,7 @@ from .base import Part, TensorSpec, build_part, register_part, to_device
 @register_part("mixer", "attention")
 class GroupedQueryAttention(Part):
     graph_safe = True
+    accepts_row_scale = True
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
@@ -85,6 +86,10 @@ class GroupedQueryAttention(Part):
         table = ctx.block_table(group)
         width = self.q_width if borrow else self.q_width + 2 * self.kv_width
         pos = self.position
+        row_scale = ctx.take_row_scale()          # the rows of x may still lack their norm's scale
+        if row_scale is not None and n <= linear.DECODE_ROWS:
+            ops.scale_rows(x, row_scale)
+            row_scale = None
         part = linear.partial_sums(ctx, x, self.w_qkv[:width], "qkv_partial")
         out = ctx.buffer("attn_out", (n, self.q_width))
         splits = self._decode_splits(ctx, n, 1, True) if ctx.decode else 1
@@ -104,7 +109,7 @@ class GroupedQueryAttention(Part):
                                       write_kv=not borrow)
         else:
             qkv = ctx.buffer("qkv", (n, width))
-            linear.linear(ctx, x, self.w_qkv[:width], qkv, linear.STORE)
+            linear.linear(ctx, x, self.w_qkv[:width], qkv, linear.STORE, row_scale=row_scale)
             ops.rope_kv_write(qkv, ctx.row_pos, ctx.row_seq, table, k_pages, v_pages, pos.inv_freq, pos.rotary_dim,
                               self.num_heads, self.num_kv_heads, self.head_dim, write_kv=not borrow)
             q = qkv[:, :self.q_width]

@@ -44,6 +44,10 @@ class Part:
     # reads of the step, no allocation that must outlive the call): such a part can run
     # inside a captured CUDA graph. Parts that do not say so make the model step eagerly.
     graph_safe: bool = False
+    # True if ``forward`` takes ``ctx.take_row_scale()`` before it reads its input rows and
+    # applies the scale itself (to the rows, or to the output of a product of them). The norm
+    # before such a part may then leave its rows' scale to the part.
+    accepts_row_scale: bool = False
 
     def __init__(self, params: dict, prefix: str = ""):
         self.params = dict(params)

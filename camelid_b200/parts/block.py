@@ -42,11 +42,13 @@ class PreNormBlock(Part):
         # A built-in mixer or feed-forward may leave split sums pending on the context; the
         # norm that reads the stream next adds them. Parts from outside the library get a
         # settled stream.
-        x = self.norm1.forward(ctx, h)
+        # A part that declares ``accepts_row_scale`` takes ``ctx.take_row_scale()`` and applies
+        # it, which lets the norm before it run inside the product before that.
+        x = self.norm1.forward(ctx, h, allow_row_scale=self.mixer.accepts_row_scale and self.mixer.graph_safe)
         if not self.mixer.graph_safe:
             ctx.settle(h)
         self.mixer.forward(ctx, x, h)
-        x = self.norm2.forward(ctx, h)
+        x = self.norm2.forward(ctx, h, allow_row_scale=self.ffn.accepts_row_scale and self.ffn.graph_safe)
         if not self.ffn.graph_safe:
             ctx.settle(h)
         self.ffn.forward(ctx, x, h)

@@ -11,6 +11,7 @@ from .base import Part, TensorSpec, register_part, to_device
 @register_part("ffn", "swiglu")
 class SwiGLU(Part):
     graph_safe = True
+    accepts_row_scale = True
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
@@ -37,5 +38,5 @@ class SwiGLU(Part):
 
     def forward(self, ctx, x, residual):
         act = ctx.buffer("ffn_act", (ctx.n_rows, self.intermediate_size))
-        linear.linear(ctx, x, self.w_gate_up, act, linear.SWIGLU, self.group)
+        linear.linear(ctx, x, self.w_gate_up, act, linear.SWIGLU, self.group, row_scale=ctx.take_row_scale())
         linear.add_into_residual(ctx, act, self.w_down, residual, "down_partial")

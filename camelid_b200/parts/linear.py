@@ -14,6 +14,8 @@ go into the residual stream (``add_into_residual`` leaves them *pending* on the 
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..csrc import ops
@@ -46,6 +48,7 @@ def _bn_decode(rows: int) -> int:
     return 16 if rows <= 16 else (32 if rows <= 32 else 64)
 
 
+FUSE_NORM = os.environ.get("CAMELID_FUSE_NORM", "1") != "0"   # the norm after a product of many rows runs inside it
 PAIR_ROWS = 128     # above this many rows the product runs on 256 x 256 tiles of two blocks
 
 
@@ -63,15 +66,23 @@ def _splits(out_features: int, k: int) -> int:
     return max(1, min((k + 63) // 64, round(SM_COUNT / tiles))) if tiles < SM_COUNT else 1
 
 
-def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, group: int = 0) -> None:
+def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, group: int = 0,
+           row_scale=None) -> None:
     """out (op)= x @ w.T, complete on return. For SWIGLU ``w`` is the packed [2N, K] matrix
-    and ``out`` is [M, N]."""
-    if ops.gemm_tc_usable(x, w):
-        rows = x.shape[0]
+    and ``out`` is [M, N]. ``row_scale`` (``ops.RowScale``): what the rows of ``x`` still lack;
+    the two-block kernel applies it to its output rows, any other path to ``x`` first."""
+    tc = ops.gemm_tc_usable(x, w)
+    rows = x.shape[0]
+    pair = tc and rows > PAIR_ROWS          # tiles of 256 x 256 on two blocks: less operand traffic per flop
+    swiglu_tc = group == 16 and w.shape[0] % 32 == 0
+    if row_scale is not None and not (pair and (epilogue == STORE or (epilogue == SWIGLU and swiglu_tc))):
+        ops.scale_rows(x, row_scale)
+        row_scale = None
+    if tc:
         err = _err_word(x.device)
         if rows <= DECODE_ROWS:
             bn = _bn_decode(rows)
-            if epilogue == SWIGLU and group == 16 and w.shape[0] % 32 == 0:
+            if epilogue == SWIGLU and swiglu_tc:
                 ops.gemm_tc(w, x, out, ops.TC_T_SWIGLU, bn, 1, err)
                 return
             if epilogue == STORE_F32:
@@ -79,18 +90,17 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
                 return
         else:
             bn = _bn_prefill(rows, w.shape[0])
-            pair = rows > PAIR_ROWS          # tiles of 256 x 256 on two blocks: less operand traffic per flop
             if epilogue == SWIGLU:
-                if group == 16 and w.shape[0] % 32 == 0:
+                if swiglu_tc:
                     if pair:
-                        ops.gemm_tc_pair(x, w, out, ops.TC_SWIGLU, err)
+                        ops.gemm_tc_pair(x, w, out, ops.TC_SWIGLU, err, row_scale)
                     else:
                         ops.gemm_tc(x, w, out, ops.TC_SWIGLU, bn, 1, err)
                     return
             else:
                 epi = {STORE: ops.TC_STORE, STORE_F32: ops.TC_STORE_F32, ADD_F32: ops.TC_ADD_F32}[epilogue]
                 if pair:
-                    ops.gemm_tc_pair(x, w, out, epi, err)
+                    ops.gemm_tc_pair(x, w, out, epi, err, row_scale)
                 else:
                     ops.gemm_tc(x, w, out, epi, bn, 1, err)
                 return
@@ -112,13 +122,43 @@ def partial_sums(ctx, x: torch.Tensor, w: torch.Tensor, name: str):
 
 def add_into_residual(ctx, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, name: str) -> None:
     """residual += x @ w.T. On the decode path the split sums are left pending on the context
-    and the next norm adds them; otherwise the product's epilogue adds."""
+    and the next norm adds them. A product of many rows on the tensor cores is *deferred*: the
+    norm that reads the stream next launches it with the weight half of that norm in its
+    epilogue (``product_add_norm``), or plainly where that does not fit. Otherwise the product's
+    own epilogue adds now."""
     ctx.settle(residual)
     part = partial_sums(ctx, x, w, name)
     if part is not None:
         ctx.pending = part
+    elif FUSE_NORM and x.shape[0] > PAIR_ROWS and ops.gemm_tc_usable(x, w) and residual.dtype == torch.float32:
+        ctx.deferred = (x, w, residual)
     else:
         linear(ctx, x, w, residual, ADD_F32)
+
+
+def run_deferred(ctx) -> None:
+    """Launch a deferred product with its plain epilogue: the residual stream is complete after."""
+    if ctx.deferred is not None:
+        (x, w, residual), ctx.deferred = ctx.deferred, None
+        linear(ctx, x, w, residual, ADD_F32)
+
+
+def product_add_norm(ctx, residual: torch.Tensor, norm_w: torch.Tensor, eps: float, out: torch.Tensor) -> bool:
+    """If a product into ``residual`` is deferred and the sizes allow: one launch that runs it,
+    adds it into ``residual`` and writes ``out`` = bfloat16(residual * norm_w), and the rows'
+    scale rsqrt(mean(residual^2) + eps) goes to ``ctx.row_scale`` for the reader of ``out`` to
+    apply. False (and nothing done) otherwise."""
+    if ctx.deferred is None:
+        return False
+    x, w, res = ctx.deferred
+    rows, n = x.shape[0], w.shape[0]
+    if (res is not residual or out.dtype != torch.bfloat16 or out.shape != (rows, n) or residual.shape != (rows, n)
+            or norm_w.dtype not in (torch.float32, torch.bfloat16) or norm_w.numel() != n):
+        return False
+    ctx.deferred = None
+    sumsq = ctx.buffer("norm_sumsq", ((n + 255) // 256, rows), torch.float32)
+    ctx.row_scale = ops.gemm_tc_pair_add_norm(x, w, residual, _err_word(x.device), norm_w, eps, out, sumsq)
+    return True
 
 
 def pack_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int) -> torch.Tensor:

@@ -6,6 +6,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
+from . import linear
 from .base import Part, TensorSpec, register_part, to_device
 
 
@@ -28,9 +29,17 @@ class RMSNorm(Part):
         keep = None if w.dtype == torch.float32 else dtype
         self.weight = to_device(w, device, keep)
 
-    def forward(self, ctx, h, rows_index=None, n_rows=None, name="normed"):
+    def forward(self, ctx, h, rows_index=None, n_rows=None, name="normed", allow_row_scale=False):
+        """The normalised rows of ``h``. With ``allow_row_scale`` the caller promises that whoever
+        reads the result takes ``ctx.take_row_scale()`` and applies it: then a product into ``h``
+        that is still deferred runs here together with the residual add and the weight half of
+        this norm, and only the rows' scale is left to the reader."""
         rows = h.shape[0] if n_rows is None else n_rows
         out = ctx.buffer(name, (rows, self.hidden_size))
+        if ctx.deferred is not None:
+            if allow_row_scale and rows_index is None and linear.product_add_norm(ctx, h, self.weight, self.eps, out):
+                return out
+            linear.run_deferred(ctx)
         pending, ctx.pending = ctx.pending, None            # split sums still to be added to h: added here
         ops.rmsnorm(h, self.weight, self.eps, out, rows_index, pending)
         return out

@@ -158,6 +158,53 @@ def test_pair_tiles_swiglu(cuda, m, inter, k):
     ref = torch.nn.functional.silu(gate) * (x.cpu().double() @ wu.double().T)
     err = torch.zeros(1, dtype=torch.int32, device=cuda)
     out = torch.full((m, inter), float("nan"), dtype=BF, device=cuda)
-    ops.gemm_tc_pair(x, packed, out, ops.TC_SWIGLU, err)
-    assert rel_err(out.cpu(), ref) <= 2 ** -7
+    for bn in (128, 256):
+        out.fill_(float("nan"))
+        ops.gemm_tc_pair(x, packed, out, ops.TC_SWIGLU, err)
+        assert rel_err(out.cpu(), ref) <= 2 ** -7, bn
+    assert int(err) == 0
+
+
+@pytest.mark.parametrize("w_dtype", [torch.float32, BF])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 520, 136), (2048, 2048, 512), (513, 72, 200)])
+def test_pair_product_with_the_norm_split_over_two_products(cuda, m, n, k, w_dtype):
+    """The product before a norm adds into the residual stream and writes the rows times the
+    norm's weight and their sums of squares; the product after it applies the rows' scale to its
+    output. Together: the plain residual add, RMS norm and product."""
+    import plain_llama as pl
+    ops = _ops()
+    a, w, prod = _operands(m, n, k, cuda, seed=6)
+    g = torch.Generator().manual_seed(8)
+    h0 = torch.randn(m, n, generator=g)
+    norm_w = (1 + 0.1 * torch.randn(n, generator=g)).to(w_dtype)
+    eps = 1e-5
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    h = h0.to(cuda)
+    x_out = torch.full((m, n), float("nan"), dtype=BF, device=cuda)
+    sumsq = torch.full(((n + 255) // 256, m), float("nan"), device=cuda)
+    scale = ops.gemm_tc_pair_add_norm(a, w, h, err, norm_w.to(cuda), eps, x_out, sumsq)
+    want_h = h0.double() + prod
+    assert rel_err(h.cpu(), want_h) <= 1e-5
+    assert rel_err(scale.sumsq.sum(dim=0).cpu(), (want_h * want_h).sum(dim=-1)) <= 1e-5
+    normed = pl.rms_norm(want_h, norm_w.double(), eps)
+    # scaled in place: the norm's output
+    x_done = x_out.clone()
+    ops.scale_rows(x_done, scale)
+    assert rel_err(x_done.cpu(), normed) <= 2 ** -7
+    # or left to the next product, which scales its own output rows
+    n2 = 264 if n % 8 == 0 else 64
+    w2 = (torch.randn(n2, n, generator=g) / math.sqrt(n)).to(BF).to(cuda)
+    ref2 = normed.to(BF).double() @ w2.cpu().double().T
+    out2 = torch.full((m, n2), float("nan"), dtype=BF, device=cuda)
+    ops.gemm_tc_pair(x_out, w2, out2, ops.TC_STORE, err, scale)
+    assert rel_err(out2.cpu(), ref2) <= 2 ** -6
+    from camelid_b200.parts.linear import pack_gate_up
+    inter = 48
+    wg = (torch.randn(inter, n, generator=g) / math.sqrt(n)).to(BF)
+    wu = (torch.randn(inter, n, generator=g) / math.sqrt(n)).to(BF)
+    xn = normed.to(BF).double()
+    ref3 = torch.nn.functional.silu(xn @ wg.double().T) * (xn @ wu.double().T)
+    out3 = torch.full((m, inter), float("nan"), dtype=BF, device=cuda)
+    ops.gemm_tc_pair(x_out, pack_gate_up(wg, wu, 16).to(cuda), out3, ops.TC_SWIGLU, err, scale)
+    assert rel_err(out3.cpu(), ref3) <= 2 ** -6
     assert int(err) == 0

@@ -78,3 +78,20 @@ def test_1b_widths_unequal_prompts_then_decode(cuda, shape_1b, dtype):
 def test_3b_widths_head_size_128(cuda, shape_3b, dtype):
     folder, cfg = shape_3b
     _check(folder, cfg, dtype, lens=[200, 65], decode=2)
+
+
+def test_norm_inside_the_product_before_it_or_on_its_own(cuda, shape_1b, monkeypatch):
+    """A prefill of many rows runs each norm inside the products around it (the one before adds
+    into the residual stream and writes the rows times the norm's weight, the one after applies
+    the rows' scale); with that switched off the norm is a kernel of its own. Both match the
+    plain implementation, and a launch count shows that the switch does switch."""
+    from camelid_b200.csrc import ops
+    from camelid_b200.parts import linear
+    folder, cfg = shape_1b
+    counts = []
+    for fuse in (True, False):
+        monkeypatch.setattr(linear, "FUSE_NORM", fuse)
+        before = ops.launch_count()
+        _check(folder, cfg, "bfloat16", lens=[300, 140], decode=1)
+        counts.append(ops.launch_count() - before)
+    assert counts[0] < counts[1]
