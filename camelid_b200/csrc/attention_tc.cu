@@ -8,8 +8,10 @@
 // P V by tcgen05.mma accumulates the output rows in a second tensor-memory buffer, which the
 // same threads rescale in place on the rare pages where a row's reference maximum moves. Keys and values come straight from the cache pages by TMA (128-byte
 // swizzle, no multicast); V is used as an MN-major operand, so no transpose is stored.
-// MMA of the next page's S overlaps the softmax of this page; several blocks per SM overlap
-// the rest.
+// MMA of the next page's S overlaps the softmax of this page; two blocks per SM (head size 64)
+// overlap the rest: a softmax thread keeps its 64 scores and 32 packed probabilities in
+// registers, and a third block per SM would make them spill. Blocks are numbered so that the
+// tiles that see the most keys start first, for all kv heads alike.
 //
 // It replaces attention_batched / flash_pref_* (src/cuda_resident.rs:1994, :2523-2705);
 // the arithmetic is the reference's (src/inference.rs:23945-24025): (q . k) * scale, running
@@ -23,13 +25,14 @@
 
 #define AT_ROWS 128
 #define AT_KEYS 64
-#define AT_STAGES 2
+#define AT_STAGES 4
 #define AT_THREADS 192
 #define AT_WAIT_CYCLES 2000000000ll
 
 struct AtParams {
     AttnParams a;
     int* err;
+    int n_tiles;
 };
 
 __device__ __forceinline__ uint32_t at_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -67,6 +70,11 @@ __device__ __forceinline__ void at_tma_load_2d(uint32_t dst, const CUtensorMap* 
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ float at_max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 __device__ __forceinline__ void at_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void at_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -152,7 +160,7 @@ __device__ __forceinline__ uint32_t at_swizzled(int row, int chunk) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(AT_THREADS, HD == 64 ? 3 : 1)
+__global__ void __launch_bounds__(AT_THREADS, HD == 64 ? 2 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, AtParams ap) {
     const AttnParams& p = ap.a;
     constexpr int KB = HD / 64;                               // 64-column blocks of a head
@@ -177,11 +185,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                    pv_full = s_full + 24, q_ready = s_full + 32;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = gridDim.x - 1 - blockIdx.x;              // the tiles that see the most keys first
+    // Blocks start in the order of blockIdx.x: the tiles that see the most keys come first, for
+    // every kv head alike, so that no long tile starts late.
+    const int n_cols = p.n_kv_heads * p.head_chunks;
+    const int tile = ap.n_tiles - 1 - (int)(blockIdx.x / n_cols);
+    const int col = (int)(blockIdx.x % n_cols);
     const int seq = p.tile_seq[tile];
     const int q0 = p.tile_q0[tile];
-    const int kvh = blockIdx.y / p.head_chunks;
-    const int chunk = blockIdx.y - kvh * p.head_chunks;
+    const int kvh = col / p.head_chunks;
+    const int chunk = col - kvh * p.head_chunks;
     const int start = p.seq_start[seq];
     const int n_new = p.seq_new[seq];
     const int row0 = p.seq_row0[seq];
@@ -338,16 +350,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
             const int key0 = t * AT_KEYS;
             // A page that every row of the block sees whole needs no masking (block-uniform test).
             const bool page_whole = key0 + AT_KEYS <= start + q0 + 1 && key0 >= blk_lo;
-            if (page_whole) {
-#pragma unroll
-                for (int c = 0; c < AT_KEYS; ++c) mx = fmaxf(mx, s[c]);
-            } else {
+            if (!page_whole) {
 #pragma unroll
                 for (int c = 0; c < AT_KEYS; ++c) {
                     const bool in = valid && key0 + c <= pos && key0 + c >= lo;
                     s[c] = in ? s[c] : -CUDART_INF_F;
-                    mx = fmaxf(mx, s[c]);
                 }
+            }
+            {   // eight independent chains of three-input maxima, not one chain of 64
+                float mx8[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) mx8[j] = at_max3(s[j], s[8 + j], s[16 + j]);
+#pragma unroll
+                for (int c = 24; c + 16 <= AT_KEYS; c += 16)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) mx8[j] = at_max3(mx8[j], s[c + j], s[c + 8 + j]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) mx8[j] = fmaxf(mx8[j], s[56 + j]);
+                mx = fmaxf(at_max3(mx8[0], mx8[1], mx8[2]), at_max3(mx8[3], mx8[4], mx8[5]));
+                mx = at_max3(mx, mx8[6], mx8[7]);
             }
             float corr = 1.0f;
             if (mx > m && (m == -CUDART_INF_F || (mx - m) * sl2 > 8.0f)) {
@@ -356,15 +377,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
             }
             const float m_use = (m == -CUDART_INF_F) ? 0.f : m;
             uint32_t pk[AT_KEYS / 2];
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};       // four chains of adds, always in this order
             const float neg = -m_use * sl2;
 #pragma unroll
             for (int c = 0; c < AT_KEYS; c += 2) {
                 const float e0 = at_exp2(fmaf(s[c], sl2, neg)), e1 = at_exp2(fmaf(s[c + 1], sl2, neg));
-                sum += e0 + e1;
+                sum4[(c >> 1) & 3] += e0 + e1;
                 __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
                 pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
             }
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             if (it > 0) {
                 // The product of the page before is complete: its P tile is free, and the output
                 // rows in tensor memory can be rescaled if a row of this warp moved its reference.
@@ -472,10 +494,12 @@ static int at_make_map(CUtensorMap* map, const void* base, long rows, int head_d
 }
 
 template <int HD>
-static int at_launch(const CUtensorMap& mk, const CUtensorMap& mv, const AtParams& ap, int n_tiles, cudaStream_t s) {
+static int at_launch(const CUtensorMap& mk, const CUtensorMap& mv, AtParams ap, int n_tiles, cudaStream_t s) {
     constexpr int KB = HD / 64;
     constexpr size_t smem = 1024 + (size_t)AT_ROWS * 128 * KB + AT_ROWS * 128 + 2 * AT_STAGES * AT_KEYS * 128 * KB + 256;
-    dim3 grid(n_tiles, ap.a.n_kv_heads * ap.a.head_chunks, 1);
+    if ((long)n_tiles * ap.a.n_kv_heads * ap.a.head_chunks > 0x7fffffffL) return CML_ERR_BAD_SIZE;
+    ap.n_tiles = n_tiles;
+    dim3 grid((unsigned)(n_tiles * ap.a.n_kv_heads * ap.a.head_chunks), 1, 1);
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     e = launch_pdl(attn_prefill_tc_kernel<HD>, grid, dim3(AT_THREADS), smem, s, mk, mv, ap);
