@@ -370,3 +370,66 @@ def ablate_decode(batch: int = 8, prompt_tokens: int = 2048, dtype: str = "bfloa
         v["us_per_step"] = round(v["us_per_step"], 1)
     return {"batch": batch, "prompt_tokens": prompt_tokens, "dtype": dtype, "model": shape["name"],
             "layers": cfg["num_hidden_layers"], "steps": out}
+
+
+def ablate_prefill(tokens: int = 2048, dtype: str = "bfloat16", layers: int | None = None, config_index: int = 2) -> dict:
+    """Where a prefill step's time goes: the step of one prompt is timed whole (as
+    ``measure_prefill`` does) and again with one kind of kernel switched off at a time; the
+    results are then wrong, only the time is read. The difference is that kernel's cost in
+    place, with programmatic dependent launch overlapping its neighbours."""
+    from . import api
+    from .csrc import ops
+    shape = SHAPES[config_index]
+    cfg = config_for(config_index, layers)
+    lm = api.from_random(cfg, seed=shape["seed"], dtype=dtype)
+    rng = np.random.default_rng(0)
+
+    def timed():
+        return {"us_per_step": measure_prefill(lm, cfg, tokens, rng)["ms"] * 1e3}
+
+    def noop(*_a, **_k):
+        return None
+
+    out = {"full": timed()}
+    for name in ("attn_prefill_tc", "attn_paged_mma", "rope_kv_write", "rmsnorm", "embed_gather"):
+        real = getattr(ops, name)
+        setattr(ops, name, noop)
+        out["without " + name] = timed()
+        setattr(ops, name, real)
+    real_pair, real_add_norm, real_gemm = ops.gemm_tc_pair, ops.gemm_tc_pair_add_norm, ops.gemm_tc
+    hidden, inter = cfg["hidden_size"], cfg["intermediate_size"]
+    qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
+
+    def pair_without(pred):
+        def f(a, b, c, epi, err, row_scale=None):
+            return None if pred(b, epi) else real_pair(a, b, c, epi, err, row_scale)
+        return f
+
+    def add_norm_without(pred):
+        def f(a, b, h, err, norm_w, eps, x_out, sumsq):
+            if pred(b):
+                return ops.RowScale(sumsq, b.shape[0], eps)
+            return real_add_norm(a, b, h, err, norm_w, eps, x_out, sumsq)
+        return f
+
+    ops.gemm_tc_pair = pair_without(lambda b, e: b.shape[0] == qkv and e == ops.TC_STORE)
+    out["without qkv product"] = timed()
+    ops.gemm_tc_pair = pair_without(lambda b, e: e == ops.TC_SWIGLU)
+    out["without gate-up product"] = timed()
+    ops.gemm_tc_pair = real_pair
+    o_shape = (hidden, cfg["num_attention_heads"] * cfg["head_dim"])
+    ops.gemm_tc_pair_add_norm = add_norm_without(lambda b: tuple(b.shape) == o_shape)
+    out["without output product (+ norm)"] = timed()
+    ops.gemm_tc_pair_add_norm = add_norm_without(lambda b: tuple(b.shape) == (hidden, inter))
+    out["without down product (+ norm)"] = timed()
+    ops.gemm_tc_pair_add_norm = real_add_norm
+    ops.gemm_tc = lambda *a, **k: None
+    out["without output head"] = timed()
+    ops.gemm_tc_pair, ops.gemm_tc_pair_add_norm = pair_without(lambda b, e: True), add_norm_without(lambda b: True)
+    out["without any product"] = timed()
+    ops.gemm_tc_pair, ops.gemm_tc_pair_add_norm, ops.gemm_tc = real_pair, real_add_norm, real_gemm
+    full = out["full"]["us_per_step"]
+    for v in out.values():
+        v["cost_us"] = round(full - v["us_per_step"], 1)
+        v["us_per_step"] = round(v["us_per_step"], 1)
+    return {"tokens": tokens, "dtype": dtype, "model": shape["name"], "layers": cfg["num_hidden_layers"], "steps": out}

@@ -116,6 +116,11 @@ def cmd_random_model(args) -> int:
 
 def cmd_bench(args) -> int:
     from . import benchmark
+    if args.ablate and args.no_decode:
+        rec = benchmark.ablate_prefill(tokens=args.prefill_tokens, dtype=args.dtype, layers=args.layers,
+                                       config_index=args.config)
+        print(json.dumps(rec, indent=1), flush=True)
+        return 0
     if args.ablate:
         rec = benchmark.ablate_decode(batch=args.batch, prompt_tokens=args.prompt_tokens, dtype=args.dtype,
                                       layers=args.layers, config_index=args.config)
@@ -155,7 +160,8 @@ def main(argv=None) -> int:
     be.add_argument("--no-prefill", action="store_true")
     be.add_argument("--no-decode", action="store_true")
     be.add_argument("--ablate", action="store_true",
-                    help="time the decode step with one kind of kernel switched off at a time")
+                    help="time the decode step (with --no-decode: the prefill step) with one kind of kernel "
+                         "switched off at a time")
     args = ap.parse_args(argv)
     if args.command == "generate":
         return cmd_generate(args)

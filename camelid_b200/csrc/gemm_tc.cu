@@ -647,7 +647,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 ok = mbar_wait(acc_empty(buf), (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * 256);
                 for (int i = 0; i < p.num_kb && ok; ++i, ++g) {
                     const int s = g % STAGES;
                     const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
@@ -678,7 +678,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             ok = mbar_wait(acc_full(buf), ((uint32_t)j >> 1) & 1u, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
+            const uint32_t taddr = tmem_base + (uint32_t)(buf * 256) + ((uint32_t)(q * 32) << 16);
             float row_scale = 1.f;                   // what the norm before this product left to it
             if (p.in_sumsq != nullptr && rowA < p.rowsA) {
                 float ssq = 0.f;
@@ -888,12 +888,22 @@ static int launch_tc_pair2(const CUtensorMap& ma, const CUtensorMap& mb, const T
     e = launch_pdl(gemm_tc_pair_kernel<EPI, BN>, grid, dim3(TC_THREADS), smem, s, ma, mb, p);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
-// Tiles of 256 x 128 were measured too: they move as much operand data per flop as a 128 x 256
-// tile of one block and ran at little more than half the rate of 256 x 256 on every shape tried.
-#define TC_PAIR_BN 256
+// Tiles are 256 x 256, or 256 x 192 where that needs fewer rounds of clusters (see pair_tile_width).
+// 256 x 128 was measured too: it moves as much operand data per flop as a 128 x 256 tile of one
+// block and ran at little more than half the rate of 256 x 256 on every shape tried.
 template <int EPI>
-static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t s) {
-    return launch_tc_pair2<EPI, TC_PAIR_BN>(ma, mb, p, grid, s);
+static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int bn, dim3 grid, cudaStream_t s) {
+    return bn == 192 ? launch_tc_pair2<EPI, 192>(ma, mb, p, grid, s) : launch_tc_pair2<EPI, 256>(ma, mb, p, grid, s);
+}
+
+// Columns of a tile: 192 if the rounds of `clusters` clusters it needs, times its width, are
+// clearly fewer than with 256 (a narrower tile moves more operand data per flop), else 256.
+static int pair_tile_width(int rowsA, int rowsB, int clusters) {
+    auto cost = [&](int bn) {
+        const long tiles = (long)((rowsA + 255) / 256) * ((rowsB + bn - 1) / bn);
+        return ((tiles + clusters - 1) / clusters) * bn;
+    };
+    return cost(192) * 10 < cost(256) * 9 ? 192 : 256;
 }
 
 struct TcPairNorm {
@@ -905,7 +915,10 @@ static int gemm_tc_pair_launch(const void* A, long lda, int rowsA, const void* B
                                long ldc, int epilogue, int* err, const TcPairNorm& nm, void* stream) {
     if (rowsA <= 0 || rowsB <= 0) return 0;
     if (K <= 0 || (K & 7)) return CML_ERR_BAD_SIZE;
-    constexpr int bn = TC_PAIR_BN;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    // the norm's sums of squares are kept per 256 columns: that epilogue stays on the wide tile
+    const int bn = epilogue == TC_ADD_NORM ? 256 : pair_tile_width(rowsA, rowsB, sms / 2);
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, rowsA, K, lda, TC_BM);
     if (rc) return rc;
@@ -930,17 +943,15 @@ static int gemm_tc_pair_launch(const void* A, long lda, int rowsA, const void* B
                        (epilogue != TC_ADD_NORM || (((uintptr_t)nm.x_out % 8 == 0) && (nm.ldx % 4 == 0)));
     const long work = (long)p.tiles_a * p.tiles_b;
     if (work > 0x7fffffffL) return CML_ERR_BAD_SIZE;
-    int sms = 148;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
     const long clusters = work < sms / 2 ? work : sms / 2;
     dim3 grid((unsigned)(2 * clusters), 1, 1);
     cudaStream_t s = (cudaStream_t)stream;
     switch (epilogue) {
-        case TC_STORE: return launch_tc_pair<TC_STORE>(ma, mb, p, grid, s);
-        case TC_STORE_F32: return launch_tc_pair<TC_STORE_F32>(ma, mb, p, grid, s);
-        case TC_ADD_F32: return launch_tc_pair<TC_ADD_F32>(ma, mb, p, grid, s);
-        case TC_SWIGLU: return launch_tc_pair<TC_SWIGLU>(ma, mb, p, grid, s);
-        case TC_ADD_NORM: return launch_tc_pair<TC_ADD_NORM>(ma, mb, p, grid, s);
+        case TC_STORE: return launch_tc_pair<TC_STORE>(ma, mb, p, bn, grid, s);
+        case TC_STORE_F32: return launch_tc_pair<TC_STORE_F32>(ma, mb, p, bn, grid, s);
+        case TC_ADD_F32: return launch_tc_pair<TC_ADD_F32>(ma, mb, p, bn, grid, s);
+        case TC_SWIGLU: return launch_tc_pair<TC_SWIGLU>(ma, mb, p, bn, grid, s);
+        case TC_ADD_NORM: return launch_tc_pair<TC_ADD_NORM>(ma, mb, p, bn, grid, s);
     }
     return CML_ERR_BAD_SIZE;
 }

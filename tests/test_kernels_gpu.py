@@ -191,7 +191,8 @@ def test_attention_window_edges(cuda, dtype, window):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("n_heads,n_kv,hd,rot", [(4, 2, 16, 16), (3, 1, 48, 32), (2, 2, 64, 0)])
+@pytest.mark.parametrize("n_heads,n_kv,hd,rot", [(4, 2, 16, 16), (3, 1, 48, 32), (2, 2, 64, 0), (32, 8, 64, 64), (5, 1, 128, 64),
+                                                 (3, 3, 48, 24), (2, 1, 32, 6)])
 def test_rope_kv_write(cuda, dtype, n_heads, n_kv, hd, rot):
     from camelid_b200.csrc import ops
     from camelid_b200.parts.position import rotary_frequencies
