@@ -150,6 +150,22 @@ __host__ __device__ constexpr size_t tc_smem_bytes(int bn, bool deep) {
     return 1024 /*alignment slack*/ + (size_t)tc_stages(bn, deep) * (TC_BM * 128 + bn * 128) + 512 /*barriers*/;
 }
 
+// rsqrt(sum_t sumsq[t][row] / hidden + eps): the scale a row still lacks when the norm before a
+// product was split over the products around it. The sums are added in index order; every
+// load is unconditional (of a clamped place) so that all are in flight together.
+__device__ __forceinline__ float tc_row_scale(const float* __restrict__ sumsq, int parts, int rows, int row,
+                                              float inv_hidden, float eps) {
+    float ssq = 0.f;
+    for (int t0 = 0; t0 < parts; t0 += 16) {
+        float t[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) t[i] = sumsq[(size_t)min(t0 + i, parts - 1) * rows + row];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) ssq += (t0 + i < parts) ? t[i] : 0.f;
+    }
+    return 1.0f / sqrtf(ssq * inv_hidden + eps);
+}
+
 // One 16-column chunk of one accumulator row, already in registers, to its place in the output.
 template <int EPI>
 __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const uint32_t (&r)[16], const uint32_t (&u)[16],
@@ -680,11 +696,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             tc_fence_after();
             const uint32_t taddr = tmem_base + (uint32_t)(buf * 256) + ((uint32_t)(q * 32) << 16);
             float row_scale = 1.f;                   // what the norm before this product left to it
-            if (p.in_sumsq != nullptr && rowA < p.rowsA) {
-                float ssq = 0.f;
-                for (int t = 0; t < p.in_parts; ++t) ssq += p.in_sumsq[(size_t)t * p.rowsA + rowA];
-                row_scale = 1.0f / sqrtf(ssq * p.in_inv_hidden + p.in_eps);
-            }
+            if (p.in_sumsq != nullptr)
+                row_scale = tc_row_scale(p.in_sumsq, p.in_parts, p.rowsA, min(rowA, p.rowsA - 1), p.in_inv_hidden, p.in_eps);
             float ssq_out = 0.f;                     // sum of squares of this thread's row (columns that took the plain path)
             float ssq_st[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // and of rows it * 4 + lane / 8, this lane's 4 columns (staged path)
             constexpr bool CAN_STAGE = EPI == TC_STORE || EPI == TC_ADD_F32 || EPI == TC_ADD_NORM;

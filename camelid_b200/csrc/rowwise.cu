@@ -112,6 +112,89 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TW* __restrict__ w, 
     }
 }
 
+// The same with split sums to add, when the row is a whole number of 16-byte groups: a thread
+// owns groups of 4 columns, and the row's values and every split's reach it by cp.async into
+// shared memory, all in flight at once (loads into registers, one chain of adds behind them,
+// came out of the compiler as one round trip to L2 per few splits: 4 us of a 6 us launch). A
+// thread reads back only what it copied itself, so no barrier stands between copy and use.
+// Shared memory: the settled row [hidden], then [units_per_round][blockDim] groups.
+template <typename TW, typename TO>
+__global__ void rmsnorm_settle_kernel(float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
+                                      const int* __restrict__ rows_index, int hidden, float eps,
+                                      const float* __restrict__ partial, int n_splits, size_t split_stride,
+                                      int units_per_round) {
+    __shared__ float red[33];
+    extern __shared__ __align__(16) float dyn[];
+    float4* rowbuf = reinterpret_cast<float4*>(dyn);
+    const float4* stage = reinterpret_cast<const float4*>(dyn + hidden);
+    const uint32_t stage_u32 = (uint32_t)__cvta_generic_to_shared(dyn + hidden) + threadIdx.x * 16u;
+    const int groups = hidden >> 2;
+    const int g0 = threadIdx.x;
+    float wv[4] = {0.f, 0.f, 0.f, 0.f};             // the norm's weight does not depend on the kernels before
+    if (g0 < groups) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) wv[i] = to_f32(w[4 * g0 + i]);
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const int src = rows_index ? rows_index[r] : r;
+    float* xr = x + (size_t)src * hidden;
+    const float* pr = partial + (size_t)src * hidden;
+    const int units = n_splits + 1;                 // unit 0: the row itself; unit u: split u - 1
+    float ss = 0.f;
+    for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int u0 = 0; u0 < units; u0 += units_per_round) {
+            const int nu = min(units_per_round, units - u0);
+            for (int uu = 0; uu < nu; ++uu) {
+                const float* from = (u0 + uu == 0) ? xr + 4 * g : pr + (size_t)(u0 + uu - 1) * split_stride + 4 * g;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stage_u32 + (uint32_t)uu * blockDim.x * 16u), "l"(from) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            for (int uu = 0; uu < nu; ++uu) {       // the row, then the splits in order
+                const float4 t = stage[(size_t)uu * blockDim.x + threadIdx.x];
+                v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+            }
+        }
+        rowbuf[g] = v;
+        if (!rows_index) *reinterpret_cast<float4*>(xr + 4 * g) = v;
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+    TO* o = out + (size_t)r * hidden;
+    for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+        const float4 v = rowbuf[g];
+        float wc[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) wc[i] = g == g0 ? wv[i] : to_f32(w[4 * g + i]);
+        o[4 * g] = from_f32<TO>(v.x * scale * wc[0]);
+        o[4 * g + 1] = from_f32<TO>(v.y * scale * wc[1]);
+        o[4 * g + 2] = from_f32<TO>(v.z * scale * wc[2]);
+        o[4 * g + 3] = from_f32<TO>(v.w * scale * wc[3]);
+    }
+}
+
+template <typename TW, typename TO>
+static int launch_rmsnorm_settle(float* x, const void* w, void* out, const int* rows_index, int rows, int hidden, float eps,
+                                 const float* partial, int n_splits, long split_stride, cudaStream_t s) {
+    const int groups = hidden / 4;
+    int block = ((groups + 31) / 32) * 32;
+    if (block > 1024) block = 1024;
+    int upr = (96 * 1024) / (block * 16);
+    if (upr > n_splits + 1) upr = n_splits + 1;
+    if (upr < 1) upr = 1;
+    const size_t smem = (size_t)hidden * sizeof(float) + (size_t)upr * block * 16;
+    if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
+    cudaError_t e = cudaFuncSetAttribute(rmsnorm_settle_kernel<TW, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    launch_pdl(rmsnorm_settle_kernel<TW, TO>, dim3(rows), dim3(block), smem, s, x, (const TW*)w, (TO*)out, rows_index, hidden,
+               eps, partial, n_splits, (size_t)split_stride, upr);
+    return cml_launch_status();
+}
+
 // Many rows (prefill): one warp per row, the row held in registers, so the row is read once
 // and nothing waits on a block-wide barrier. VPL float4 per lane cover hidden = 128 * VPL.
 template <typename TW, typename TO, int VPL>
@@ -181,6 +264,14 @@ extern "C" int cml_rmsnorm(float* x, const void* w, int w_dtype, void* out, int 
         else if (w_dtype == CML_DTYPE_BF16 && out_dtype == CML_DTYPE_F32) done = launch_rmsnorm_rows<bf16, float>(x, w, out, rows_index, rows, hidden, eps, s);
         else if (w_dtype == CML_DTYPE_BF16 && out_dtype == CML_DTYPE_BF16) done = launch_rmsnorm_rows<bf16, bf16>(x, w, out, rows_index, rows, hidden, eps, s);
         if (done) return cml_launch_status();
+    }
+    if (partial && hidden % 4 == 0 && split_stride % 4 == 0 && (((uintptr_t)x | (uintptr_t)partial) & 15) == 0 &&
+        (size_t)hidden * sizeof(float) <= 100 * 1024) {
+        if (w_dtype == CML_DTYPE_F32 && out_dtype == CML_DTYPE_F32) return launch_rmsnorm_settle<float, float>(x, w, out, rows_index, rows, hidden, eps, partial, n_splits, split_stride, s);
+        if (w_dtype == CML_DTYPE_F32 && out_dtype == CML_DTYPE_BF16) return launch_rmsnorm_settle<float, bf16>(x, w, out, rows_index, rows, hidden, eps, partial, n_splits, split_stride, s);
+        if (w_dtype == CML_DTYPE_BF16 && out_dtype == CML_DTYPE_F32) return launch_rmsnorm_settle<bf16, float>(x, w, out, rows_index, rows, hidden, eps, partial, n_splits, split_stride, s);
+        if (w_dtype == CML_DTYPE_BF16 && out_dtype == CML_DTYPE_BF16) return launch_rmsnorm_settle<bf16, bf16>(x, w, out, rows_index, rows, hidden, eps, partial, n_splits, split_stride, s);
+        return CML_ERR_BAD_DTYPE;
     }
     // few rows (decode): many threads per row shorten the chain; many rows: several blocks per SM
     const int block = hidden >= 1024 ? (rows <= 256 ? 1024 : 256) : (hidden >= 512 ? 256 : 128);

@@ -99,25 +99,35 @@ def test_swiglu_transposed(cuda, rows, inter, k):
     assert rel_err(act.cpu(), ref) <= 2 ** -7
 
 
-def test_consumers_of_split_sums(cuda):
-    """The norm and the rotary kernel add the split sums themselves."""
+@pytest.mark.parametrize("rows,hidden,splits", [(5, 96, 3), (8, 2048, 9), (3, 517, 4), (2, 8192, 20), (1, 3000, 1), (6, 6, 2)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, BF])
+def test_consumers_of_split_sums(cuda, rows, hidden, splits, out_dtype):
+    """The norm adds the split sums itself, row first and then split by split (rows that are
+    whole 16-byte groups by cp.async through shared memory, others element by element)."""
     ops = _ops()
     import plain_llama as pl
     g = torch.Generator().manual_seed(0)
-    h = torch.randn(5, 96, generator=g).to(cuda)
-    part = torch.randn(3, 5, 96, generator=g).to(cuda)
-    w = (1 + 0.1 * torch.randn(96, generator=g)).to(cuda)
-    total = h.cpu().double() + part.cpu().double().sum(0)
-    out = torch.empty(5, 96, device=cuda)
+    h = torch.randn(rows, hidden, generator=g).to(cuda)
+    part = torch.randn(splits, rows, hidden, generator=g).to(cuda)
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(cuda)
+    total = h.cpu().double()
+    exact = h.cpu().clone()
+    for sp in range(splits):
+        total = total + part[sp].cpu().double()
+        exact = exact + part[sp].cpu()                                  # the kernel's order, in float32
+    tol = 1e-5 if out_dtype == torch.float32 else 2 ** -8
+    out = torch.empty(rows, hidden, dtype=out_dtype, device=cuda)
     h2 = h.clone()
     ops.rmsnorm(h2, w, 1e-5, out, None, part)
-    assert rel_err(h2.cpu(), total) <= 1e-6 and rel_err(out.cpu(), pl.rms_norm(total, w.cpu().double(), 1e-5)) <= 1e-5
-    idx = torch.tensor([4, 4, 1], dtype=torch.int32, device=cuda)
+    assert torch.equal(h2.cpu(), exact)
+    assert rel_err(out.cpu(), pl.rms_norm(total, w.cpu().double(), 1e-5)) <= tol
+    pick = [rows - 1, rows - 1, 0]
+    idx = torch.tensor(pick, dtype=torch.int32, device=cuda)
     h3 = h.clone()
-    out3 = torch.empty(3, 96, device=cuda)
+    out3 = torch.empty(3, hidden, dtype=out_dtype, device=cuda)
     ops.rmsnorm(h3, w, 1e-5, out3, idx, part)
     assert torch.equal(h3, h)                                           # gathered rows: nothing is written back
-    assert rel_err(out3.cpu(), pl.rms_norm(total[[4, 4, 1]], w.cpu().double(), 1e-5)) <= 1e-5
+    assert rel_err(out3.cpu(), pl.rms_norm(total[pick], w.cpu().double(), 1e-5)) <= tol
     h4 = h.clone()
     ops.add_partials(h4, part)
     assert rel_err(h4.cpu(), total) <= 1e-6
