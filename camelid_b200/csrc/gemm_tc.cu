@@ -701,13 +701,50 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             float ssq_out = 0.f;                     // sum of squares of this thread's row (columns that took the plain path)
             float ssq_st[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // and of rows it * 4 + lane / 8, this lane's 4 columns (staged path)
             constexpr bool CAN_STAGE = EPI == TC_STORE || EPI == TC_ADD_F32 || EPI == TC_ADD_NORM;
+            constexpr bool READS_C = EPI == TC_ADD_F32 || EPI == TC_ADD_NORM;
             float* st = stage + q * 32 * TC_STAGE_LD;
+            const int cl = (lane & 7) * 4;           // staged path: this lane's 4 columns of a chunk ...
+            const int row_base = a0 + q * 32 + (lane >> 3);   // ... of rows row_base + 4 * it
+            auto staged = [&](int c) { return CAN_STAGE && p.staged_ok && c < BN && b0 + c + 32 <= p.rowsB; };
+            // The loop is software-pipelined: while a chunk of 32 columns is worked on, the next
+            // chunk's accumulators are on their way from tensor memory and its values of C (and
+            // the norm's weight) from global memory. Either round trip, taken per chunk, was most
+            // of an epilogue that took as long as the products of a 2,048-deep tile.
+            auto fetch_c = [&](int c, float4 (&o)[8], float (&g4)[4]) {
+                if (!READS_C || !staged(c)) return;
+                const int col = b0 + c + cl;
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int grow = min(row_base + it * 4, p.rowsA - 1);          // a valid place always
+                    o[it] = *reinterpret_cast<const float4*>((const float*)p.C + (size_t)grow * p.ldc + col);
+                }
+                if (EPI == TC_ADD_NORM) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        g4[i] = p.norm_w_dtype == CML_DTYPE_F32 ? ((const float*)p.norm_w)[col + i]
+                                                                : __bfloat162float(((const bf16*)p.norm_w)[col + i]);
+                }
+            };
+            uint32_t r[16], u[16], rn[16], un[16];
+            float4 o[8], on[8];
+            float g4[4] = {1.f, 1.f, 1.f, 1.f}, g4n[4] = {1.f, 1.f, 1.f, 1.f};
+            tc_ld16_nowait(taddr, rn);
+            tc_ld16_nowait(taddr + 16, un);
+            fetch_c(0, on, g4n);
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
-                uint32_t r[16], u[16];
-                tc_ld16_nowait(taddr + c, r);
-                tc_ld16_nowait(taddr + c + 16, u);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 16; ++i) r[i] = rn[i], u[i] = un[i];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = on[i];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) g4[i] = g4n[i];
+                if (c + 32 < BN) {
+                    tc_ld16_nowait(taddr + c + 32, rn);
+                    tc_ld16_nowait(taddr + c + 48, un);
+                    fetch_c(c + 32, on, g4n);
+                }
                 if (p.in_sumsq != nullptr) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
@@ -715,7 +752,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                         u[i] = __float_as_uint(__uint_as_float(u[i]) * row_scale);
                     }
                 }
-                if (CAN_STAGE && p.staged_ok && b0 + c + 32 <= p.rowsB) {
+                if (staged(c)) {
                     // Through shared memory, so that a warp's accesses to the output are whole
                     // 128-byte pieces of four rows instead of 16 bytes of each of 32 rows.
 #pragma unroll
@@ -724,24 +761,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                         *reinterpret_cast<uint4*>(st + lane * TC_STAGE_LD + 16 + 4 * i) = make_uint4(u[4 * i], u[4 * i + 1], u[4 * i + 2], u[4 * i + 3]);
                     }
                     __syncwarp();
-                    const int cl = (lane & 7) * 4;
                     const int col = b0 + c + cl;
-                    const int row_base = a0 + q * 32 + (lane >> 3);
-                    float g4[4] = {1.f, 1.f, 1.f, 1.f};
-                    if (EPI == TC_ADD_NORM) {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            g4[i] = p.norm_w_dtype == CML_DTYPE_F32 ? ((const float*)p.norm_w)[col + i]
-                                                                    : __bfloat162float(((const bf16*)p.norm_w)[col + i]);
-                    }
-                    float4 o[8];
-                    if (EPI != TC_STORE) {
-#pragma unroll
-                        for (int it = 0; it < 8; ++it) {
-                            const int grow = min(row_base + it * 4, p.rowsA - 1);          // a valid place always
-                            o[it] = *reinterpret_cast<const float4*>((const float*)p.C + (size_t)grow * p.ldc + col);
-                        }
-                    }
 #pragma unroll
                     for (int it = 0; it < 8; ++it) {
                         const int grow = row_base + it * 4;
