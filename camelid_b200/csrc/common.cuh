@@ -39,22 +39,16 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-// Sum over the block in a fixed order (lane tree, then warps in index order), so the result
-// of a row does not depend on anything but the row. `red` holds at least 33 floats.
+// Sum over the block in a fixed order (lane tree inside a warp, then the same tree over the
+// warps' sums, which every warp computes for itself), so the result of a row does not depend
+// on anything but the row, and one barrier is enough. `red` holds at least 32 floats; a second
+// call may follow only after another barrier of the block (the settled-row loops have one).
 __device__ __forceinline__ float block_sum(float v, float* red) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
     v = warp_sum(v);
     if (lane == 0) red[warp] = v;
     __syncthreads();
-    if (warp == 0) {
-        float t = 0.f;
-        for (int i = 0; i < nwarps; ++i) t += red[i];
-        if (lane == 0) red[32] = t;
-    }
-    __syncthreads();
-    float out = red[32];
-    __syncthreads();
-    return out;
+    return warp_sum(lane < nwarps ? red[lane] : 0.f);
 }
 
 // Programmatic dependent launch: a kernel launched with `launch_pdl` may begin while the
