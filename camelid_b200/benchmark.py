@@ -350,7 +350,8 @@ def ablate_decode(batch: int = 8, prompt_tokens: int = 2048, dtype: str = "bfloa
     hidden, inter = cfg["hidden_size"], cfg["intermediate_size"]
     qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
     out = {"full": time_graph()}
-    for name in ("attn_decode_fused", "attn_paged_mma", "attn_paged_simt", "rope_kv_from_partials", "rmsnorm", "argmax_rows"):
+    for name in ("attn_decode_fused", "attn_paged_mma", "attn_paged_simt", "rope_kv_from_partials", "rope_kv_write", "rmsnorm",
+                 "argmax_rows", "gemm_tn_simt"):
         real = getattr(ops, name)
         setattr(ops, name, noop)
         out["without " + name] = time_graph()
