@@ -1,7 +1,9 @@
 """Generality of the parts, shown with toy parts that exist only here: a mixer with state of
 its own (no keys and values), registered, built and stepped without a change to the
 library's files; a schedule that names layers twice and lets an entry read another entry's
-cache; a layer with a window next to layers without one (two cache groups)."""
+cache; a layer with a window next to layers without one (two cache groups); a feed-forward
+that routes every row to one of several experts; a position encoding with a frequency law of
+its own, used by the library's attention."""
 import dataclasses
 
 import pytest
@@ -63,6 +65,64 @@ def _register_toys():
         layers[1] = dataclasses.replace(layers[1], mixer=PartSpec(mixer.kind, {**mixer.params, "window": 70}, mixer.prefix))
         return dataclasses.replace(base, layers=tuple(layers))
 
+    @register_part("ffn", "toy_top1_experts")
+    class Top1Experts(Part):
+        """Router logits in float32; every row goes to its best expert e and gets
+        softmax(logits)[e] * (x W_e^T). Plain torch on the device: not graph safe."""
+
+        def __init__(self, params, prefix=""):
+            super().__init__(params, prefix)
+            self.hidden, self.experts = params["hidden_size"], params["experts"]
+
+        def tensor_specs(self):
+            return {self.prefix + "router": TensorSpec((self.experts, self.hidden)),
+                    self.prefix + "experts": TensorSpec((self.experts * self.hidden, self.hidden))}
+
+        def load(self, tensors, device, dtype):
+            self.router = tensors[self.prefix + "router"].to(device=device, dtype=torch.float32)
+            self.w = tensors[self.prefix + "experts"].to(device=device, dtype=torch.float32).view(self.experts, self.hidden, self.hidden)
+
+        def forward(self, ctx, x, residual):
+            xf = x.float()
+            prob = torch.softmax(xf @ self.router.T, dim=-1)
+            best = prob.argmax(dim=-1)
+            for e in range(self.experts):
+                rows = (best == e).nonzero().flatten()
+                if rows.numel():
+                    residual[rows] += prob[rows, e, None] * (xf[rows] @ self.w[e].T)
+
+    @register_part("position", "toy_harmonic")
+    class HarmonicRotary(Part):
+        """A rotary encoding whose frequency i is 1 / (i + 2): the attention kernels rotate by
+        whatever frequencies the position part hands them."""
+        graph_safe = True
+
+        def __init__(self, params, prefix=""):
+            super().__init__(params, prefix)
+            self.rotary_dim = int(params["rotary_dim"])
+            self.inv_freq = None
+
+        def load(self, tensors, device, dtype):
+            self.inv_freq = (1.0 / (torch.arange(self.rotary_dim // 2, dtype=torch.float32) + 2.0)).to(device)
+
+    def routed_plan(cfg):
+        base = llama_plan(cfg)
+        layers = list(base.layers)
+        layers[0] = dataclasses.replace(layers[0], ffn=PartSpec("toy_top1_experts", {"hidden_size": cfg.hidden_size, "experts": 3},
+                                                                "model.layers.0.moe."))
+        return dataclasses.replace(base, layers=tuple(layers))
+
+    def harmonic_plan(cfg):
+        base = llama_plan(cfg)
+        layers = []
+        for layer in base.layers:
+            m = layer.mixer
+            pos = PartSpec("toy_harmonic", {"rotary_dim": cfg.head_dim // 2})          # half of every head rotates
+            layers.append(dataclasses.replace(layer, mixer=PartSpec(m.kind, {**m.params, "position": pos}, m.prefix)))
+        return dataclasses.replace(base, layers=tuple(layers))
+
+    register_architecture("ToyRoutedForCausalLM", LlamaConfig.from_dict, routed_plan)
+    register_architecture("ToyHarmonicForCausalLM", LlamaConfig.from_dict, harmonic_plan)
     register_architecture("ToyStateForCausalLM", LlamaConfig.from_dict, toy_plan)
     register_architecture("ToyTwiceForCausalLM", LlamaConfig.from_dict, twice_plan)
     register_architecture("ToyWindowForCausalLM", LlamaConfig.from_dict, window_plan)
@@ -143,10 +203,16 @@ def test_toy_mixer_with_state(cuda, dtype):
         assert_close(got[i], plain(seqs[i]), dtype, f"toy state, request {i}")      # request 2: a used slot starts from zero
 
 
+WIDE = {"hidden_size": 256, "head_dim": 64, "num_attention_heads": 4, "num_key_value_heads": 2, "intermediate_size": 256}
+
+
+@pytest.mark.parametrize("over", [{}, WIDE], ids=["head16", "head64"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_schedule_names_layers_twice_and_shares_a_cache(cuda, dtype):
+def test_schedule_names_layers_twice_and_shares_a_cache(cuda, dtype, over):
+    """head64 in bfloat16 decodes with the kernel that goes from the q/k/v product to the
+    attention output in one launch; the entry that borrows a cache must not write it."""
     _register_toys()
-    cfg, model, w = _model("ToyTwiceForCausalLM", dtype)
+    cfg, model, w = _model("ToyTwiceForCausalLM", dtype, **over)
     cache = model.new_cache(256)
     assert cache.k[0].shape[0] == 3 and cache.entry_kv[3] == cache.entry_kv[1]      # four runs, three caches
     seqs = [tokens(4, 70, 256), tokens(5, 33, 256), tokens(6, 66, 256)]
@@ -184,3 +250,54 @@ def test_window_layer_has_storage_of_its_own(cuda, dtype):
     got = _drive(model, seqs, cut=[200, 140])
     for i in range(3):
         assert_close(got[i], plain(seqs[i]), dtype, f"window, request {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_feed_forward_that_routes(cuda, dtype):
+    _register_toys()
+    cfg, model, w = _model("ToyRoutedForCausalLM", dtype, seed=5)
+    assert "model.layers.0.moe.router" in w and "model.layers.0.mlp.gate_proj.weight" not in w
+
+    def plain(ids):
+        ids = torch.as_tensor(ids)
+        pos = torch.arange(len(ids))
+        fr = pl.rope_frequencies(cfg)
+        h = pl.embedding(ids, w["model.embed_tokens.weight"], torch.float64)
+        p = "model.layers.0."
+        h = h + pl.attention_block(pl.rms_norm(h, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"]), w, p, cfg, pos, fr)[0]
+        n = pl.rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+        if dtype == "bfloat16":
+            n = n.to(torch.bfloat16).double()          # the toy reads the normed rows in the compute type
+        prob = torch.softmax(n @ w[p + "moe.router"].double().T, dim=-1)
+        best = prob.argmax(dim=-1)
+        experts = w[p + "moe.experts"].double().view(3, cfg["hidden_size"], cfg["hidden_size"])
+        h = h + torch.stack([prob[t, best[t]] * (experts[best[t]] @ n[t]) for t in range(len(ids))])
+        h, _ = pl.decoder_layer(h, w, 1, cfg, pos, fr)
+        return pl.rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"]) @ pl.output_weight(cfg, w).double().T
+
+    seqs = [tokens(7, 40, 256), tokens(8, 23, 256), tokens(9, 30, 256)]
+    got = _drive(model, seqs, cut=[17, 20])
+    for i in range(3):
+        assert_close(got[i], plain(seqs[i]), dtype, f"routed feed-forward, request {i}")
+
+
+@pytest.mark.parametrize("over", [{}, WIDE], ids=["head16", "head64"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_position_encoding_of_its_own(cuda, dtype, over):
+    _register_toys()
+    cfg, model, w = _model("ToyHarmonicForCausalLM", dtype, seed=6, **over)
+    rot = cfg["head_dim"] // 2
+    fr = (1.0 / (torch.arange(rot // 2, dtype=torch.float32) + 2.0)).numpy()
+
+    def plain(ids):
+        ids = torch.as_tensor(ids)
+        pos = torch.arange(len(ids))
+        h = pl.embedding(ids, w["model.embed_tokens.weight"], torch.float64)
+        for layer in range(cfg["num_hidden_layers"]):
+            h, _ = pl.decoder_layer(h, w, layer, cfg, pos, fr)
+        return pl.rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"]) @ pl.output_weight(cfg, w).double().T
+
+    seqs = [tokens(10, 70, 256), tokens(11, 33, 256), tokens(12, 66, 256)]
+    got = _drive(model, seqs, cut=[64, 3])
+    for i in range(3):
+        assert_close(got[i], plain(seqs[i]), dtype, f"harmonic rotary, request {i}")
