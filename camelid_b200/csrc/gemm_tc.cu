@@ -898,10 +898,14 @@ extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, lo
     const long work = (long)p.tiles_a * p.tiles_b * splits;
     if (work > 0x7fffffffL) return CML_ERR_BAD_SIZE;
     // Large tiles fill an SM: one persistent block per SM walks the items. Decode tiles are
-    // small: one block per item, several per SM.
+    // small: one block per item, several per SM; but where the items are many times the SMs (the
+    // output head: a thousand tiles) persistent blocks, one per SM with the deep ring, spare
+    // every wave after the first its start-up (barriers, tensor memory, an empty ring).
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
-    dim3 grid((unsigned)(bn >= 128 ? (work < sms ? work : sms) : work), 1, 1);
+    const bool deep = bn <= 64 && p.kb_per_split >= 12;             // as launch_tc chooses
+    const bool persistent = bn >= 128 || (deep && work >= 4L * sms);
+    dim3 grid((unsigned)(persistent ? (work < sms ? work : sms) : work), 1, 1);
     cudaStream_t s = (cudaStream_t)stream;
 #define TC_CASE(BN_, EPI_) if (bn == BN_ && epilogue == EPI_) return launch_tc<BN_, EPI_>(ma, mb, p, grid, s)
     TC_CASE(128, TC_STORE); TC_CASE(128, TC_STORE_F32); TC_CASE(128, TC_ADD_F32); TC_CASE(128, TC_SWIGLU);
