@@ -125,19 +125,35 @@ gemv_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ 
     const bool vec = ((K & 3) == 0) && ((lda & 3) == 0) && ((ldw & 3) == 0) && (((uintptr_t)A & 15) == 0) &&
                      (((uintptr_t)W & 15) == 0);
     if (vec) {
-        for (int k = lane * 4; k < K; k += 128) {
-            const float4 w4 = *reinterpret_cast<const float4*>(wr + k);
-            float4 u4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (EPI == EPI_SWIGLU) u4 = *reinterpret_cast<const float4*>(ur + k);
+        // Four steps of 128 columns at a time: the weight loads of all four are issued before the
+        // first use (they come from HBM; the activations come from cache), and no row is skipped
+        // by a branch (rows beyond M repeat the last row and are not stored), so nothing keeps
+        // the compiler from having them in flight together.
+        for (int k0 = lane * 4; k0 < K; k0 += 512) {
+            float4 w4[4], u4[4];
 #pragma unroll
-            for (int m = 0; m < MB; ++m) {
-                if (m0 + m >= M) break;
-                const float4 a4 = *reinterpret_cast<const float4*>(A + (size_t)(m0 + m) * lda + k);
-                acc[m] = fmaf(a4.x, w4.x, acc[m]); acc[m] = fmaf(a4.y, w4.y, acc[m]);
-                acc[m] = fmaf(a4.z, w4.z, acc[m]); acc[m] = fmaf(a4.w, w4.w, acc[m]);
-                if (EPI == EPI_SWIGLU) {
-                    acc2[m] = fmaf(a4.x, u4.x, acc2[m]); acc2[m] = fmaf(a4.y, u4.y, acc2[m]);
-                    acc2[m] = fmaf(a4.z, u4.z, acc2[m]); acc2[m] = fmaf(a4.w, u4.w, acc2[m]);
+            for (int j = 0; j < 4; ++j) {
+                const int k = min(k0 + j * 128, K - 4);
+                w4[j] = *reinterpret_cast<const float4*>(wr + k);
+                u4[j] = EPI == EPI_SWIGLU ? *reinterpret_cast<const float4*>(ur + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int k = k0 + j * 128;
+                if (k >= K) {                      // past the end: the clamped load above does not count
+                    w4[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    u4[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                const int kc = min(k, K - 4);
+#pragma unroll
+                for (int m = 0; m < MB; ++m) {
+                    const float4 a4 = *reinterpret_cast<const float4*>(A + (size_t)min(m0 + m, M - 1) * lda + kc);
+                    acc[m] = fmaf(a4.x, w4[j].x, acc[m]); acc[m] = fmaf(a4.y, w4[j].y, acc[m]);
+                    acc[m] = fmaf(a4.z, w4[j].z, acc[m]); acc[m] = fmaf(a4.w, w4[j].w, acc[m]);
+                    if (EPI == EPI_SWIGLU) {
+                        acc2[m] = fmaf(a4.x, u4[j].x, acc2[m]); acc2[m] = fmaf(a4.y, u4[j].y, acc2[m]);
+                        acc2[m] = fmaf(a4.z, u4[j].z, acc2[m]); acc2[m] = fmaf(a4.w, u4[j].w, acc2[m]);
+                    }
                 }
             }
         }
