@@ -131,7 +131,11 @@ class GroupedQueryAttention(Part):
         keys = ctx.max_len if not self.window else min(ctx.max_len, self.window + PAGE)
         ctas = n_tiles * self.num_kv_heads * chunks
         unit = 8 * 32 if tensor_cores else PAGE               # keys a block should at least have
-        resident = (2 if self.head_dim <= 64 else 1) * linear.SM_COUNT    # blocks that run at the same time
+        if tensor_cores:
+            per_sm = 2 if self.head_dim <= 64 else 1          # blocks that run at the same time on an SM
+        else:                                                 # the float kernel keeps one page of keys and values
+            per_sm = max(1, min(8, (200 * 1024) // (4 * PAGE * (2 * self.head_dim + 1) + 4096)))
+        resident = per_sm * linear.SM_COUNT
         return max(1, min((keys + unit - 1) // unit, resident // ctas, 64))
 
     def _attend(self, ctx, q, out, k_pages, v_pages, table, tensor_cores: bool):
