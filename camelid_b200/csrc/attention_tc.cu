@@ -185,6 +185,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                    pv_full = s_full + 24, q_ready = s_full + 32;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 32) {      // the maps' own round trip, beside the set-up
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&mapK) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&mapV) : "memory");
+    }
     // Blocks start in the order of blockIdx.x: the tiles that see the most keys come first, for
     // every kv head alike, so that no long tile starts late.
     const int n_cols = p.n_kv_heads * p.head_chunks;
