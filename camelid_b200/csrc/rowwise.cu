@@ -135,13 +135,21 @@ __global__ void rmsnorm_settle_kernel(float* __restrict__ x, const TW* __restric
 #pragma unroll
         for (int i = 0; i < 4; ++i) wv[i] = to_f32(w[4 * g0 + i]);
     }
+    const int r = blockIdx.x;
+    const int units = n_splits + 1;                 // unit 0: the row itself; unit u: split u - 1
+    if (!rows_index && g0 < groups) {
+        // Touch what this thread will copy, ahead of the wait: the lines may still change (they
+        // are only asked into L2, nothing is read), but the address translations are warm after.
+        for (int u = 0; u < units; ++u) {
+            const float* at = (u == 0) ? x + (size_t)r * hidden + 4 * g0 : partial + (size_t)(u - 1) * split_stride + (size_t)r * hidden + 4 * g0;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(at));
+        }
+    }
     pdl_wait();
     pdl_launch_dependents();
-    const int r = blockIdx.x;
     const int src = rows_index ? rows_index[r] : r;
     float* xr = x + (size_t)src * hidden;
     const float* pr = partial + (size_t)src * hidden;
-    const int units = n_splits + 1;                 // unit 0: the row itself; unit u: split u - 1
     float ss = 0.f;
     for (int g = threadIdx.x; g < groups; g += blockDim.x) {
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
