@@ -356,7 +356,8 @@ def test_attention_tc_window_edges(cuda, window):
     _attn_tc_case(cuda, 4, 2, 64, starts=[0, 190], news=[150, 10], window=window, spike=(1, max(0, 199 - window)))
 
 
-def _attn_fused_case(cuda, n_heads, n_kv, hd, rot, starts, window, n_splits, gsplits, write_kv=True, spike=None):
+def _attn_fused_case(cuda, n_heads, n_kv, hd, rot, starts, window, n_splits, gsplits, write_kv=True, spike=None,
+                     n_pages=64):
     """Decode attention in one launch from the partial sums of the q/k/v product: against the
     plain rotary encoding and attention of the whole sequences, and the cache rows it writes."""
     from camelid_b200.csrc import ops
@@ -364,7 +365,7 @@ def _attn_fused_case(cuda, n_heads, n_kv, hd, rot, starts, window, n_splits, gsp
     dt = torch.bfloat16
     n = len(starts)
     totals = [s + 1 for s in starts]
-    k_pages, v_pages, table, ks, vs = _paged(totals, n_kv, hd, dt, cuda, seed=4)
+    k_pages, v_pages, table, ks, vs = _paged(totals, n_kv, hd, dt, cuda, n_pages=n_pages, seed=4)
     freqs = rotary_frequencies(rot, 10000.0, None) if rot else np.zeros(0, dtype=np.float32)
     g = torch.Generator().manual_seed(7)
     width = (n_heads + 2 * n_kv) * hd
@@ -430,3 +431,11 @@ def test_attention_decode_fused_window_and_borrowed_cache(cuda, window):
     _attn_fused_case(cuda, 4, 2, 64, 64, starts=[199, 80, 0], window=window, n_splits=4, gsplits=1, write_kv=False,
                      spike=(0, max(0, 200 - window)))
     _attn_fused_case(cuda, 8, 2, 128, 128, starts=[300, 5], window=None, n_splits=2, gsplits=2, write_kv=False)
+
+
+@pytest.mark.parametrize("n_splits", [1, 3])
+def test_attention_decode_fused_long_context(cuda, n_splits):
+    """Thousands of cached keys: a warp walks more tiles than it keeps page numbers for in
+    registers, and a far key must still be found."""
+    _attn_fused_case(cuda, 8, 2, 64, 64, starts=[9000, 4100, 64], window=None, n_splits=n_splits, gsplits=2,
+                     spike=(0, 130), n_pages=256)
