@@ -617,9 +617,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     __syncthreads();
     pdl_launch_dependents();
 
+    // Items are numbered so that the clusters at work at one time share operands that fit L2:
+    // the tiles of A in groups of 8, all tiles of B for a group before the next group. (With
+    // the A tile simply fastest, a product of 16,384 rows streamed all of A from HBM once per
+    // tile of B.)
     auto item = [&](int w, int& a0, int& b0) {
-        a0 = (w % p.tiles_a) * 256 + (int)rank * TC_BM;
-        b0 = (w / p.tiles_a) * BN + (int)rank * (BN / 2);
+        constexpr int G = 8;
+        const int per_group = G * p.tiles_b;
+        const int g = w / per_group, within = w - g * per_group;
+        const int gsz = min(G, p.tiles_a - g * G);
+        const int tb = within / gsz, ta = g * G + (within - tb * gsz);
+        a0 = ta * 256 + (int)rank * TC_BM;
+        b0 = tb * BN + (int)rank * (BN / 2);
     };
 
     if (warp == 0) {
