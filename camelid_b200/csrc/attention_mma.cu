@@ -7,7 +7,10 @@
 // tokens) reuse every key and value that is read. Keys are walked in tiles of 32; the four
 // warps of a block take tiles round-robin, each with its own cp.async pipeline into padded
 // shared memory, and merge their running (max, sum, output) at the end. A range of keys
-// can also be split over gridDim.z; the partial results are merged by attn_combine_kernel.
+// can also be split over gridDim.z; the partial results are merged by the block that
+// finishes last (a ticket per column of blocks), or by attn_combine_kernel where no tickets
+// are given. Decode steps normally run attn_decode_fused_kernel further down instead: one
+// launch from the split sums of the q/k/v product to the attention output.
 //
 // It replaces attention_decode / attn_sk_* and attention_batched / flash_pref_*
 // (src/cuda_resident.rs:1587, :2332-2487, :1994, :2523-2705); the arithmetic is the

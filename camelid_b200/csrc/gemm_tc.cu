@@ -5,14 +5,16 @@
 //
 //   D[128 x BN] tile = Arows[128, K] * Brows[BN, K]^T        (both operands K-major)
 //
-// * prefill: Arows = activations [tokens, K], Brows = weights [out, K]; BN = 128 or 256;
-//   epilogues: store bfloat16, store float, add into the float residual stream, SwiGLU on
-//   packed gate/up rows (interleaved in groups of 16 output columns).
+// * prefill of up to 128 rows: Arows = activations [tokens, K], Brows = weights [out, K];
+//   BN = 128 or 256; epilogues: store bfloat16, store float, add into the float residual
+//   stream, SwiGLU on packed gate/up rows (interleaved in groups of 16 output columns).
 // * decode ("transposed"): Arows = weights [out, K], Brows = activations [batch, K] with
 //   BN = 16..64 >= batch, so every weight byte crosses the memory bus once and no tensor-core
-//   row is wasted on padding; K may be split over gridDim.z, each split writing a float
-//   partial [split][batch][out] that the consumer sums in order (no atomics: the result does
-//   not depend on timing); epilogues: float partial, SwiGLU to bfloat16 (no split).
+//   row is wasted on padding; K may be split (the split is part of the work item's number),
+//   each split writing a float partial [split][batch][out] that the consumer sums in order
+//   (no atomics: the result does not depend on timing); epilogues: float partial, SwiGLU to
+//   bfloat16 (no split). The output head, with many times more tiles than SMs, runs on
+//   persistent blocks.
 //
 // It stands where the reference runs q8_gemv / q8_gemm_batched
 // (src/cuda_resident.rs:230, :1494), whose batched form re-reads the weights once per 8
