@@ -222,10 +222,14 @@ def test_schedule_names_layers_twice_and_shares_a_cache(cuda, dtype, over):
         assert_close(got[i], pl.forward(cfg, w, seqs[i], dtype=torch.float64, schedule=sched), dtype, f"request {i}")
 
 
+@pytest.mark.parametrize("over", [{}, WIDE], ids=["head16", "head64"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_window_layer_has_storage_of_its_own(cuda, dtype):
+def test_window_layer_has_storage_of_its_own(cuda, dtype, over):
+    """head64 in bfloat16: the tcgen05 prefill kernel (prompts of 200 and 140 rows also take the
+    two-block products with the norms inside them) and the fused decode kernel, both with a
+    window whose older pages have been given back."""
     _register_toys()
-    cfg, model, w = _model("ToyWindowForCausalLM", dtype)
+    cfg, model, w = _model("ToyWindowForCausalLM", dtype, **over)
     cache = model.new_cache(1024, max_slots=2)
     assert len(cache.k) == 2 and cache.book.kv_specs[1].window == 70
 
@@ -237,7 +241,7 @@ def test_window_layer_has_storage_of_its_own(cuda, dtype):
         h, _ = pl.decoder_layer(h, w, 0, cfg, pos, fr)
         p = "model.layers.1."
         n = pl.rms_norm(h, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
-        T, nH, nKV, hd = len(ids), 4, 2, 16
+        T, nH, nKV, hd = len(ids), cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
         q = pl.rope((n @ w[p + "self_attn.q_proj.weight"].double().T).view(T, nH, hd), pos, fr)
         k = pl.rope((n @ w[p + "self_attn.k_proj.weight"].double().T).view(T, nKV, hd), pos, fr)
         v = (n @ w[p + "self_attn.v_proj.weight"].double().T).view(T, nKV, hd)
