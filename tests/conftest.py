@@ -40,8 +40,19 @@ TINY_C = {
                      "original_max_position_embeddings": 128},
     "tie_word_embeddings": True,
 }
-CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
-SEEDS = {"tiny_a": 0, "tiny_b": 1, "tiny_c": 5}
+# a fourth with the head size of the tensor-core attention kernels (64), three query heads to
+# a kv head, and a width, feed-forward and vocabulary that fill no tile
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 331, "hidden_size": 200, "num_hidden_layers": 2, "intermediate_size": 328,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 64, "max_position_embeddings": 2048,
+    "rms_norm_eps": 2e-5, "rope_theta": 50000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 2.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 256},
+    "tie_word_embeddings": False, "eos_token_id": 2,
+}
+CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D}
+SEEDS = {"tiny_a": 0, "tiny_b": 1, "tiny_c": 5, "tiny_d": 9}
 
 
 @pytest.fixture(scope="session")
