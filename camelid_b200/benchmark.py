@@ -116,8 +116,14 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def _prompts(rng, n: int, length: int, vocab: int) -> list:
-    return [rng.integers(0, vocab, size=length).tolist() for _ in range(n)]
+def _prompts(rng, n: int, length, vocab: int) -> list:
+    """``n`` prompts of seeded uniform ids; ``length`` is one number or (lowest, highest) for
+    lengths drawn uniformly between the two."""
+    if isinstance(length, (tuple, list)):
+        lengths = rng.integers(int(length[0]), int(length[1]) + 1, size=n).tolist()
+    else:
+        lengths = [int(length)] * n
+    return [rng.integers(0, vocab, size=t).tolist() for t in lengths]
 
 
 def linear_params(cfg: dict) -> int:
@@ -161,6 +167,31 @@ def measure_prefill(lm, cfg, tokens: int, rng, reps: int = 5, warmup: int = 3) -
     return {"ms": ms, "tokens": tokens, "value": tokens / (ms / 1e3)}
 
 
+def measure_prefill_batch(lm, cfg, prompts, reps: int = 3, warmup: int = 2) -> dict:
+    """All prompts of a batch, of unequal lengths, in one step."""
+    from .engine.model import StepEntry
+    cache = lm.new_cache(sum(((len(p) + 63) // 64) * 64 for p in prompts), max_slots=len(prompts))
+    times = []
+    for r in range(warmup + reps):
+        slots = [cache.alloc_slot() for _ in prompts]
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        lm.step(cache, [StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        b.record()
+        torch.cuda.synchronize()
+        for s in slots:
+            cache.free_slot(s)
+        if r >= warmup:
+            times.append(a.elapsed_time(b))
+    ms = statistics.median(times)
+    del cache
+    tokens = sum(len(p) for p in prompts)
+    return {"ms": ms, "tokens": tokens, "value": tokens / (ms / 1e3), "prompts": len(prompts),
+            "shortest": min(len(p) for p in prompts), "longest": max(len(p) for p in prompts),
+            "flops": sum(prefill_flops(cfg, len(p)) for p in prompts)}
+
+
 def _prefill_batch(lm, cache, prompts, chunk: int = 8):
     """Prefill all prompts (a few per step, to bound the workspace); returns slots and the
     greedy first token of each."""
@@ -175,13 +206,15 @@ def _prefill_batch(lm, cache, prompts, chunk: int = 8):
     return slots, firsts
 
 
-def measure_decode_device(lm, cfg, batch: int, prompt_tokens: int, steps: int, warmup: int, rng) -> dict:
+def measure_decode_device(lm, cfg, batch: int, prompt_tokens, steps: int, warmup: int, rng, prompts=None) -> dict:
     """K decode steps timed on the device: the captured step graph with the greedy token fed
-    back on the device; the host only sends each step's positions."""
+    back on the device; the host only sends each step's positions. ``prompt_tokens`` is one
+    length or (lowest, highest); ``prompts`` given wins over it."""
     from .csrc import ops
-    total = prompt_tokens + steps + warmup + 1
-    cache = lm.new_cache(batch * ((total + 63) // 64) * 64, max_slots=batch)
-    slots, firsts = _prefill_batch(lm, cache, _prompts(rng, batch, prompt_tokens, cfg["vocab_size"]))
+    if prompts is None:
+        prompts = _prompts(rng, batch, prompt_tokens, cfg["vocab_size"])
+    cache = lm.new_cache(sum(((len(p) + steps + warmup + 1 + 63) // 64) * 64 for p in prompts), max_slots=batch)
+    slots, firsts = _prefill_batch(lm, cache, prompts)
     book = cache.book
     horizon = warmup + steps
     book.check_extend([(s, horizon) for s in slots])
@@ -216,15 +249,16 @@ def measure_decode_device(lm, cfg, batch: int, prompt_tokens: int, steps: int, w
         cache.free_slot(s)
     return {"ms_total": ms, "ms_per_step": ms / steps, "value": batch * steps / (ms / 1e3), "launches": launches,
             "h2d_bytes_per_step": h2d, "clocks": clocks.summary(),
-            "context": prompt_tokens + warmup + steps / 2.0}
+            "context": sum(len(p) for p in prompts) / float(batch) + warmup + steps / 2.0}
 
 
-def measure_decode_e2e(lm, cfg, batch: int, prompt_tokens: int, steps: int, warmup: int, rng) -> dict:
+def measure_decode_e2e(lm, cfg, batch: int, prompt_tokens, steps: int, warmup: int, rng, prompts=None) -> dict:
     """The same through ``LanguageModel.generate``, the call a user makes: every step sends its
     tokens and positions from pinned host memory and reads the sampled tokens back. Two calls
     on the same prompts, one that stops after the warm-up steps and one that goes on for
     ``steps`` more; the difference of their wall-clock times is the time of exactly those steps."""
-    prompts = _prompts(rng, batch, prompt_tokens, cfg["vocab_size"])
+    if prompts is None:
+        prompts = _prompts(rng, batch, prompt_tokens, cfg["vocab_size"])
 
     def timed(n_tokens):
         best = None
@@ -247,7 +281,9 @@ def measure_decode_e2e(lm, cfg, batch: int, prompt_tokens: int, steps: int, warm
 
 def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warmup: int = 8, dtype: str = "bfloat16",
         layers: int | None = None, config_index: int = 2, points: bool = True, e2e: bool = True,
-        prefill_tokens: int = 2048, prefill: bool = True, decode: bool = True) -> dict:
+        prefill_tokens: int = 2048, prefill: bool = True, decode: bool = True, prompt_range=None) -> dict:
+    """``prompt_range`` (lowest, highest): prompts of unequal lengths drawn uniformly between the
+    two instead of ``prompt_tokens`` each; the record then also times their one prefill step."""
     from . import api
     shape = SHAPES[config_index]
     cfg = config_for(config_index, layers)
@@ -263,7 +299,12 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
         pre = {"value": None, "tokens": prefill_tokens, "ms": None, "frac": None}
     if not decode:
         return {"prefill": pre, "dtype": dtype, "config": {"model": shape["name"], "layers": cfg["num_hidden_layers"]}}
-    dec = measure_decode_device(lm, cfg, batch, prompt_tokens, decode_steps, warmup, rng)
+    prompts = _prompts(rng, batch, prompt_range, cfg["vocab_size"]) if prompt_range else None
+    pre_batch = None
+    if prompts is not None and prefill:
+        pre_batch = measure_prefill_batch(lm, cfg, prompts)
+        pre_batch["frac"] = pre_batch.pop("flops") / (pre_batch["ms"] / 1e3) / flop_peak
+    dec = measure_decode_device(lm, cfg, batch, prompt_tokens, decode_steps, warmup, rng, prompts=prompts)
     bytes_step = decode_bytes(cfg, batch, dec["context"], elem)
     achieved = bytes_step / (dec["ms_per_step"] / 1e3) / 1e9
     rec = {
@@ -273,7 +314,8 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
         "ms_per_step": dec["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if dtype == "bfloat16" else "fp32", "data": "synthetic (seeded uniform token ids, random weights)",
         "config": {"model": shape["name"], "global_batch": batch, "seq_len": shape["context"],
-                   "prompt_tokens": prompt_tokens, "decode_steps": decode_steps, "parallelism": "single-gpu",
+                   "prompt_tokens": prompt_tokens if prompts is None else f"uniform in {list(prompt_range)}",
+                   "decode_steps": decode_steps, "parallelism": "single-gpu",
                    "layers": cfg["num_hidden_layers"], "layers_of_model": shape["num_hidden_layers"],
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
@@ -285,8 +327,10 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
                      "frac": achieved / pk["hbm_gbs"]},
         "clocks": dec["clocks"], "gpu_launches": dec["launches"],
     }
+    if pre_batch is not None:
+        rec["prefill_batch"] = pre_batch
     if e2e:
-        e = measure_decode_e2e(lm, cfg, batch, prompt_tokens, decode_steps, warmup, rng)
+        e = measure_decode_e2e(lm, cfg, batch, prompt_tokens, decode_steps, warmup, rng, prompts=prompts)
         rec["e2e"] = {"value": e["value"], "unit": "tokens/s", "h2d_bytes_per_step": e["h2d_bytes_per_step"],
                       "d2h_bytes_per_step": e["d2h_bytes_per_step"], "ms_per_step": e["ms_per_step"]}
     if points:

@@ -129,7 +129,7 @@ def cmd_bench(args) -> int:
     rec = benchmark.run(batch=args.batch, prompt_tokens=args.prompt_tokens, decode_steps=args.decode_steps,
                         warmup=args.warmup, dtype=args.dtype, layers=args.layers, config_index=args.config,
                         points=args.points, e2e=args.e2e, prefill=not args.no_prefill, decode=not args.no_decode,
-                        prefill_tokens=args.prefill_tokens)
+                        prefill_tokens=args.prefill_tokens, prompt_range=args.prompt_range)
     print(json.dumps(rec), flush=True)
     return 0
 
@@ -149,6 +149,9 @@ def main(argv=None) -> int:
     be = sub.add_parser("bench", help="decode and prefill throughput with random weights")
     be.add_argument("--batch", type=int, default=8)
     be.add_argument("--prompt-tokens", type=int, default=2048)
+    be.add_argument("--prompt-range", type=int, nargs=2, metavar=("LOWEST", "HIGHEST"), default=None,
+                    help="prompts of unequal lengths, uniform between the two, instead of --prompt-tokens each; "
+                         "their one prefill step is timed too")
     be.add_argument("--decode-steps", type=int, default=64)
     be.add_argument("--warmup", type=int, default=3)
     be.add_argument("--layers", type=int, default=None)
