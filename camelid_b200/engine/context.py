@@ -98,13 +98,15 @@ class StepContext:
 
     @staticmethod
     def host_arrays(slots, starts, tokens, want, tables, tile_sizes):
-        """The step's integer arrays as one int32 numpy vector, with its layout."""
-        news = [len(t) for t in tokens]
+        """The step's integer arrays as one int32 numpy vector, with its layout. ``tokens``: one
+        list or integer array per sequence."""
+        tokens = [np.asarray(t).reshape(-1) for t in tokens]
+        news = [int(t.size) for t in tokens]
         row0 = np.zeros(len(news), dtype=np.int64)
         if len(news) > 1:
             row0[1:] = np.cumsum(news[:-1])
         n_rows = int(sum(news))
-        flat = np.fromiter((t for ts in tokens for t in ts), dtype=np.int32, count=n_rows)
+        flat = np.concatenate(tokens).astype(np.int32, copy=False)
         row_seq = np.repeat(np.arange(len(news), dtype=np.int32), news)
         row_pos = (np.arange(n_rows, dtype=np.int64) - np.repeat(row0, news) + np.repeat(np.asarray(starts), news))
         want_rows = [int(row0[i]) + w for i, ws in enumerate(want) for w in ws]
@@ -112,9 +114,9 @@ class StepContext:
         for r in (tile_sizes if max(news) > 1 else [1]):
             tile_seq, tile_q0 = [], []
             for i, n in enumerate(news):
-                for q0 in range(0, n, r):
-                    tile_seq.append(i)
-                    tile_q0.append(q0)
+                q0s = range(0, n, r)
+                tile_seq += [i] * len(q0s)
+                tile_q0 += q0s
             tiles[r] = (tile_seq, tile_q0)
         layout = StepLayout(n_rows, len(news), len(want_rows), [len(t[0]) for t in tables],
                             {r: len(t[0]) for r, t in tiles.items()})

@@ -16,6 +16,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from ..cache.sequence_cache import SequenceCache
@@ -137,39 +138,46 @@ class DecoderModel:
                              device=self.device, max_slots=max_slots)
 
     # ---- the step ----
-    def _validate(self, cache: SequenceCache, entries: list) -> None:
+    def _validate(self, cache: SequenceCache, entries: list) -> list:
+        """Checks a step before anything changes; returns each entry's tokens as an int64 array."""
         if not self.loaded:
             raise StepError("the model has no weights yet")
         if self.device.type != "cuda":
             raise KernelError("steps run on a CUDA device only; there is no CPU path")
         if not entries:
             raise StepError("a step needs at least one sequence")
+        arrays = []
         for e in entries:
-            if len(e.tokens) == 0:
+            try:
+                a = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
+            except (TypeError, ValueError, OverflowError):
+                raise StepError(f"slot {e.slot}: the tokens are not a flat sequence of integer ids") from None
+            if a.size == 0:
                 raise StepError(f"slot {e.slot}: a step must bring at least one token")
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise StepError(f"slot {e.slot}: token id {t} is outside the vocabulary of {self.vocab_size}")
+            if int(a.min()) < 0 or int(a.max()) >= self.vocab_size:
+                bad = int(a[(a < 0) | (a >= self.vocab_size)][0])
+                raise StepError(f"slot {e.slot}: token id {bad} is outside the vocabulary of {self.vocab_size}")
             for w in e.want:
-                if not 0 <= int(w) < len(e.tokens):
-                    raise StepError(f"slot {e.slot}: wanted place {w} is outside the step's {len(e.tokens)} tokens")
-        cache.book.check_extend([(e.slot, len(e.tokens)) for e in entries])
+                if not 0 <= int(w) < a.size:
+                    raise StepError(f"slot {e.slot}: wanted place {w} is outside the step's {a.size} tokens")
+            arrays.append(a)
+        cache.book.check_extend([(e.slot, a.size) for e, a in zip(entries, arrays)])
+        return arrays
 
     def step(self, cache: SequenceCache, entries: list) -> torch.Tensor:
         """Run the given tokens; returns float32 logits [wanted places, vocabulary] in the order
         of the entries and of their ``want`` lists (an empty tensor if nothing is wanted)."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
-        self._validate(cache, entries)
-        if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+        arrays = self._validate(cache, entries)
+        if self.use_graphs and all(a.size == 1 and list(e.want) == [0] for e, a in zip(entries, arrays)):
             return self._graph_step(cache, entries)
-        starts = [cache.book.extend(e.slot, len(e.tokens)) for e in entries]
+        starts = [cache.book.extend(e.slot, a.size) for e, a in zip(entries, arrays)]
         ctx = StepContext.for_step(cache=cache, workspace=self.workspace, dtype=self.dtype, device=self.device,
-                                   slots=[e.slot for e in entries], starts=starts,
-                                   tokens=[[int(t) for t in e.tokens] for e in entries],
+                                   slots=[e.slot for e in entries], starts=starts, tokens=arrays,
                                    want=[[int(w) for w in e.want] for e in entries], tile_sizes=self.tile_sizes)
         logits = self.run(ctx)
-        for e in entries:
-            cache.book.commit(e.slot, len(e.tokens))
+        for e, a in zip(entries, arrays):
+            cache.book.commit(e.slot, a.size)
         self.last_h2d_bytes = ctx.h2d_bytes
         return logits
 
