@@ -58,6 +58,7 @@ struct TcParams {
     int in_parts;
     float in_inv_hidden, in_eps;
     int staged_ok;      // the outputs are aligned for 16-byte (float) and 8-byte (bfloat16) row pieces
+    long split_stride;  // TC_STORE_F32 of a product split over K: split s writes C + s * split_stride (elements)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -198,7 +199,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const uint3
                 for (int i = 0; i < n_ok; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
             }
         } else {
-            float* dst = (float*)p.C + (size_t)rowA * p.ldc + colB;
+            float* dst = (float*)p.C + (size_t)split * p.split_stride + (size_t)rowA * p.ldc + colB;
             if (n_ok == 16 && (((uintptr_t)dst & 15) == 0)) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -584,7 +585,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
     const int cluster = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
-    const int n_work = p.tiles_a * p.tiles_b;
+    const int n_tiles = p.tiles_a * p.tiles_b;
+    const int n_work = n_tiles * p.splits;       // a split of K is a work item of its own (float partial sums)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -624,6 +626,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     // the A tile simply fastest, a product of 16,384 rows streamed all of A from HBM once per
     // tile of B.)
     auto item = [&](int w, int& a0, int& b0) {
+        w %= n_tiles;                                    // splits of K are the slowest index
         constexpr int G = 8;
         const int per_group = G * p.tiles_b;
         const int g = w / per_group, within = w - g * per_group;
@@ -632,6 +635,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         a0 = ta * 256 + (int)rank * TC_BM;
         b0 = tb * BN + (int)rank * (BN / 2);
     };
+    auto k_range = [&](int w, int& kb0) {                // first k-block and number of k-blocks of item w
+        kb0 = (w / n_tiles) * p.kb_per_split;
+        return min(p.kb_per_split, p.num_kb - kb0);
+    };
 
     if (warp == 0) {
         if (lane == 0 && !*abort_flag) {
@@ -639,31 +646,32 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             bool waited = false, ok = true;
             auto leader_full = [&](int s) { return map_to_cta(full_bar(s), 0); };
             for (int w = cluster; w < n_work && ok; w += n_clusters) {
-                int a0, b0;
+                int a0, b0, kb0;
                 item(w, a0, b0);
+                const int nkb = k_range(w, kb0);
                 int i = 0;
                 if (!waited) {
-                    const int pre = min(p.num_kb, STAGES);
+                    const int pre = min(nkb, STAGES);
                     for (; i < pre; ++i) {
                         if (leader) mbar_expect_tx(full_bar(i), 2 * (A_BYTES + B_BYTES));
-                        if (p.independent == 0) tma_load_2d_pair(smemA + i * A_BYTES, &mapA, leader_full(i), i * TC_BK, a0);
-                        else tma_load_2d_pair(smemB + i * B_BYTES, &mapB, leader_full(i), i * TC_BK, b0);
+                        if (p.independent == 0) tma_load_2d_pair(smemA + i * A_BYTES, &mapA, leader_full(i), (kb0 + i) * TC_BK, a0);
+                        else tma_load_2d_pair(smemB + i * B_BYTES, &mapB, leader_full(i), (kb0 + i) * TC_BK, b0);
                     }
                     pdl_wait();
                     waited = true;
                     for (int j = 0; j < pre; ++j) {
-                        if (p.independent == 0) tma_load_2d_pair(smemB + j * B_BYTES, &mapB, leader_full(j), j * TC_BK, b0);
-                        else tma_load_2d_pair(smemA + j * A_BYTES, &mapA, leader_full(j), j * TC_BK, a0);
+                        if (p.independent == 0) tma_load_2d_pair(smemB + j * B_BYTES, &mapB, leader_full(j), (kb0 + j) * TC_BK, b0);
+                        else tma_load_2d_pair(smemA + j * A_BYTES, &mapA, leader_full(j), (kb0 + j) * TC_BK, a0);
                     }
                     g = pre;
                 }
-                for (; i < p.num_kb; ++i, ++g) {
+                for (; i < nkb; ++i, ++g) {
                     const int s = g % STAGES;
                     const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
                     if (leader) mbar_expect_tx(full_bar(s), 2 * (A_BYTES + B_BYTES));
-                    tma_load_2d_pair(smemA + s * A_BYTES, &mapA, leader_full(s), i * TC_BK, a0);
-                    tma_load_2d_pair(smemB + s * B_BYTES, &mapB, leader_full(s), i * TC_BK, b0);
+                    tma_load_2d_pair(smemA + s * A_BYTES, &mapA, leader_full(s), (kb0 + i) * TC_BK, a0);
+                    tma_load_2d_pair(smemB + s * B_BYTES, &mapB, leader_full(s), (kb0 + i) * TC_BK, b0);
                 }
             }
             if (*abort_flag) {
@@ -691,7 +699,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * 256);
-                for (int i = 0; i < p.num_kb && ok; ++i, ++g) {
+                int kb0;
+                const int nkb = k_range(w, kb0);
+                for (int i = 0; i < nkb && ok; ++i, ++g) {
                     const int s = g % STAGES;
                     const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
                     ok = mbar_wait(full_bar(s), ph, abort_flag);
@@ -716,6 +726,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             int a0, b0;
             item(w, a0, b0);
             b0 -= (int)rank * (BN / 2);                  // every block holds all BN columns of its rows
+            const int split = w / n_tiles;
             const int buf = j & 1;
             const int rowA = a0 + q * 32 + lane;
             ok = mbar_wait(acc_full(buf), ((uint32_t)j >> 1) & 1u, abort_flag);
@@ -727,7 +738,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 row_scale = tc_row_scale(p.in_sumsq, p.in_parts, p.rowsA, min(rowA, p.rowsA - 1), p.in_inv_hidden, p.in_eps);
             float ssq_out = 0.f;                     // sum of squares of this thread's row (columns that took the plain path)
             float ssq_st[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // and of rows it * 4 + lane / 8, this lane's 4 columns (staged path)
-            constexpr bool CAN_STAGE = EPI == TC_STORE || EPI == TC_ADD_F32 || EPI == TC_ADD_NORM;
+            constexpr bool CAN_STAGE = EPI == TC_STORE || EPI == TC_STORE_F32 || EPI == TC_ADD_F32 || EPI == TC_ADD_NORM;
             constexpr bool READS_C = EPI == TC_ADD_F32 || EPI == TC_ADD_NORM;
             float* st = stage + q * 32 * TC_STAGE_LD;
             const int cl = (lane & 7) * 4;           // staged path: this lane's 4 columns of a chunk ...
@@ -799,8 +810,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                             *reinterpret_cast<uint2*>((bf16*)p.C + (size_t)grow * p.ldc + col) =
                                 make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
                         } else {
-                            v.x += o[it].x; v.y += o[it].y; v.z += o[it].z; v.w += o[it].w;
-                            *reinterpret_cast<float4*>((float*)p.C + (size_t)grow * p.ldc + col) = v;
+                            if (READS_C) { v.x += o[it].x; v.y += o[it].y; v.z += o[it].z; v.w += o[it].w; }
+                            *reinterpret_cast<float4*>((float*)p.C + (size_t)split * p.split_stride + (size_t)grow * p.ldc + col) = v;
                             if (EPI == TC_ADD_NORM) {
                                 ssq_st[it] = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ssq_st[it]))));
                                 __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * g4[0], v.y * g4[1]);
@@ -817,8 +828,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     ssq_out += tc_add_norm_chunk(p, r, rowA, b0 + c);
                     ssq_out += tc_add_norm_chunk(p, u, rowA, b0 + c + 16);
                 } else {
-                    tc_epilogue_chunk<EPI>(p, r, r, rowA, b0 + c, 0, lane, 0);
-                    tc_epilogue_chunk<EPI>(p, u, u, rowA, b0 + c + 16, 0, lane, 0);
+                    tc_epilogue_chunk<EPI>(p, r, r, rowA, b0 + c, split, lane, 0);
+                    tc_epilogue_chunk<EPI>(p, u, u, rowA, b0 + c + 16, split, lane, 0);
                 }
             }
             if (EPI == TC_ADD_NORM) {
@@ -893,13 +904,15 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
 
 template <int BN, int EPI>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t s) {
-    if (BN <= 64 && p.kb_per_split >= 12) return launch_tc2<BN, EPI, true>(ma, mb, p, grid, s);
+    if constexpr (BN <= 64) {
+        if (p.kb_per_split >= 12) return launch_tc2<BN, EPI, true>(ma, mb, p, grid, s);
+    }
     return launch_tc2<BN, EPI, false>(ma, mb, p, grid, s);
 }
 
 // A: [rowsA, K] bfloat16 (ld lda), B: [rowsB, K] bfloat16 (ld ldb).
 // Normal epilogues (0..3) write C[rowA][rowB]; transposed ones (4, 5) write C[..][rowA] per rowB.
-// bn: tile over B rows (16, 32, 64, 128 or 256). splits > 1 only with TC_T_PARTIAL.
+// bn: tile over B rows (64, 128 or 256; transposed: 16, 32, 64 or 128). splits > 1 only with TC_T_PARTIAL.
 extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, long ldb, int rowsB, int K, void* C,
                            long ldc, int epilogue, int bn, int splits, int* err, void* stream) {
     if (rowsA <= 0 || rowsB <= 0) return 0;
@@ -918,6 +931,7 @@ extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, lo
     p.err = err;
     p.norm_w = nullptr; p.norm_w_dtype = 0; p.x_out = nullptr; p.ldx = 0; p.out_sumsq = nullptr;
     p.in_sumsq = nullptr; p.in_parts = 0; p.in_inv_hidden = 0.f; p.in_eps = 0.f; p.staged_ok = 0;
+    p.split_stride = 0;
     p.independent = (epilogue == TC_T_PARTIAL || epilogue == TC_T_SWIGLU) ? 0 : 1;
     p.tiles_a = (rowsA + TC_BM - 1) / TC_BM;
     p.tiles_b = (rowsB + bn - 1) / bn;
@@ -939,7 +953,9 @@ extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, lo
     TC_CASE(256, TC_STORE); TC_CASE(256, TC_STORE_F32); TC_CASE(256, TC_ADD_F32); TC_CASE(256, TC_SWIGLU);
     TC_CASE(64, TC_STORE); TC_CASE(64, TC_STORE_F32); TC_CASE(64, TC_ADD_F32); TC_CASE(64, TC_SWIGLU);
     TC_CASE(16, TC_T_PARTIAL); TC_CASE(32, TC_T_PARTIAL); TC_CASE(64, TC_T_PARTIAL);
+    TC_CASE(128, TC_T_PARTIAL);
     TC_CASE(16, TC_T_SWIGLU); TC_CASE(32, TC_T_SWIGLU); TC_CASE(64, TC_T_SWIGLU);
+    TC_CASE(128, TC_T_SWIGLU);
 #undef TC_CASE
     return CML_ERR_BAD_SIZE;
 }
@@ -973,6 +989,7 @@ static int pair_tile_width(int rowsA, int rowsB, int clusters) {
 struct TcPairNorm {
     const void* norm_w; int norm_w_dtype; void* x_out; long ldx; float* out_sumsq;     // TC_ADD_NORM
     const float* in_sumsq; int in_parts; int in_hidden; float in_eps;                  // rows of A still lack their scale
+    int splits; long split_stride;                                                     // TC_STORE_F32 split over K
 };
 
 static int gemm_tc_pair_launch(const void* A, long lda, int rowsA, const void* B, long ldb, int rowsB, int K, void* C,
@@ -982,7 +999,8 @@ static int gemm_tc_pair_launch(const void* A, long lda, int rowsA, const void* B
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
     // the norm's sums of squares are kept per 256 columns: that epilogue stays on the wide tile
-    const int bn = epilogue == TC_ADD_NORM ? 256 : pair_tile_width(rowsA, rowsB, sms / 2);
+    // (so does a product split over K: its splits, not a narrower tile, fill the clusters)
+    const int bn = (epilogue == TC_ADD_NORM || nm.splits > 1) ? 256 : pair_tile_width(rowsA, rowsB, sms / 2);
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, rowsA, K, lda, TC_BM);
     if (rc) return rc;
@@ -991,21 +1009,25 @@ static int gemm_tc_pair_launch(const void* A, long lda, int rowsA, const void* B
     TcParams p;
     p.C = C; p.ldc = ldc; p.rowsA = rowsA; p.rowsB = rowsB;
     p.num_kb = (K + TC_BK - 1) / TC_BK;
-    p.kb_per_split = p.num_kb;
+    int splits = nm.splits < 1 ? 1 : (nm.splits > p.num_kb ? p.num_kb : nm.splits);
+    if (splits > 1 && epilogue != TC_STORE_F32) return CML_ERR_BAD_SIZE;
+    p.kb_per_split = (p.num_kb + splits - 1) / splits;
+    splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;      // no split without a k-block
     p.err = err;
     p.independent = 1;
     p.tiles_a = (rowsA + 255) / 256;
     p.tiles_b = (rowsB + bn - 1) / bn;
-    p.splits = 1;
+    p.splits = splits;
+    p.split_stride = nm.split_stride;
     p.norm_w = nm.norm_w; p.norm_w_dtype = nm.norm_w_dtype; p.x_out = (bf16*)nm.x_out; p.ldx = nm.ldx;
     p.out_sumsq = nm.out_sumsq;
     p.in_sumsq = nm.in_sumsq; p.in_parts = nm.in_parts;
     p.in_inv_hidden = nm.in_hidden > 0 ? 1.0f / (float)nm.in_hidden : 0.f;
     p.in_eps = nm.in_eps;
     if (epilogue == TC_STORE) p.staged_ok = ((uintptr_t)C % 8 == 0) && (ldc % 4 == 0);
-    else p.staged_ok = ((uintptr_t)C % 16 == 0) && (ldc % 4 == 0) &&
+    else p.staged_ok = ((uintptr_t)C % 16 == 0) && (ldc % 4 == 0) && (nm.split_stride % 4 == 0) &&
                        (epilogue != TC_ADD_NORM || (((uintptr_t)nm.x_out % 8 == 0) && (nm.ldx % 4 == 0)));
-    const long work = (long)p.tiles_a * p.tiles_b;
+    const long work = (long)p.tiles_a * p.tiles_b * p.splits;
     if (work > 0x7fffffffL) return CML_ERR_BAD_SIZE;
     const long clusters = work < sms / 2 ? work : sms / 2;
     dim3 grid((unsigned)(2 * clusters), 1, 1);
@@ -1030,8 +1052,23 @@ extern "C" int cml_gemm_tc_pair(const void* A, long lda, int rowsA, const void* 
                                 float in_eps, void* stream) {
     if (epilogue < TC_STORE || epilogue > TC_SWIGLU) return CML_ERR_BAD_SIZE;
     if (in_sumsq && (in_parts < 1 || in_hidden < 1)) return CML_ERR_BAD_SIZE;
-    TcPairNorm nm = {nullptr, 0, nullptr, 0, nullptr, in_sumsq, in_parts, in_hidden, in_eps};
+    TcPairNorm nm = {nullptr, 0, nullptr, 0, nullptr, in_sumsq, in_parts, in_hidden, in_eps, 1, 0};
     return gemm_tc_pair_launch(A, lda, rowsA, B, ldb, rowsB, K, C, ldc, epilogue, err, nm, stream);
+}
+
+// The same product split over K into `splits` float partial sums: split s (k-blocks of 64 dealt
+// out evenly, in order) writes C + s * split_stride; their sum over s is A B^T. For products of a
+// few hundred rows, whose tiles alone would leave most of the SMs without work. `splits` must
+// leave no split without a k-block: with n k-blocks, ceil(n / ceil(n / splits)) == splits.
+extern "C" int cml_gemm_tc_pair_partial(const void* A, long lda, int rowsA, const void* B, long ldb, int rowsB, int K,
+                                        float* C, long ldc, long split_stride, int splits, int* err,
+                                        const float* in_sumsq, int in_parts, int in_hidden, float in_eps, void* stream) {
+    if (splits < 1 || (in_sumsq && (in_parts < 1 || in_hidden < 1))) return CML_ERR_BAD_SIZE;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const int per = (num_kb + (splits > num_kb ? num_kb : splits) - 1) / (splits > num_kb ? num_kb : splits);
+    if ((num_kb + per - 1) / per != splits) return CML_ERR_BAD_SIZE;
+    TcPairNorm nm = {nullptr, 0, nullptr, 0, nullptr, in_sumsq, in_parts, in_hidden, in_eps, splits, split_stride};
+    return gemm_tc_pair_launch(A, lda, rowsA, B, ldb, rowsB, K, C, ldc, TC_STORE_F32, err, nm, stream);
 }
 
 // C [rowsA, rowsB] float (the residual stream) += A B^T, and for the norm that reads C next:
@@ -1043,6 +1080,6 @@ extern "C" int cml_gemm_tc_pair_add_norm(const void* A, long lda, int rowsA, con
                                          void* x_out, long ldx, float* out_sumsq, void* stream) {
     if (!norm_w || !x_out || !out_sumsq) return CML_ERR_BAD_SIZE;
     if (norm_w_dtype != CML_DTYPE_F32 && norm_w_dtype != CML_DTYPE_BF16) return CML_ERR_BAD_DTYPE;
-    TcPairNorm nm = {norm_w, norm_w_dtype, x_out, ldx, out_sumsq, nullptr, 0, 0, 0.f};
+    TcPairNorm nm = {norm_w, norm_w_dtype, x_out, ldx, out_sumsq, nullptr, 0, 0, 0.f, 1, 0};
     return gemm_tc_pair_launch(A, lda, rowsA, B, ldb, rowsB, K, C, ldc, TC_ADD_NORM, err, nm, stream);
 }

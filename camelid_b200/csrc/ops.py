@@ -34,6 +34,8 @@ _SIGNATURES = {
                                  c_int, c_void_p, c_void_p],
     ("gemm_tc", "cml_gemm_tc_pair"): [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_void_p, c_long, c_int,
                                       c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+    ("gemm_tc", "cml_gemm_tc_pair_partial"): [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_void_p, c_long,
+                                              c_long, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
     ("gemm_tc", "cml_gemm_tc_pair_add_norm"): [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_void_p, c_long,
                                                c_void_p, c_void_p, c_int, c_void_p, c_long, c_void_p, c_void_p],
     ("rowwise", "cml_scale_rows"): [c_void_p, c_int, c_long, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
@@ -108,7 +110,15 @@ def _p(t):
     return None if t is None else t.data_ptr()
 
 
+try:        # the raw handle of the current stream without building a Stream object (a third of a launch's host time)
+    _raw_stream, _device_now = torch._C._cuda_getCurrentRawStream, torch._C._cuda_getDevice
+except AttributeError:      # a torch without these: the public way
+    _raw_stream = None
+
+
 def _stream():
+    if _raw_stream is not None:
+        return _raw_stream(_device_now())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -259,6 +269,37 @@ def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, epilogue: in
     _check(_fn("gemm_tc", "cml_gemm_tc_pair")(_p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], a.shape[1],
                                              _p(c), c.stride(-2), epilogue, _p(err), _p(sumsq), parts, hidden, eps,
                                              _stream()), "gemm_tc_pair")
+
+
+def pair_partial_splits(k: int, wanted: int) -> int:
+    """How many splits of K ``gemm_tc_pair_partial`` makes when asked for ``wanted``: k-blocks of
+    64 are dealt out evenly and no split stays empty."""
+    blocks = (k + 63) // 64
+    per = (blocks + max(1, min(wanted, blocks)) - 1) // max(1, min(wanted, blocks))
+    return (blocks + per - 1) // per
+
+
+def gemm_tc_pair_partial(a: torch.Tensor, b: torch.Tensor, part: torch.Tensor, err: torch.Tensor,
+                         row_scale: "RowScale | None" = None):
+    """part[s] (float32 [splits, rows of a, rows of b]) = the share of a @ b.T of the s-th split of
+    K, on the two-block tiles of ``gemm_tc_pair``; the splits are work items of their own, which
+    gives a product of a few hundred rows enough of them for every SM. ``part.shape[0]`` must be
+    a count that ``pair_partial_splits`` returns."""
+    _dev(a, b, part, err)
+    if not gemm_tc_usable(a, b):
+        raise KernelError("gemm_tc_pair_partial: operands must be bfloat16 [rows, K] with K and the row strides "
+                          "multiples of 8 and 16-byte aligned bases")
+    assert part.dtype == torch.float32 and part.dim() == 3 and part.stride(2) == 1
+    assert part.shape[1:] == (a.shape[0], b.shape[0])
+    sumsq, parts, hidden, eps = None, 0, 0, 0.0
+    if row_scale is not None:
+        sumsq, hidden, eps = row_scale.sumsq, row_scale.hidden, row_scale.eps
+        _dev(sumsq)
+        parts = sumsq.shape[0]
+        assert sumsq.shape[1] == a.shape[0]
+    _check(_fn("gemm_tc", "cml_gemm_tc_pair_partial")(
+        _p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], a.shape[1], _p(part), part.stride(1),
+        part.stride(0), part.shape[0], _p(err), _p(sumsq), parts, hidden, eps, _stream()), "gemm_tc_pair_partial")
 
 
 def gemm_tc_pair_add_norm(a: torch.Tensor, b: torch.Tensor, h: torch.Tensor, err: torch.Tensor, norm_w: torch.Tensor,

@@ -23,8 +23,13 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._bufs: dict = {}
+        self._views: dict = {}          # (name, dtype, shape) -> view: steps of a size seen before make no new tensors
 
     def get(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
+        shape = tuple(shape)
+        view = self._views.get((name, dtype, shape))
+        if view is not None:
+            return view
         n = 1
         for s in shape:
             n *= int(s)
@@ -33,7 +38,12 @@ class Workspace:
         if buf is None or buf.numel() < n:
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
-        return buf[:n].view(shape)
+            self._views = {k: v for k, v in self._views.items() if k[:2] != key}
+        if len(self._views) > 4096:
+            self._views.clear()
+        view = buf[:n].view(shape)
+        self._views[(name, dtype, shape)] = view
+        return view
 
 
 class StepLayout:

@@ -87,10 +87,9 @@ class GroupedQueryAttention(Part):
         width = self.q_width if borrow else self.q_width + 2 * self.kv_width
         pos = self.position
         row_scale = ctx.take_row_scale()          # the rows of x may still lack their norm's scale
-        if row_scale is not None and n <= linear.DECODE_ROWS:
-            ops.scale_rows(x, row_scale)
+        part = linear.partial_sums(ctx, x, self.w_qkv[:width], "qkv_partial", row_scale)
+        if part is not None:
             row_scale = None
-        part = linear.partial_sums(ctx, x, self.w_qkv[:width], "qkv_partial")
         out = ctx.buffer("attn_out", (n, self.q_width))
         splits = self._decode_splits(ctx, n, 1, True) if ctx.decode else 1
         if (part is not None and ctx.decode and self.decode_fused and (splits <= 8 or ctx.max_len <= 8192)

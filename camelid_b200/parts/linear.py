@@ -6,8 +6,10 @@ to the CUDA-core kernel. Both accumulate in float32 and share the epilogues: sto
 compute type, store float32, add into the float32 residual stream, or SwiGLU on packed
 gate/up rows.
 
-Steps of at most 64 rows (decode) run the tensor-core kernel transposed, with the weights as
-the 128-row operand and K split over several blocks so that every SM streams weights. The
+Steps of at most 128 rows (decode, short prompts) run the tensor-core kernel transposed, with
+the weights as the 128-row operand and K split over several blocks so that every SM streams
+weights. Steps of more rows run on tiles of 256 x 256 of two blocks; where a product has too
+few of those for the SMs (a few hundred rows, a narrow output), K is split there too. The
 split sums stay in float32 and are added, in split order, by the kernel that reads the
 result next: the rotary kernel for q/k/v (``partial_sums``), the next norm for products that
 go into the residual stream (``add_into_residual`` leaves them *pending* on the context).
@@ -23,7 +25,12 @@ from ..csrc import ops
 STORE, STORE_F32, ADD_F32, SWIGLU = ops.EPI_STORE, ops.EPI_STORE_F32, ops.EPI_ADD_F32, ops.EPI_SWIGLU
 
 SM_COUNT = 148
-DECODE_ROWS = 64              # up to here a step runs the transposed kernel
+# Up to here a step runs the transposed kernel. Measured on the 1B shape (prefill step, ms): 96 rows
+# 1.24 transposed against 1.38 on the tiles below, 128 rows 1.31 against 1.42; 144 rows 1.54 against
+# 1.42, 256 rows 1.87 against 1.50: the float split sums that the transposed form writes and its
+# readers sum again grow with the rows, the weights it streams do not.
+DECODE_ROWS = int(os.environ.get("CAMELID_DECODE_ROWS", "128"))
+CLUSTERS = SM_COUNT // 2      # pairs of blocks that run tiles of 256 x 256
 _err: dict = {}
 
 
@@ -45,11 +52,12 @@ def check_errors() -> None:
 
 
 def _bn_decode(rows: int) -> int:
-    return 16 if rows <= 16 else (32 if rows <= 32 else 64)
+    return next((bn for bn in (16, 32, 64) if rows <= bn), 128)
 
 
+PAIR_SPLITS = os.environ.get("CAMELID_PAIR_SPLITS", "1") != "0"
 FUSE_NORM = os.environ.get("CAMELID_FUSE_NORM", "1") != "0"   # the norm after a product of many rows runs inside it
-PAIR_ROWS = 128     # above this many rows the product runs on 256 x 256 tiles of two blocks
+PAIR_ROWS = max(128, DECODE_ROWS)     # above this many rows the product runs on 256 x 256 tiles of two blocks
 
 
 def _bn_prefill(rows: int, out_features: int) -> int:
@@ -107,16 +115,38 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     ops.gemm_tn_simt(x, w, out, epilogue, group)
 
 
-def partial_sums(ctx, x: torch.Tensor, w: torch.Tensor, name: str):
-    """For a decode-sized step on the tensor-core path: float32 [splits, rows, out] whose sum
-    over splits is x @ w.T. None when the operands do not take that path."""
+def _pair_splits(rows: int, n: int, k: int) -> int:
+    """Splits of K for a product on two-block tiles: more than 1 only for a deep product (K of
+    4,096 or more) whose tiles leave half of the clusters or more without work; then as many as
+    fill them, of at least 16 k-blocks of 64. (Measured at 512 rows of the 1B shape: the down
+    product 53 -> 33 us with 4 splits, but a product of K = 2,048 gains less than the slower
+    kernels that then read its split sums cost.)"""
+    tiles = ((rows + 255) // 256) * ((n + 255) // 256)
+    if 2 * tiles > CLUSTERS or k < 4096:
+        return 1
+    return ops.pair_partial_splits(k, max(1, min(CLUSTERS // tiles, (k + 63) // 64 // 16)))
+
+
+def partial_sums(ctx, x: torch.Tensor, w: torch.Tensor, name: str, row_scale=None):
+    """float32 [splits, rows, out] whose sum over splits is x @ w.T, where the tensor-core path
+    splits K for this step's size; None (and nothing done) where it does not. ``row_scale``
+    (``ops.RowScale``): what the rows of ``x`` still lack; applied if a result is returned."""
     rows = x.shape[0]
-    if rows > DECODE_ROWS or not ops.gemm_tc_usable(x, w):
+    if not ops.gemm_tc_usable(x, w):
         return None
     n, k = w.shape
-    splits = min(_splits(n, k), (k + 63) // 64)
+    if rows <= DECODE_ROWS:
+        if row_scale is not None:
+            ops.scale_rows(x, row_scale)
+        splits = min(_splits(n, k), (k + 63) // 64)
+        part = ctx.buffer(name, (splits, rows, n), torch.float32)
+        ops.gemm_tc(w, x, part, ops.TC_T_PARTIAL, _bn_decode(rows), splits, _err_word(x.device))
+        return part
+    splits = _pair_splits(rows, n, k) if PAIR_SPLITS else 1
+    if splits == 1:
+        return None
     part = ctx.buffer(name, (splits, rows, n), torch.float32)
-    ops.gemm_tc(w, x, part, ops.TC_T_PARTIAL, _bn_decode(rows), splits, _err_word(x.device))
+    ops.gemm_tc_pair_partial(x, w, part, _err_word(x.device), row_scale)
     return part
 
 

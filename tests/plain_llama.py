@@ -229,10 +229,11 @@ def output_weight(cfg: dict, w: dict) -> torch.Tensor:
     return w["model.embed_tokens.weight"]
 
 
-def forward(cfg: dict, w: dict, ids, dtype=torch.float32, schedule=None) -> torch.Tensor:
+def forward(cfg: dict, w: dict, ids, dtype=torch.float32, schedule=None, rows=None) -> torch.Tensor:
     """Logits [T, V] of one whole sequence: embedding, the layers in order, final norm
     (src/inference.rs:4259-4264), output projection without bias or scaling
-    (src/inference.rs:4284-4290).
+    (src/inference.rs:4284-4290). ``rows``: only these positions' logits (the output projection
+    of a large vocabulary is most of the work), in the order given.
 
     ``schedule`` is the order in which layers run, as a list of (layer, source) pairs:
     ``source`` None means the entry makes its own keys and values, an integer means it
@@ -250,6 +251,8 @@ def forward(cfg: dict, w: dict, ids, dtype=torch.float32, schedule=None) -> torc
         h, kv = decoder_layer(h, w, layer, cfg, positions, freqs, override)
         kept.append(kv)
     n = rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
+    if rows is not None:
+        n = n[torch.as_tensor(list(rows), dtype=torch.int64)]
     return n @ output_weight(cfg, w).to(dtype).T
 
 

@@ -69,12 +69,18 @@ def test_swiglu_normal(cuda, m, inter, k):
         assert rel_err(act.cpu(), ref) <= 2 ** -7, bn
 
 
-@pytest.mark.parametrize("rows", [1, 8, 17, 64])
+def _bn_for(rows):
+    return next((bn for bn in (16, 32, 64) if rows <= bn), 128)
+
+
+@pytest.mark.parametrize("rows", [1, 8, 17, 64, 100, 129, 256, 300])
 @pytest.mark.parametrize("n,k,splits", [(100, 64, 1), (384, 200, 3), (3072, 2048, 6), (2048, 8192, 9), (517, 136, 7)])
 def test_transposed_partials(cuda, rows, n, k, splits):
+    """Weights as the 128-row operand, the step's rows as the other (tiles of 16 to 128 of them,
+    several tiles beyond that), K split."""
     ops = _ops()
     x, w, ref = _operands(rows, n, k, cuda, 3)
-    bn = 16 if rows <= 16 else (32 if rows <= 32 else 64)
+    bn = _bn_for(rows)
     splits = min(splits, (k + 63) // 64)
     part = torch.full((splits, rows, n), float("nan"), device=cuda)
     err = torch.zeros(1, dtype=torch.int32, device=cuda)
@@ -83,7 +89,7 @@ def test_transposed_partials(cuda, rows, n, k, splits):
     assert int(err) == 0
 
 
-@pytest.mark.parametrize("rows", [1, 8, 33])
+@pytest.mark.parametrize("rows", [1, 8, 33, 90, 200, 260])
 @pytest.mark.parametrize("inter,k", [(160, 64), (528, 200), (8192, 2048)])
 def test_swiglu_transposed(cuda, rows, inter, k):
     ops = _ops()
@@ -92,7 +98,7 @@ def test_swiglu_transposed(cuda, rows, inter, k):
     _, wu, _ = _operands(rows, inter, k, cuda, 5)
     u = x.cpu().double() @ wu.cpu().double().T
     ref = (g / (1 + torch.exp(-g))) * u
-    bn = 16 if rows <= 16 else (32 if rows <= 32 else 64)
+    bn = _bn_for(rows)
     act = torch.full((rows, inter), float("nan"), dtype=BF, device=cuda)
     err = torch.zeros(1, dtype=torch.int32, device=cuda)
     ops.gemm_tc(pack_gate_up(wg, wu, 16), x, act, ops.TC_T_SWIGLU, bn, 1, err)
@@ -152,6 +158,33 @@ def test_pair_tiles(cuda, m, n, k):
     want = res.cpu().double() + ref
     ops.gemm_tc_pair(a, w, res, ops.TC_ADD_F32, err)
     assert rel_err(res.cpu(), want) <= 1e-5
+    assert int(err) == 0
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(300, 300, 136, 3), (512, 2048, 8192, 4), (257, 517, 2048, 5), (1000, 3072, 2048, 3),
+                                          (400, 256, 64, 2), (300, 2048, 1088, 17)])
+def test_pair_tiles_split_over_k(cuda, m, n, k, splits):
+    """The two-block tiles with K split into partial sums (the splits are work items of their
+    own): ragged edges, more splits asked than there are k-blocks, rows that still lack a scale."""
+    ops = _ops()
+    a, w, ref = _operands(m, n, k, cuda, seed=6)
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    n_splits = ops.pair_partial_splits(k, splits)
+    assert 1 <= n_splits <= min(splits, (k + 63) // 64)
+    part = torch.full((n_splits, m, n), float("nan"), device=cuda)
+    ops.gemm_tc_pair_partial(a, w, part, err)
+    assert rel_err(part.sum(0).cpu(), ref) <= 1e-5
+    if n_splits > 1:                              # every split holds only its own share
+        per = -(-((k + 63) // 64) // n_splits) * 64
+        first = a.cpu().double()[:, :per] @ w.cpu().double()[:, :per].T
+        assert rel_err(part[0].cpu(), first) <= 1e-5
+    sumsq = torch.rand(2, m, device=cuda) * 50 + 1
+    scale = torch.rsqrt(sumsq.sum(0).cpu().double() / 77 + 1e-5)
+    part.fill_(float("nan"))
+    ops.gemm_tc_pair_partial(a, w, part, err, ops.RowScale(sumsq, 77, 1e-5))
+    assert rel_err(part.sum(0).cpu(), ref * scale[:, None]) <= 1e-5
+    with pytest.raises(Exception):
+        ops.gemm_tc_pair_partial(a, w, torch.empty(n_splits + 64, m, n, device=cuda), err)
     assert int(err) == 0
 
 
