@@ -996,7 +996,7 @@ template <int HD>
 static int launch_prefill_mma(const AttnParams& p, int n_tiles, cudaStream_t s) {
     constexpr size_t smem = (size_t)AP_STAGES * 2 * AP_TILE * (HD + 8) * sizeof(bf16);
     dim3 grid(n_tiles, p.n_kv_heads * p.head_chunks, 1);
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cml_allow_smem<attn_prefill_mma_kernel<HD>>(smem);
     if (e != cudaSuccess) return (int)e;
     e = launch_pdl(attn_prefill_mma_kernel<HD>, grid, dim3(AP_WARPS * 32), smem, s, p);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
@@ -1008,7 +1008,7 @@ static int launch_mma(const AttnParams& p, int n_tiles, int n_rows, cudaStream_t
     constexpr size_t red_bytes = (size_t)AM_WARPS * 16 * (HD + 2) * sizeof(float);
     constexpr size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
     dim3 grid(n_tiles, p.n_kv_heads * p.head_chunks, p.n_splits);
-    cudaError_t e = cudaFuncSetAttribute(attn_paged_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cml_allow_smem<attn_paged_mma_kernel<HD>>(smem);
     if (e != cudaSuccess) return (int)e;
     e = launch_pdl(attn_paged_mma_kernel<HD>, grid, dim3(AM_WARPS * 32), smem, s, p);
     if (e == cudaSuccess) e = cudaGetLastError();
@@ -1067,7 +1067,7 @@ static int launch_decode_fused(const AdParams& p, int rows, cudaStream_t s) {
     // the ranges of all blocks of a cluster land in block 0, beyond its stages
     const size_t smem = stage_bytes + (p.n_splits > 1 ? (size_t)p.n_splits * group * (HD + 2) * sizeof(float) : 0);
     if (smem + 8 * 1024 > 227 * 1024) return CML_ERR_BAD_SIZE;
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_fused_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cml_allow_smem<attn_decode_fused_kernel<HD>>(smem);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.n_splits, p.n_kv_heads, rows);

@@ -154,8 +154,7 @@ static int launch_attn(const AttnParams& p, int n_tiles, int n_rows, cudaStream_
     cudaError_t e = cudaSuccess;
 #define CML_ATTN(N)                                                                                        \
     do {                                                                                                   \
-        e = cudaFuncSetAttribute(attn_paged_simt_kernel<T, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                 (int)smem);                                                               \
+        e = cml_allow_smem<attn_paged_simt_kernel<T, N>>(smem);                                            \
         if (e != cudaSuccess) return (int)e;                                                               \
         launch_pdl(attn_paged_simt_kernel<T, N>, grid, block, smem, s, p);                                 \
     } while (0)

@@ -504,7 +504,7 @@ static int at_launch(const CUtensorMap& mk, const CUtensorMap& mv, AtParams ap, 
     if ((long)n_tiles * ap.a.n_kv_heads * ap.a.head_chunks > 0x7fffffffL) return CML_ERR_BAD_SIZE;
     ap.n_tiles = n_tiles;
     dim3 grid((unsigned)(n_tiles * ap.a.n_kv_heads * ap.a.head_chunks), 1, 1);
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cml_allow_smem<attn_prefill_tc_kernel<HD>>(smem);
     if (e != cudaSuccess) return (int)e;
     e = launch_pdl(attn_prefill_tc_kernel<HD>, grid, dim3(AT_THREADS), smem, s, mk, mv, ap);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();

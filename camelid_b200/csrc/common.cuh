@@ -86,6 +86,27 @@ static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 b
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// Raises a kernel's limit of dynamic shared memory, once per kernel and size: the call costs
+// about as much as a launch's own bookkeeping and a step launches each kernel many times.
+template <auto Kernel>
+static inline cudaError_t cml_allow_smem(size_t smem) {
+    static size_t allowed = 0;
+    if (smem <= allowed) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) allowed = smem;
+    return e;
+}
+
+static inline int cml_sm_count() {
+    static int sms = 0;
+    if (sms <= 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
+}
+
 static inline int cml_launch_status() {
     cudaError_t e = cudaGetLastError();
     return (int)e;

@@ -896,7 +896,7 @@ static int make_map(CUtensorMap* map, const void* base, long rows, long K, long 
 template <int BN, int EPI, bool DEEP>
 static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t s) {
     const size_t smem = tc_smem_bytes(BN, DEEP);
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cml_allow_smem<gemm_tc_kernel<BN, EPI, DEEP>>(smem);
     if (e != cudaSuccess) return (int)e;
     e = launch_pdl(gemm_tc_kernel<BN, EPI, DEEP>, grid, dim3(TC_THREADS), smem, s, ma, mb, p);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
@@ -942,8 +942,7 @@ extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, lo
     // small: one block per item, several per SM; but where the items are many times the SMs (the
     // output head: a thousand tiles) persistent blocks, one per SM with the deep ring, spare
     // every wave after the first its start-up (barriers, tensor memory, an empty ring).
-    int sms = 148;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    const int sms = cml_sm_count();
     const bool deep = bn <= 64 && p.kb_per_split >= 12;             // as launch_tc chooses
     const bool persistent = bn >= 128 || (deep && work >= 4L * sms);
     dim3 grid((unsigned)(persistent ? (work < sms ? work : sms) : work), 1, 1);
@@ -963,7 +962,7 @@ extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, lo
 template <int EPI, int BN>
 static int launch_tc_pair2(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t s) {
     const size_t smem = tc_pair_smem_bytes();
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cml_allow_smem<gemm_tc_pair_kernel<EPI, BN>>(smem);
     if (e != cudaSuccess) return (int)e;
     e = launch_pdl(gemm_tc_pair_kernel<EPI, BN>, grid, dim3(TC_THREADS), smem, s, ma, mb, p);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
@@ -996,8 +995,7 @@ static int gemm_tc_pair_launch(const void* A, long lda, int rowsA, const void* B
                                long ldc, int epilogue, int* err, const TcPairNorm& nm, void* stream) {
     if (rowsA <= 0 || rowsB <= 0) return 0;
     if (K <= 0 || (K & 7)) return CML_ERR_BAD_SIZE;
-    int sms = 148;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    const int sms = cml_sm_count();
     // the norm's sums of squares are kept per 256 columns: that epilogue stays on the wide tile
     // (so does a product split over K: its splits, not a narrower tile, fill the clusters)
     const int bn = (epilogue == TC_ADD_NORM || nm.splits > 1) ? 256 : pair_tile_width(rowsA, rowsB, sms / 2);

@@ -218,12 +218,23 @@ def rope_kv_from_partials(partial: torch.Tensor, q_out: torch.Tensor, row_pos, r
 TC_STORE, TC_STORE_F32, TC_ADD_F32, TC_SWIGLU, TC_T_PARTIAL, TC_T_SWIGLU = 0, 1, 2, 3, 4, 5
 
 
+def _tc_operand(t: torch.Tensor) -> bool:
+    """Whether TMA can fetch tiles of ``t`` ([rows, K] bfloat16, K-major): 16-byte aligned base and
+    row stride, so K and the stride are multiples of 8. Remembered on the tensor: weights and
+    the workspace's views are the same objects step after step."""
+    try:
+        return t._cml_tc_operand
+    except AttributeError:
+        ok = (t.dtype == torch.bfloat16 and t.dim() == 2 and t.shape[1] % 8 == 0 and t.stride(1) == 1
+              and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0)
+        t._cml_tc_operand = ok
+        return ok
+
+
 def gemm_tc_usable(a: torch.Tensor, b: torch.Tensor) -> bool:
     """Whether the tensor-core kernel takes these operands ([rows, K] bfloat16, K-major): TMA
     needs 16-byte aligned bases and row strides, so K and the strides must be multiples of 8."""
-    return (a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.shape[1] == b.shape[1]
-            and a.shape[1] % 8 == 0 and a.stride(1) == 1 and b.stride(1) == 1 and a.stride(0) % 8 == 0
-            and b.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0)
+    return _tc_operand(a) and _tc_operand(b) and a.shape[1] == b.shape[1]
 
 
 def gemm_tc(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, epilogue: int, bn: int, splits: int, err: torch.Tensor):

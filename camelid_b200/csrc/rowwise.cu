@@ -196,7 +196,7 @@ static int launch_rmsnorm_settle(float* x, const void* w, void* out, const int* 
     if (upr < 1) upr = 1;
     const size_t smem = (size_t)hidden * sizeof(float) + (size_t)upr * block * 16;
     if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
-    cudaError_t e = cudaFuncSetAttribute(rmsnorm_settle_kernel<TW, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cml_allow_smem<rmsnorm_settle_kernel<TW, TO>>(smem);
     if (e != cudaSuccess) return (int)e;
     launch_pdl(rmsnorm_settle_kernel<TW, TO>, dim3(rows), dim3(block), smem, s, x, (const TW*)w, (TO*)out, rows_index, hidden,
                eps, partial, n_splits, (size_t)split_stride, upr);

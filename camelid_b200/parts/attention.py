@@ -85,9 +85,10 @@ class GroupedQueryAttention(Part):
         group, k_pages, v_pages = ctx.kv()
         table = ctx.block_table(group)
         width = self.q_width if borrow else self.q_width + 2 * self.kv_width
+        w_in = self.w_qkv[:width] if borrow else self.w_qkv      # a borrowed cache needs no keys or values of its own
         pos = self.position
         row_scale = ctx.take_row_scale()          # the rows of x may still lack their norm's scale
-        part = linear.partial_sums(ctx, x, self.w_qkv[:width], "qkv_partial", row_scale)
+        part = linear.partial_sums(ctx, x, w_in, "qkv_partial", row_scale)
         if part is not None:
             row_scale = None
         out = ctx.buffer("attn_out", (n, self.q_width))
@@ -108,7 +109,7 @@ class GroupedQueryAttention(Part):
                                       write_kv=not borrow)
         else:
             qkv = ctx.buffer("qkv", (n, width))
-            linear.linear(ctx, x, self.w_qkv[:width], qkv, linear.STORE, row_scale=row_scale)
+            linear.linear(ctx, x, w_in, qkv, linear.STORE, row_scale=row_scale)
             ops.rope_kv_write(qkv, ctx.row_pos, ctx.row_seq, table, k_pages, v_pages, pos.inv_freq, pos.rotary_dim,
                               self.num_heads, self.num_kv_heads, self.head_dim, write_kv=not borrow)
             q = qkv[:, :self.q_width]
