@@ -196,3 +196,34 @@ def test_refused_step_leaves_cache(cuda, model_folders):
         lm.step(cache, [StepEntry(1, [1], [])])                # slot not in use
     assert before == (cache.length(s), list(cache.book.pages[0][s]), cache.book.pools[0].n_free)
     cache.free_slot(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_d"])
+def test_more_sequences_than_a_tile_of_rows(cuda, model_folders, name, dtype):
+    """140 sequences in one batch: their prompts in one step, then decode steps of 140 rows (more
+    than the 128 rows up to which products run transposed), then of 100 after 40 have ended."""
+    from camelid_b200 import StepEntry
+    lm = load(model_folders, name, dtype)
+    vocab = CONFIGS[name]["vocab_size"]
+    n, steps = 140, 4
+    lens = [1 + (7 * i) % 13 for i in range(n)]
+    seqs = [tokens(5000 + i, lens[i] + steps, vocab) for i in range(n)]
+    refs = [oracle(model_folders[name], s) for s in seqs]
+    cache = lm.new_cache(n * 64, max_slots=n)
+    slots = [cache.alloc_slot() for _ in range(n)]
+    logits = lm.step(cache, [StepEntry(slots[i], seqs[i][:lens[i]], [lens[i] - 1]) for i in range(n)]).cpu()
+    assert_close(logits, torch.stack([refs[i][lens[i] - 1] for i in range(n)]), dtype, f"{name} prompts of {n} sequences")
+    live = list(range(n))
+    for t in range(steps):
+        if t == 2:
+            for i in live[100:]:
+                cache.free_slot(slots[i])
+            live = live[:100]
+        logits = lm.step(cache, [StepEntry(slots[i], [seqs[i][lens[i] + t]], [0]) for i in live]).cpu()
+        assert_close(logits, torch.stack([refs[i][lens[i] + t] for i in live]), dtype,
+                     f"{name} decode step {t} of {len(live)} sequences")
+    for i in live:
+        cache.free_slot(slots[i])
+    cache.book.audit()
+    assert cache.book.slots.n_held == 0 and cache.book.pools[0].n_held == 0
