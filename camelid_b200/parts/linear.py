@@ -96,22 +96,23 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
             if epilogue == STORE_F32:
                 ops.gemm_tc(w, x, out.unsqueeze(0), ops.TC_T_PARTIAL, bn, 1, err)
                 return
-        else:
-            bn = _bn_prefill(rows, w.shape[0])
-            if epilogue == SWIGLU:
-                if swiglu_tc:
-                    if pair:
-                        ops.gemm_tc_pair(x, w, out, ops.TC_SWIGLU, err, row_scale)
-                    else:
-                        ops.gemm_tc(x, w, out, ops.TC_SWIGLU, bn, 1, err)
-                    return
-            else:
-                epi = {STORE: ops.TC_STORE, STORE_F32: ops.TC_STORE_F32, ADD_F32: ops.TC_ADD_F32}[epilogue]
+        # everything else on tiles of this step's rows by the weights' rows (for few rows only
+        # what a part outside the library asks for: the library's own few-row products are above)
+        bn = _bn_prefill(rows, w.shape[0])
+        if epilogue == SWIGLU:
+            if swiglu_tc:
                 if pair:
-                    ops.gemm_tc_pair(x, w, out, epi, err, row_scale)
+                    ops.gemm_tc_pair(x, w, out, ops.TC_SWIGLU, err, row_scale)
                 else:
-                    ops.gemm_tc(x, w, out, epi, bn, 1, err)
+                    ops.gemm_tc(x, w, out, ops.TC_SWIGLU, bn, 1, err)
                 return
+        else:
+            epi = {STORE: ops.TC_STORE, STORE_F32: ops.TC_STORE_F32, ADD_F32: ops.TC_ADD_F32}[epilogue]
+            if pair:
+                ops.gemm_tc_pair(x, w, out, epi, err, row_scale)
+            else:
+                ops.gemm_tc(x, w, out, epi, bn, 1, err)
+            return
     ops.gemm_tn_simt(x, w, out, epilogue, group)
 
 

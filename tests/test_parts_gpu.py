@@ -158,3 +158,34 @@ def test_unknown_part_is_a_clear_error():
     assert "attention" in str(e.value)
     with pytest.raises(ValueError):
         build_part("mixer", PartSpec("attention", {"hidden_size": 8, "num_heads": 2, "num_kv_heads": 1, "head_dim": 24}))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows", [3, 70, 128, 129, 300, 600])
+def test_linear_every_epilogue_at_every_step_size(cuda, dtype, rows):
+    """``parts.linear.linear`` as a part from outside the library may call it: store, float store
+    and add into a float stream, whatever form the product takes for the step's rows; and the
+    split sums of ``partial_sums`` where it gives some."""
+    from camelid_b200.parts import linear
+    g = torch.Generator().manual_seed(rows)
+    k, n = 264, 200
+    x = torch.randn(rows, k, generator=g).to(DT[dtype]).cuda()
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(DT[dtype]).cuda()
+    ref = x.cpu().double() @ w.cpu().double().T
+    ctx = _ctx(None, dtype, [0], [0], [[0] * rows])
+    tol = 1e-5 if dtype == "float32" else 2 ** -7
+    out = torch.full((rows, n), float("nan"), dtype=DT[dtype], device="cuda")
+    linear.linear(ctx, x, w, out, linear.STORE)
+    assert rel_err(out.cpu(), ref) <= tol
+    out32 = torch.full((rows, n), float("nan"), device="cuda")
+    linear.linear(ctx, x, w, out32, linear.STORE_F32)
+    assert rel_err(out32.cpu(), ref) <= 1e-5
+    res = torch.randn(rows, n, generator=g).cuda()
+    want = res.cpu().double() + ref
+    linear.linear(ctx, x, w, res, linear.ADD_F32)
+    assert rel_err(res.cpu(), want) <= 1e-5
+    part = linear.partial_sums(ctx, x, w, "test_partial")
+    if part is not None:
+        assert part.dtype == torch.float32 and part.shape[1:] == (rows, n)
+        assert rel_err(part.sum(0).cpu(), ref) <= 1e-5
+    linear.check_errors()
