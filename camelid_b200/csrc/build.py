@@ -32,6 +32,7 @@ MODULES = {
     "gemm_simt": ["gemm_simt.cu"],
     "sampling": ["sampling.cu", "decode_loop.cu"],
     "gemm_tc": ["gemm_tc.cu"],
+    "random_fill": ["random_fill.cu"],
 }
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]

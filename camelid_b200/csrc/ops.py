@@ -65,6 +65,8 @@ _SIGNATURES = {
                                          c_int, c_float, c_int, c_float, c_float, ctypes.c_ulonglong, c_void_p, c_void_p],
     ("sampling", "cml_sample_rows"): [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_void_p,
                                       c_void_p, c_void_p, c_void_p],
+    ("random_fill", "cml_random_fill"): [c_void_p, c_int, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_ulonglong,
+                                         ctypes.c_double, ctypes.c_double, c_void_p],
 }
 _fns: dict = {}
 _launches = 0
@@ -130,6 +132,15 @@ def dtype_code(dt: torch.dtype) -> int:
 
 
 # ---------------------------------------------------------------------------------------
+
+def random_fill(out: torch.Tensor, key: int, first: int, mean: float, std: float):
+    """out.view(-1)[i] = element ``first + i`` of the counter-based generator under ``key``
+    (weights/counter_random.py is the host's definition of the same numbers)."""
+    _dev(out)
+    assert out.is_contiguous()
+    _check(_fn("random_fill", "cml_random_fill")(_p(out), dtype_code(out.dtype), out.numel(), int(key), int(first),
+                                                 float(mean), float(std), _stream()), "random_fill")
+
 
 def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err: torch.Tensor):
     """out[r] = table[tokens[r]] as float32. ``err`` (int32[1]) gets bit 1 on a bad id."""

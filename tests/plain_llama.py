@@ -6,9 +6,11 @@ from. It runs whole sequences without a cache, has one function for each part, a
 shares no code with the ``camelid_b200`` package: it reads ``config.json`` as a plain
 dict and ``model.safetensors`` with a reader of its own.
 
-Everything is computed on the CPU in ``dtype`` (float32 as in the reference, or
-float64 as a tighter ground truth); weights are taken as stored (bfloat16 values are
-exactly representable in both).
+Everything is computed in ``dtype`` (float32 as in the reference, or float64 as a tighter
+ground truth), on the CPU unless ``forward`` is given a device: the wide shapes of the
+benchmark take minutes in float64 on a CPU, so tests of those run these same plain torch
+operations on the GPU. Weights are taken as stored (bfloat16 values are exactly
+representable in both types).
 """
 from __future__ import annotations
 
@@ -83,7 +85,7 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, dtype) -> torch.Tensor:
     an error (src/tensor/mod.rs:2253-2283, error at :2266-2270)."""
     if int(ids.max()) >= table.shape[0] or int(ids.min()) < 0:
         raise ValueError("token id outside the vocabulary")
-    return table.to(dtype)[ids.long()]
+    return table.to(ids.device, dtype)[ids.long()]
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -91,7 +93,7 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     out = x * scale * weight, in that order (src/tensor/mod.rs:2086-2096)."""
     mean_square = (x * x).sum(dim=-1, keepdim=True) / x.shape[-1]
     scale = 1.0 / torch.sqrt(mean_square + eps)
-    return x * scale * weight.to(x.dtype)
+    return x * scale * weight.to(x.device, x.dtype)
 
 
 def rope_frequencies(cfg: dict) -> np.ndarray:
@@ -136,7 +138,7 @@ def rope(x: torch.Tensor, positions: torch.Tensor, freqs: np.ndarray) -> torch.T
     x0' = x0 cos - x1 sin, x1' = x0 sin + x1 cos
     (src/inference/rope.rs:489-524, pairing at :501-509)."""
     half = freqs.shape[0]
-    f = torch.from_numpy(freqs)
+    f = torch.from_numpy(freqs).to(x.device)
     angle = positions.to(torch.float32)[:, None] * f[None, :]        # float32 product
     cos = torch.cos(angle.to(torch.float64)).to(x.dtype)[:, None, :]
     sin = torch.sin(angle.to(torch.float64)).to(x.dtype)[:, None, :]
@@ -163,7 +165,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int | N
     for h in range(nH):
         kvh = h // group
         scores = (q[:, h, :] @ k[:, kvh, :].T) * scale              # [T, T]
-        idx = torch.arange(T)
+        idx = torch.arange(T, device=q.device)
         mask = idx[None, :] > idx[:, None]
         if window is not None:
             mask = mask | (idx[None, :] <= idx[:, None] - window)
@@ -178,10 +180,20 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int | N
 def swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
     """g = x Wg^T, u = x Wu^T, act = (g / (1 + exp(-g))) * u, d = act Wd^T
     (src/inference.rs:9657-9664, :6654-6706)."""
-    g = x @ w_gate.to(x.dtype).T
-    u = x @ w_up.to(x.dtype).T
+    g = x @ w_gate.to(x.device, x.dtype).T
+    u = x @ w_up.to(x.device, x.dtype).T
     act = (g / (1.0 + torch.exp(-g))) * u
-    return act @ w_down.to(x.dtype).T
+    return act @ w_down.to(x.device, x.dtype).T
+
+
+class _On:
+    """``w[name]`` on a device."""
+
+    def __init__(self, w, device):
+        self.w, self.device = w, device
+
+    def __getitem__(self, name):
+        return self.w[name].to(self.device)
 
 
 def attention_block(x: torch.Tensor, w: dict, prefix: str, cfg: dict, positions: torch.Tensor,
@@ -192,6 +204,7 @@ def attention_block(x: torch.Tensor, w: dict, prefix: str, cfg: dict, positions:
     T = x.shape[0]
     nH, nKV, hd = cfg["num_attention_heads"], kv_heads_of(cfg), head_dim_of(cfg)
     dt = x.dtype
+    w = _On(w, x.device)
     q = (x @ w[prefix + "self_attn.q_proj.weight"].to(dt).T).reshape(T, nH, hd)
     q = rope(q, positions, freqs)
     if kv_override is None:
@@ -229,7 +242,7 @@ def output_weight(cfg: dict, w: dict) -> torch.Tensor:
     return w["model.embed_tokens.weight"]
 
 
-def forward(cfg: dict, w: dict, ids, dtype=torch.float32, schedule=None, rows=None) -> torch.Tensor:
+def forward(cfg: dict, w: dict, ids, dtype=torch.float32, schedule=None, rows=None, device="cpu") -> torch.Tensor:
     """Logits [T, V] of one whole sequence: embedding, the layers in order, final norm
     (src/inference.rs:4259-4264), output projection without bias or scaling
     (src/inference.rs:4284-4290). ``rows``: only these positions' logits (the output projection
@@ -238,9 +251,9 @@ def forward(cfg: dict, w: dict, ids, dtype=torch.float32, schedule=None, rows=No
     ``schedule`` is the order in which layers run, as a list of (layer, source) pairs:
     ``source`` None means the entry makes its own keys and values, an integer means it
     reads those made by that earlier entry of the list. The default is every layer once."""
-    ids = torch.as_tensor(ids, dtype=torch.int64)
+    ids = torch.as_tensor(ids, dtype=torch.int64).to(device)
     T = ids.shape[0]
-    positions = torch.arange(T)
+    positions = torch.arange(T, device=device)
     freqs = rope_frequencies(cfg)
     h = embedding(ids, w["model.embed_tokens.weight"], dtype)
     if schedule is None:
@@ -252,8 +265,8 @@ def forward(cfg: dict, w: dict, ids, dtype=torch.float32, schedule=None, rows=No
         kept.append(kv)
     n = rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
     if rows is not None:
-        n = n[torch.as_tensor(list(rows), dtype=torch.int64)]
-    return n @ output_weight(cfg, w).to(dtype).T
+        n = n[torch.as_tensor(list(rows), dtype=torch.int64).to(device)]
+    return (n @ output_weight(cfg, w).to(n.device, dtype).T).cpu()
 
 
 # --------------------------------------------------------------------------------------
@@ -369,6 +382,56 @@ def sample(logits: np.ndarray, history, *, temperature=0.0, top_k=None, top_p=No
         if draw < cum:
             return i
     return cand[-1][0]
+
+
+# --------------------------------------------------------------------------------------
+# random weights (the library's generator restated one element at a time)
+
+
+def _fnv1a64(data: bytes) -> int:
+    h = 0xCBF29CE484222325
+    for b in data:
+        h = ((h ^ b) * 0x100000001B3) & _MASK64
+    return h
+
+
+def random_weight(seed: int, name: str, index: int, kind: str = "linear") -> np.float32:
+    """Element ``index`` (row-major) of the random tensor ``name``: Box-Muller on the two halves
+    of splitmix64(key + (index + 1) * golden), key = splitmix64(fnv1a64(name) ^ splitmix64(seed)),
+    with the logarithm and cosine as written-out polynomials in correctly rounded double
+    operations; N(0, 0.02), norm weights 1 + N(0, 0.02). Ours: the reference's only random
+    weights are an LCG in its tests (src/cuda_resident/tests.rs:537-553)."""
+    key = splitmix64(_fnv1a64(name.encode("utf-8")) ^ splitmix64(seed))
+    z = splitmix64(key + (index + 1) * 0x9E3779B97F4A7C15)
+    n = float((z >> 32) + 1)
+    b = z & 0xFFFFFFFF
+    mant, ex = math.frexp(n)
+    if mant < 0.7071067811865476:
+        mant, ex = mant * 2.0, ex - 1
+    s = (mant - 1.0) / (mant + 1.0)
+    w = s * s
+    p = 1.0 / 21.0
+    for k in range(9, -1, -1):
+        p = p * w + 1.0 / (2 * k + 1)
+    ln_u = float(ex - 32) * 0.6931471805599453 + (2.0 * s) * p
+    r = math.sqrt(-2.0 * ln_u)
+    octant = b >> 29
+    f = float(b & 0x1FFFFFFF) * (1.0 / 536870912.0)
+    t = ((1.0 - f) if octant & 1 else f) * 0.7853981633974483
+    w = t * t
+    if octant in (1, 2, 5, 6):
+        p = 1.0 / math.factorial(17)
+        for k in range(7, -1, -1):
+            p = p * w + (-1.0) ** k / math.factorial(2 * k + 1)
+        trig = t * p
+    else:
+        p = 1.0 / math.factorial(16)
+        for k in range(7, -1, -1):
+            p = p * w + (-1.0) ** k / math.factorial(2 * k)
+        trig = p
+    if octant in (2, 3, 4, 5):
+        trig = -trig
+    return np.float32((1.0 if kind == "norm" else 0.0) + 0.02 * (r * trig))
 
 
 # --------------------------------------------------------------------------------------

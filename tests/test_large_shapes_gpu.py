@@ -20,7 +20,7 @@ def _folder(tmp_path_factory, name, **over):
            "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                             "original_max_position_embeddings": 8192}, "tie_word_embeddings": True, **over}
     d = str(tmp_path_factory.mktemp(name))
-    write_random_model(d, cfg, 2, torch.bfloat16)
+    write_random_model(d, cfg, 2, torch.bfloat16, device="cuda")
     return d, cfg
 
 
