@@ -179,3 +179,110 @@ def test_pinned_logits_of_the_micro_model():
     assert np.allclose(got["logits_last"], want["logits_last"], atol=1e-9)
     assert np.allclose(got["logits_first"], want["logits_first"], atol=1e-9)
     assert abs(got["sum_abs"] - want["sum_abs"]) < 1e-6
+
+
+# ---- the reference's own hand-built models and the numbers its tests expect of them ----
+
+def _select_rows(rows, cols, source_cols, scale=1.0):
+    m = torch.zeros(rows, cols)
+    for r, c in enumerate(source_cols):
+        m[r, c] = scale
+    return m
+
+
+def _session_model():
+    """The model of tests/inference_session.rs:545-614: hidden 4, 2 heads on 1 kv head of 2,
+    feed-forward 6, vocabulary 3, eps 1e-6, theta 10000; every matrix selects columns. Its
+    rotary pairs are adjacent; with a rotary size of 2 that is also the split-half pair."""
+    cfg = {"hidden_size": 4, "num_hidden_layers": 1, "intermediate_size": 6, "num_attention_heads": 2,
+           "num_key_value_heads": 1, "head_dim": 2, "vocab_size": 3, "rms_norm_eps": 1e-6, "rope_theta": 10000.0,
+           "tie_word_embeddings": False}
+    p = "model.layers.0."
+    w = {"model.embed_tokens.weight": torch.tensor([[1.0, 0, 0, 0], [0.5, 0, 0, 0], [0, 1.0, 0, 0]]),
+         "model.norm.weight": torch.ones(4),
+         "lm_head.weight": torch.tensor([[1.0, 0, 0, 0], [0, 1.0, 0, 0], [0, 0, 1.0, 0]]),
+         p + "input_layernorm.weight": torch.ones(4), p + "post_attention_layernorm.weight": torch.ones(4),
+         p + "self_attn.q_proj.weight": _select_rows(4, 4, [0, 1, 2, 3]),
+         p + "self_attn.k_proj.weight": _select_rows(2, 4, [0, 1]),
+         p + "self_attn.v_proj.weight": _select_rows(2, 4, [0, 1], 0.5),
+         p + "self_attn.o_proj.weight": _select_rows(4, 4, [0, 1, 2, 3]),
+         p + "mlp.gate_proj.weight": _select_rows(6, 4, [0, 1, 2, 3, 0, 1]),
+         p + "mlp.up_proj.weight": _select_rows(6, 4, [0, 1, 2, 3, 0, 1]),
+         p + "mlp.down_proj.weight": _select_rows(4, 6, [0, 1, 2, 3])}
+    return cfg, w
+
+
+def _kept_keys_and_values(cfg, w, ids):
+    x = pl.embedding(torch.tensor(ids), w["model.embed_tokens.weight"], torch.float32)
+    n = pl.rms_norm(x, w["model.layers.0.input_layernorm.weight"], cfg["rms_norm_eps"])
+    _out, (k, v) = pl.attention_block(n, w, "model.layers.0.", cfg, torch.arange(len(ids)), pl.rope_frequencies(cfg))
+    return k, v
+
+
+def test_reference_session_model_keys_and_values_after_one_token():
+    """tests/inference_session.rs:27-40: after token 1 the cache holds keys (1.999984, 0) and
+    values (0.999992, 0): the norm's scale 1/sqrt(0.25/4 + 1e-6) on 0.5, the value matrix 0.5."""
+    cfg, w = _session_model()
+    k, v = _kept_keys_and_values(cfg, w, [1])
+    assert k.shape == (1, 1, 2) and v.shape == (1, 1, 2)
+    assert abs(float(k[0, 0, 0]) - 1.999984) < 5e-4 and abs(float(k[0, 0, 1])) < 5e-4
+    assert abs(float(v[0, 0, 0]) - 0.999992) < 5e-4 and abs(float(v[0, 0, 1])) < 5e-4
+    logits = pl.forward(cfg, w, [1])
+    assert logits.shape == (1, 3) and torch.isfinite(logits).all()
+
+
+def test_reference_session_model_rotates_the_key_before_it_is_kept():
+    """tests/inference_session.rs:43-56: token 2 at position 1 has the key (0, y) before the
+    rotation, y = 1/sqrt(0.25 + 1e-6); the cache holds (-y sin 1, y cos 1)."""
+    cfg, w = _session_model()
+    k, _v = _kept_keys_and_values(cfg, w, [1, 2])
+    y = 1.0 / math.sqrt(0.25 + 1e-6)
+    assert abs(float(k[1, 0, 0]) + y * math.sin(1.0)) < 5e-4
+    assert abs(float(k[1, 0, 1]) - y * math.cos(1.0)) < 5e-4
+    assert abs(float(k[0, 0, 0]) - 1.999984) < 5e-4          # the first key is as after one token
+
+
+def test_reference_session_model_whole_layer_by_hand():
+    """The same model carried through the whole layer by hand for token 1 alone (one key: the
+    attention output is the value), with the reference's order of operations
+    (src/inference.rs:6228-6804): every matrix selects columns, so each step is a line."""
+    cfg, w = _session_model()
+    s1 = 1.0 / math.sqrt(0.25 / 4 + 1e-6)
+    v0 = 0.5 * 0.5 * s1                                   # value = 0.5 * normed x0; both heads copy it
+    r = [0.5 + v0, 0.0, v0, 0.0]                          # residual + attention output (heads 0 and 1, first lane each)
+    s2 = 1.0 / math.sqrt((r[0] ** 2 + r[2] ** 2) / 4 + 1e-6)
+    n2 = [x * s2 for x in r]
+    act = [(g / (1 + math.exp(-g))) * g for g in n2]      # gate and up select the same columns
+    out = [r[i] + act[i] for i in range(4)]               # down selects the first four of six
+    s3 = 1.0 / math.sqrt(sum(x * x for x in out) / 4 + 1e-6)
+    want = [out[0] * s3, out[1] * s3, out[2] * s3]        # the output matrix selects columns 0, 1, 2
+    got = pl.forward(cfg, w, [1])[0]
+    assert torch.allclose(got, torch.tensor(want, dtype=torch.float32), atol=1e-6)
+
+
+def test_reference_tied_output_rows():
+    """src/inference/tests.rs:8830-8852: hidden (2, 3) against the tied embedding rows (1, 0),
+    (0, 1), (2, 3) gives logits 2, 3, 13; :8854-8893: (2, -1, 0.5) against the row
+    (2, -0.5, 1.5) gives 5.25."""
+    cfg = {"tie_word_embeddings": True}
+    w = {"model.embed_tokens.weight": torch.tensor([[1.0, 0.0], [0.0, 1.0], [2.0, 3.0]])}
+    logits = torch.tensor([[2.0, 3.0]]) @ pl.output_weight(cfg, w).T
+    assert torch.allclose(logits, torch.tensor([[2.0, 3.0, 13.0]]), atol=1e-6)
+    w = {"model.embed_tokens.weight": torch.tensor([[0.5, 1.0, -2.0], [-1.0, 0.25, 0.75], [2.0, -0.5, 1.5], [0.0, 3.0, -1.0]])}
+    logits = torch.tensor([[2.0, -1.0, 0.5]]) @ pl.output_weight(cfg, w).T
+    assert abs(float(logits[0, 2]) - 5.25) < 1e-6
+    # through forward: an identity layer stack is not available, so the final norm's factor is divided out
+    cfg = {"hidden_size": 2, "num_hidden_layers": 0, "num_attention_heads": 1, "head_dim": 2, "vocab_size": 3,
+           "rms_norm_eps": 1e-6, "tie_word_embeddings": True}
+    w = {"model.embed_tokens.weight": torch.tensor([[1.0, 0.0], [0.0, 1.0], [2.0, 3.0]]), "model.norm.weight": torch.ones(2)}
+    got = pl.forward(cfg, w, [2])[0] * math.sqrt((4 + 9) / 2 + 1e-6)
+    assert torch.allclose(got, torch.tensor([2.0, 3.0, 13.0]), atol=1e-5)
+
+
+def test_reference_norm_mean_square():
+    """src/inference/tests.rs:1852-1862: (3, 4, 0, -5) has mean square 12.5; the norm's output is
+    x / sqrt(12.5 + eps) * weight."""
+    x = torch.tensor([[3.0, 4.0, 0.0, -5.0]])
+    w = torch.tensor([1.0, 2.0, 3.0, 4.0])
+    s = 1 / math.sqrt(12.5 + 1e-5)
+    assert torch.allclose(pl.rms_norm(x, w, 1e-5), torch.tensor([[3 * s, 8 * s, 0.0, -20 * s]]), atol=1e-6)
