@@ -2,7 +2,9 @@
 (tests/inference_session.rs:27-56), on that test's model widened to a head size the kernels
 take: hidden 32, two heads on one kv head of 16, matrices that select columns. Token 1 is
 0.5 in column 0, token 2 is 1 in column 8, which the split-half rotation pairs with column 0
-at frequency 1, so the kept key of token 2 at position 1 is (-y sin 1, ..., y cos 1) as there."""
+at frequency 1, so the kept key of token 2 at position 1 is (-y sin 1, ..., y cos 1) as there.
+Column 31, which no key or value reads, carries what brings each token's mean square to the
+reference's (0.0625 and 0.25), so the expected numbers are the reference's own digits."""
 import math
 
 import pytest
@@ -26,6 +28,7 @@ def _model(dtype):
            "tie_word_embeddings": False}
     emb = torch.zeros(3, 32)
     emb[0, 0], emb[1, 0], emb[2, 8] = 1.0, 0.5, 1.0
+    emb[1, 31], emb[2, 31] = math.sqrt(0.0625 * 32 - 0.25), math.sqrt(0.25 * 32 - 1.0)
     p = "model.layers.0."
     w = {"model.embed_tokens.weight": emb, "model.norm.weight": torch.ones(32), "lm_head.weight": _select_rows(3, 32, [0, 1, 2]),
          p + "input_layernorm.weight": torch.ones(32), p + "post_attention_layernorm.weight": torch.ones(32),
@@ -55,11 +58,9 @@ def test_kept_keys_and_values_are_the_reference_sessions(cuda, cut):
     page = cache.book.pages[0][slot][0]
     _group, k_pages, v_pages = cache.kv_pages(0)
     k, v = k_pages[page, 0].float().cpu(), v_pages[page, 0].float().cpu()      # [64 positions, 16]
-    # hidden 32 instead of 4: the mean square of token 1 is 0.25 / 32, of token 2 it is 1 / 32
-    s1 = 1.0 / math.sqrt(0.25 / 32 + 1e-6)
-    y = 1.0 / math.sqrt(1.0 / 32 + 1e-6)
-    assert abs(float(k[0, 0]) - 0.5 * s1) < 5e-4 and float(k[0, 1:].abs().max()) < 5e-4
-    assert abs(float(v[0, 0]) - 0.25 * s1) < 5e-4 and float(v[0, 1:].abs().max()) < 5e-4
+    y = 1.0 / math.sqrt(0.25 + 1e-6)
+    assert abs(float(k[0, 0]) - 1.999984) < 5e-4 and float(k[0, 1:].abs().max()) < 5e-4
+    assert abs(float(v[0, 0]) - 0.999992) < 5e-4 and float(v[0, 1:].abs().max()) < 5e-4
     assert abs(float(k[1, 0]) + y * math.sin(1.0)) < 5e-4
     assert abs(float(k[1, 8]) - y * math.cos(1.0)) < 5e-4
     rest = k[1].clone()
