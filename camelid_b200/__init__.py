@@ -8,7 +8,7 @@ from .errors import (CacheError, CamelidError, ConfigError, KernelError, Safeten
 
 __version__ = "0.1.0"
 __all__ = ["LlamaConfig", "load_config", "register_architecture", "load", "from_random", "LanguageModel",
-           "DecoderModel", "StepEntry", "SamplingOptions", "write_random_model",
+           "DecoderModel", "StepEntry", "SamplingOptions", "KernelOptions", "write_random_model", "memory_plan", "MemoryPlan", "MemoryBudgetError",
            "CacheError", "CamelidError", "ConfigError", "KernelError", "SafetensorsError", "SamplingError",
            "StepError", "UnknownArchitectureError", "WeightsError"]
 
@@ -18,6 +18,10 @@ _LAZY = {
     "DecoderModel": ("camelid_b200.engine.model", "DecoderModel"),
     "StepEntry": ("camelid_b200.engine.model", "StepEntry"),
     "SamplingOptions": ("camelid_b200.sampling.options", "SamplingOptions"),
+    "KernelOptions": ("camelid_b200.options", "KernelOptions"),
+    "memory_plan": ("camelid_b200.memory", "memory_plan"),
+    "MemoryPlan": ("camelid_b200.memory", "MemoryPlan"),
+    "MemoryBudgetError": ("camelid_b200.memory", "MemoryBudgetError"),
     "write_random_model": ("camelid_b200.weights.random_init", "write_random_model"),
 }
 

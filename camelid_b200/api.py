@@ -77,10 +77,11 @@ class LanguageModel:
         return out[0] if single else out
 
 
-def load(folder: str, dtype="bfloat16", device="cuda") -> LanguageModel:
+def load(folder: str, dtype="bfloat16", device="cuda", options=None) -> LanguageModel:
     """Load ``folder`` (config.json, model.safetensors or shards). Stop tokens come from
-    ``generation_config.json``'s ``eos_token_id`` if that file exists, else from config.json."""
-    model = DecoderModel.from_folder(folder, dtype=parse_dtype(dtype), device=device)
+    ``generation_config.json``'s ``eos_token_id`` if that file exists, else from config.json.
+    ``options``: a ``KernelOptions`` (the defaults are the product path)."""
+    model = DecoderModel.from_folder(folder, dtype=parse_dtype(dtype), device=device, options=options)
     stops = model.plan.stop_token_ids
     gen = os.path.join(folder, "generation_config.json")
     if os.path.isfile(gen):
@@ -91,12 +92,12 @@ def load(folder: str, dtype="bfloat16", device="cuda") -> LanguageModel:
     return LanguageModel(model, stops)
 
 
-def from_random(config: dict, seed: int, dtype="bfloat16", device="cuda") -> LanguageModel:
+def from_random(config: dict, seed: int, dtype="bfloat16", device="cuda", options=None) -> LanguageModel:
     """A model of ``config`` (a config.json dict) with random weights drawn on the device:
     the same distributions as the random-weights folder, without the folder."""
     from .weights.random_init import random_tensors
     dt = parse_dtype(dtype)
-    model = DecoderModel.from_config(config, dtype=dt, device=device)
+    model = DecoderModel.from_config(config, dtype=dt, device=device, options=options)
     store = torch.bfloat16 if dt == torch.bfloat16 else torch.float32
     model.load_tensors(_DeviceRandom(model.tensor_specs(), seed, store, device))
     return LanguageModel(model, model.plan.stop_token_ids)

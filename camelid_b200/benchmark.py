@@ -207,44 +207,31 @@ def _prefill_batch(lm, cache, prompts, chunk: int = 8):
 
 
 def measure_decode_device(lm, cfg, batch: int, prompt_tokens, steps: int, warmup: int, rng, prompts=None) -> dict:
-    """K decode steps timed on the device: the captured step graph with the greedy token fed
-    back on the device; the host only sends each step's positions. ``prompt_tokens`` is one
-    length or (lowest, highest); ``prompts`` given wins over it."""
+    """K decode steps timed on the device, in the loop that ``generate`` runs for greedy requests
+    (``DecoderModel.decode_fed``): the captured step graph picks each token and feeds it back on the
+    device; per step the host sends the positions from pinned memory and reads the chosen tokens.
+    CUDA events bracket exactly the K steps. ``prompt_tokens`` is one length or (lowest, highest);
+    ``prompts`` given wins over it."""
     from .csrc import ops
     if prompts is None:
         prompts = _prompts(rng, batch, prompt_tokens, cfg["vocab_size"])
     cache = lm.new_cache(sum(((len(p) + steps + warmup + 1 + 63) // 64) * 64 for p in prompts), max_slots=batch)
     slots, firsts = _prefill_batch(lm, cache, prompts)
-    book = cache.book
-    horizon = warmup + steps
-    book.check_extend([(s, horizon) for s in slots])
-    starts = np.array([book.extend(s, horizon) for s in slots], dtype=np.int32)
-    graph = lm.model.decode_graph(cache, slots, feed=True)
-    i = graph.fill(slots, starts, firsts)
-    graph.send(i, with_tokens=True)
-    if graph.graph is None:
-        graph.capture()
-    h2d = 0
+    model = lm.model
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches0 = 0
     with ClockSampler() as clocks:
-        for step in range(horizon):
-            if step == warmup:
-                torch.cuda.synchronize()
-                launches0 = ops.launch_count()
-                ev0.record()
-            if step > 0:
-                i = graph.fill(slots, starts + step, None)
-                h2d = graph.send(i, with_tokens=False)
-            graph.replay()
+        warm = model.decode_fed(cache, slots, firsts, warmup)
+        torch.cuda.synchronize()
+        launches0 = ops.launch_count()
+        ev0.record()
+        model.decode_fed(cache, slots, warm[-1].tolist(), steps)
         ev1.record()
         torch.cuda.synchronize()
     launches = ops.launch_count() - launches0
-    for s in slots:
-        book.commit(s, horizon)
-    lm.model.check_device_errors()
+    model.check_device_errors()
     ms = ev0.elapsed_time(ev1)
-    lm.model.drop_graphs(cache)
+    h2d = model.last_h2d_bytes
+    model.drop_graphs(cache)
     for s in slots:
         cache.free_slot(s)
     return {"ms_total": ms, "ms_per_step": ms / steps, "value": batch * steps / (ms / 1e3), "launches": launches,
@@ -279,11 +266,23 @@ def measure_decode_e2e(lm, cfg, batch: int, prompt_tokens, steps: int, warmup: i
             "d2h_bytes_per_step": batch * 4}
 
 
+FP32_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12        # plain FMA on every lane of 148 SMs at 1,965 MHz: nominal, 74.4
+
+
+def _roofline(cfg, batch, dec, elem, pk) -> dict:
+    bytes_step = decode_bytes(cfg, batch, dec["context"], elem)
+    achieved = bytes_step / (dec["ms_per_step"] / 1e3) / 1e9
+    return {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+            "bytes": bytes_step}
+
+
 def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warmup: int = 8, dtype: str = "bfloat16",
         layers: int | None = None, config_index: int = 2, points: bool = True, e2e: bool = True,
-        prefill_tokens: int = 2048, prefill: bool = True, decode: bool = True, prompt_range=None) -> dict:
+        prefill_tokens: int = 2048, prefill: bool = True, decode: bool = True, prompt_range=None,
+        fp32: bool = False, fp32_steps: int = 32) -> dict:
     """``prompt_range`` (lowest, highest): prompts of unequal lengths drawn uniformly between the
-    two instead of ``prompt_tokens`` each; the record then also times their one prefill step."""
+    two instead of ``prompt_tokens`` each; the record then also times their one prefill step.
+    ``fp32``: the same decode step and prefill again with a float32 model, as an ``fp32`` object."""
     from . import api
     shape = SHAPES[config_index]
     cfg = config_for(config_index, layers)
@@ -291,7 +290,7 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
     lm = api.from_random(cfg, seed=shape["seed"], dtype=dtype)
     rng = np.random.default_rng(shape["seed"])
     elem = 2 if dtype == "bfloat16" else 4
-    flop_peak = (pk["bf16_tflops"] if dtype == "bfloat16" else 75.0) * 1e12
+    flop_peak = (pk["bf16_tflops"] if dtype == "bfloat16" else FP32_TFLOPS) * 1e12
     if prefill:
         pre = measure_prefill(lm, cfg, prefill_tokens, rng)
         pre["frac"] = prefill_flops(cfg, prefill_tokens) / (pre["ms"] / 1e3) / flop_peak
@@ -305,8 +304,8 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
         pre_batch = measure_prefill_batch(lm, cfg, prompts)
         pre_batch["frac"] = pre_batch.pop("flops") / (pre_batch["ms"] / 1e3) / flop_peak
     dec = measure_decode_device(lm, cfg, batch, prompt_tokens, decode_steps, warmup, rng, prompts=prompts)
-    bytes_step = decode_bytes(cfg, batch, dec["context"], elem)
-    achieved = bytes_step / (dec["ms_per_step"] / 1e3) / 1e9
+    roof = _roofline(cfg, batch, dec, elem, pk)
+    e2e_steps = max(decode_steps, 128)
     rec = {
         "metric": "decode tokens/s, Llama 3.2 1B shape, batch 8 (2048-token prompts)" if (config_index, batch) == (2, 8)
                   else f"decode tokens/s, {shape['name']} shape, batch {batch}",
@@ -321,27 +320,41 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                    "tied": cfg["tie_word_embeddings"], "weights": f"random, seed {shape['seed']}",
-                   "l2": "inputs larger than L2 (every step reads all weights)", "peaks": pk["source"]},
+                   "l2": "inputs larger than L2 (every step reads all weights)", "peaks": pk["source"],
+                   "e2e_steps": e2e_steps, "fp32_steps": fp32_steps if fp32 else 0},
         "prefill": {"value": pre["value"], "tokens": pre["tokens"], "ms": pre["ms"], "frac": pre["frac"]},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / pk["hbm_gbs"]},
+        "roofline": {k: roof[k] for k in ("bound", "achieved", "peak", "unit", "frac")},
         "clocks": dec["clocks"], "gpu_launches": dec["launches"],
     }
     if pre_batch is not None:
         rec["prefill_batch"] = pre_batch
     if e2e:
-        e = measure_decode_e2e(lm, cfg, batch, prompt_tokens, decode_steps, warmup, rng, prompts=prompts)
+        e = measure_decode_e2e(lm, cfg, batch, prompt_tokens, e2e_steps, warmup, rng, prompts=prompts)
         rec["e2e"] = {"value": e["value"], "unit": "tokens/s", "h2d_bytes_per_step": e["h2d_bytes_per_step"],
-                      "d2h_bytes_per_step": e["d2h_bytes_per_step"], "ms_per_step": e["ms_per_step"]}
+                      "d2h_bytes_per_step": e["d2h_bytes_per_step"], "ms_per_step": e["ms_per_step"], "steps": e2e_steps}
     if points:
-        pts = {}
+        pts, detail = {}, {}
         for b in (1, 64):
-            if b == batch:
-                pts[f"decode_b{b}"] = dec["value"]
-                continue
-            d = measure_decode_device(lm, cfg, b, prompt_tokens, min(decode_steps, 64), min(warmup, 4), rng)
+            d = dec if b == batch else measure_decode_device(lm, cfg, b, prompt_tokens, min(decode_steps, 64),
+                                                             min(warmup, 4), rng)
+            r = _roofline(cfg, b, d, elem, pk)
             pts[f"decode_b{b}"] = d["value"]
+            detail[f"decode_b{b}"] = {"value": d["value"], "ms_per_step": d["ms_per_step"], "bytes": r["bytes"],
+                                      "frac": r["frac"]}
         rec["points"] = pts
+        rec["points_detail"] = detail
+    if fp32 and dtype == "bfloat16":
+        del lm
+        torch.cuda.empty_cache()
+        lm32 = api.from_random(cfg, seed=shape["seed"], dtype="float32")
+        d = measure_decode_device(lm32, cfg, batch, prompt_tokens, fp32_steps, 3, rng)
+        r = _roofline(cfg, batch, d, 4, pk)
+        p32 = measure_prefill(lm32, cfg, prefill_tokens, rng, reps=3, warmup=3)
+        rec["fp32"] = {"value": d["value"], "ms_per_step": d["ms_per_step"], "bytes": r["bytes"], "frac": r["frac"],
+                       "steps": fp32_steps,
+                       "prefill": {"value": p32["value"], "tokens": p32["tokens"], "ms": p32["ms"],
+                                   "frac": prefill_flops(cfg, prefill_tokens) / (p32["ms"] / 1e3) / (FP32_TFLOPS * 1e12),
+                                   "peak_tflops": FP32_TFLOPS}}
     return rec
 
 

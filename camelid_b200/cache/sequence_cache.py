@@ -104,6 +104,11 @@ class SequenceCache:
         return self.book.length[slot]
 
     def truncate(self, slot: int, length: int) -> None:
+        """Forget the positions of ``slot`` at and beyond ``length`` (the reference's
+        ``rollback_to_position``, src/inference/kv_cache.rs:246-269). State of fixed size has no
+        positions to go back to: a cache that keeps any refuses."""
+        if self.state and length < self.length(slot):
+            raise CacheError(f"slot {slot}: this model keeps per-sequence state of fixed size, which cannot be rolled back")
         self.book.truncate(slot, length)
 
     # ---- storage of one schedule entry ----

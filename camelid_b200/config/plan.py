@@ -10,6 +10,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Optional
 
+from ..errors import ConfigError
+
 
 @dataclass(frozen=True)
 class PartSpec:
@@ -56,9 +58,9 @@ class ModelPlan:
     def __post_init__(self):
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
-                raise ValueError(f"schedule entry {i} names layer {e.layer}, the plan has {len(self.layers)}")
+                raise ConfigError("schedule", f"schedule entry {i} names layer {e.layer}, the plan has {len(self.layers)}")
             if e.cache_source is not None:
                 if not 0 <= e.cache_source < i:
-                    raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_source}, which does not run before it")
+                    raise ConfigError("schedule", f"schedule entry {i} reads the cache of entry {e.cache_source}, which does not run before it")
                 if self.schedule[e.cache_source].cache_source is not None:
-                    raise ValueError(f"schedule entry {i} reads entry {e.cache_source}, which has no cache of its own")
+                    raise ConfigError("schedule", f"schedule entry {i} reads entry {e.cache_source}, which has no cache of its own")

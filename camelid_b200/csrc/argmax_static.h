@@ -31,7 +31,12 @@
  *  - The first call on each GPU looks up the array's device address
  *    (cudaGetSymbolAddress, with that GPU current). Make that first call outside any
  *    stream capture; later calls only enqueue a memset and a kernel.
+ *  - The address is remembered per GPU ordinal and belongs to the context the CUDA runtime
+ *    uses on that GPU (its primary context). A caller that creates further driver-API
+ *    contexts on the same GPU must call this only with the primary context current; from
+ *    another context the remembered address is not valid.
  *  - The call allocates nothing: no cudaMalloc, cudaFree or library routine that allocates.
+ *  - Every refusal and every failed CUDA call leaves a message in msg (when msg is given).
  */
 #ifndef CAMELID_B200_ARGMAX_STATIC_H
 #define CAMELID_B200_ARGMAX_STATIC_H

@@ -1,5 +1,5 @@
-// bfloat16 attention over the paged cache on the tensor cores, for prefill tiles and for
-// decode, with float softmax and float accumulation.
+// bfloat16 attention over the paged cache with mma.sync tensor-core tiles, for decode steps
+// (prefill runs the tcgen05 kernel of attention_tc.cu), with float softmax and float accumulation.
 //
 // One block handles up to 16 (token, head) pairs that share one kv head: `rows_per_tile`
 // consecutive new tokens of one sequence times `heads_per_cta` query heads, which fill the
@@ -407,6 +407,9 @@ attn_decode_fused_kernel(AdParams p) {
     __shared__ float s_new[16];                       // their scores
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     pdl_launch_dependents();
+    // Distributed shared memory may be touched only once every block of the cluster runs: each
+    // block arrives here, at its start, and waits just before its first store into block 0.
+    if (p.n_splits > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
     const int split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -711,6 +714,7 @@ attn_decode_fused_kernel(AdParams p) {
         }
     }
     __syncthreads();
+    if (p.n_splits > 1) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");      // all blocks have started
     uint32_t to_block0;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
                  : "=r"(to_block0) : "r"((uint32_t)__cvta_generic_to_shared(ranges + (size_t)split * group * RW)), "r"(0u));
@@ -767,241 +771,6 @@ attn_decode_fused_kernel(AdParams p) {
     }
 }
 
-// ------------------------------------------------------------------------------------
-// Prefill: one block handles 64 (token, head) pairs of one kv head (four warps of 16 MMA
-// rows each) and all its warps walk the same key tiles of 64, fetched once per block through
-// one cp.async ring, so every key and value read from the cache serves 64 queries. A warp
-// skips the tiles that none of its rows may see. No split over keys: each row's softmax is
-// finished inside its warp and written straight to the output.
-#define AP_WARPS 4
-#define AP_TILE 64
-#define AP_STAGES 3
-
-template <int HD>
-__global__ void __launch_bounds__(AP_WARPS * 32)
-attn_prefill_mma_kernel(AttnParams p) {
-    constexpr int LDS = HD + 8;
-    constexpr int TILE_ELEMS = AP_TILE * LDS;
-    constexpr int STAGE_ELEMS = 2 * TILE_ELEMS;
-    constexpr int KSTEPS = HD / 16, DTILES = HD / 8, CHUNKS = HD / 8;
-    extern __shared__ __align__(16) uint8_t smem_raw[];
-    bf16* smem = reinterpret_cast<bf16*>(smem_raw);
-    pdl_launch_dependents();
-
-    // the last tiles of a sequence see the most keys: they are handed out first
-    const int tile = gridDim.x - 1 - blockIdx.x;
-    const int seq = p.tile_seq[tile];
-    const int q0 = p.tile_q0[tile];
-    const int kvh = blockIdx.y / p.head_chunks;
-    const int chunk = blockIdx.y - kvh * p.head_chunks;
-    const int start = p.seq_start[seq];
-    const int n_new = p.seq_new[seq];
-    const int row0 = p.seq_row0[seq];
-    const int group = p.n_heads / p.n_kv_heads;
-    const int hpc = p.heads_per_cta;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int rows_in_tile = min(p.rows_per_tile, n_new - q0);
-    const int kend = start + q0 + rows_in_tile;
-    const int kbeg = p.window > 0 ? max(0, start + q0 - p.window + 1) : 0;
-    const int t_first = kbeg / AP_TILE;
-    const int t_last = (kend + AP_TILE - 1) / AP_TILE;
-    const int n_tiles_k = t_last - t_first;
-
-    int pos_r[2], lo_r[2];
-    bool valid_r[2];
-    const bf16* q_r[2];
-    bf16* o_r[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int i = warp * 16 + (lane >> 2) + 8 * h;
-        const int r_local = i / hpc;
-        const int hg = chunk * hpc + (i - r_local * hpc);
-        valid_r[h] = (r_local < rows_in_tile) && (hg < group);
-        pos_r[h] = start + q0 + r_local;
-        lo_r[h] = p.window > 0 ? max(0, pos_r[h] - p.window + 1) : 0;
-        const size_t row = (size_t)(row0 + q0 + r_local);
-        q_r[h] = (const bf16*)p.q + row * p.q_stride + (size_t)(kvh * group + hg) * HD;
-        o_r[h] = (bf16*)p.out + row * p.out_stride + (size_t)(kvh * group + hg) * HD;
-    }
-    // what this warp's rows can see at all (warp-uniform)
-    int w_hi = -1, w_lo = 0x7fffffff;
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-        if (valid_r[h]) {
-            w_hi = max(w_hi, pos_r[h]);
-            w_lo = min(w_lo, lo_r[h]);
-        }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        w_hi = max(w_hi, __shfl_xor_sync(0xffffffffu, w_hi, o));
-        w_lo = min(w_lo, __shfl_xor_sync(0xffffffffu, w_lo, o));
-    }
-
-    const bf16* kp = (const bf16*)p.k_pages;
-    const bf16* vp = (const bf16*)p.v_pages;
-    const uint32_t smem_u32 = (uint32_t)__cvta_generic_to_shared(smem);
-    const int* table_row = p.block_table + (size_t)seq * p.max_blocks;
-    auto issue = [&](int t, int stage) {
-        const int page = table_row[t];
-        const size_t base = ((size_t)page * p.n_kv_heads + kvh) * CML_PAGE * HD;
-        const uint32_t dst = smem_u32 + (uint32_t)stage * STAGE_ELEMS * 2;
-        for (int c = threadIdx.x; c < AP_TILE * CHUNKS; c += AP_WARPS * 32) {
-            const int r = c / CHUNKS, cc = c - r * CHUNKS;
-            cp_async16(dst + (uint32_t)(r * LDS + cc * 8) * 2, kp + base + (size_t)r * HD + cc * 8);
-            cp_async16(dst + (uint32_t)(TILE_ELEMS + r * LDS + cc * 8) * 2, vp + base + (size_t)r * HD + cc * 8);
-        }
-    };
-    pdl_wait();
-#pragma unroll
-    for (int s = 0; s < AP_STAGES - 1; ++s) {
-        if (s < n_tiles_k) issue(t_first + s, s);
-        cp_async_commit();
-    }
-    uint32_t qa[KSTEPS][4];
-#pragma unroll
-    for (int ks = 0; ks < KSTEPS; ++ks) {
-        const int c = ks * 16 + 2 * (lane & 3);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            qa[ks][h] = valid_r[h] ? *reinterpret_cast<const uint32_t*>(q_r[h] + c) : 0u;
-            qa[ks][h + 2] = valid_r[h] ? *reinterpret_cast<const uint32_t*>(q_r[h] + c + 8) : 0u;
-        }
-    }
-    float m_r[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_r[2] = {0.f, 0.f};
-    float o[DTILES][4];
-#pragma unroll
-    for (int dt = 0; dt < DTILES; ++dt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) o[dt][i] = 0.f;
-    const float scale = p.scale;
-
-    for (int it = 0; it < n_tiles_k; ++it) {
-        const int t = t_first + it;
-        cp_async_wait<AP_STAGES - 2>();
-        __syncthreads();                 // the tile has landed for everyone; the stage read last round is free
-        {
-            const int nxt = it + AP_STAGES - 1;
-            if (nxt < n_tiles_k) issue(t_first + nxt, nxt % AP_STAGES);
-            cp_async_commit();
-        }
-        if ((t + 1) * AP_TILE > kend) {
-            // value rows past the end of the sequence: their probability is zero, make the
-            // product zero too whatever the page holds (block-uniform branch)
-            bf16* vs = smem + (size_t)(it % AP_STAGES) * STAGE_ELEMS + TILE_ELEMS;
-            const int first = kend - t * AP_TILE;
-            for (int c = threadIdx.x; c < (AP_TILE - first) * (HD / 2); c += AP_WARPS * 32) {
-                const int r = first + c / (HD / 2), d = (c % (HD / 2)) * 2;
-                *reinterpret_cast<uint32_t*>(vs + r * LDS + d) = 0u;
-            }
-            __syncthreads();
-        }
-        if (t * AP_TILE > w_hi || (t + 1) * AP_TILE <= w_lo) continue;      // nothing here for this warp
-        const uint32_t ks_u32 = smem_u32 + (uint32_t)(it % AP_STAGES) * STAGE_ELEMS * 2;
-        const uint32_t vs_u32 = ks_u32 + TILE_ELEMS * 2;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {          // 32 keys at a time keeps the registers in hand
-            const int kb = half * 32;
-            if (t * AP_TILE + kb > w_hi) break;
-            float s[4][4];
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS; ++ks) {
-#pragma unroll
-                for (int np = 0; np < 2; ++np) {
-                    const int mat = lane >> 3, rr = lane & 7;
-                    const int key = kb + np * 16 + (mat >> 1) * 8 + rr;
-                    const int d = ks * 16 + (mat & 1) * 8;
-                    uint32_t b0, b1, b2, b3;
-                    ldsm_x4(ks_u32 + (uint32_t)(key * LDS + d) * 2, b0, b1, b2, b3);
-                    mma_bf16(s[np * 2], qa[ks], b0, b1);
-                    mma_bf16(s[np * 2 + 1], qa[ks], b2, b3);
-                }
-            }
-            const int key_base = t * AP_TILE + kb + 2 * (lane & 3);
-            float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int h = i >> 1;
-                    const int key = key_base + nt * 8 + (i & 1);
-                    const bool in = valid_r[h] && key <= pos_r[h] && key >= lo_r[h];
-                    s[nt][i] = in ? s[nt][i] * scale : -CUDART_INF_F;
-                    mx[h] = fmaxf(mx[h], s[nt][i]);
-                }
-            float corr[2], m_use[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-                const float mn = fmaxf(m_r[h], mx[h]);
-                m_use[h] = (mn == -CUDART_INF_F) ? 0.f : mn;
-                corr[h] = (m_r[h] == -CUDART_INF_F) ? 0.f : __expf(m_r[h] - m_use[h]);
-                m_r[h] = mn;
-                l_r[h] *= corr[h];
-            }
-#pragma unroll
-            for (int dt = 0; dt < DTILES; ++dt) {
-                o[dt][0] *= corr[0]; o[dt][1] *= corr[0];
-                o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
-            }
-            uint32_t pa[2][4];
-#pragma unroll
-            for (int kk = 0; kk < 2; ++kk) {
-                float e[2][4];
-#pragma unroll
-                for (int j = 0; j < 2; ++j)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        e[j][i] = __expf(s[kk * 2 + j][i] - m_use[i >> 1]);
-                        l_r[i >> 1] += e[j][i];
-                    }
-                pa[kk][0] = pack_bf16(e[0][0], e[0][1]);
-                pa[kk][1] = pack_bf16(e[0][2], e[0][3]);
-                pa[kk][2] = pack_bf16(e[1][0], e[1][1]);
-                pa[kk][3] = pack_bf16(e[1][2], e[1][3]);
-            }
-#pragma unroll
-            for (int kk = 0; kk < 2; ++kk) {
-#pragma unroll
-                for (int dp = 0; dp < DTILES / 2; ++dp) {
-                    const int mat = lane >> 3, rr = lane & 7;
-                    const int key = kb + kk * 16 + (mat & 1) * 8 + rr;
-                    const int d = dp * 16 + (mat >> 1) * 8;
-                    uint32_t b0, b1, b2, b3;
-                    ldsm_x4_t(vs_u32 + (uint32_t)(key * LDS + d) * 2, b0, b1, b2, b3);
-                    mma_bf16(o[dp * 2], pa[kk], b0, b1);
-                    mma_bf16(o[dp * 2 + 1], pa[kk], b2, b3);
-                }
-            }
-        }
-    }
-    cp_async_wait<0>();
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        l_r[h] += __shfl_xor_sync(0xffffffffu, l_r[h], 1);
-        l_r[h] += __shfl_xor_sync(0xffffffffu, l_r[h], 2);
-        if (!valid_r[h]) continue;
-        const float inv = 1.0f / l_r[h];
-#pragma unroll
-        for (int dt = 0; dt < DTILES; ++dt)
-            *reinterpret_cast<uint32_t*>(o_r[h] + dt * 8 + 2 * (lane & 3)) = pack_bf16(o[dt][2 * h] * inv, o[dt][2 * h + 1] * inv);
-    }
-}
-
-template <int HD>
-static int launch_prefill_mma(const AttnParams& p, int n_tiles, cudaStream_t s) {
-    constexpr size_t smem = (size_t)AP_STAGES * 2 * AP_TILE * (HD + 8) * sizeof(bf16);
-    dim3 grid(n_tiles, p.n_kv_heads * p.head_chunks, 1);
-    cudaError_t e = cml_allow_smem<attn_prefill_mma_kernel<HD>>(smem);
-    if (e != cudaSuccess) return (int)e;
-    e = launch_pdl(attn_prefill_mma_kernel<HD>, grid, dim3(AP_WARPS * 32), smem, s, p);
-    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
-}
-
 template <int HD>
 static int launch_mma(const AttnParams& p, int n_tiles, int n_rows, cudaStream_t s) {
     constexpr size_t stage_bytes = (size_t)AM_WARPS * AM_STAGES * 2 * AM_TILE * (HD + 8) * sizeof(bf16);
@@ -1023,8 +792,7 @@ static int launch_mma(const AttnParams& p, int n_tiles, int n_rows, cudaStream_t
 
 // `tickets` (may be null): n_tiles * n_kv_heads * head_chunks ints, zero before the first call and left zero;
 // with it the last block of each column merges the splits itself, without it a second kernel does.
-// bfloat16 only; head_dim 64 or 128 (others take the float kernel). rows_per_tile * heads_per_cta <= 16 runs
-// the kernel that splits keys over warps and blocks (decode); up to 64 the prefill kernel (n_splits 1).
+// bfloat16 only; head_dim 64 or 128 (others take the float kernel); rows_per_tile * heads_per_cta <= 16.
 // q rows and the output must be 4-byte aligned (even strides).
 extern "C" int cml_attn_paged_mma(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                   const void* v_pages, const int* block_table, int max_blocks, const int* tile_seq,
@@ -1034,9 +802,8 @@ extern "C" int cml_attn_paged_mma(const void* q, int q_stride, void* out, int ou
                                   float scale, float* partial, int* tickets, void* stream) {
     if (n_tiles <= 0 || n_rows <= 0) return 0;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return CML_ERR_BAD_SIZE;
-    const int block_rows = rows_per_tile * heads_per_cta;       // 16 at most: split kernel; up to 64: prefill kernel
-    if (block_rows > 64 || rows_per_tile < 1 || heads_per_cta < 1 || heads_per_cta > 16) return CML_ERR_BAD_SIZE;
-    if (block_rows > 16 && n_splits != 1) return CML_ERR_BAD_SIZE;
+    const int block_rows = rows_per_tile * heads_per_cta;       // the 16 rows of an MMA at most
+    if (block_rows > 16 || rows_per_tile < 1 || heads_per_cta < 1) return CML_ERR_BAD_SIZE;
     if (heads_per_cta * head_chunks < n_heads / n_kv_heads) return CML_ERR_BAD_SIZE;
     if (n_splits < 1 || (n_splits > 1 && partial == nullptr)) return CML_ERR_BAD_SIZE;
     if ((q_stride & 1) || (out_stride & 1) || ((uintptr_t)q & 3) || ((uintptr_t)out & 3)) return CML_ERR_BAD_ALIGN;
@@ -1049,11 +816,6 @@ extern "C" int cml_attn_paged_mma(const void* q, int q_stride, void* out, int ou
     p.rows_per_tile = rows_per_tile; p.heads_per_cta = heads_per_cta; p.head_chunks = head_chunks;
     p.n_splits = n_splits; p.window = window; p.scale = scale; p.partial = partial; p.tickets = tickets;
     cudaStream_t s = (cudaStream_t)stream;
-    if (block_rows > 16) {
-        if (head_dim == 64) return launch_prefill_mma<64>(p, n_tiles, s);
-        if (head_dim == 128) return launch_prefill_mma<128>(p, n_tiles, s);
-        return CML_ERR_BAD_SIZE;
-    }
     if (head_dim == 64) return launch_mma<64>(p, n_tiles, n_rows, s);
     if (head_dim == 128) return launch_mma<128>(p, n_tiles, n_rows, s);
     return CML_ERR_BAD_SIZE;

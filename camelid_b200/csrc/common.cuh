@@ -56,19 +56,15 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // earlier kernel has completed and its writes are visible, so it comes before the first
 // access to anything an earlier kernel wrote (or still reads). `pdl_launch_dependents()`
 // lets the next kernel start its own prologue early. Without the launch attribute both are
-// no-ops. Set CAMELID_NO_PDL=1 to launch plainly.
+// no-ops. cml_set_dependent_launch(0) makes this module launch plainly.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-#include <stdlib.h>
-static inline bool cml_pdl_enabled() {
-    static int on = -1;
-    if (on < 0) {
-        const char* e = getenv("CAMELID_NO_PDL");
-        on = (e && e[0] && e[0] != '0') ? 0 : 1;
-    }
-    return on == 1;
-}
+static int cml_dependent_launch_on = 1;
+static inline bool cml_pdl_enabled() { return cml_dependent_launch_on == 1; }
+#ifndef CML_NO_LAUNCH_SETTER      // one definition per module: a second source file of a module defines this first
+extern "C" void cml_set_dependent_launch(int on) { cml_dependent_launch_on = on ? 1 : 0; }
+#endif
 
 template <typename... KArgs, typename... Args>
 static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

@@ -21,7 +21,7 @@ extern "C" int cml_sample_rows(const float* logits, int ld, int rows, int vocab,
 
 struct CmlDecodeLoop {
     int n;                    // sequences of the batch
-    int off_tokens, off_row_pos, off_seq_start, head_ints;   // places in the step's integer buffer
+    int off_tokens, off_row_pos, off_seq_slot, off_seq_start, head_ints;   // places in the step's integer buffer
     int* meta_dev;
     int* meta_host;           // pinned, head_ints ints
     const float* logits;      // [n, ld] written by the graph
@@ -47,14 +47,16 @@ static float unit_draw(uint64_t seed, uint64_t position) {
 // Fills `loop` (caller-owned, at least cml_decode_loop_size() bytes).
 extern "C" int cml_decode_loop_size() { return (int)sizeof(CmlDecodeLoop); }
 
-extern "C" int cml_decode_loop_init(void* loop, int n, int off_tokens, int off_row_pos, int off_seq_start, int head_ints,
+extern "C" int cml_decode_loop_init(void* loop, int n, int off_tokens, int off_row_pos, int off_seq_slot, int off_seq_start,
+                                    int head_ints,
                                     void* meta_dev, void* meta_host, const void* logits, int ld, int vocab,
                                     void* tokens_dev, void* tokens_host, void* err_dev, void* argmax_scratch,
                                     void* draws_dev, void* draws_host) {
     if (!loop || n <= 0 || head_ints <= 0) return -3;
     CmlDecodeLoop* L = (CmlDecodeLoop*)loop;
     L->n = n;
-    L->off_tokens = off_tokens; L->off_row_pos = off_row_pos; L->off_seq_start = off_seq_start; L->head_ints = head_ints;
+    L->off_tokens = off_tokens; L->off_row_pos = off_row_pos; L->off_seq_slot = off_seq_slot;
+    L->off_seq_start = off_seq_start; L->head_ints = head_ints;
     L->meta_dev = (int*)meta_dev; L->meta_host = (int*)meta_host;
     L->logits = (const float*)logits; L->ld = ld; L->vocab = vocab;
     L->tokens_dev = (int*)tokens_dev; L->tokens_host = (int*)tokens_host;
@@ -63,13 +65,15 @@ extern "C" int cml_decode_loop_init(void* loop, int n, int off_tokens, int off_r
     return 0;
 }
 
-// tokens: the token each sequence feeds first; positions: its length now (the place of that token).
+// tokens: the token each sequence feeds first; positions: its length now (the place of that token);
+// slots: the cache slot of each sequence (the head of the buffer that is sent every step holds them,
+// so they are written here and not taken from an earlier batch of the same size).
 // history_lens: tokens of each request so far, prompt included (the stream position of its next draw).
 // out_tokens: [max_steps][n] chosen tokens; *steps_done: steps run. Stops after the step in which a
 // sequence chose one of stop_ids. temperature 0: greedy. Returns 0 or a CUDA error code.
 // The block tables in the device buffer must already cover positions[i] + max_steps - 1.
 extern "C" int cml_decode_loop_run(void* loop, void* graph_exec, void* stream, const int* tokens, const int* positions,
-                                   const int* history_lens, int max_steps, const int* stop_ids, int n_stop,
+                                   const int* slots, const int* history_lens, int max_steps, const int* stop_ids, int n_stop,
                                    float temperature, int top_k, float top_p, float min_p, unsigned long long seed,
                                    int* out_tokens, int* steps_done) {
     CmlDecodeLoop* L = (CmlDecodeLoop*)loop;
@@ -80,6 +84,7 @@ extern "C" int cml_decode_loop_run(void* loop, void* graph_exec, void* stream, c
     for (int i = 0; i < n; ++i) {
         L->meta_host[L->off_tokens + i] = tokens[i];
         L->meta_host[L->off_row_pos + i] = positions[i];
+        L->meta_host[L->off_seq_slot + i] = slots[i];
         L->meta_host[L->off_seq_start + i] = positions[i];
     }
     for (int step = 0; step < max_steps; ++step) {
@@ -117,4 +122,42 @@ extern "C" int cml_decode_loop_run(void* loop, void* graph_exec, void* stream, c
         if (stop) break;
     }
     return 0;
+}
+
+// The loop for greedy requests when the captured graph itself picks each row's token and writes
+// it where the next step reads its tokens (the step's integer buffer starts with the tokens).
+// Nothing has to come back before the next step can start, so all `steps` steps are queued at
+// once: per step one pinned->device copy of that step's positions, the graph, and one
+// device->pinned copy of the tokens it chose; the host waits once, at the end.
+//   meta_ring: pinned [steps or more][head_ints], every row pre-filled with the arrays that never
+//              change (the row -> sequence map); this call writes tokens (row 0), positions and slots.
+//   out_tokens: pinned [steps][n].
+extern "C" int cml_decode_fed_run(int n, int off_tokens, int off_row_pos, int off_seq_slot, int off_seq_start,
+                                  int head_ints, void* meta_dev, int* meta_ring, void* graph_exec, void* stream,
+                                  const int* tokens, const int* positions, const int* slots, int steps,
+                                  int* out_tokens) {
+    if (n <= 0 || steps <= 0 || head_ints < n || off_tokens != 0) return -3;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaGraphExec_t exec = (cudaGraphExec_t)graph_exec;
+    int* dev = (int*)meta_dev;
+    for (int step = 0; step < steps; ++step) {
+        int* row = meta_ring + (size_t)step * head_ints;
+        for (int i = 0; i < n; ++i) {
+            if (step == 0) row[off_tokens + i] = tokens[i];
+            row[off_row_pos + i] = positions[i] + step;
+            row[off_seq_slot + i] = slots[i];
+            row[off_seq_start + i] = positions[i] + step;
+        }
+        // the first step brings its tokens; later ones leave the device's own choice in place
+        const int skip = step == 0 ? 0 : n;
+        cudaError_t e = cudaMemcpyAsync(dev + skip, row + skip, (size_t)(head_ints - skip) * sizeof(int),
+                                        cudaMemcpyHostToDevice, s);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaGraphLaunch(exec, s);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaMemcpyAsync(out_tokens + (size_t)step * n, dev + off_tokens, (size_t)n * sizeof(int),
+                            cudaMemcpyDeviceToHost, s);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return (int)cudaStreamSynchronize(s);
 }

@@ -59,16 +59,19 @@ _SIGNATURES = {
     ("sampling", "cml_adjust_logits"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_float,
                                         c_void_p],
     ("sampling", "cml_decode_loop_size"): [],
-    ("sampling", "cml_decode_loop_init"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                          c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
-    ("sampling", "cml_decode_loop_run"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+    ("sampling", "cml_decode_loop_init"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                          c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    ("sampling", "cml_decode_loop_run"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                          c_int, c_float, c_int, c_float, c_float, ctypes.c_ulonglong, c_void_p, c_void_p],
+    ("sampling", "cml_decode_fed_run"): [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     ("sampling", "cml_sample_rows"): [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_void_p,
                                       c_void_p, c_void_p, c_void_p],
     ("random_fill", "cml_random_fill"): [c_void_p, c_int, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_ulonglong,
                                          ctypes.c_double, ctypes.c_double, c_void_p],
 }
 _fns: dict = {}
+_libs: dict = {}
 _launches = 0
 
 
@@ -86,6 +89,9 @@ def _fn(module: str, name: str):
     f = _fns.get(name)
     if f is None:
         lib = build.load(module)
+        if module not in _libs:
+            _libs[module] = lib
+            _apply_dependent_launch(lib)
         f = getattr(lib, name)
         f.argtypes = _SIGNATURES[(module, name)]
         f.restype = c_int
@@ -110,6 +116,42 @@ def _dev(*tensors):
 
 def _p(t):
     return None if t is None else t.data_ptr()
+
+
+_sm_counts: dict = {}
+
+
+def sm_count(device) -> int:
+    """Multiprocessors of ``device`` (the number the launchers read from the runtime too)."""
+    device = torch.device(device)
+    n = _sm_counts.get(device)
+    if n is None:
+        n = int(torch.cuda.get_device_properties(device).multi_processor_count)
+        _sm_counts[device] = n
+    return n
+
+
+_dependent_launch = True
+
+
+def set_dependent_launch(on: bool) -> None:
+    """Whether kernels are launched with programmatic dependent launch (the default). Applies
+    to every kernel module, those loaded later included."""
+    global _dependent_launch
+    if bool(on) == _dependent_launch:
+        return
+    _dependent_launch = bool(on)
+    for lib in _libs.values():
+        _apply_dependent_launch(lib)
+
+
+def _apply_dependent_launch(lib) -> None:
+    try:
+        setter = lib.cml_set_dependent_launch
+    except AttributeError:          # a module without kernels that depend on their predecessors
+        return
+    setter.argtypes, setter.restype = [c_int], None
+    setter(1 if _dependent_launch else 0)
 
 
 try:        # the raw handle of the current stream without building a Stream object (a third of a launch's host time)
@@ -387,12 +429,12 @@ def attn_paged_simt(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_
 
 
 def attn_mma_tiling(n_heads: int, n_kv_heads: int, decode: bool) -> tuple[int, int, int]:
-    """(rows_per_tile, heads_per_cta, head_chunks) of the tensor-core attention kernel: the 16
+    """(rows_per_tile, heads_per_cta, head_chunks) of the mma.sync attention kernel: the 16
     rows of an MMA hold the grouped heads of one kv head times a few consecutive tokens."""
     group = n_heads // n_kv_heads
     chunks = (group + 15) // 16
     hpc = (group + chunks - 1) // chunks
-    rows = 1 if decode else max(1, 64 // hpc)          # prefill: four MMA row tiles share each key tile
+    rows = 1 if decode else max(1, 16 // hpc)
     return rows, hpc, chunks
 
 
@@ -570,25 +612,60 @@ class NativeDecodeLoop:
         self._np = np
         _check(_fn("sampling", "cml_decode_loop_init")(
             ctypes.addressof(self._state), n, layout.offsets["tokens"][0], layout.offsets["row_pos"][0],
-            layout.offsets["seq_start"][0], self.head_ints, _p(meta_dev), _p(self.meta_host), _p(logits),
+            layout.offsets["seq_slot"][0], layout.offsets["seq_start"][0], self.head_ints, _p(meta_dev), _p(self.meta_host), _p(logits),
             logits.stride(0), logits.shape[1], _p(self.tokens_dev), _p(self.tokens_host), _p(err), _p(self.scratch),
             _p(self.draws_dev), _p(self.draws_host)), "decode_loop_init", 0)
         self.h2d_bytes_per_step = self.head_ints * 4
         self.d2h_bytes_per_step = n * 4
 
-    def run(self, graph_exec: int, tokens, positions, history_lens, max_steps: int, stop_ids, temperature: float,
+    def run(self, graph_exec: int, tokens, positions, slots, history_lens, max_steps: int, stop_ids, temperature: float,
             top_k: int, top_p: float, min_p: float, seed: int, launches_per_step: int):
         np = self._np
         tok = np.ascontiguousarray(tokens, dtype=np.int32)
         pos = np.ascontiguousarray(positions, dtype=np.int32)
+        slo = np.ascontiguousarray(slots, dtype=np.int32)
+        assert tok.size == pos.size == slo.size == self.n
         hist = np.ascontiguousarray(history_lens, dtype=np.int32)
         stops = np.ascontiguousarray(list(stop_ids), dtype=np.int32)
         out = np.empty((max_steps, self.n), dtype=np.int32)
         done = ctypes.c_int(0)
         rc = _fn("sampling", "cml_decode_loop_run")(
-            ctypes.addressof(self._state), graph_exec, _stream(), tok.ctypes.data, pos.ctypes.data, hist.ctypes.data,
+            ctypes.addressof(self._state), graph_exec, _stream(), tok.ctypes.data, pos.ctypes.data, slo.ctypes.data,
+            hist.ctypes.data,
             max_steps, stops.ctypes.data if stops.size else None, int(stops.size), float(temperature), int(top_k or 0),
             float(top_p if top_p is not None else 1.0), float(min_p or 0.0), int(seed or 0), out.ctypes.data,
             ctypes.addressof(done))
         _check(rc, "decode_loop_run", (launches_per_step + 1) * done.value)
         return out[:done.value], done.value
+
+
+class FedDecodeLoop:
+    """The C++ loop for a captured step graph that picks the greedy token itself and feeds it to
+    the next step on the device: ``run`` queues all its steps at once and waits once."""
+    RING = 256                  # steps one call can queue
+
+    def __init__(self, n: int, layout, meta_dev: torch.Tensor, head_template):
+        import numpy as np
+        self._np = np
+        self.n = n
+        self.offsets = [layout.offsets[k][0] for k in ("tokens", "row_pos", "seq_slot", "seq_start")]
+        self.head_ints = layout.offsets["seq_start"][0] + n
+        self.meta_dev = meta_dev
+        self.ring = torch.zeros((self.RING, self.head_ints), dtype=torch.int32).pin_memory()
+        self.ring.numpy()[:] = head_template[:self.head_ints]
+        self.out = torch.zeros((self.RING, n), dtype=torch.int32).pin_memory()
+        self.h2d_bytes_per_step = (self.head_ints - n) * 4
+        self.d2h_bytes_per_step = n * 4
+
+    def run(self, graph_exec: int, tokens, positions, slots, steps: int, launches_per_step: int):
+        np = self._np
+        assert 1 <= steps <= self.RING
+        tok = np.ascontiguousarray(tokens, dtype=np.int32)
+        pos = np.ascontiguousarray(positions, dtype=np.int32)
+        slo = np.ascontiguousarray(slots, dtype=np.int32)
+        assert tok.size == pos.size == slo.size == self.n
+        rc = _fn("sampling", "cml_decode_fed_run")(
+            self.n, *self.offsets, self.head_ints, _p(self.meta_dev), self.ring.data_ptr(), graph_exec, _stream(),
+            tok.ctypes.data, pos.ctypes.data, slo.ctypes.data, int(steps), self.out.data_ptr())
+        _check(rc, "decode_fed_run", launches_per_step * steps)
+        return self.out.numpy()[:steps].copy()

@@ -356,7 +356,10 @@ extern "C" int cml_argmax_rows_static(const float* logits, int ld, int rows, int
     }
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return (int)e;
+    if (e != cudaSuccess) {
+        refuse(msg, msg_len, "cml_argmax_rows_static: cudaGetDevice failed");
+        return (int)e;
+    }
     if (dev < 0 || dev >= CML_MAX_DEVICES) {
         refuse(msg, msg_len, "cml_argmax_rows_static: device index beyond the table of this library");
         return CML_ARGMAX_STATIC_BAD_ARGUMENT;
@@ -380,8 +383,13 @@ extern "C" int cml_argmax_rows_static(const float* logits, int ld, int rows, int
     cudaStream_t s = (cudaStream_t)stream;
     // the words of these rows must start at zero, whatever an earlier call left
     e = cudaMemsetAsync(words, 0, (size_t)rows * 2 * sizeof(unsigned long long), s);
-    if (e != cudaSuccess) return (int)e;
+    if (e != cudaSuccess) {
+        refuse(msg, msg_len, "cml_argmax_rows_static: clearing the scratch words failed");
+        return (int)e;
+    }
     const int blocks = max(1, min(64, vocab / 2048));
     argmax_rows_kernel<<<dim3(blocks, rows), 256, 0, s>>>(logits, ld, vocab, out, err, words);
-    return (int)cudaGetLastError();
+    e = cudaGetLastError();
+    if (e != cudaSuccess) refuse(msg, msg_len, "cml_argmax_rows_static: the kernel launch failed");
+    return (int)e;
 }

@@ -10,11 +10,15 @@ lets it run as a captured CUDA graph on a static buffer.
 """
 from __future__ import annotations
 
+import weakref
+
 import numpy as np
 import torch
 
 from ..cache.book import PAGE
 from ..csrc import ops
+from ..errors import KernelError
+from ..options import KernelOptions
 
 
 class Workspace:
@@ -77,8 +81,10 @@ class StepContext:
 
     # ---- construction ----
     def __init__(self, *, cache, workspace: Workspace, dtype: torch.dtype, device, layout: StepLayout,
-                 meta_dev: torch.Tensor):
-        self.cache = cache
+                 meta_dev: torch.Tensor, options: KernelOptions | None = None):
+        # the context of a captured graph lives as long as the graph: it must not keep the cache alive
+        self._cache = weakref.ref(cache) if cache is not None else None
+        self.options = options if options is not None else KernelOptions()
         self.ws = workspace
         self.dtype = dtype
         self.device = device
@@ -105,6 +111,10 @@ class StepContext:
         self.max_len = 1
         self.decode = True
         self.h2d_bytes = 0
+
+    @property
+    def cache(self):
+        return self._cache() if self._cache is not None else None
 
     @staticmethod
     def host_arrays(slots, starts, tokens, want, tables, tile_sizes):
@@ -139,7 +149,7 @@ class StepContext:
         return layout, np.concatenate(parts), news, row0.tolist()
 
     @classmethod
-    def for_step(cls, *, cache, workspace, dtype, device, slots, starts, tokens, want, tile_sizes=(1,)):
+    def for_step(cls, *, cache, workspace, dtype, device, slots, starts, tokens, want, tile_sizes=(1,), options=None):
         """A context for one eager step: arrays built on the host and sent in one copy."""
         n_groups = len(cache.book.kv_specs) if cache is not None else 0
         tables = [cache.book.block_table(g, list(slots)) for g in range(n_groups)]
@@ -148,19 +158,20 @@ class StepContext:
         if torch.device(device).type == "cuda":
             t = t.pin_memory()
         ctx = cls(cache=cache, workspace=workspace, dtype=dtype, device=device, layout=layout,
-                  meta_dev=t.to(device, non_blocking=True))
+                  meta_dev=t.to(device, non_blocking=True), options=options)
         ctx._host_meta = t                # keep the pinned buffer alive until the copy ran
         ctx._set_host(slots, starts, news, row0)
         ctx.h2d_bytes = host.nbytes
         return ctx
 
     @classmethod
-    def static(cls, *, cache, workspace, dtype, device, n_seqs, table_widths):
+    def static(cls, *, cache, workspace, dtype, device, n_seqs, table_widths, options=None):
         """A context on a fixed buffer for decode steps of ``n_seqs`` sequences (one token each,
         every sequence's logits wanted); ``meta_dev`` is refilled before every replay."""
         layout = StepLayout(n_seqs, n_seqs, n_seqs, table_widths, {1: n_seqs})
         meta = torch.zeros(layout.total, dtype=torch.int32, device=device)
-        ctx = cls(cache=cache, workspace=workspace, dtype=dtype, device=device, layout=layout, meta_dev=meta)
+        ctx = cls(cache=cache, workspace=workspace, dtype=dtype, device=device, layout=layout, meta_dev=meta,
+                  options=options)
         ctx._set_host([0] * n_seqs, [0] * n_seqs, [1] * n_seqs, list(range(n_seqs)))
         ctx.max_len = max(table_widths) * PAGE if table_widths else 1
         return ctx
@@ -213,7 +224,7 @@ class StepContext:
         try:
             return self._tiles[rows_per_tile]
         except KeyError:
-            raise ValueError(f"this step has tiles of {sorted(self._tiles)} rows, not of {rows_per_tile}; the "
+            raise KernelError(f"this step has tiles of {sorted(self._tiles)} rows, not of {rows_per_tile}; the "
                              f"mixer's query_tile_sizes() must name every size it uses") from None
 
     @property

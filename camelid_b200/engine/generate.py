@@ -27,6 +27,10 @@ class GenerationResult:
     prompt_tokens: int = 0
 
 
+# Steps a greedy batch runs on the device between looks at its tokens when stop tokens are set.
+FED_RUN_WITH_STOPS = 16
+
+
 def pages_for(n_tokens: int) -> int:
     return (n_tokens + PAGE - 1) // PAGE
 
@@ -85,16 +89,32 @@ def run_batch(model, cache, sampler, prompts: list, budgets: list, requested: li
         # per-history adjustments hand the one-token steps to the C++ loop: many steps per call.
         native = (getattr(model, "use_graphs", False) and hasattr(model, "decode_natively")
                   and getattr(sampler, "native_ok", False))
+        # Greedy requests go one better: the captured step picks the token itself and feeds it to
+        # the next step on the device, so a run of steps is queued at once and read back at its
+        # end. Sequences do not depend on one another, so a sequence that meets a stop token
+        # inside such a run just drops what it produced after it; with stop tokens the runs are
+        # short, so that little is produced in vain.
+        fed = (native and hasattr(model, "decode_fed") and getattr(sampler.options, "greedy", False)
+               and getattr(getattr(model, "options", None), "feed_on_device", False))
         first = True
         while live:
             if native and not first:
                 k = min(budgets[i] - len(results[i].tokens) for i in live)
-                out, steps = model.decode_natively(cache, [slots[i] for i in live], [results[i].tokens[-1] for i in live],
-                                                   [len(histories[i]) for i in live], k, sorted(stop_ids),
-                                                   sampler.options, sampler.error_word)
+                if fed:
+                    steps = min(k, FED_RUN_WITH_STOPS) if stop_ids else k
+                    out = model.decode_fed(cache, [slots[i] for i in live], [results[i].tokens[-1] for i in live], steps)
+                else:
+                    out, steps = model.decode_natively(cache, [slots[i] for i in live],
+                                                       [results[i].tokens[-1] for i in live],
+                                                       [len(histories[i]) for i in live], k, sorted(stop_ids),
+                                                       sampler.options, sampler.error_word)
                 still = []
                 for j, i in enumerate(live):
                     new = [int(t) for t in out[:steps, j]]
+                    for at, tok in enumerate(new):          # a run on the device goes on past a stop token
+                        if tok in stop_ids:
+                            new = new[:at + 1]
+                            break
                     results[i].tokens.extend(new)
                     histories[i].extend(new)
                     if new[-1] in stop_ids:

@@ -13,6 +13,8 @@ launch gaps are most of the step without them.
 """
 from __future__ import annotations
 
+import weakref
+
 import numpy as np
 import torch
 
@@ -32,10 +34,11 @@ def bucket_width(blocks: int) -> int:
 
 class DecodeGraph:
     def __init__(self, model, cache, n_seqs: int, widths: list, feed: bool):
-        self.model, self.cache, self.n_seqs, self.widths, self.feed = model, cache, n_seqs, list(widths), feed
+        self.model, self.n_seqs, self.widths, self.feed = model, n_seqs, list(widths), feed
+        self._cache = weakref.ref(cache)        # the model keeps its graphs per cache and drops them with it
         dev = model.device
         self.ctx = StepContext.static(cache=cache, workspace=Workspace(dev), dtype=model.dtype, device=dev,
-                                      n_seqs=n_seqs, table_widths=self.widths)
+                                      n_seqs=n_seqs, table_widths=self.widths, options=model.options)
         lay = self.ctx.layout
         self.host = [torch.zeros(lay.total, dtype=torch.int32).pin_memory() for _ in range(_RING)]
         self.host_np = [h.numpy() for h in self.host]
@@ -51,6 +54,10 @@ class DecodeGraph:
         self.next_tokens = None
         self.launches = 0
         self._table_key = [None] * _RING
+
+    @property
+    def cache(self):
+        return self._cache()
 
     def fill(self, slots: list, starts: list, tokens) -> int:
         """Write the step's arrays into the next pinned buffer; returns its index."""
@@ -84,14 +91,20 @@ class DecodeGraph:
     def _forward(self):
         logits = self.model.run(self.ctx)
         if self.feed:
-            ops.argmax_rows(logits, self.ctx.tokens, self.model._err)
+            ops.argmax_rows(logits, self.ctx.tokens, self.model.logit_error_word())
         return logits
 
     def capture(self):
-        """Warm up eagerly on the buffer's present contents, then capture."""
+        """Warm up eagerly on the buffer's present contents, then capture. The warm-up runs the
+        step once for real: keys and values it writes are written again, identically, by the
+        first replay, but per-sequence state of fixed size would be advanced twice, so it is put
+        back as it was."""
         tokens_before = self.ctx.tokens.clone()
+        state_before = [t.clone() for t in self.cache.state]
         self._forward()
         self.ctx.tokens.copy_(tokens_before)
+        for t, saved in zip(self.cache.state, state_before):
+            t.copy_(saved)
         torch.cuda.synchronize()
         before = ops.launch_count()
         g = torch.cuda.CUDAGraph()
@@ -122,5 +135,26 @@ class DecodeGraph:
         if self.graph is None:
             self.capture()
         loop = self.native_loop(err)
-        return loop.run(self.graph.raw_cuda_graph_exec(), tokens, starts, history_lens, max_steps, stop_ids,
+        return loop.run(self.graph.raw_cuda_graph_exec(), tokens, starts, slots, history_lens, max_steps, stop_ids,
                         temperature, top_k, top_p, min_p, seed, self.launches)
+
+    def run_fed(self, slots: list, starts: list, tokens: list, steps: int):
+        """``steps`` greedy steps of a graph captured with ``feed``, queued at once by the C++ loop:
+        the device feeds itself, the host sends positions and reads the chosen tokens. Returns
+        the tokens [steps, sequences] as a numpy array."""
+        assert self.feed
+        i = self.fill(slots, starts, tokens)
+        self.send(i, with_tokens=True)                  # block tables and the static arrays
+        if self.graph is None:
+            self.capture()
+        if getattr(self, "_fed", None) is None:
+            self._fed = ops.FedDecodeLoop(self.n_seqs, self.ctx.layout, self.ctx.meta_dev, self.host_np[i])
+        out = []
+        done = 0
+        while done < steps:
+            k = min(steps - done, self._fed.RING)
+            first = tokens if done == 0 else out[-1][-1]
+            out.append(self._fed.run(self.graph.raw_cuda_graph_exec(), first, [s + done for s in starts], slots, k,
+                                     self.launches))
+            done += k
+        return np.concatenate(out) if len(out) > 1 else out[0]

@@ -14,6 +14,7 @@ the resident engine's ``forward_pass_inner`` / ``run_batched_layer_stack``
 """
 from __future__ import annotations
 
+import weakref
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -22,7 +23,8 @@ import torch
 from ..cache.sequence_cache import SequenceCache
 from ..config.plan import ModelPlan
 from ..config.registry import load_config
-from ..errors import KernelError, StepError
+from ..errors import ConfigError, KernelError, StepError
+from ..options import KernelOptions
 from ..parts import build_block, build_part
 from ..weights.loader import check_tensors
 from ..weights.safetensors_io import ModelFiles
@@ -34,12 +36,12 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
 def parse_dtype(dtype) -> torch.dtype:
     if isinstance(dtype, torch.dtype):
         if dtype not in (torch.bfloat16, torch.float32):
-            raise ValueError(f"compute type must be bfloat16 or float32, got {dtype}")
+            raise ConfigError("dtype", f"the compute type must be bfloat16 or float32, got {dtype}")
         return dtype
     try:
         return _DTYPES[str(dtype)]
     except KeyError:
-        raise ValueError(f"compute type must be 'bfloat16' or 'float32', got {dtype!r}") from None
+        raise ConfigError("dtype", f"the compute type must be 'bfloat16' or 'float32', got {dtype!r}") from None
 
 
 @dataclass
@@ -52,9 +54,11 @@ class StepEntry:
 
 
 class DecoderModel:
-    def __init__(self, plan: ModelPlan, *, dtype=torch.bfloat16, device="cuda", typed_config=None):
+    def __init__(self, plan: ModelPlan, *, dtype=torch.bfloat16, device="cuda", typed_config=None,
+                 options: KernelOptions | None = None):
         self.plan = plan
         self.typed_config = typed_config
+        self.options = options if options is not None else KernelOptions()
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
         self.embedding = build_part("embedding", plan.embedding)
@@ -67,23 +71,24 @@ class DecoderModel:
         self.loaded = False
         self.workspace = Workspace(self.device)
         self._err = None
+        self._logit_err = None
         self.last_h2d_bytes = 0
         self.tile_sizes = sorted({r for b in self.blocks for r in b.query_tile_sizes()}) or [1]
         # decode steps replay captured CUDA graphs when every part can run inside one
         self.use_graphs = all(b.graph_safe for b in self.blocks) and all(
             p.graph_safe for p in (self.embedding, self.final_norm, self.head))
-        self._graphs: dict = {}
+        self._graphs = weakref.WeakKeyDictionary()      # cache -> {(sequences, widths, feed): DecodeGraph}
 
     # ---- construction ----
     @classmethod
-    def from_config(cls, config, *, dtype=torch.bfloat16, device="cuda") -> "DecoderModel":
+    def from_config(cls, config, *, dtype=torch.bfloat16, device="cuda", options=None) -> "DecoderModel":
         """``config``: a config.json dict or a model folder. Builds the parts; no weights yet."""
         _arch, typed, plan = load_config(config)
-        return cls(plan, dtype=dtype, device=device, typed_config=typed)
+        return cls(plan, dtype=dtype, device=device, typed_config=typed, options=options)
 
     @classmethod
-    def from_folder(cls, folder: str, *, dtype=torch.bfloat16, device="cuda") -> "DecoderModel":
-        model = cls.from_config(folder, dtype=dtype, device=device)
+    def from_folder(cls, folder: str, *, dtype=torch.bfloat16, device="cuda", options=None) -> "DecoderModel":
+        model = cls.from_config(folder, dtype=dtype, device=device, options=options)
         files = ModelFiles(folder)
         try:
             model.load_tensors(files)
@@ -99,8 +104,13 @@ class DecoderModel:
         specs.update(self.head.tensor_specs())
         return specs
 
-    def load_tensors(self, source) -> None:
-        """``source``: ``ModelFiles`` or a dict name -> tensor. Checks names and shapes first."""
+    def memory_plan(self, max_tokens: int = 0, max_slots: int | None = None, step_tokens: int | None = None):
+        from ..memory import plan_for_model
+        return plan_for_model(self, max_tokens, max_slots, step_tokens)
+
+    def load_tensors(self, source, available_bytes: int | None = None) -> None:
+        """``source``: ``ModelFiles`` or a dict name -> tensor. Checks names and shapes first, then
+        that the weights fit the device's free memory (``available_bytes`` stands in for it)."""
         specs = self.tensor_specs()
         if isinstance(source, dict):
             found = {n: (tuple(t.shape), t.dtype) for n, t in source.items()}
@@ -111,6 +121,11 @@ class DecoderModel:
         tied = getattr(self.head, "tied_to", None)
         tolerated = (self.head.prefix + "weight",) if tied else ()
         check_tensors(specs, found, tolerated=tolerated)
+        from ..memory import device_free_bytes
+        free = available_bytes if available_bytes is not None else device_free_bytes(self.device)
+        if free is not None:
+            held = sum(t.numel() * t.element_size() for t in source.values() if t.is_cuda) if isinstance(source, dict) else 0
+            self.memory_plan().check(free + held, f"loading the weights onto {self.device}", parts=("weights",))
 
         class _Lazy(dict):
             def __missing__(self, name):
@@ -133,6 +148,11 @@ class DecoderModel:
     def new_cache(self, max_tokens: int, max_slots: int | None = None) -> SequenceCache:
         """A cache for at most ``max_tokens`` live tokens (each sequence's count rounded up to
         a multiple of 64) and ``max_slots`` live sequences (default: one per page)."""
+        from ..memory import device_free_bytes
+        free = device_free_bytes(self.device)
+        if free is not None:
+            self.memory_plan(max_tokens, max_slots).check(free, f"a cache for {max_tokens} tokens on {self.device}",
+                                                          parts=("cache", "workspace"))
         return SequenceCache(self.entry_cache_specs(), [e.cache_source for e in self.schedule],
                              max_tokens=max_tokens, max_position=self.plan.max_position, dtype=self.dtype,
                              device=self.device, max_slots=max_slots)
@@ -174,7 +194,8 @@ class DecoderModel:
         starts = [cache.book.extend(e.slot, a.size) for e, a in zip(entries, arrays)]
         ctx = StepContext.for_step(cache=cache, workspace=self.workspace, dtype=self.dtype, device=self.device,
                                    slots=[e.slot for e in entries], starts=starts, tokens=arrays,
-                                   want=[[int(w) for w in e.want] for e in entries], tile_sizes=self.tile_sizes)
+                                   want=[[int(w) for w in e.want] for e in entries], tile_sizes=self.tile_sizes,
+                                   options=self.options)
         logits = self.run(ctx)
         for e, a in zip(entries, arrays):
             cache.book.commit(e.slot, a.size)
@@ -186,11 +207,12 @@ class DecoderModel:
         from .graphs import DecodeGraph, bucket_width
         book = cache.book
         widths = [bucket_width(max(len(book.pages[g][s]) for s in slots)) for g in range(len(book.kv_specs))]
-        key = (id(cache), len(slots), tuple(widths), feed)
-        graph = self._graphs.get(key)
+        graphs = self._graphs.setdefault(cache, {})
+        key = (len(slots), tuple(widths), feed)
+        graph = graphs.get(key)
         if graph is None:
             graph = DecodeGraph(self, cache, len(slots), widths, feed)
-            self._graphs[key] = graph
+            graphs[key] = graph
         return graph
 
     def decode_natively(self, cache: SequenceCache, slots: list, tokens: list, history_lens: list, max_steps: int,
@@ -217,10 +239,43 @@ class DecoderModel:
         self.last_h2d_bytes = graph.native_loop(err).h2d_bytes_per_step
         return out, steps
 
+    def logit_error_word(self) -> torch.Tensor:
+        """int32[1] on the device: set by the greedy choice inside a captured step when a logit is
+        not finite; ``check_device_errors`` reads it."""
+        if self._logit_err is None:
+            self._logit_err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        return self._logit_err
+
+    def decode_fed(self, cache: SequenceCache, slots: list, tokens: list, steps: int):
+        """Exactly ``steps`` greedy one-token steps of these sequences with the chosen token fed
+        back on the device: all steps are queued at once and the host waits once at the end.
+        Returns the tokens [steps][sequence] (numpy); the cache's lengths have moved by ``steps``."""
+        if not self.use_graphs:
+            raise StepError("decoding with the token fed back on the device needs a model whose parts can run in a captured graph")
+        if not self.loaded:
+            raise StepError("the model has no weights yet")
+        for t in tokens:
+            if not 0 <= int(t) < self.vocab_size:
+                raise StepError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
+        if steps <= 0:
+            raise StepError("decode_fed needs at least one step")
+        book = cache.book
+        book.check_extend([(s, steps) for s in slots])
+        starts = [book.extend(s, steps) for s in slots]
+        graph = self.decode_graph(cache, slots, feed=True)
+        out = graph.run_fed(slots, starts, [int(t) for t in tokens], steps)
+        for s in slots:
+            book.commit(s, steps)
+        self.last_h2d_bytes = graph._fed.h2d_bytes_per_step
+        return out
+
     def drop_graphs(self, cache=None) -> None:
-        """Forget the captured graphs (of one cache, or all): they keep their cache alive."""
-        for key in [k for k, g in self._graphs.items() if cache is None or g.cache is cache]:
-            del self._graphs[key]
+        """Forget the captured graphs of one cache, or all. (A cache that is no longer referenced
+        takes its graphs with it: they are kept per cache and hold no reference to it.)"""
+        if cache is None:
+            self._graphs.clear()
+        else:
+            self._graphs.pop(cache, None)
 
     def _graph_step(self, cache: SequenceCache, entries: list) -> torch.Tensor:
         slots = [e.slot for e in entries]
@@ -237,6 +292,8 @@ class DecoderModel:
 
     def run(self, ctx: StepContext) -> torch.Tensor:
         """The forward pass of one step on a prepared context."""
+        from ..csrc import ops
+        ops.set_dependent_launch(self.options.dependent_launch)
         if self._err is None:
             self._err = torch.zeros(1, dtype=torch.int32, device=self.device)
         ctx.pending = None
@@ -262,5 +319,9 @@ class DecoderModel:
         if self._err is not None and int(self._err.item()) != 0:
             self._err.zero_()
             raise StepError("a kernel met a token id outside the vocabulary")
+        if self._logit_err is not None and int(self._logit_err.item()) != 0:
+            self._logit_err.zero_()
+            from ..errors import SamplingError
+            raise SamplingError("the logits of a greedy step contain a non-finite value")
         from ..parts import linear
         linear.check_errors()

@@ -8,11 +8,12 @@ class CamelidError(Exception):
 
 
 class ConfigError(CamelidError):
-    """A key of config.json is missing, of the wrong type or outside its range."""
+    """A key of config.json, a parameter of a part or an option is missing, of the wrong
+    type or outside its range. ``key`` names it."""
 
     def __init__(self, key: str, message: str):
         self.key = key
-        super().__init__(f"config.json: {key}: {message}")
+        super().__init__(f"configuration: {key}: {message}")
 
 
 class UnknownArchitectureError(CamelidError):

@@ -13,19 +13,21 @@ nothing. ``window`` (None for Llama) limits every query to the last ``window`` k
 from __future__ import annotations
 
 import math
-import os
 
 import torch
 
 from ..cache.book import PAGE, KVSpec
 from ..config.plan import PartSpec
 from ..csrc import ops
+from ..errors import ConfigError
 from . import linear
 from .base import Part, TensorSpec, build_part, register_part, to_device
+
 
 @register_part("mixer", "attention")
 class GroupedQueryAttention(Part):
     graph_safe = True
+    handles_pending = True
     accepts_row_scale = True
 
     def __init__(self, params, prefix=""):
@@ -35,24 +37,21 @@ class GroupedQueryAttention(Part):
         self.num_kv_heads = int(params["num_kv_heads"])
         self.head_dim = int(params["head_dim"])
         self.window = params.get("window")
-        if self.num_heads % self.num_kv_heads:
-            raise ValueError(f"{self.num_kv_heads} kv heads do not divide {self.num_heads} heads")
+        if self.num_kv_heads <= 0 or self.num_heads % self.num_kv_heads:
+            raise ConfigError("num_kv_heads", f"{self.num_kv_heads} kv heads do not divide {self.num_heads} heads")
         if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
-            raise ValueError(f"the attention kernels take head sizes 16..256 in steps of 16, got {self.head_dim}")
+            raise ConfigError("head_dim", f"the attention kernels take head sizes 16..256 in steps of 16, got {self.head_dim}")
+        if self.window is not None and int(self.window) <= 0:
+            raise ConfigError("window", f"must be greater than zero, got {self.window}")
         pos = params.get("position") or PartSpec("none")
         self.position = build_part("position", pos)
         if self.position.rotary_dim > self.head_dim:
-            raise ValueError(f"rotary_dim {self.position.rotary_dim} exceeds head_dim {self.head_dim}")
+            raise ConfigError("rotary_dim", f"{self.position.rotary_dim} exceeds head_dim {self.head_dim}")
         self.q_width = self.num_heads * self.head_dim
         self.kv_width = self.num_kv_heads * self.head_dim
         self.scale = 1.0 / math.sqrt(self.head_dim)
         self.w_qkv = None
         self.w_o = None
-        # prefill steps of bfloat16 models with head size 64 or 128 use the tcgen05 kernel;
-        # CAMELID_PREFILL_ATTENTION=mma keeps the mma.sync kernel (for comparisons)
-        self.prefill_tcgen05 = os.environ.get("CAMELID_PREFILL_ATTENTION", "tcgen05") != "mma"
-        # decode in one launch from the q/k/v product (the default) or as rotary kernel + split attention kernel
-        self.decode_fused = os.environ.get("CAMELID_DECODE_ATTENTION", "fused") != "split"
 
     def tensor_specs(self):
         p = self.prefix
@@ -75,7 +74,6 @@ class GroupedQueryAttention(Part):
 
     def query_tile_sizes(self):
         return [ops.attn_tiling(self.num_heads, self.num_kv_heads, False)[0],
-                ops.attn_mma_tiling(self.num_heads, self.num_kv_heads, False)[0],
                 ops.attn_tc_tiling(self.num_heads, self.num_kv_heads)[0]]
 
     # ------------------------------------------------------------------------------
@@ -93,7 +91,7 @@ class GroupedQueryAttention(Part):
             row_scale = None
         out = ctx.buffer("attn_out", (n, self.q_width))
         splits = self._decode_splits(ctx, n, 1, True) if ctx.decode else 1
-        if (part is not None and ctx.decode and self.decode_fused and (splits <= 8 or ctx.max_len <= 8192)
+        if (part is not None and ctx.decode and ctx.options.decode_attention == "fused" and (splits <= 8 or ctx.max_len <= 8192)
                 and ops.attn_decode_fused_usable(part, out, self.head_dim, self.num_heads, self.num_kv_heads)):
             # decode: one launch sums the product's splits, rotates, writes the cache and attends
             ops.attn_decode_fused(part, out, ctx.row_pos, ctx.row_seq, table, k_pages, v_pages, pos.inv_freq,
@@ -113,13 +111,16 @@ class GroupedQueryAttention(Part):
             ops.rope_kv_write(qkv, ctx.row_pos, ctx.row_seq, table, k_pages, v_pages, pos.inv_freq, pos.rotary_dim,
                               self.num_heads, self.num_kv_heads, self.head_dim, write_kv=not borrow)
             q = qkv[:, :self.q_width]
-        if not ctx.decode and self.prefill_tcgen05 and ops.attn_tc_usable(q, out, self.head_dim):
+        # prefill: bfloat16 with a head size of 64 or 128 on the tcgen05 kernel, everything else in
+        # float on the CUDA cores; decode (where the fused kernel did not take it): mma.sync tiles
+        # for those head sizes, split over blocks
+        if not ctx.decode and ops.attn_tc_usable(q, out, self.head_dim):
             rows, hpc, chunks = ops.attn_tc_tiling(self.num_heads, self.num_kv_heads)
             tile_seq, tile_q0, n_tiles = ctx.query_tiles(rows)
             ops.attn_prefill_tc(q, out, k_pages, v_pages, table, tile_seq, tile_q0, n_tiles, ctx.seq_row0,
                                 ctx.seq_start, ctx.seq_new, self.num_heads, self.num_kv_heads, self.head_dim, rows,
                                 hpc, chunks, self.window or 0, self.scale, linear._err_word(q.device))
-        elif ops.attn_mma_usable(q, self.head_dim):
+        elif ctx.decode and ops.attn_mma_usable(q, self.head_dim):
             self._attend(ctx, q, out, k_pages, v_pages, table, tensor_cores=True)
         else:
             self._attend(ctx, q, out, k_pages, v_pages, table, tensor_cores=False)
@@ -135,7 +136,7 @@ class GroupedQueryAttention(Part):
             per_sm = 2 if self.head_dim <= 64 else 1          # blocks that run at the same time on an SM
         else:                                                 # the float kernel keeps one page of keys and values
             per_sm = max(1, min(8, (200 * 1024) // (4 * PAGE * (2 * self.head_dim + 1) + 4096)))
-        resident = per_sm * linear.SM_COUNT
+        resident = per_sm * ops.sm_count(ctx.device)
         return max(1, min((keys + unit - 1) // unit, resident // ctas, 64))
 
     def _attend(self, ctx, q, out, k_pages, v_pages, table, tensor_cores: bool):

@@ -25,6 +25,7 @@ from dataclasses import dataclass
 import torch
 
 from ..config.plan import PartSpec
+from ..errors import ConfigError
 
 ROLES = ("norm", "mixer", "ffn", "position", "embedding", "head", "block")
 
@@ -44,6 +45,11 @@ class Part:
     # reads of the step, no allocation that must outlive the call): such a part can run
     # inside a captured CUDA graph. Parts that do not say so make the model step eagerly.
     graph_safe: bool = False
+    # True if the part knows what built-in parts may leave on the context instead of adding it
+    # into the residual stream at once (``ctx.pending``: split sums; ``ctx.deferred``: a product
+    # not yet launched) and deals with both itself. The block settles the stream before every
+    # part that does not say so: a part from outside the library always sees complete rows.
+    handles_pending: bool = False
     # True if ``forward`` takes ``ctx.take_row_scale()`` before it reads its input rows and
     # applies the scale itself (to the rows, or to the output of a product of them). The norm
     # before such a part may then leave its rows' scale to the part.
@@ -76,7 +82,7 @@ def register_part(role: str, kind: str):
     """Class decorator: ``@register_part("mixer", "attention")``. A later registration of the
     same name replaces the earlier one."""
     if role not in _REGISTRY:
-        raise ValueError(f"unknown role {role!r}; roles are {ROLES}")
+        raise ConfigError("role", f"unknown role {role!r}; roles are {ROLES}")
 
     def deco(cls):
         cls.role, cls.kind = role, kind
@@ -93,7 +99,7 @@ def build_part(role: str, spec: PartSpec):
     try:
         cls = _REGISTRY[role][spec.kind]
     except KeyError:
-        raise ValueError(f"no {role} named {spec.kind!r} is registered; known: {known_parts(role)}") from None
+        raise ConfigError(f"{role}.kind", f"no {role} named {spec.kind!r} is registered; known: {known_parts(role)}") from None
     return cls(spec.params, spec.prefix)
 
 
@@ -102,8 +108,8 @@ def build_block(layer_spec):
     try:
         cls = _REGISTRY["block"][layer_spec.arrangement]
     except KeyError:
-        raise ValueError(f"no block arrangement named {layer_spec.arrangement!r} is registered; "
-                         f"known: {known_parts('block')}") from None
+        raise ConfigError("block.arrangement", f"no block arrangement named {layer_spec.arrangement!r} is registered; "
+                          f"known: {known_parts('block')}") from None
     return cls(layer_spec)
 
 

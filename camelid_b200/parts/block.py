@@ -39,16 +39,16 @@ class PreNormBlock(Part):
         return self.mixer.query_tile_sizes()
 
     def forward(self, ctx, h):
-        # A built-in mixer or feed-forward may leave split sums pending on the context; the
-        # norm that reads the stream next adds them. Parts from outside the library get a
-        # settled stream.
+        # A built-in mixer or feed-forward may leave split sums pending on the context (or a
+        # product deferred); the norm that reads the stream next adds them. Before any part that
+        # does not declare ``handles_pending`` the block settles the stream itself, so a part
+        # from outside the library, graph safe or not, reads and writes complete rows.
         # A part that declares ``accepts_row_scale`` takes ``ctx.take_row_scale()`` and applies
         # it, which lets the norm before it run inside the product before that.
-        x = self.norm1.forward(ctx, h, allow_row_scale=self.mixer.accepts_row_scale and self.mixer.graph_safe)
-        if not self.mixer.graph_safe:
-            ctx.settle(h)
-        self.mixer.forward(ctx, x, h)
-        x = self.norm2.forward(ctx, h, allow_row_scale=self.ffn.accepts_row_scale and self.ffn.graph_safe)
-        if not self.ffn.graph_safe:
-            ctx.settle(h)
-        self.ffn.forward(ctx, x, h)
+        for norm, part in ((self.norm1, self.mixer), (self.norm2, self.ffn)):
+            if not norm.handles_pending:
+                ctx.settle(h)
+            x = norm.forward(ctx, h, allow_row_scale=part.accepts_row_scale)
+            if not part.handles_pending:
+                ctx.settle(h)
+            part.forward(ctx, x, h)

@@ -16,21 +16,17 @@ go into the residual stream (``add_into_residual`` leaves them *pending* on the 
 """
 from __future__ import annotations
 
-import os
-
 import torch
 
 from ..csrc import ops
+from ..options import KernelOptions
 
 STORE, STORE_F32, ADD_F32, SWIGLU = ops.EPI_STORE, ops.EPI_STORE_F32, ops.EPI_ADD_F32, ops.EPI_SWIGLU
 
-SM_COUNT = 148
-# Up to here a step runs the transposed kernel. Measured on the 1B shape (prefill step, ms): 96 rows
-# 1.24 transposed against 1.38 on the tiles below, 128 rows 1.31 against 1.42; 144 rows 1.54 against
-# 1.42, 256 rows 1.87 against 1.50: the float split sums that the transposed form writes and its
-# readers sum again grow with the rows, the weights it streams do not.
-DECODE_ROWS = int(os.environ.get("CAMELID_DECODE_ROWS", "128"))
-CLUSTERS = SM_COUNT // 2      # pairs of blocks that run tiles of 256 x 256
+# Which form a product takes is decided by the step's rows and ``ctx.options`` (KernelOptions):
+# up to ``decode_rows`` rows the transposed kernel (the float split sums that form writes, and
+# that its readers sum again, grow with the rows; the weights it streams do not), above that
+# tiles of 256 x 256 on pairs of blocks. The number of SMs is the device's own.
 _err: dict = {}
 
 
@@ -55,23 +51,31 @@ def _bn_decode(rows: int) -> int:
     return next((bn for bn in (16, 32, 64) if rows <= bn), 128)
 
 
-PAIR_SPLITS = os.environ.get("CAMELID_PAIR_SPLITS", "1") != "0"
-FUSE_NORM = os.environ.get("CAMELID_FUSE_NORM", "1") != "0"   # the norm after a product of many rows runs inside it
-PAIR_ROWS = max(128, DECODE_ROWS)     # above this many rows the product runs on 256 x 256 tiles of two blocks
+_DEFAULTS = KernelOptions()
 
 
-def _bn_prefill(rows: int, out_features: int) -> int:
+def _opt(ctx) -> KernelOptions:
+    """The options of the step (the defaults where a part is driven without a context)."""
+    return ctx.options if ctx is not None else _DEFAULTS
+
+
+def _pair_rows(ctx) -> int:
+    """Above this many rows a product runs on 256 x 256 tiles of two blocks."""
+    return max(128, _opt(ctx).decode_rows)
+
+
+def _bn_prefill(rows: int, out_features: int, sms: int) -> int:
     """Tile width over the weight rows for a persistent launch: the one that needs fewer
-    rounds of SM_COUNT blocks times its width (wider tiles reuse operands better on a tie)."""
+    rounds of one block per SM times its width (wider tiles reuse operands better on a tie)."""
     def cost(bn):
         tiles = ((rows + 127) // 128) * ((out_features + bn - 1) // bn)
-        return ((tiles + SM_COUNT - 1) // SM_COUNT) * bn
+        return ((tiles + sms - 1) // sms) * bn
     return 256 if cost(256) <= cost(128) else 128
 
 
-def _splits(out_features: int, k: int) -> int:
+def _splits(out_features: int, k: int, sms: int) -> int:
     tiles = (out_features + 127) // 128
-    return max(1, min((k + 63) // 64, round(SM_COUNT / tiles))) if tiles < SM_COUNT else 1
+    return max(1, min((k + 63) // 64, round(sms / tiles))) if tiles < sms else 1
 
 
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, group: int = 0,
@@ -81,14 +85,14 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     the two-block kernel applies it to its output rows, any other path to ``x`` first."""
     tc = ops.gemm_tc_usable(x, w)
     rows = x.shape[0]
-    pair = tc and rows > PAIR_ROWS          # tiles of 256 x 256 on two blocks: less operand traffic per flop
+    pair = tc and rows > _pair_rows(ctx)    # tiles of 256 x 256 on two blocks: less operand traffic per flop
     swiglu_tc = group == 16 and w.shape[0] % 32 == 0
     if row_scale is not None and not (pair and (epilogue == STORE or (epilogue == SWIGLU and swiglu_tc))):
         ops.scale_rows(x, row_scale)
         row_scale = None
     if tc:
         err = _err_word(x.device)
-        if rows <= DECODE_ROWS:
+        if rows <= _opt(ctx).decode_rows:
             bn = _bn_decode(rows)
             if epilogue == SWIGLU and swiglu_tc:
                 ops.gemm_tc(w, x, out, ops.TC_T_SWIGLU, bn, 1, err)
@@ -98,7 +102,7 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
                 return
         # everything else on tiles of this step's rows by the weights' rows (for few rows only
         # what a part outside the library asks for: the library's own few-row products are above)
-        bn = _bn_prefill(rows, w.shape[0])
+        bn = _bn_prefill(rows, w.shape[0], ops.sm_count(x.device))
         if epilogue == SWIGLU:
             if swiglu_tc:
                 if pair:
@@ -116,16 +120,16 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     ops.gemm_tn_simt(x, w, out, epilogue, group)
 
 
-def _pair_splits(rows: int, n: int, k: int) -> int:
+def _pair_splits(rows: int, n: int, k: int, clusters: int) -> int:
     """Splits of K for a product on two-block tiles: more than 1 only for a deep product (K of
     4,096 or more) whose tiles leave half of the clusters or more without work; then as many as
     fill them, of at least 16 k-blocks of 64. (Measured at 512 rows of the 1B shape: the down
     product 53 -> 33 us with 4 splits, but a product of K = 2,048 gains less than the slower
     kernels that then read its split sums cost.)"""
     tiles = ((rows + 255) // 256) * ((n + 255) // 256)
-    if 2 * tiles > CLUSTERS or k < 4096:
+    if 2 * tiles > clusters or k < 4096:
         return 1
-    return ops.pair_partial_splits(k, max(1, min(CLUSTERS // tiles, (k + 63) // 64 // 16)))
+    return ops.pair_partial_splits(k, max(1, min(clusters // tiles, (k + 63) // 64 // 16)))
 
 
 def partial_sums(ctx, x: torch.Tensor, w: torch.Tensor, name: str, row_scale=None):
@@ -136,14 +140,15 @@ def partial_sums(ctx, x: torch.Tensor, w: torch.Tensor, name: str, row_scale=Non
     if not ops.gemm_tc_usable(x, w):
         return None
     n, k = w.shape
-    if rows <= DECODE_ROWS:
+    sms = ops.sm_count(x.device)
+    if rows <= _opt(ctx).decode_rows:
         if row_scale is not None:
             ops.scale_rows(x, row_scale)
-        splits = min(_splits(n, k), (k + 63) // 64)
+        splits = min(_splits(n, k, sms), (k + 63) // 64)
         part = ctx.buffer(name, (splits, rows, n), torch.float32)
         ops.gemm_tc(w, x, part, ops.TC_T_PARTIAL, _bn_decode(rows), splits, _err_word(x.device))
         return part
-    splits = _pair_splits(rows, n, k) if PAIR_SPLITS else 1
+    splits = _pair_splits(rows, n, k, sms // 2) if _opt(ctx).pair_splits else 1
     if splits == 1:
         return None
     part = ctx.buffer(name, (splits, rows, n), torch.float32)
@@ -161,7 +166,8 @@ def add_into_residual(ctx, x: torch.Tensor, w: torch.Tensor, residual: torch.Ten
     part = partial_sums(ctx, x, w, name)
     if part is not None:
         ctx.pending = part
-    elif FUSE_NORM and x.shape[0] > PAIR_ROWS and ops.gemm_tc_usable(x, w) and residual.dtype == torch.float32:
+    elif (_opt(ctx).fuse_norm and x.shape[0] > _pair_rows(ctx) and ops.gemm_tc_usable(x, w)
+          and residual.dtype == torch.float32):
         ctx.deferred = (x, w, residual)
     else:
         linear(ctx, x, w, residual, ADD_F32)

@@ -13,6 +13,7 @@ import math
 import numpy as np
 import torch
 
+from ..errors import ConfigError
 from .base import Part, register_part
 
 
@@ -34,7 +35,7 @@ def rotary_frequencies(rotary_dim: int, theta: float, scaling: dict | None) -> n
             freq = np.where(wavelength < orig / high, freq,
                             np.where(wavelength > orig / low, (freq / factor).astype(np.float32), blended)).astype(np.float32)
         elif kind not in (None, "default"):
-            raise ValueError(f"rotary scaling {kind!r} is not known to this position encoding")
+            raise ConfigError("scaling.rope_type", f"rotary scaling {kind!r} is not known to this position encoding")
     return freq
 
 
@@ -46,7 +47,7 @@ class RotaryEncoding(Part):
         super().__init__(params, prefix)
         self.rotary_dim = int(params["rotary_dim"])
         if self.rotary_dim % 2:
-            raise ValueError(f"rotary_dim must be even, got {self.rotary_dim}")
+            raise ConfigError("rotary_dim", f"must be even, got {self.rotary_dim}")
         self.theta = float(params["theta"])
         self.scaling = params.get("scaling")
         self.inv_freq = None

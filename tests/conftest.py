@@ -1,5 +1,6 @@
-"""Shared fixtures: two tiny configurations of the architecture that differ in every size
-and option, written as model folders with random weights into a temporary folder."""
+"""Shared fixtures: the two tiny configurations of the architecture that differ in every size
+and option (tiny_a and tiny_b), and three more with sizes that are harder for the kernels,
+written as model folders with random weights into a temporary folder."""
 import os
 import sys
 
@@ -22,13 +23,15 @@ TINY_A = {
 }
 TINY_B = {
     "architectures": ["LlamaForCausalLM"], "model_type": "llama",
-    "vocab_size": 517, "hidden_size": 192, "num_hidden_layers": 3, "intermediate_size": 520,
+    "vocab_size": 512, "hidden_size": 192, "num_hidden_layers": 3, "intermediate_size": 512,
     "num_attention_heads": 6, "num_key_value_heads": 1, "head_dim": 32, "max_position_embeddings": 256,
     "rms_norm_eps": 1e-6, "rope_theta": 500000.0,
     "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                      "original_max_position_embeddings": 64},
     "tie_word_embeddings": False, "eos_token_id": [3, 11],
 }
+# the same with a vocabulary and a feed-forward width that are no multiple of 8: nothing fills a tile
+TINY_B_ODD = {**TINY_B, "vocab_size": 517, "intermediate_size": 520}
 # a third shape for long decoding and the first tokens of a sequence: more heads than a
 # block's warps per kv head, a head size that is no power of two, a long context
 TINY_C = {
@@ -51,8 +54,8 @@ TINY_D = {
                      "original_max_position_embeddings": 256},
     "tie_word_embeddings": False, "eos_token_id": 2,
 }
-CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D}
-SEEDS = {"tiny_a": 0, "tiny_b": 1, "tiny_c": 5, "tiny_d": 9}
+CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_b_odd": TINY_B_ODD, "tiny_c": TINY_C, "tiny_d": TINY_D}
+SEEDS = {"tiny_a": 0, "tiny_b": 1, "tiny_b_odd": 1, "tiny_c": 5, "tiny_d": 9}
 
 
 @pytest.fixture(scope="session")
@@ -65,7 +68,7 @@ def model_folders(tmp_path_factory):
     for name, cfg in CONFIGS.items():
         d = str(tmp_path_factory.mktemp(name))
         write_random_model(d, cfg, SEEDS[name], torch.bfloat16,
-                           norm_dtype=torch.float32 if name == "tiny_b" else None)
+                           norm_dtype=torch.float32 if name.startswith("tiny_b") else None)
         out[name] = d
     return out
 

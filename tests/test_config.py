@@ -71,7 +71,7 @@ def test_registry(tmp_path):
     assert "LlamaForCausalLM" in known_architectures()
     arch, cfg, plan = load_config(TINY_B)
     assert arch.name == "LlamaForCausalLM" and len(plan.layers) == 3 and len(plan.schedule) == 3
-    assert plan.layers[1].mixer.params["num_kv_heads"] == 1 and plan.layers[1].ffn.params["intermediate_size"] == 520
+    assert plan.layers[1].mixer.params["num_kv_heads"] == 1 and plan.layers[1].ffn.params["intermediate_size"] == 512
     assert plan.head.params["tied_to"] is None
     assert load_config(TINY_A)[2].head.params["tied_to"] == "model.embed_tokens."
     with pytest.raises(UnknownArchitectureError) as e:
@@ -97,6 +97,6 @@ def test_plan_rejects_bad_schedule():
     _a, _c, plan = load_config(TINY_A)
     kw = {f: getattr(plan, f) for f in plan.__dataclass_fields__}
     for bad in ([ScheduleEntry(5)], [ScheduleEntry(0, 0)], [ScheduleEntry(0), ScheduleEntry(1, 0), ScheduleEntry(1, 1)]):
-        with pytest.raises(ValueError):
+        with pytest.raises(ConfigError):
             ModelPlan(**{**kw, "schedule": tuple(bad)})
     ModelPlan(**{**kw, "schedule": (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1, 1))})

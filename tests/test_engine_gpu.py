@@ -33,7 +33,7 @@ def run_whole(lm, cache, ids):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,length", [("tiny_a", 1), ("tiny_a", 5), ("tiny_a", 100), ("tiny_b", 2), ("tiny_b", 77),
-                                         ("tiny_b", 200), ("tiny_c", 300), ("tiny_d", 3), ("tiny_d", 300)])
+                                         ("tiny_b", 200), ("tiny_b_odd", 3), ("tiny_b_odd", 130), ("tiny_c", 300), ("tiny_d", 3), ("tiny_d", 300)])
 def test_whole_request(cuda, model_folders, name, length, dtype):
     lm = load(model_folders, name, dtype)
     ids = tokens(100 + length, length, CONFIGS[name]["vocab_size"])
@@ -45,7 +45,7 @@ def test_whole_request(cuda, model_folders, name, length, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name,length", [("tiny_a", 100), ("tiny_b", 150), ("tiny_c", 40), ("tiny_d", 170)])
+@pytest.mark.parametrize("name,length", [("tiny_a", 100), ("tiny_b", 150), ("tiny_b_odd", 90), ("tiny_c", 40), ("tiny_d", 170)])
 def test_last_32_one_by_one(cuda, model_folders, name, length, dtype):
     """The prefix in one step, then the last 32 tokens (all of them if there are fewer) one
     by one: the same logits as the whole sequence."""
@@ -73,7 +73,7 @@ def test_last_32_one_by_one(cuda, model_folders, name, length, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_d"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_b_odd", "tiny_d"])
 def test_unequal_batches_reuse_slots(cuda, model_folders, name, dtype):
     """Batches of unequal prompts, decoded a different number of steps each so that the
     shorter requests end earlier; three batches one after another in a cache that only fits

@@ -118,3 +118,56 @@ def test_bad_requests_and_failures_leave_no_slot_behind():
     with pytest.raises(RuntimeError):
         generate(Boom(), cache, sampler, [[1], [2]], 10)
     assert cache.book.slots.n_held == 0 and cache.book.pools[0].n_held == 0
+
+
+class FedModel(FakeModel):
+    """A stand-in that decodes runs of steps on its own, as a model with captured graphs does:
+    every run is remembered as (slots, first tokens, steps)."""
+    use_graphs = True
+
+    class options:
+        feed_on_device = True
+
+    def __init__(self):
+        super().__init__()
+        self.runs = []
+
+    def decode_natively(self, *a, **k):
+        raise AssertionError("a greedy batch must take the fed loop")
+
+    def decode_fed(self, cache, slots, tokens, steps):
+        import numpy as np
+        cache.book.check_extend([(s, steps) for s in slots])
+        for s in slots:
+            cache.book.extend(s, steps)
+            cache.book.commit(s, steps)
+        self.runs.append((list(slots), list(tokens), steps))
+        return np.array([[(t + 1 + k) % 100 for t in tokens] for k in range(steps)], dtype=np.int32)
+
+
+class GreedySampler(FakeSampler):
+    native_ok = True
+    error_word = None
+
+    class options:
+        greedy = True
+
+
+def test_greedy_batches_run_on_the_device_and_cut_at_stop_tokens():
+    from camelid_b200.engine.generate import FED_RUN_WITH_STOPS
+    model, cache, sampler = FedModel(), FakeCache(64, 8), GreedySampler()
+    # without stop tokens: one run for everything the shortest budget allows, then the rest
+    out = generate(model, cache, sampler, [[1, 2, 3], [50]], [40, 6])
+    assert out[0].tokens == [(4 + k) % 100 for k in range(40)] and out[0].finish_reason == "length"
+    assert out[1].tokens == [51, 52, 53, 54, 55, 56] and out[1].finish_reason == "length"
+    assert model.runs == [([0, 1], [4, 51], 5), ([0], [9], 34)]
+    assert cache.book.slots.n_held == 0 and cache.book.pools[0].n_held == 0
+    # with stop tokens: short runs; what a sequence produced after its stop token is dropped
+    model = FedModel()
+    out = generate(model, cache, sampler, [[1, 2, 3], [50]], 60, stop_ids={57})
+    assert out[1].tokens == [51, 52, 53, 54, 55, 56, 57] and out[1].finish_reason == "stop"
+    assert out[0].tokens == [(4 + k) % 100 for k in range(54)] and out[0].tokens[-1] == 57 and out[0].finish_reason == "stop"
+    assert [r[2] for r in model.runs] == [FED_RUN_WITH_STOPS] * 3 + [60 - 1 - 3 * FED_RUN_WITH_STOPS]
+    assert model.runs[1][0] == [0]                       # the stopped sequence left after the first run
+    cache.book.audit()
+    assert cache.book.slots.n_held == 0 and cache.book.pools[0].n_held == 0

@@ -181,13 +181,15 @@ def test_attention_decode_splits(cuda, dtype, n_splits):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("window", [1, 64, 70, 200])
-def test_attention_window_edges(cuda, dtype, window):
-    """A key just outside the window must not count: put the spike there and compare."""
+@pytest.mark.parametrize("edge", [0, 1], ids=["first key outside", "first key inside"])
+@pytest.mark.parametrize("window", [1, 64, 70, 199])
+def test_attention_window_edges(cuda, dtype, window, edge):
+    """The query at position 199 sees keys 200 - window .. 199. A key just outside the window must
+    not count and the first one inside must: the outstanding key sits on each in turn."""
     _attn_case(cuda, dtype, 4, 2, 32, starts=[0, 190], news=[150, 10], window=window, decode=False,
-               spike=(1, max(0, 199 - window)))
+               spike=(1, 199 - window + edge))
     _attn_case(cuda, dtype, 4, 2, 32, starts=[199, 80], news=[1, 1], window=window, decode=True, n_splits=3,
-               spike=(0, max(0, 199 - window)))
+               spike=(0, 199 - window + edge))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -282,7 +284,7 @@ def _attn_mma_case(cuda, n_heads, n_kv, hd, starts, news, window, decode, n_spli
 
 
 @pytest.mark.parametrize("n_heads,n_kv,hd", [(4, 1, 64), (32, 8, 64), (6, 2, 128), (5, 5, 64), (34, 1, 128), (12, 2, 64)])
-def test_attention_mma_prefill_shapes(cuda, n_heads, n_kv, hd):
+def test_attention_mma_rows_of_several_tokens(cuda, n_heads, n_kv, hd):
     _attn_mma_case(cuda, n_heads, n_kv, hd, starts=[0, 0, 0, 64], news=[1, 70, 129, 33], window=None, decode=False,
                    spike=(2, 3))
 
@@ -294,12 +296,13 @@ def test_attention_mma_decode_splits(cuda, hd, n_splits):
                    n_splits=n_splits, spike=(5, 130))
 
 
-@pytest.mark.parametrize("window", [1, 32, 70, 200])
-def test_attention_mma_window_edges(cuda, window):
+@pytest.mark.parametrize("edge", [0, 1], ids=["first key outside", "first key inside"])
+@pytest.mark.parametrize("window", [1, 32, 70, 199])
+def test_attention_mma_window_edges(cuda, window, edge):
     _attn_mma_case(cuda, 4, 2, 64, starts=[0, 190], news=[150, 10], window=window, decode=False,
-                   spike=(1, max(0, 199 - window)))
+                   spike=(1, 199 - window + edge))
     _attn_mma_case(cuda, 4, 2, 64, starts=[199, 80], news=[1, 1], window=window, decode=True, n_splits=3,
-                   spike=(0, max(0, 199 - window)))
+                   spike=(0, 199 - window + edge))
 
 
 # ---- the tcgen05 prefill attention kernel ----
@@ -351,9 +354,10 @@ def test_attention_tc_continues_from_cache(cuda, hd):
     _attn_tc_case(cuda, 8, 2, hd, starts=[64, 300, 5, 0], news=[3, 200, 64, 129], spike=(1, 7), window=None)
 
 
-@pytest.mark.parametrize("window", [1, 32, 70, 200])
-def test_attention_tc_window_edges(cuda, window):
-    _attn_tc_case(cuda, 4, 2, 64, starts=[0, 190], news=[150, 10], window=window, spike=(1, max(0, 199 - window)))
+@pytest.mark.parametrize("edge", [0, 1], ids=["first key outside", "first key inside"])
+@pytest.mark.parametrize("window", [1, 32, 70, 199])
+def test_attention_tc_window_edges(cuda, window, edge):
+    _attn_tc_case(cuda, 4, 2, 64, starts=[0, 190], news=[150, 10], window=window, spike=(1, 199 - window + edge))
 
 
 def _attn_fused_case(cuda, n_heads, n_kv, hd, rot, starts, window, n_splits, gsplits, write_kv=True, spike=None,
@@ -370,16 +374,26 @@ def _attn_fused_case(cuda, n_heads, n_kv, hd, rot, starts, window, n_splits, gsp
     g = torch.Generator().manual_seed(7)
     width = (n_heads + 2 * n_kv) * hd
     part = torch.randn(gsplits, n, width, generator=g) / math.sqrt(gsplits)
+    pos = torch.tensor(starts)
+    if spike is not None:
+        # One cached key gets a score that stands out for every head of its sequence: the key is
+        # 8 in its last dimension and nothing else, and the query is made so that, after the
+        # kernel's rotation at its position, it is large in that dimension (the query before
+        # the rotation is the wanted one turned back). A kernel that drops that key, or counts
+        # it when the window excludes it, is off by far more than the tolerance.
+        seq, key = spike
+        ks[seq][key] *= 0
+        ks[seq][key, :, hd - 1] = 8.0
+        k_pages[int(table[seq, key // 64]), :, key % 64] = ks[seq][key].to(cuda)
+        want_q = torch.randn(1, n_heads, hd, generator=g, dtype=torch.float64)
+        want_q[..., hd - 1] = 8.0 * math.sqrt(hd) / 4
+        before = pl.rope(want_q, -pos[seq:seq + 1], freqs) if rot else want_q
+        rest = part[1:, seq, :n_heads * hd].sum(0) if gsplits > 1 else 0.0
+        part[0, seq, :n_heads * hd] = before.reshape(-1).float() - rest
     total = torch.zeros(n, width)
     for s in range(gsplits):
         total = total + part[s]                       # the kernel's order of adding
     qkv = total.to(dt)
-    if spike is not None:                             # one far key gets a score that stands out
-        seq, key = spike
-        ks[seq][key] *= 0
-        ks[seq][key, :, hd - 1] = 8.0                 # a dimension the rotation leaves alone when rot < hd
-        k_pages[int(table[seq, key // 64]), :, key % 64] = ks[seq][key].to(cuda)
-    pos = torch.tensor(starts)
     q = qkv[:, :n_heads * hd].double().view(n, n_heads, hd)
     k = qkv[:, n_heads * hd:(n_heads + n_kv) * hd].double().view(n, n_kv, hd)
     v = qkv[:, (n_heads + n_kv) * hd:].view(n, n_kv, hd)
@@ -424,18 +438,26 @@ def test_attention_decode_fused(cuda, n_heads, n_kv, hd, rot, n_splits):
                      gsplits=3, spike=(5, 130))
 
 
-@pytest.mark.parametrize("window", [1, 32, 70, 200])
-def test_attention_decode_fused_window_and_borrowed_cache(cuda, window):
+@pytest.mark.parametrize("edge", ["first key inside", "first key outside"])
+@pytest.mark.parametrize("window", [1, 32, 70, 199])
+def test_attention_decode_fused_window_and_borrowed_cache(cuda, window, edge):
+    """The query at position 199 with a window of w sees keys 200 - w .. 199: the outstanding key
+    sits once on the first key inside the window (it must count) and once on the first key
+    outside (it must not)."""
+    key = 200 - window if edge == "first key inside" else 199 - window
+    if key == 199:              # a window of 1 sees only the new key, which the kernel makes itself
+        key = None
     _attn_fused_case(cuda, 4, 2, 64, 64, starts=[199, 80, 0], window=window, n_splits=3, gsplits=9,
-                     spike=(0, max(0, 200 - window)))
+                     spike=None if key is None else (0, key))
     _attn_fused_case(cuda, 4, 2, 64, 64, starts=[199, 80, 0], window=window, n_splits=4, gsplits=1, write_kv=False,
-                     spike=(0, max(0, 200 - window)))
+                     spike=None if key is None else (0, key))
     _attn_fused_case(cuda, 8, 2, 128, 128, starts=[300, 5], window=None, n_splits=2, gsplits=2, write_kv=False)
 
 
-@pytest.mark.parametrize("n_splits", [1, 3])
-def test_attention_decode_fused_long_context(cuda, n_splits):
-    """Thousands of cached keys: a warp walks more tiles than it keeps page numbers for in
-    registers, and a far key must still be found."""
+@pytest.mark.parametrize("n_splits,key", [(1, 2100), (1, 8999), (3, 130), (3, 5003), (8, 2100), (8, 8999)])
+def test_attention_decode_fused_long_context(cuda, n_splits, key):
+    """Thousands of cached keys: a warp walks more tiles than the 32 page numbers it keeps in
+    registers, and one outstanding key, near the start, past a warp's first 32 pages, in the
+    middle or at the very end of the range, must be found."""
     _attn_fused_case(cuda, 8, 2, 64, 64, starts=[9000, 4100, 64], window=None, n_splits=n_splits, gsplits=2,
-                     spike=(0, 130), n_pages=256)
+                     spike=(0, key), n_pages=256)

@@ -35,10 +35,10 @@ def shape_3b(tmp_path_factory):
                    num_hidden_layers=1, vocab_size=32000)
 
 
-def _check(folder, cfg, dtype, lens, decode):
+def _check(folder, cfg, dtype, lens, decode, options=None):
     import camelid_b200
     from camelid_b200 import StepEntry
-    lm = camelid_b200.load(folder, dtype=dtype)
+    lm = camelid_b200.load(folder, dtype=dtype, options=options)
     config, w = pl.read_model(folder)
     seqs = [tokens(40 + i, n + decode, cfg["vocab_size"]) for i, n in enumerate(lens)]
     # the oracle's logits only at the places that are compared (its output product is the slow part)
@@ -78,20 +78,19 @@ def test_3b_widths_head_size_128(cuda, shape_3b, dtype):
     _check(folder, cfg, dtype, lens=[200, 65], decode=2)
 
 
-def test_norm_inside_the_product_before_it_or_on_its_own(cuda, shape_1b, monkeypatch):
+def test_norm_inside_the_product_before_it_or_on_its_own(cuda, shape_1b):
     """A prefill of many rows runs each norm inside the products around it (the one before adds
     into the residual stream and writes the rows times the norm's weight, the one after applies
     the rows' scale); with that switched off the norm is a kernel of its own. Both match the
     plain implementation, and a launch count shows that the switch does switch. (Enough rows that
     the narrow products have tiles for most SMs: with fewer they split K and leave their sums to
     the norm kernel, as decode steps do.)"""
+    from camelid_b200 import KernelOptions
     from camelid_b200.csrc import ops
-    from camelid_b200.parts import linear
     folder, cfg = shape_1b
     counts = []
     for fuse in (True, False):
-        monkeypatch.setattr(linear, "FUSE_NORM", fuse)
         before = ops.launch_count()
-        _check(folder, cfg, "bfloat16", lens=[900, 400], decode=1)
+        _check(folder, cfg, "bfloat16", lens=[900, 400], decode=1, options=KernelOptions(fuse_norm=fuse))
         counts.append(ops.launch_count() - before)
     assert counts[0] < counts[1]

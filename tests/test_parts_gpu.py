@@ -21,6 +21,7 @@ def _ctx(cache, dtype, slots, starts, token_lists, want=None, tile_sizes=(1,)):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_norm_part(cuda, dtype):
+    from camelid_b200 import ConfigError
     from camelid_b200.config import PartSpec
     from camelid_b200.parts import build_part
     norm = build_part("norm", PartSpec("rmsnorm", {"hidden_size": 88, "eps": 1e-3}, "n."))
@@ -40,6 +41,7 @@ def test_norm_part(cuda, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("hidden,inter", [(40, 48), (72, 136)])
 def test_swiglu_part(cuda, dtype, hidden, inter):
+    from camelid_b200 import ConfigError
     from camelid_b200.config import PartSpec
     from camelid_b200.parts import build_part
     from camelid_b200.weights import random_tensors
@@ -57,6 +59,7 @@ def test_swiglu_part(cuda, dtype, hidden, inter):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_embedding_and_head_parts(cuda, dtype):
+    from camelid_b200 import ConfigError
     from camelid_b200.config import PartSpec
     from camelid_b200.parts import build_part
     emb = build_part("embedding", PartSpec("embedding", {"vocab_size": 99, "hidden_size": 24}, "e."))
@@ -80,6 +83,7 @@ def test_embedding_and_head_parts(cuda, dtype):
 
 
 def test_rotary_part_frequencies(cuda):
+    from camelid_b200 import ConfigError
     from camelid_b200.config import PartSpec
     from camelid_b200.parts import build_part
     sc = {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
@@ -100,6 +104,7 @@ def test_attention_part(cuda, dtype, heads, kv_heads, hd, rot):
     """The mixer alone with a cache of its own: a prompt in one step, then three single
     tokens, for two sequences of unequal length; partial rotary dimensions and none."""
     from camelid_b200.cache.sequence_cache import SequenceCache
+    from camelid_b200 import ConfigError
     from camelid_b200.config import PartSpec
     from camelid_b200.parts import build_part
     from camelid_b200.weights import random_tensors
@@ -151,12 +156,13 @@ def test_attention_part(cuda, dtype, heads, kv_heads, hd, rot):
 
 @pytest.mark.skipif(False, reason="")
 def test_unknown_part_is_a_clear_error():
+    from camelid_b200 import ConfigError
     from camelid_b200.config import PartSpec
     from camelid_b200.parts import build_part
-    with pytest.raises(ValueError) as e:
+    with pytest.raises(ConfigError) as e:
         build_part("mixer", PartSpec("mamba"))
     assert "attention" in str(e.value)
-    with pytest.raises(ValueError):
+    with pytest.raises(ConfigError):
         build_part("mixer", PartSpec("attention", {"hidden_size": 8, "num_heads": 2, "num_kv_heads": 1, "head_dim": 24}))
 
 

@@ -46,6 +46,47 @@ def _register_toys():
                 residual[r0:r0 + n] += sums * self.w
                 state[slot] = sums[-1]
 
+    @register_part("mixer", "toy_device_sum")
+    class DeviceRunningSum(Part):
+        """The running sum again, but written for a captured graph: a one-token step finds its
+        sequences' state through ``ctx.seq_slot`` on the device and reads nothing on the host.
+        It also reads the residual stream (its output is sum * w + 0.1 * residual) and knows
+        nothing of what the library's own parts may have left pending on the context."""
+        graph_safe = True
+
+        def __init__(self, params, prefix=""):
+            super().__init__(params, prefix)
+            self.hidden = params["hidden_size"]
+
+        def tensor_specs(self):
+            return {self.prefix + "w": TensorSpec((self.hidden,), "norm")}
+
+        def load(self, tensors, device, dtype):
+            self.w = tensors[self.prefix + "w"].to(device=device, dtype=torch.float32)
+
+        def cache_spec(self):
+            return StateSpec((self.hidden,), "float32")
+
+        def forward(self, ctx, x, residual):
+            state = ctx.state()
+            if ctx.decode:                                        # device arrays only
+                slots = ctx.seq_slot.long()
+                sums = state.index_select(0, slots) + x.float()
+                state.index_copy_(0, slots, sums)
+                residual.add_(sums * self.w + 0.1 * residual)
+                return
+            for slot, r0, n in zip(ctx.h_slots, ctx.h_row0, ctx.h_new):
+                sums = torch.cumsum(x[r0:r0 + n].float(), 0) + state[slot]
+                residual[r0:r0 + n] += sums * self.w + 0.1 * residual[r0:r0 + n]
+                state[slot] = sums[-1]
+
+    def device_sum_plan(cfg):
+        base = llama_plan(cfg)
+        layers = list(base.layers)
+        layers[1] = dataclasses.replace(layers[1], mixer=PartSpec("toy_device_sum", {"hidden_size": cfg.hidden_size},
+                                                                  "model.layers.1.toy."))
+        return dataclasses.replace(base, layers=tuple(layers))
+
     def toy_plan(cfg):
         base = llama_plan(cfg)
         layers = list(base.layers)
@@ -124,6 +165,7 @@ def _register_toys():
     register_architecture("ToyRoutedForCausalLM", LlamaConfig.from_dict, routed_plan)
     register_architecture("ToyHarmonicForCausalLM", LlamaConfig.from_dict, harmonic_plan)
     register_architecture("ToyStateForCausalLM", LlamaConfig.from_dict, toy_plan)
+    register_architecture("ToyDeviceSumForCausalLM", LlamaConfig.from_dict, device_sum_plan)
     register_architecture("ToyTwiceForCausalLM", LlamaConfig.from_dict, twice_plan)
     register_architecture("ToyWindowForCausalLM", LlamaConfig.from_dict, window_plan)
 
@@ -305,3 +347,57 @@ def test_position_encoding_of_its_own(cuda, dtype, over):
     got = _drive(model, seqs, cut=[64, 3])
     for i in range(3):
         assert_close(got[i], plain(seqs[i]), dtype, f"harmonic rotary, request {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_safe_mixer_from_outside_finds_its_state_by_slot(cuda, dtype):
+    """A mixer from outside the library that is safe to capture, keeps state per sequence, reads
+    the residual stream and ignores the context's pending sums: stepped by hand (graph path for
+    the single tokens), and through the generation loop with two batches of equal size that sit
+    in different slots, so that the captured graph and the C++ decode loop must pick up each
+    batch's own slots."""
+    from camelid_b200 import StepEntry
+    from camelid_b200.engine.generate import generate
+    from camelid_b200.sampling.options import SamplingOptions
+    from camelid_b200.sampling.sampler import Sampler
+    _register_toys()
+    cfg, model, w = _model("ToyDeviceSumForCausalLM", dtype)
+    assert model.use_graphs
+
+    def plain(ids):
+        ids = torch.as_tensor(ids)
+        pos = torch.arange(len(ids))
+        fr = pl.rope_frequencies(cfg)
+        h = pl.embedding(ids, w["model.embed_tokens.weight"], torch.float64)
+        h, _ = pl.decoder_layer(h, w, 0, cfg, pos, fr)
+        p = "model.layers.1."
+        n = pl.rms_norm(h, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        if dtype == "bfloat16":
+            n = n.to(torch.bfloat16).double()
+        r = h + torch.cumsum(n, 0) * w[p + "toy.w"].double() + 0.1 * h
+        n2 = pl.rms_norm(r, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+        r = r + pl.swiglu(n2, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+        return pl.rms_norm(r, w["model.norm.weight"], cfg["rms_norm_eps"]) @ pl.output_weight(cfg, w).double().T
+
+    seqs = [tokens(21, 40, 256), tokens(22, 23, 256), tokens(23, 30, 256)]
+    got = _drive(model, seqs, cut=[17, 20])
+    for i in range(3):
+        assert_close(got[i], plain(seqs[i]), dtype, f"device running sum, request {i}")
+
+    # through the loop: the same two prompts first in slots 0 and 1, then, with slot 0 held by
+    # someone else, in slots 1 and 2; teacher-forced against the plain implementation
+    cache = model.new_cache(1024, max_slots=4)
+    sampler = Sampler(SamplingOptions(), model.vocab_size, model.device)
+    prompts = [tokens(31, 9, 256), tokens(32, 14, 256)]
+    first = [r.tokens for r in generate(model, cache, sampler, prompts, 12)]
+    held = cache.alloc_slot()
+    assert held == 0
+    again = [r.tokens for r in generate(model, cache, sampler, prompts, 12)]
+    cache.free_slot(held)
+    assert first == again, "the same prompts gave other tokens in other slots"
+    for prompt, gen in zip(prompts, first):
+        ref = plain(prompt + gen[:-1])
+        scale = float(ref.abs().max())
+        for i, tok in enumerate(gen):
+            row = ref[len(prompt) - 1 + i]
+            assert float(row.max() - row[tok]) <= (1e-4 if dtype == "float32" else 3e-2) * scale, (i, tok)

@@ -35,7 +35,7 @@ def replay(folder, dtype, steps, out_dir, max_tokens):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_d"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_b_odd", "tiny_d"])
 def test_replay_three_ways(cuda, model_folders, tmp_path, name, dtype):
     vocab = CONFIGS[name]["vocab_size"]
     lens = [100, 37, 64, 5]

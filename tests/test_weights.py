@@ -139,8 +139,8 @@ def test_random_model_folder(tmp_path):
     d = write_random_model(str(tmp_path / "m"), TINY_B, seed=1, norm_dtype=torch.float32)
     assert sorted(os.listdir(d)) == ["config.json", "model.safetensors"]
     cfg, w = pl.read_model(d)
-    assert cfg["architectures"] == ["LlamaForCausalLM"] and cfg["intermediate_size"] == 520
-    assert w["model.layers.2.mlp.down_proj.weight"].shape == (192, 520)
+    assert cfg["architectures"] == ["LlamaForCausalLM"] and cfg["intermediate_size"] == 512
+    assert w["model.layers.2.mlp.down_proj.weight"].shape == (192, 512)
     assert w["model.layers.0.mlp.gate_proj.weight"].dtype == torch.bfloat16
     assert w["model.norm.weight"].dtype == torch.float32
     lin = w["model.embed_tokens.weight"].float()
