@@ -98,7 +98,7 @@ gemm_tn_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, i
     }
 }
 
-// Few rows (decode) in float: every output column is one warp's dot products, the weight row
+// Few rows in float, the plain form (any K, any alignment, any interleave group): every output column is one warp's dot products, the weight row
 // read once with 16-byte loads and used for all MB activation rows, which stay in cache.
 // Each lane sums its k's in ascending order, then the lanes are summed in a fixed tree: the
 // value of a row does not depend on the other rows of the step.
@@ -183,6 +183,182 @@ gemv_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ 
     }
 }
 
+// Few rows in float, the form that streams weights: a block owns 32 consecutive weight rows and a
+// range of K; its activations (MB rows of that range) are staged in shared memory once and every
+// warp walks COLS weight rows at a time, so an activation read from shared memory serves COLS
+// dot products and each lane keeps 2 * COLS 16-byte weight loads in flight. The first weight
+// loads are issued before the wait on the previous kernel (weights do not depend on it). Where a
+// product has too few 32-row tiles for the SMs, K is split over gridDim.y: every block leaves
+// its sums in `scratch`, and the block that arrives last at the tile's ticket adds them in split
+// order and runs the epilogue. The order of summation is fixed by N and K alone: lanes take
+// their k's in ascending order, the lanes are summed in a fixed tree, the splits in index order.
+// SwiGLU needs interleave groups of 16, so that a tile of 32 packed rows is 16 gate rows and the
+// 16 up rows of the same outputs.
+#define GV_WARPS 8
+#define GV_ROWS 32          // weight rows per block
+#define GV_AHEAD 2          // steps of 128 columns a lane has weight loads in flight for
+template <int MB, int EPI>
+__global__ void __launch_bounds__(GV_WARPS * 32, 2)
+gemv_f32_stream_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw, float* __restrict__ C,
+                       int ldc, int M, int n_wrows, int K, int kc, float* __restrict__ scratch, int* __restrict__ tickets) {
+    constexpr int COLS = GV_ROWS / GV_WARPS;            // 4 weight rows per warp
+    extern __shared__ __align__(16) float a_s[];        // [MB][kc]
+    __shared__ int s_last;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tile = blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
+    const int m0 = blockIdx.z * MB;
+    const int k_begin = split * kc, k_end = min(K, k_begin + kc);
+    const int steps = (k_end - k_begin + 127) / 128;
+    const float* wp[COLS];
+#pragma unroll
+    for (int c = 0; c < COLS; ++c) wp[c] = W + (size_t)min(tile * GV_ROWS + warp * COLS + c, n_wrows - 1) * ldw;
+    float acc[MB][COLS];
+#pragma unroll
+    for (int m = 0; m < MB; ++m)
+#pragma unroll
+        for (int c = 0; c < COLS; ++c) acc[m][c] = 0.f;
+
+    // weights of the first GV_AHEAD steps: on their way before the previous kernel has finished
+    float4 w[GV_AHEAD][COLS];
+#pragma unroll
+    for (int u = 0; u < GV_AHEAD; ++u)
+#pragma unroll
+        for (int c = 0; c < COLS; ++c) w[u][c] = __ldg(reinterpret_cast<const float4*>(wp[c] + min(k_begin + u * 128 + lane * 4, K - 4)));
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int i = threadIdx.x; i < MB * (kc / 4); i += blockDim.x) {
+        const int m = i / (kc / 4), k4 = (i - m * (kc / 4)) * 4;
+        const int k = min(k_begin + k4, K - 4);
+        *reinterpret_cast<float4*>(a_s + (size_t)m * kc + k4) =
+            *reinterpret_cast<const float4*>(A + (size_t)min(m0 + m, M - 1) * lda + k);
+    }
+    __syncthreads();
+
+    for (int st = 0; st < steps; st += GV_AHEAD) {
+#pragma unroll
+        for (int u = 0; u < GV_AHEAD; ++u) {
+            const int kl = (st + u) * 128 + lane * 4;
+            const bool live = k_begin + kl < k_end;      // past the range the clamped load does not count
+            const int ka = min(kl, kc - 4);
+#pragma unroll
+            for (int m = 0; m < MB; ++m) {
+                const float4 a4 = live ? *reinterpret_cast<const float4*>(a_s + (size_t)m * kc + ka) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int c = 0; c < COLS; ++c) {
+                    acc[m][c] = fmaf(a4.x, w[u][c].x, acc[m][c]); acc[m][c] = fmaf(a4.y, w[u][c].y, acc[m][c]);
+                    acc[m][c] = fmaf(a4.z, w[u][c].z, acc[m][c]); acc[m][c] = fmaf(a4.w, w[u][c].w, acc[m][c]);
+                }
+            }
+            // this slot's next weights, GV_AHEAD steps on (clamped to a valid address at the end)
+            if (st + GV_AHEAD + u < steps) {
+#pragma unroll
+                for (int c = 0; c < COLS; ++c)
+                    w[u][c] = __ldg(reinterpret_cast<const float4*>(wp[c] + min(k_begin + (st + GV_AHEAD + u) * 128 + lane * 4, K - 4)));
+            }
+        }
+    }
+    // this block's sums of its 32 weight rows, [MB][32], into shared memory (the staging area is free now)
+    __syncthreads();
+    float* sums = a_s;
+#pragma unroll
+    for (int m = 0; m < MB; ++m)
+#pragma unroll
+        for (int c = 0; c < COLS; ++c) {
+            const float v = warp_sum(acc[m][c]);
+            if (lane == 0) sums[m * GV_ROWS + warp * COLS + c] = v;
+        }
+    __syncthreads();
+    if (n_splits > 1) {
+        float* mine = scratch + (((size_t)blockIdx.z * gridDim.x + tile) * n_splits + split) * (MB * GV_ROWS);
+        for (int i = threadIdx.x; i < MB * GV_ROWS; i += blockDim.x) mine[i] = sums[i];
+        __threadfence();
+        __syncthreads();
+        int* ticket = tickets + blockIdx.z * gridDim.x + tile;
+        if (threadIdx.x == 0) {
+            const int t = atomicAdd(ticket, 1);
+            s_last = (t == n_splits - 1);
+            if (s_last) *ticket = 0;                     // left zero for the next launch
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        const float* all = scratch + ((size_t)blockIdx.z * gridDim.x + tile) * n_splits * (MB * GV_ROWS);
+        for (int i = threadIdx.x; i < MB * GV_ROWS; i += blockDim.x) {
+            float v = 0.f;
+            for (int sp = 0; sp < n_splits; ++sp) v += __ldcg(all + (size_t)sp * (MB * GV_ROWS) + i);
+            sums[i] = v;
+        }
+        __syncthreads();
+    }
+    if (EPI == EPI_SWIGLU) {
+        for (int i = threadIdx.x; i < MB * (GV_ROWS / 2); i += blockDim.x) {
+            const int m = i / (GV_ROWS / 2), j = i - m * (GV_ROWS / 2);
+            const int n = tile * (GV_ROWS / 2) + j;
+            if (m0 + m < M && 2 * n < n_wrows) {
+                const float g = sums[m * GV_ROWS + j], u = sums[m * GV_ROWS + GV_ROWS / 2 + j];
+                C[(size_t)(m0 + m) * ldc + n] = (g / (1.0f + expf(-g))) * u;
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < MB * GV_ROWS; i += blockDim.x) {
+            const int m = i / GV_ROWS, j = i - m * GV_ROWS;
+            const int n = tile * GV_ROWS + j;
+            if (m0 + m < M && n < n_wrows) {
+                float* o = C + (size_t)(m0 + m) * ldc + n;
+                if (EPI == EPI_ADD_F32) *o += sums[i];
+                else *o = sums[i];
+            }
+        }
+    }
+}
+
+// Scratch the streaming form needs for a product: tickets (ints, kept zero) first, then the splits' sums.
+static int gemv_stream_splits(int n_wrows, int K) {
+    const int tiles = (n_wrows + GV_ROWS - 1) / GV_ROWS;
+    int splits = (3 * cml_sm_count() + tiles - 1) / tiles;          // about three blocks per SM
+    splits = max(1, min(splits, K / 512));                          // a range of at least 512 columns
+    splits = max(splits, (K + 2047) / 2048);                        // and of at most 2,048 (shared memory)
+    return splits;
+}
+
+extern "C" long cml_gemv_f32_scratch_bytes(int M, int N, int K, int epilogue) {
+    const int n_wrows = epilogue == EPI_SWIGLU ? 2 * N : N;
+    const int tiles = (n_wrows + GV_ROWS - 1) / GV_ROWS, groups = (M + 7) / 8;
+    const int splits = gemv_stream_splits(n_wrows, K);
+    const long ticket_bytes = ((long)tiles * groups * sizeof(int) + 255) / 256 * 256;
+    return ticket_bytes + (splits > 1 ? (long)tiles * groups * splits * 8 * GV_ROWS * sizeof(float) : 0);
+}
+
+static int launch_gemv_f32_stream(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
+                                  int epilogue, void* scratch, cudaStream_t s) {
+    constexpr int MB = 8;
+    const int n_wrows = epilogue == EPI_SWIGLU ? 2 * N : N;
+    const int tiles = (n_wrows + GV_ROWS - 1) / GV_ROWS, groups = (M + MB - 1) / MB;
+    const int splits = gemv_stream_splits(n_wrows, K);
+    const int kc = ((K + splits - 1) / splits + 127) / 128 * 128;
+    const int n_splits = (K + kc - 1) / kc;
+    const size_t smem = (size_t)max(MB * kc, MB * GV_ROWS) * sizeof(float);
+    const long ticket_bytes = ((long)tiles * groups * sizeof(int) + 255) / 256 * 256;
+    int* tickets = (int*)scratch;
+    float* sums = (float*)((char*)scratch + ticket_bytes);
+    dim3 grid(tiles, n_splits, groups);
+    cudaError_t e;
+#define CML_GEMVS(E)                                                                                                   \
+    e = cml_allow_smem<gemv_f32_stream_kernel<MB, E>>(smem);                                                           \
+    if (e != cudaSuccess) return (int)e;                                                                               \
+    launch_pdl(gemv_f32_stream_kernel<MB, E>, grid, dim3(GV_WARPS * 32), smem, s, (const float*)A, lda, (const float*)W, \
+               ldw, (float*)C, ldc, M, n_wrows, K, kc, sums, tickets)
+    switch (epilogue) {
+        case EPI_STORE:
+        case EPI_STORE_F32: CML_GEMVS(EPI_STORE_F32); break;
+        case EPI_ADD_F32: CML_GEMVS(EPI_ADD_F32); break;
+        case EPI_SWIGLU: CML_GEMVS(EPI_SWIGLU); break;
+        default: return CML_ERR_BAD_SIZE;
+    }
+#undef CML_GEMVS
+    return cml_launch_status();
+}
+
 static int launch_gemv_f32(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
                            int epilogue, int group, cudaStream_t s) {
     constexpr int MB = 8;
@@ -223,11 +399,18 @@ static int launch_gemm(const void* A, int lda, const void* W, int ldw, void* C, 
 }
 
 // A: [M, K] (row stride lda), W: [N, K] (or [2N, K] for SwiGLU; row stride ldw), C: [M, N] (ldc).
+// `scratch` (may be null): device memory of at least cml_gemv_f32_scratch_bytes(M, N, K, epilogue) bytes whose
+// first part (the tickets) is zero before the first call and left zero; with it, float products of at most 32 rows
+// whose sizes allow 16-byte loads take the streaming form.
 extern "C" int cml_gemm_tn_simt(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
-                                int dtype, int epilogue, int group, void* stream) {
+                                int dtype, int epilogue, int group, void* scratch, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CML_DTYPE_F32 && M <= 32 && scratch != nullptr && K >= 128 && (K & 3) == 0 && (lda & 3) == 0 &&
+        (ldw & 3) == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0 &&
+        (epilogue != EPI_SWIGLU || (group == GV_ROWS / 2 && N % (GV_ROWS / 2) == 0)))
+        return launch_gemv_f32_stream(A, lda, W, ldw, C, ldc, M, N, K, epilogue, scratch, s);
     if (dtype == CML_DTYPE_F32 && M <= 32) return launch_gemv_f32(A, lda, W, ldw, C, ldc, M, N, K, epilogue, group, s);
     if (dtype == CML_DTYPE_F32) return launch_gemm<float>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, group, s);
     if (dtype == CML_DTYPE_BF16) return launch_gemm<bf16>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, group, s);

@@ -54,7 +54,8 @@ _SIGNATURES = {
                                               c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     ("gemm_simt", "cml_gemm_tn_simt"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                        c_int, c_int, c_void_p],
+                                        c_int, c_int, c_void_p, c_void_p],
+    ("gemm_simt", "cml_gemv_f32_scratch_bytes"): [c_int, c_int, c_int, c_int],
     ("sampling", "cml_argmax_rows"): [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     ("sampling", "cml_adjust_logits"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_float,
                                         c_void_p],
@@ -536,8 +537,14 @@ def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
     else:
         assert w.shape[0] == N
         assert c.dtype == (a.dtype if epilogue == EPI_STORE else torch.float32)
+    scratch = None
+    if a.dtype == torch.float32 and M <= 32:      # the streaming form for few float rows: tickets and split sums
+        f = _fn("gemm_simt", "cml_gemv_f32_scratch_bytes")
+        f.restype = c_long
+        scratch = zeroed_scratch(a.device, "gemv_f32", int(f(M, N, K, epilogue)))
     _check(_fn("gemm_simt", "cml_gemm_tn_simt")(_p(a), a.stride(0), _p(w), w.stride(0), _p(c), c.stride(0), M, N, K,
-                                                dtype_code(a.dtype), epilogue, group, _stream()), "gemm_tn_simt")
+                                                dtype_code(a.dtype), epilogue, group, _p(scratch), _stream()),
+           "gemm_tn_simt")
 
 
 _scratch: dict = {}

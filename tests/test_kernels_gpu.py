@@ -74,6 +74,39 @@ def test_gemm_simt_epilogues(cuda, dtype, M, N, K):
     assert rel_err(c32.cpu(), wide[:, 8:].cpu().double() @ w.cpu().double().T) <= 1e-5
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 3072, 2048), (8, 2048, 2048), (8, 2048, 8192), (5, 517, 132), (32, 100, 640),
+                                   (17, 33, 4100), (2, 128256, 256), (8, 40, 128)])
+def test_gemv_float_streaming_form(cuda, M, N, K):
+    """Float products of at most 32 rows whose sizes allow 16-byte loads: tiles of 32 weight rows,
+    K split over blocks where there are few tiles, the splits summed in index order by the
+    block that comes last. Every epilogue; tickets are left zero, so a second call is as good; a row's
+    value does not depend on the other rows of the step."""
+    from camelid_b200.csrc import ops
+    g = torch.Generator().manual_seed(M * 1000 + N + K)
+    a = torch.randn(M, K, generator=g).to(cuda)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(cuda)
+    ref = a.cpu().double() @ w.cpu().double().T
+    for rep in range(2):
+        c = torch.full((M, N), float("nan"), device=cuda)
+        ops.gemm_tn_simt(a, w, c, ops.EPI_STORE_F32)
+        assert rel_err(c.cpu(), ref) <= 2e-6, rep
+    res = torch.randn(M, N, generator=g).to(cuda)
+    want = res.cpu().double() + ref
+    ops.gemm_tn_simt(a, w, res, ops.EPI_ADD_F32)
+    assert rel_err(res.cpu(), want) <= 2e-6
+    one = torch.empty(1, N, device=cuda)
+    ops.gemm_tn_simt(a[M - 1:], w, one, ops.EPI_STORE_F32)
+    assert torch.equal(one[0], c[M - 1]), "a row alone differs from the same row in a step of several"
+    if N % 32 == 0:
+        inter = N // 2
+        act = torch.full((M, inter), float("nan"), device=cuda)
+        from camelid_b200.parts.linear import pack_gate_up
+        packed = pack_gate_up(w[:inter].contiguous(), w[inter:].contiguous(), 16)
+        ops.gemm_tn_simt(a, packed, act, ops.EPI_SWIGLU, 16)
+        gate, up = ref[:, :inter], ref[:, inter:]
+        assert rel_err(act.cpu(), (gate / (1 + torch.exp(-gate))) * up) <= 2e-6
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M,inter,K,group", [(3, 48, 40, 16), (66, 136, 72, 136), (9, 160, 64, 16)])
 def test_gemm_swiglu_and_packing(cuda, dtype, M, inter, K, group):
