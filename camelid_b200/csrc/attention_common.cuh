@@ -23,6 +23,7 @@ struct AttnParams {
     float scale;
     float* partial;
     int* tickets;       // one zeroed counter per block column (tile, kv head chunk), or null
+    int n_stages;       // float kernel: pages of keys and values a block keeps in shared memory (set by its launcher)
 };
 
 // Merge of the key ranges: out = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s, the

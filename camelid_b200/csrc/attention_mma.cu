@@ -814,7 +814,7 @@ extern "C" int cml_attn_paged_mma(const void* q, int q_stride, void* out, int ou
     p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.seq_row0 = seq_row0; p.seq_start = seq_start; p.seq_new = seq_new;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
     p.rows_per_tile = rows_per_tile; p.heads_per_cta = heads_per_cta; p.head_chunks = head_chunks;
-    p.n_splits = n_splits; p.window = window; p.scale = scale; p.partial = partial; p.tickets = tickets;
+    p.n_splits = n_splits; p.window = window; p.scale = scale; p.partial = partial; p.tickets = tickets; p.n_stages = 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 64) return launch_mma<64>(p, n_tiles, n_rows, s);
     if (head_dim == 128) return launch_mma<128>(p, n_tiles, n_rows, s);

@@ -13,20 +13,53 @@
 // Work split: one block handles `rows_per_tile` consecutive new tokens of one sequence,
 // `heads_per_cta` query heads of one kv head, and one contiguous range of key pages
 // (`n_splits` ranges; partial results are merged by attn_combine_kernel). One warp owns one
-// (token, head) pair; the block shares each key/value page through shared memory.
+// (token, head) pair; the block shares each key/value page through shared memory, two pages
+// deep: the next page is fetched while the warps work on this one.
 #include "attention_common.cuh"
+
+__device__ __forceinline__ void cp_async16_f(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_f() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait_f() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// One page of keys and values into a stage of shared memory. Keys lie in rows of hd floats whose
+// 16-byte chunks are exchanged by the row number (chunk c of row j at c ^ (j & mask)), so that the
+// lanes of a warp, each reading its own key row, meet different banks without padding; values lie
+// as they are. Float pages come by cp.async (the next page is on its way while this one is worked
+// on); other types are converted on the way.
+template <typename T>
+__device__ __forceinline__ void attn_stage_page(float* Ks, float* Vs, const T* kp, const T* vp, size_t base, int hd, int mask) {
+    const int chunks = hd >> 2;
+    for (int idx = threadIdx.x; idx < CML_PAGE * chunks; idx += blockDim.x) {
+        const int j = idx / chunks, c = idx - j * chunks;
+        float* kd = Ks + ((size_t)j * chunks + (c ^ (j & mask))) * 4;
+        float* vd = Vs + (size_t)idx * 4;
+        if (sizeof(T) == 4) {
+            cp_async16_f(kd, reinterpret_cast<const float*>(kp) + base + (size_t)idx * 4);
+            cp_async16_f(vd, reinterpret_cast<const float*>(vp) + base + (size_t)idx * 4);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                kd[e] = to_f32(kp[base + (size_t)idx * 4 + e]);
+                vd[e] = to_f32(vp[base + (size_t)idx * 4 + e]);
+            }
+        }
+    }
+}
 
 template <typename T, int NACC>
 __global__ void attn_paged_simt_kernel(AttnParams p) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     pdl_wait();
     pdl_launch_dependents();
     const int hd = p.head_dim;
-    const int kstride = hd + 1;
+    const int chunks = hd >> 2;
+    const int mask = (chunks & 7) == 0 ? 7 : 3;
     const int n_warps = blockDim.x >> 5;
-    float* Ks = smem;                          // [PAGE][hd + 1]
-    float* Vs = Ks + CML_PAGE * kstride;       // [PAGE][hd]
-    float* Qs = Vs + CML_PAGE * hd;            // [warps][hd]
+    const int stage_floats = 2 * CML_PAGE * hd;          // keys, then values
+    const int n_stages = p.n_stages;                     // 2, or 1 where two pages of this head size do not fit
+    float* Qs = smem + n_stages * stage_floats;          // [warps][hd]
     float* Ps = Qs + n_warps * hd;             // [warps][PAGE]
 
     const int tile = blockIdx.x;
@@ -67,56 +100,79 @@ __global__ void attn_paged_simt_kernel(AttnParams p) {
 
     const T* kp = (const T*)p.k_pages;
     const T* vp = (const T*)p.v_pages;
-    for (int b = sb; b < se; ++b) {
+    auto page_base = [&](int b) {
         const int page = p.block_table[(size_t)seq * p.max_blocks + b];
-        const size_t base = ((size_t)page * p.n_kv_heads + kvh) * CML_PAGE * hd;
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < CML_PAGE * hd; idx += blockDim.x) {
-            const int j = idx / hd, d = idx - j * hd;
-            const bool live = (b * CML_PAGE + j) < kend;          // rows past the end may hold anything
-            Ks[j * kstride + d] = live ? to_f32(kp[base + idx]) : 0.f;
-            Vs[idx] = live ? to_f32(vp[base + idx]) : 0.f;
+        return ((size_t)page * p.n_kv_heads + kvh) * CML_PAGE * hd;
+    };
+    if (n_stages == 2 && sb < se) attn_stage_page<T>(smem, smem + CML_PAGE * hd, kp, vp, page_base(sb), hd, mask);
+    cp_async_commit_f();
+    for (int b = sb; b < se; ++b) {
+        float* Ks = smem + (n_stages == 2 ? ((b - sb) & 1) * stage_floats : 0);
+        float* Vs = Ks + CML_PAGE * hd;
+        if (n_stages == 2) {
+            if (b + 1 < se) {          // the other stage was read in the round before; all warps are past it
+                float* Kn = smem + ((b + 1 - sb) & 1) * stage_floats;
+                attn_stage_page<T>(Kn, Kn + CML_PAGE * hd, kp, vp, page_base(b + 1), hd, mask);
+            }
+            cp_async_commit_f();
+            cp_async_wait_f<1>();
+        } else {
+            attn_stage_page<T>(Ks, Vs, kp, vp, page_base(b), hd, mask);
+            cp_async_commit_f();
+            cp_async_wait_f<0>();
         }
         __syncthreads();
-        if (!valid) continue;
-        const int k0 = b * CML_PAGE + lane, k1 = k0 + 32;
-        const float* qv = Qs + warp * hd;
-        const float* ka = Ks + lane * kstride;
-        const float* kb = Ks + (lane + 32) * kstride;
-        float s0 = 0.f, s1 = 0.f;
-        for (int d = 0; d < hd; ++d) {
-            const float qd = qv[d];
-            s0 = fmaf(qd, ka[d], s0);
-            s1 = fmaf(qd, kb[d], s1);
+        const int live_rows = kend - b * CML_PAGE;                  // rows past the end may hold anything:
+        if (live_rows < CML_PAGE) {                                 // their values must not meet a zero probability
+            for (int idx = threadIdx.x + live_rows * hd; idx < CML_PAGE * hd; idx += blockDim.x) Vs[idx] = 0.f;
+            __syncthreads();
         }
-        const bool in0 = (k0 >= lo) && (k0 <= pos), in1 = (k1 >= lo) && (k1 <= pos);
-        s0 = in0 ? s0 * p.scale : -CUDART_INF_F;
-        s1 = in1 ? s1 * p.scale : -CUDART_INF_F;
-        const float bm = warp_max(fmaxf(s0, s1));
-        if (bm == -CUDART_INF_F) continue;                         // no visible key in this page
-        const float mn = fmaxf(m, bm);
-        const float corr = (m == -CUDART_INF_F) ? 0.f : expf(m - mn);
-        const float p0 = in0 ? expf(s0 - mn) : 0.f;
-        const float p1 = in1 ? expf(s1 - mn) : 0.f;
-        l = l * corr + warp_sum(p0 + p1);
+        if (valid) {
+            const int k0 = b * CML_PAGE + lane, k1 = k0 + 32;
+            const float4* q4 = reinterpret_cast<const float4*>(Qs + warp * hd);
+            const float4* ka = reinterpret_cast<const float4*>(Ks) + (size_t)lane * chunks;
+            const float4* kb = reinterpret_cast<const float4*>(Ks) + (size_t)(lane + 32) * chunks;
+            const int x0 = lane & mask, x1 = (lane + 32) & mask;
+            float s0 = 0.f, s1 = 0.f;
+            for (int c = 0; c < chunks; ++c) {
+                const float4 qq = q4[c];
+                const float4 a = ka[c ^ x0], bb = kb[c ^ x1];
+                s0 = fmaf(qq.x, a.x, s0); s0 = fmaf(qq.y, a.y, s0); s0 = fmaf(qq.z, a.z, s0); s0 = fmaf(qq.w, a.w, s0);
+                s1 = fmaf(qq.x, bb.x, s1); s1 = fmaf(qq.y, bb.y, s1); s1 = fmaf(qq.z, bb.z, s1); s1 = fmaf(qq.w, bb.w, s1);
+            }
+            const bool in0 = (k0 >= lo) && (k0 <= pos), in1 = (k1 >= lo) && (k1 <= pos);
+            s0 = in0 ? s0 * p.scale : -CUDART_INF_F;
+            s1 = in1 ? s1 * p.scale : -CUDART_INF_F;
+            const float bm = warp_max(fmaxf(s0, s1));
+            if (bm != -CUDART_INF_F) {                                  // a visible key in this page
+                const float mn = fmaxf(m, bm);
+                const float corr = (m == -CUDART_INF_F) ? 0.f : expf(m - mn);
+                const float p0 = in0 ? expf(s0 - mn) : 0.f;
+                const float p1 = in1 ? expf(s1 - mn) : 0.f;
+                l = l * corr + warp_sum(p0 + p1);
 #pragma unroll
-        for (int i = 0; i < NACC; ++i) acc[i] *= corr;
-        float* pw = Ps + warp * CML_PAGE;
-        pw[lane] = p0;
-        pw[lane + 32] = p1;
-        __syncwarp();
-        for (int j = 0; j < CML_PAGE; ++j) {
-            const float pj = pw[j];
-            const float* vr = Vs + j * hd;
+                for (int i = 0; i < NACC; ++i) acc[i] *= corr;
+                float* pw = Ps + warp * CML_PAGE;
+                pw[lane] = p0;
+                pw[lane + 32] = p1;
+                __syncwarp();
+                const int jend = min(CML_PAGE, live_rows);
+                for (int j = 0; j < jend; ++j) {
+                    const float pj = pw[j];
+                    const float* vr = Vs + j * hd;
 #pragma unroll
-            for (int i = 0; i < NACC; ++i) {
-                const int d = lane + 32 * i;
-                if (d < hd) acc[i] = fmaf(pj, vr[d], acc[i]);
+                    for (int i = 0; i < NACC; ++i) {
+                        const int d = lane + 32 * i;
+                        if (d < hd) acc[i] = fmaf(pj, vr[d], acc[i]);
+                    }
+                }
+                __syncwarp();
+                m = mn;
             }
         }
-        __syncwarp();
-        m = mn;
+        __syncthreads();               // this stage is free for the page after the next
     }
+    cp_async_wait_f<0>();
     if (!valid) return;
     if (p.n_splits == 1) {
         T* o = (T*)p.out + (size_t)row * p.out_stride + head * hd;
@@ -141,12 +197,15 @@ __global__ void attn_paged_simt_kernel(AttnParams p) {
 }
 
 template <typename T>
-static int launch_attn(const AttnParams& p, int n_tiles, int n_rows, cudaStream_t s) {
-    const int hd = p.head_dim;
-    const int warps = p.rows_per_tile * p.heads_per_cta;
+static int launch_attn(const AttnParams& p_in, int n_tiles, int n_rows, cudaStream_t s) {
+    const int hd = p_in.head_dim;
+    const int warps = p_in.rows_per_tile * p_in.heads_per_cta;
     if (warps < 1 || warps > 32) return CML_ERR_BAD_SIZE;
-    const size_t smem = ((size_t)CML_PAGE * (hd + 1) + (size_t)CML_PAGE * hd + (size_t)warps * hd +
-                         (size_t)warps * CML_PAGE) * sizeof(float);
+    const size_t rest = ((size_t)warps * hd + (size_t)warps * CML_PAGE) * sizeof(float);
+    const size_t stage = (size_t)2 * CML_PAGE * hd * sizeof(float);
+    AttnParams p = p_in;
+    p.n_stages = 2 * stage + rest <= 200 * 1024 ? 2 : 1;
+    const size_t smem = p.n_stages * stage + rest;
     if (smem > 227 * 1024) return CML_ERR_BAD_SIZE;
     const int nacc = (hd + 31) / 32;
     dim3 grid(n_tiles, p.n_kv_heads * p.head_chunks, p.n_splits);
@@ -182,7 +241,8 @@ extern "C" int cml_attn_paged_simt(const void* q, int q_stride, void* out, int o
                                    int head_dim, int rows_per_tile, int heads_per_cta, int head_chunks, int n_splits,
                                    int window, float scale, float* partial, void* stream) {
     if (n_tiles <= 0 || n_rows <= 0) return 0;
-    if (head_dim <= 0 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return CML_ERR_BAD_SIZE;
+    if (head_dim <= 0 || head_dim > 256 || (head_dim & 15) || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return CML_ERR_BAD_SIZE;
+    if (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) return CML_ERR_BAD_ALIGN;
     if (n_splits < 1 || (n_splits > 1 && partial == nullptr)) return CML_ERR_BAD_SIZE;
     if (heads_per_cta * head_chunks < n_heads / n_kv_heads) return CML_ERR_BAD_SIZE;
     AttnParams p;
@@ -191,7 +251,7 @@ extern "C" int cml_attn_paged_simt(const void* q, int q_stride, void* out, int o
     p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.seq_row0 = seq_row0; p.seq_start = seq_start; p.seq_new = seq_new;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;
     p.rows_per_tile = rows_per_tile; p.heads_per_cta = heads_per_cta; p.head_chunks = head_chunks;
-    p.n_splits = n_splits; p.window = window; p.scale = scale; p.partial = partial; p.tickets = nullptr;
+    p.n_splits = n_splits; p.window = window; p.scale = scale; p.partial = partial; p.tickets = nullptr; p.n_stages = 2;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == CML_DTYPE_F32) return launch_attn<float>(p, n_tiles, n_rows, s);
     if (dtype == CML_DTYPE_BF16) return launch_attn<bf16>(p, n_tiles, n_rows, s);

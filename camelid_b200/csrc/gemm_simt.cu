@@ -312,7 +312,11 @@ gemv_f32_stream_kernel(const float* __restrict__ A, int lda, const float* __rest
     }
 }
 
-// Scratch the streaming form needs for a product: tickets (ints, kept zero) first, then the splits' sums.
+// Scratch the streaming form needs: tickets (ints, kept zero) in a first part of fixed size, which products of
+// every shape share, then the splits' sums. K is split only where there are fewer than 3 * SMs tiles, and a
+// step has at most 4 groups of 8 rows; a K beyond 2,048 columns is split whatever the tiles (an output head
+// over a wide model). GV_TICKETS tickets cover half a million weight rows at four groups; more are refused.
+#define GV_TICKETS 65536
 static int gemv_stream_splits(int n_wrows, int K) {
     const int tiles = (n_wrows + GV_ROWS - 1) / GV_ROWS;
     int splits = (3 * cml_sm_count() + tiles - 1) / tiles;          // about three blocks per SM
@@ -325,8 +329,7 @@ extern "C" long cml_gemv_f32_scratch_bytes(int M, int N, int K, int epilogue) {
     const int n_wrows = epilogue == EPI_SWIGLU ? 2 * N : N;
     const int tiles = (n_wrows + GV_ROWS - 1) / GV_ROWS, groups = (M + 7) / 8;
     const int splits = gemv_stream_splits(n_wrows, K);
-    const long ticket_bytes = ((long)tiles * groups * sizeof(int) + 255) / 256 * 256;
-    return ticket_bytes + (splits > 1 ? (long)tiles * groups * splits * 8 * GV_ROWS * sizeof(float) : 0);
+    return (long)GV_TICKETS * sizeof(int) + (splits > 1 ? (long)tiles * groups * splits * 8 * GV_ROWS * sizeof(float) : 0);
 }
 
 static int launch_gemv_f32_stream(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
@@ -338,9 +341,9 @@ static int launch_gemv_f32_stream(const void* A, int lda, const void* W, int ldw
     const int kc = ((K + splits - 1) / splits + 127) / 128 * 128;
     const int n_splits = (K + kc - 1) / kc;
     const size_t smem = (size_t)max(MB * kc, MB * GV_ROWS) * sizeof(float);
-    const long ticket_bytes = ((long)tiles * groups * sizeof(int) + 255) / 256 * 256;
+    if (n_splits > 1 && (long)tiles * groups > GV_TICKETS) return CML_ERR_BAD_SIZE;
     int* tickets = (int*)scratch;
-    float* sums = (float*)((char*)scratch + ticket_bytes);
+    float* sums = (float*)((char*)scratch + (size_t)GV_TICKETS * sizeof(int));
     dim3 grid(tiles, n_splits, groups);
     cudaError_t e;
 #define CML_GEMVS(E)                                                                                                   \

@@ -134,8 +134,8 @@ class GroupedQueryAttention(Part):
         unit = 8 * 32 if tensor_cores else PAGE               # keys a block should at least have
         if tensor_cores:
             per_sm = 2 if self.head_dim <= 64 else 1          # blocks that run at the same time on an SM
-        else:                                                 # the float kernel keeps one page of keys and values
-            per_sm = max(1, min(8, (200 * 1024) // (4 * PAGE * (2 * self.head_dim + 1) + 4096)))
+        else:                                                 # the float kernel keeps two pages of keys and values
+            per_sm = max(1, min(8, (200 * 1024) // (16 * PAGE * self.head_dim + 4096)))
         resident = per_sm * ops.sm_count(ctx.device)
         return max(1, min((keys + unit - 1) // unit, resident // ctas, 64))
 

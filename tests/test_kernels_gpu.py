@@ -97,6 +97,11 @@ def test_gemv_float_streaming_form(cuda, M, N, K):
     one = torch.empty(1, N, device=cuda)
     ops.gemm_tn_simt(a[M - 1:], w, one, ops.EPI_STORE_F32)
     assert torch.equal(one[0], c[M - 1]), "a row alone differs from the same row in a step of several"
+    # products of other shapes share the scratch: their sums must not land on this one's tickets
+    other = torch.randn(8, 4096, generator=g).to(cuda)
+    ops.gemm_tn_simt(other, torch.randn(64, 4096, generator=g).to(cuda), torch.empty(8, 64, device=cuda), ops.EPI_STORE_F32)
+    ops.gemm_tn_simt(a, w, c, ops.EPI_STORE_F32)
+    assert rel_err(c.cpu(), ref) <= 2e-6
     if N % 32 == 0:
         inter = N // 2
         act = torch.full((M, inter), float("nan"), device=cuda)
