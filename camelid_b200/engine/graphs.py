@@ -158,3 +158,55 @@ class DecodeGraph:
                                      self.launches))
             done += k
         return np.concatenate(out) if len(out) > 1 else out[0]
+
+
+class StepGraph:
+    """A captured step of one layout with several tokens per sequence (prompts, chunks): the
+    launches of such a step depend on the numbers of tokens, wanted places and block-table
+    widths only, everything else reaches the kernels through the step's integer buffer. The step
+    in which the layout comes back is run eagerly on this graph's own static buffers and then
+    captured; later steps of the layout copy their integers and replay."""
+
+    def __init__(self, model, cache, layout):
+        dev = model.device
+        self.model = model
+        self.rows = layout.n_rows
+        meta = torch.zeros(layout.total, dtype=torch.int32, device=dev)
+        self.ctx = StepContext(cache=cache, workspace=Workspace(dev), dtype=model.dtype, device=dev, layout=layout,
+                               meta_dev=meta, options=model.options)
+        self.host = [torch.zeros(layout.total, dtype=torch.int32).pin_memory() for _ in range(_RING)]
+        self.events = [None] * _RING
+        self.turn = 0
+        self.graph = None
+        self.logits = None
+        self.launches = 0
+
+    def load(self, host_vec, slots, starts, news, row0) -> int:
+        """The step's integers into the static buffer (one copy from pinned memory)."""
+        i = self.turn
+        self.turn = (self.turn + 1) % _RING
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        self.host[i].numpy()[:] = host_vec
+        self.ctx.meta_dev.copy_(self.host[i], non_blocking=True)
+        ev = self.events[i] or torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+        self.ctx._set_host(slots, starts, news, row0)
+        return host_vec.nbytes
+
+    def run_and_capture(self) -> torch.Tensor:
+        """This step for real, on the static buffers; then the capture (which runs nothing)."""
+        out = self.model.run(self.ctx)
+        before = ops.launch_count()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.logits = self.model.run(self.ctx)
+        self.launches = ops.launch_count() - before
+        self.graph = g
+        return out
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        ops.add_launches(self.launches)
+        return self.logits.clone()          # the next replay writes the same buffer

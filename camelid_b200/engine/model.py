@@ -78,6 +78,12 @@ class DecoderModel:
         self.use_graphs = all(b.graph_safe for b in self.blocks) and all(
             p.graph_safe for p in (self.embedding, self.final_norm, self.head))
         self._graphs = weakref.WeakKeyDictionary()      # cache -> {(sequences, widths, feed): DecodeGraph}
+        # steps of several tokens per sequence: layouts seen once, and the graphs of those seen again
+        self.capture_steps = (self.use_graphs and self.options.capture_repeated_steps
+                              and all(b.graph_safe_any_step for b in self.blocks)
+                              and all(p.graph_safe_any_step for p in (self.embedding, self.final_norm, self.head)))
+        self._seen_layouts = weakref.WeakKeyDictionary()   # cache -> {key: times seen}
+        self._step_graphs = weakref.WeakKeyDictionary()    # cache -> {key: StepGraph}, oldest first
 
     # ---- construction ----
     @classmethod
@@ -192,15 +198,53 @@ class DecoderModel:
         if self.use_graphs and all(a.size == 1 and list(e.want) == [0] for e, a in zip(entries, arrays)):
             return self._graph_step(cache, entries)
         starts = [cache.book.extend(e.slot, a.size) for e, a in zip(entries, arrays)]
-        ctx = StepContext.for_step(cache=cache, workspace=self.workspace, dtype=self.dtype, device=self.device,
-                                   slots=[e.slot for e in entries], starts=starts, tokens=arrays,
-                                   want=[[int(w) for w in e.want] for e in entries], tile_sizes=self.tile_sizes,
-                                   options=self.options)
-        logits = self.run(ctx)
+        slots = [e.slot for e in entries]
+        want = [[int(w) for w in e.want] for e in entries]
+        logits = None
+        if self.capture_steps and max(a.size for a in arrays) > 1:
+            logits = self._captured_step(cache, slots, starts, arrays, want)
+        if logits is None:
+            ctx = StepContext.for_step(cache=cache, workspace=self.workspace, dtype=self.dtype, device=self.device,
+                                       slots=slots, starts=starts, tokens=arrays, want=want, tile_sizes=self.tile_sizes,
+                                       options=self.options)
+            logits = self.run(ctx)
+            self.last_h2d_bytes = ctx.h2d_bytes
         for e, a in zip(entries, arrays):
             cache.book.commit(e.slot, a.size)
-        self.last_h2d_bytes = ctx.h2d_bytes
         return logits
+
+    def _captured_step(self, cache, slots, starts, arrays, want):
+        """The step through a captured graph if its layout was seen before (None: run it eagerly).
+        The layout is what the launches depend on: tokens per sequence, the number of wanted
+        places and the block-table widths."""
+        from .graphs import StepGraph
+        book = cache.book
+        tables = [book.block_table(g, slots) for g in range(len(book.kv_specs))]
+        key = (tuple(int(a.size) for a in arrays), sum(len(w) for w in want), tuple(len(t[0]) for t in tables))
+        graphs = self._step_graphs.setdefault(cache, {})
+        graph = graphs.get(key)
+        if graph is None:
+            seen = self._seen_layouts.setdefault(cache, {})
+            seen[key] = seen.get(key, 0) + 1
+            if seen[key] < 2:
+                if len(seen) > 4096:
+                    seen.clear()
+                return None
+        layout, host, news, row0 = StepContext.host_arrays(slots, starts, arrays, want, tables, self.tile_sizes)
+        if graph is None:
+            rows = sum(news)
+            if rows > self.options.captured_step_rows:
+                return None
+            while graphs and sum(g.rows for g in graphs.values()) + rows > self.options.captured_step_rows:
+                del graphs[next(iter(graphs))]                  # the oldest layout makes room
+            graph = StepGraph(self, cache, layout)
+            self.last_h2d_bytes = graph.load(host, slots, starts, news, row0)
+            logits = graph.run_and_capture()
+            graphs[key] = graph
+            return logits
+        graphs[key] = graphs.pop(key)                           # most recently used last
+        self.last_h2d_bytes = graph.load(host, slots, starts, news, row0)
+        return graph.replay()
 
     def decode_graph(self, cache: SequenceCache, slots: list, feed: bool = False):
         """The captured graph for one-token steps of these slots (made at its first use)."""
@@ -272,10 +316,11 @@ class DecoderModel:
     def drop_graphs(self, cache=None) -> None:
         """Forget the captured graphs of one cache, or all. (A cache that is no longer referenced
         takes its graphs with it: they are kept per cache and hold no reference to it.)"""
-        if cache is None:
-            self._graphs.clear()
-        else:
-            self._graphs.pop(cache, None)
+        for kept in (self._graphs, self._step_graphs, self._seen_layouts):
+            if cache is None:
+                kept.clear()
+            else:
+                kept.pop(cache, None)
 
     def _graph_step(self, cache: SequenceCache, entries: list) -> torch.Tensor:
         slots = [e.slot for e in entries]

@@ -27,8 +27,13 @@ class KernelOptions:
     decode_attention: str = "fused"
     # Kernels are launched with programmatic dependent launch.
     dependent_launch: bool = True
-    # Greedy requests without stop tokens decode with the token fed back on the device.
+    # Greedy requests decode with the token fed back on the device.
     feed_on_device: bool = True
+    # A step of several tokens per sequence whose layout (tokens per sequence, wanted places,
+    # block-table widths) was seen before replays a captured graph; this many rows of such
+    # layouts are kept at most (each keeps a workspace of its own), the oldest dropped first.
+    capture_repeated_steps: bool = True
+    captured_step_rows: int = 16384
 
     def __post_init__(self):
         if not 1 <= int(self.decode_rows) <= 128:

@@ -27,6 +27,7 @@ from .base import Part, TensorSpec, build_part, register_part, to_device
 @register_part("mixer", "attention")
 class GroupedQueryAttention(Part):
     graph_safe = True
+    graph_safe_any_step = True
     handles_pending = True
     accepts_row_scale = True
 

@@ -45,6 +45,9 @@ class Part:
     # reads of the step, no allocation that must outlive the call): such a part can run
     # inside a captured CUDA graph. Parts that do not say so make the model step eagerly.
     graph_safe: bool = False
+    # True if that also holds for steps that bring several tokens per sequence (prompts): a model
+    # whose parts all say so replays a captured graph for a step whose layout it has seen before.
+    graph_safe_any_step: bool = False
     # True if the part knows what built-in parts may leave on the context instead of adding it
     # into the residual stream at once (``ctx.pending``: split sums; ``ctx.deferred``: a product
     # not yet launched) and deals with both itself. The block settles the stream before every

@@ -32,6 +32,10 @@ class PreNormBlock(Part):
     def graph_safe(self):
         return all(p.graph_safe for p in self.parts())
 
+    @property
+    def graph_safe_any_step(self):
+        return all(p.graph_safe_any_step for p in self.parts())
+
     def cache_spec(self):
         return self.mixer.cache_spec()
 

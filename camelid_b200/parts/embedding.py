@@ -13,6 +13,7 @@ from .base import Part, TensorSpec, register_part, to_device
 @register_part("embedding", "embedding")
 class TokenEmbedding(Part):
     graph_safe = True
+    graph_safe_any_step = True
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
@@ -34,6 +35,7 @@ class TokenEmbedding(Part):
 class OutputProjection(Part):
     """logits = x W^T in float32, without bias, soft-cap or scale (src/inference.rs:4284-4290)."""
     graph_safe = True
+    graph_safe_any_step = True
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)

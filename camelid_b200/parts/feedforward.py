@@ -11,6 +11,7 @@ from .base import Part, TensorSpec, register_part, to_device
 @register_part("ffn", "swiglu")
 class SwiGLU(Part):
     graph_safe = True
+    graph_safe_any_step = True
     handles_pending = True
     accepts_row_scale = True
 

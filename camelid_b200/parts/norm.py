@@ -13,6 +13,7 @@ from .base import Part, TensorSpec, register_part, to_device
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
     graph_safe = True
+    graph_safe_any_step = True
     handles_pending = True
 
     def __init__(self, params, prefix=""):

@@ -42,6 +42,7 @@ def rotary_frequencies(rotary_dim: int, theta: float, scaling: dict | None) -> n
 @register_part("position", "rope")
 class RotaryEncoding(Part):
     graph_safe = True
+    graph_safe_any_step = True
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
@@ -60,6 +61,7 @@ class RotaryEncoding(Part):
 class NoPositionEncoding(Part):
     """Leaves q and k as they are: a rotary encoding of zero dimensions."""
     graph_safe = True
+    graph_safe_any_step = True
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)

@@ -163,3 +163,39 @@ def test_greedy_generation_fed_on_the_device(cuda, model_folders):
         for i, tok in enumerate(g):
             row = ref[len(p) - 1 + i]
             assert float(row.max() - row[tok]) <= 3e-2 * scale, f"token {i} of request with {len(p)} prompt tokens"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_d"])
+def test_a_layout_seen_again_replays_a_captured_step(cuda, model_folders, name, dtype):
+    """Steps of several tokens per sequence whose layout (tokens per sequence, wanted places, block
+    table widths) comes back run as a captured graph from the second time on: other tokens, other
+    slots and other starting positions must give their own logits, and a different layout in
+    between must not disturb them."""
+    import camelid_b200
+    from camelid_b200 import StepEntry
+    lm = camelid_b200.load(model_folders[name], dtype=dtype)
+    assert lm.model.capture_steps
+    vocab = CONFIGS[name]["vocab_size"]
+    cache = lm.new_cache(1024, max_slots=6)
+    lens = [37, 5, 64]
+    for rep in range(4):
+        if rep == 2:                                   # another layout in between, and a shift of the slots
+            extra = cache.alloc_slot()
+            ids = tokens(900, 21, vocab)
+            got = lm.step(cache, [StepEntry(extra, ids, [20])]).cpu()
+            assert_close(got, oracle(model_folders[name], ids)[20:], dtype, "the layout in between")
+        seqs = [tokens(700 + 10 * rep + i, n + 9, vocab) for i, n in enumerate(lens)]
+        slots = [cache.alloc_slot() for _ in seqs]
+        # a first chunk of 9 tokens each (its own layout), then the layout under test on top of it
+        lm.step(cache, [StepEntry(s, q[:9], []) for s, q in zip(slots, seqs)])
+        got = lm.step(cache, [StepEntry(s, q[9:], [0, len(q) - 10]) for s, q in zip(slots, seqs)]).cpu()
+        for i, q in enumerate(seqs):
+            ref = oracle(model_folders[name], q)
+            assert_close(got[2 * i:2 * i + 2], ref[[9, len(q) - 1]], dtype, f"{name} round {rep} request {i}")
+        for s in slots:
+            cache.free_slot(s)
+    graphs = lm.model._step_graphs[cache]
+    assert ((37, 5, 64), 6, (2,)) in graphs and ((9, 9, 9), 0, (1,)) in graphs, list(graphs)
+    lm.model.check_device_errors()
+    cache.book.audit()
