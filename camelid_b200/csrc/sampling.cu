@@ -42,15 +42,25 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int ld, int
     pdl_launch_dependents();
     const int row = blockIdx.y;
     const float* r = logits + (size_t)row * ld;
-    const int per = (vocab + gridDim.x - 1) / gridDim.x;
-    const int begin = blockIdx.x * per, end = min(vocab, begin + per);
+    // parts of whole groups of four columns, so that aligned rows are read 16 bytes at a time
+    const int per = ((vocab + gridDim.x - 1) / gridDim.x + 3) & ~3;
+    const int begin = min(vocab, blockIdx.x * per), end = min(vocab, begin + per);
     unsigned long long best = 0ull;
     bool bad = false;
-    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-        const float v = r[i];
+    auto take = [&](float v, int i) {
         if (!isfinite(v)) bad = true;
         const unsigned long long key = composite_key(v, i);
         best = key > best ? key : best;
+    };
+    if ((((uintptr_t)r) & 15) == 0) {
+        const int end4 = begin + ((end - begin) & ~3);
+        for (int i = begin + 4 * threadIdx.x; i < end4; i += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(r + i);
+            take(v.x, i); take(v.y, i + 1); take(v.z, i + 2); take(v.w, i + 3);
+        }
+        for (int i = end4 + threadIdx.x; i < end; i += blockDim.x) take(r[i], i);
+    } else {
+        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) take(r[i], i);
     }
     if (bad) atomicOr(err, SAMPLE_ERR_NONFINITE);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -80,7 +90,8 @@ extern "C" int cml_argmax_rows(const float* logits, int ld, int rows, int vocab,
                                unsigned long long* scratch, void* stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0 || rows > 65535) return CML_ERR_BAD_SIZE;
-    const int blocks = max(1, min(64, vocab / 2048));
+    // enough blocks for two a multiprocessor over all rows, none with less than 2,048 columns
+    const int blocks = max(1, min(min(64, vocab / 2048), (2 * cml_sm_count() + rows - 1) / rows));
     launch_pdl(argmax_rows_kernel, dim3(blocks, rows), dim3(256), 0, (cudaStream_t)stream, logits, ld, vocab, out, err, scratch);
     return cml_launch_status();
 }
@@ -387,7 +398,7 @@ extern "C" int cml_argmax_rows_static(const float* logits, int ld, int rows, int
         refuse(msg, msg_len, "cml_argmax_rows_static: clearing the scratch words failed");
         return (int)e;
     }
-    const int blocks = max(1, min(64, vocab / 2048));
+    const int blocks = max(1, min(min(64, vocab / 2048), (2 * cml_sm_count() + rows - 1) / rows));
     argmax_rows_kernel<<<dim3(blocks, rows), 256, 0, s>>>(logits, ld, vocab, out, err, words);
     e = cudaGetLastError();
     if (e != cudaSuccess) refuse(msg, msg_len, "cml_argmax_rows_static: the kernel launch failed");
