@@ -6,6 +6,7 @@
     camelid replay --model DIR --dtype T --out DIR --max-tokens N     (bin/trace_run)
     camelid bench [--batch 8] [--prompt-tokens 2048] [--decode-steps 256] ...
     camelid random-model CONFIG.json OUT --seed S
+    camelid memory MODEL_OR_CONFIG --dtype T --max-tokens N [--max-slots S]     bytes of weights, cache, workspace
 
 Option names and meanings are the reference's where it has them: ``bench-generate MODEL
 --prompt-file --prompt --max-tokens (128) --temperature (0.0) --iterations (1) --warmup
@@ -59,6 +60,9 @@ def _generate_args(ap):
     ap.add_argument("--deterministic", action="store_true",
                     help="run the true 32-bit path (the same as --dtype float32)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--random", action="store_true",
+                    help="MODEL is a config.json: draw random weights for it on the device (see --weights-seed)")
+    ap.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights with --random")
 
 
 def cmd_generate(args, always_json=False) -> int:
@@ -66,7 +70,11 @@ def cmd_generate(args, always_json=False) -> int:
     from . import api
     t0 = time.perf_counter()
     dtype = "float32" if args.deterministic else args.dtype
-    lm = api.load(args.model, dtype=dtype)
+    if args.random:
+        with open(args.model) as f:
+            lm = api.from_random(json.load(f), args.weights_seed, dtype=dtype)
+    else:
+        lm = api.load(args.model, dtype=dtype)
     torch.cuda.synchronize()
     load_ms = (time.perf_counter() - t0) * 1e3
     prompts = read_prompts(args)
@@ -114,6 +122,18 @@ def cmd_random_model(args) -> int:
     return 0
 
 
+def cmd_memory(args) -> int:
+    from .memory import memory_plan
+    config = args.model
+    if config.endswith(".json"):
+        with open(config) as f:
+            config = json.load(f)
+    plan = memory_plan(config, args.dtype, args.max_tokens, args.max_slots)
+    print(json.dumps({**plan.as_dict(), "max_tokens": plan.max_tokens, "max_slots": plan.max_slots,
+                      "step_tokens": plan.step_tokens, "dtype": args.dtype}), flush=True)
+    return 0
+
+
 def cmd_bench(args) -> int:
     from . import benchmark
     if args.ablate and args.no_decode:
@@ -146,6 +166,11 @@ def main(argv=None) -> int:
     rm.add_argument("out", help="folder to write")
     rm.add_argument("--seed", type=int, default=0)
     rm.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    me = sub.add_parser("memory", help="bytes of weights, cache and workspace, without touching a device")
+    me.add_argument("model", help="model folder or config.json")
+    me.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    me.add_argument("--max-tokens", type=int, default=4096)
+    me.add_argument("--max-slots", type=int, default=None)
     be = sub.add_parser("bench", help="decode and prefill throughput with random weights")
     be.add_argument("--batch", type=int, default=8)
     be.add_argument("--prompt-tokens", type=int, default=2048)
@@ -174,6 +199,8 @@ def main(argv=None) -> int:
         return replay.run(args)
     if args.command == "random-model":
         return cmd_random_model(args)
+    if args.command == "memory":
+        return cmd_memory(args)
     if args.command == "bench":
         return cmd_bench(args)
     return 2
