@@ -136,7 +136,9 @@ class GroupedQueryAttention(Part):
         if tensor_cores:
             per_sm = 2 if self.head_dim <= 64 else 1          # blocks that run at the same time on an SM
         else:                                                 # the float kernel keeps two pages of keys and values
-            per_sm = max(1, min(8, (200 * 1024) // (16 * PAGE * self.head_dim + 4096)))
+            group = self.num_heads // self.num_kv_heads
+            smem = 4 * (4 * PAGE * self.head_dim + min(group, 16) * (self.head_dim + PAGE))
+            per_sm = max(1, min(8, (227 * 1024) // smem))
         resident = per_sm * ops.sm_count(ctx.device)
         return max(1, min((keys + unit - 1) // unit, resident // ctas, 64))
 
