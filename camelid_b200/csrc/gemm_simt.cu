@@ -98,6 +98,130 @@ gemm_tn_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, i
     }
 }
 
+// Many rows in float: tiles of 128 x 128 outputs, 256 threads with 8 x 8 outputs each, K in steps of 16
+// through two shared-memory buffers (the next step's operands are fetched into registers, 16 bytes at a
+// time, while this step is multiplied). Both operands are kept transposed in shared memory, so a thread
+// reads its 8 rows and 8 columns as two 16-byte pieces each. A thread's columns are two groups of four, 16
+// apart: on a packed gate/up matrix interleaved in groups of 16 those are four gate rows and the up rows
+// of the same outputs, so SwiGLU needs no second accumulator. Every output still sums k = 0..K-1 in order.
+// Needs K and the row strides in multiples of 4 floats and 16-byte aligned operands; other sizes and types
+// take the 64 x 64 kernel above.
+#define GB_M 128
+#define GB_N 128
+#define GB_K 16
+#define GB_LD (GB_M + 4)
+template <int EPI>
+__global__ void __launch_bounds__(256, 2)
+gemm_tn_f32_big_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw, float* __restrict__ C,
+                       int ldc, int M, int n_wrows, int K) {
+    __shared__ __align__(16) float As[2][GB_K][GB_LD];
+    __shared__ __align__(16) float Ws[2][GB_K][GB_LD];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * GB_M, n0 = blockIdx.x * GB_N;
+    // this thread's output columns within the tile: two groups of four, 16 apart
+    const int cg = (tx >> 2) * 32 + (tx & 3) * 4;
+    // the two 16-byte pieces of each operand tile this thread fetches per step
+    const int lrow0 = tid >> 2, lrow1 = lrow0 + 64, lkq = (tid & 3) * 4;
+    const float* a0p = A + (size_t)min(m0 + lrow0, M - 1) * lda + lkq;
+    const float* a1p = A + (size_t)min(m0 + lrow1, M - 1) * lda + lkq;
+    const float* w0p = W + (size_t)min(n0 + lrow0, n_wrows - 1) * ldw + lkq;
+    const float* w1p = W + (size_t)min(n0 + lrow1, n_wrows - 1) * ldw + lkq;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+    auto fetch = [&](int k0, float4& ra0, float4& ra1, float4& rw0, float4& rw1) {
+        const bool in = k0 + lkq < K;
+        ra0 = in ? *reinterpret_cast<const float4*>(a0p + k0) : zero;
+        ra1 = in ? *reinterpret_cast<const float4*>(a1p + k0) : zero;
+        rw0 = in ? *reinterpret_cast<const float4*>(w0p + k0) : zero;
+        rw1 = in ? *reinterpret_cast<const float4*>(w1p + k0) : zero;
+    };
+    auto stash = [&](int buf, const float4& ra0, const float4& ra1, const float4& rw0, const float4& rw1) {
+        As[buf][lkq + 0][lrow0] = ra0.x; As[buf][lkq + 1][lrow0] = ra0.y; As[buf][lkq + 2][lrow0] = ra0.z; As[buf][lkq + 3][lrow0] = ra0.w;
+        As[buf][lkq + 0][lrow1] = ra1.x; As[buf][lkq + 1][lrow1] = ra1.y; As[buf][lkq + 2][lrow1] = ra1.z; As[buf][lkq + 3][lrow1] = ra1.w;
+        Ws[buf][lkq + 0][lrow0] = rw0.x; Ws[buf][lkq + 1][lrow0] = rw0.y; Ws[buf][lkq + 2][lrow0] = rw0.z; Ws[buf][lkq + 3][lrow0] = rw0.w;
+        Ws[buf][lkq + 0][lrow1] = rw1.x; Ws[buf][lkq + 1][lrow1] = rw1.y; Ws[buf][lkq + 2][lrow1] = rw1.z; Ws[buf][lkq + 3][lrow1] = rw1.w;
+    };
+    float4 ra0, ra1, rw0, rw1;
+    fetch(0, ra0, ra1, rw0, rw1);
+    stash(0, ra0, ra1, rw0, rw1);
+    __syncthreads();
+    const int steps = (K + GB_K - 1) / GB_K;
+    for (int st = 0; st < steps; ++st) {
+        const int buf = st & 1;
+        if (st + 1 < steps) fetch((st + 1) * GB_K, ra0, ra1, rw0, rw1);
+#pragma unroll
+        for (int k = 0; k < GB_K; ++k) {
+            const float4 av0 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 8]);
+            const float4 av1 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 8 + 4]);
+            const float4 bv0 = *reinterpret_cast<const float4*>(&Ws[buf][k][cg]);
+            const float4 bv1 = *reinterpret_cast<const float4*>(&Ws[buf][k][cg + 16]);
+            const float av[8] = {av0.x, av0.y, av0.z, av0.w, av1.x, av1.y, av1.z, av1.w};
+            const float bv[8] = {bv0.x, bv0.y, bv0.z, bv0.w, bv1.x, bv1.y, bv1.z, bv1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        if (st + 1 < steps) {
+            stash(buf ^ 1, ra0, ra1, rw0, rw1);      // the other buffer was last read a step ago, before the barrier below
+            __syncthreads();
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = m0 + ty * 8 + i;
+        if (r >= M) continue;
+        if (EPI == EPI_SWIGLU) {
+            // columns cg..cg+3 are gate rows, cg+16.. the up rows of the same outputs (interleave groups of 16)
+            const int out0 = (n0 + cg - (tx & 3) * 4) / 2 + (tx & 3) * 4;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = out0 + j;
+                if (2 * c < n_wrows) {
+                    const float g = acc[i][j];
+                    C[(size_t)r * ldc + c] = (g / (1.0f + expf(-g))) * acc[i][j + 4];
+                }
+            }
+        } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int c = n0 + cg + 16 * h + j;
+                    if (c >= n_wrows) continue;
+                    float* o = C + (size_t)r * ldc + c;
+                    if (EPI == EPI_ADD_F32) *o += acc[i][4 * h + j];
+                    else *o = acc[i][4 * h + j];
+                }
+        }
+    }
+}
+
+static int launch_gemm_f32_big(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
+                               int epilogue, cudaStream_t s) {
+    const int n_wrows = epilogue == EPI_SWIGLU ? 2 * N : N;
+    dim3 grid((n_wrows + GB_N - 1) / GB_N, (M + GB_M - 1) / GB_M);
+    if (grid.y > 65535) return CML_ERR_BAD_SIZE;
+#define CML_GEMMB(E) launch_pdl(gemm_tn_f32_big_kernel<E>, grid, dim3(256), 0, s, (const float*)A, lda, (const float*)W, ldw, (float*)C, ldc, M, n_wrows, K)
+    switch (epilogue) {
+        case EPI_STORE:
+        case EPI_STORE_F32: CML_GEMMB(EPI_STORE_F32); break;
+        case EPI_ADD_F32: CML_GEMMB(EPI_ADD_F32); break;
+        case EPI_SWIGLU: CML_GEMMB(EPI_SWIGLU); break;
+        default: return CML_ERR_BAD_SIZE;
+    }
+#undef CML_GEMMB
+    return cml_launch_status();
+}
+
 // Few rows in float, the plain form (any K, any alignment, any interleave group): every output column is one warp's dot products, the weight row
 // read once with 16-byte loads and used for all MB activation rows, which stay in cache.
 // Each lane sums its k's in ascending order, then the lanes are summed in a fixed tree: the
@@ -415,6 +539,9 @@ extern "C" int cml_gemm_tn_simt(const void* A, int lda, const void* W, int ldw, 
         (epilogue != EPI_SWIGLU || (group == GV_ROWS / 2 && N % (GV_ROWS / 2) == 0)))
         return launch_gemv_f32_stream(A, lda, W, ldw, C, ldc, M, N, K, epilogue, scratch, s);
     if (dtype == CML_DTYPE_F32 && M <= 32) return launch_gemv_f32(A, lda, W, ldw, C, ldc, M, N, K, epilogue, group, s);
+    if (dtype == CML_DTYPE_F32 && M >= 64 && (K & 3) == 0 && (lda & 3) == 0 && (ldw & 3) == 0 &&
+        (((uintptr_t)A | (uintptr_t)W) & 15) == 0 && (epilogue != EPI_SWIGLU || (group == 16 && N % 16 == 0)))
+        return launch_gemm_f32_big(A, lda, W, ldw, C, ldc, M, N, K, epilogue, s);
     if (dtype == CML_DTYPE_F32) return launch_gemm<float>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, group, s);
     if (dtype == CML_DTYPE_BF16) return launch_gemm<bf16>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, group, s);
     return CML_ERR_BAD_DTYPE;

@@ -51,7 +51,8 @@ def test_rmsnorm(cuda, out_dtype, w_dtype, rows, hidden, eps):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("M,N,K", [(1, 40, 24), (70, 130, 200), (129, 64, 1030), (5, 517, 96)])
+@pytest.mark.parametrize("M,N,K", [(1, 40, 24), (70, 130, 200), (129, 64, 1030), (5, 517, 96), (300, 520, 136),
+                                   (2048, 384, 2048), (64, 129, 4), (257, 128, 20)])
 def test_gemm_simt_epilogues(cuda, dtype, M, N, K):
     from camelid_b200.csrc import ops
     a = torch.randn(M, K).to(DT[dtype]).to(cuda)
@@ -113,7 +114,8 @@ def test_gemv_float_streaming_form(cuda, M, N, K):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("M,inter,K,group", [(3, 48, 40, 16), (66, 136, 72, 136), (9, 160, 64, 16)])
+@pytest.mark.parametrize("M,inter,K,group", [(3, 48, 40, 16), (66, 136, 72, 136), (9, 160, 64, 16), (200, 160, 64, 16),
+                                             (129, 8192, 256, 16), (64, 16, 12, 16)])
 def test_gemm_swiglu_and_packing(cuda, dtype, M, inter, K, group):
     from camelid_b200.csrc import ops
     from camelid_b200.parts.linear import pack_gate_up
