@@ -149,10 +149,9 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 // Stages of the ring. Decode tiles (bn <= 64) with little work per block keep a small ring so
 // that several blocks fit an SM: the blocks of the next kernel then become resident while
 // this one still runs and prefetch their weights. Blocks that stream many k-blocks take a
-// deeper ring, but for tiles of 16 batch rows only 5 stages (90 KB, two blocks an SM): measured
-// at batch 8, the step takes 0.920 ms with 5 stages, 0.933 with 6, 0.94 with 10 and 0.958 with
-// 4: what is in flight matters less than the next product's blocks starting early. Tiles of 32
-// and 64 batch rows were slower with fewer stages than these.
+// deeper ring, but for tiles of 16 batch rows only 5 stages (90 KB, two blocks an SM): what is
+// in flight matters less there than the next product's blocks starting early; tiles of 32 and
+// 64 batch rows were slower with fewer stages than these. (The figures are in profiles/README.md.)
 __host__ __device__ constexpr int tc_stages(int bn, bool deep) {
     return bn >= 256 ? 4 : (bn >= 128 ? 6 : (deep ? (bn >= 64 ? 8 : (bn >= 32 ? 10 : 5)) : 4));
 }

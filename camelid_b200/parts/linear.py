@@ -123,9 +123,8 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
 def _pair_splits(rows: int, n: int, k: int, clusters: int) -> int:
     """Splits of K for a product on two-block tiles: more than 1 only for a deep product (K of
     4,096 or more) whose tiles leave half of the clusters or more without work; then as many as
-    fill them, of at least 16 k-blocks of 64. (Measured at 512 rows of the 1B shape: the down
-    product 53 -> 33 us with 4 splits, but a product of K = 2,048 gains less than the slower
-    kernels that then read its split sums cost.)"""
+    fill them, of at least 16 k-blocks of 64. A product of K = 2,048 gains less from a split
+    than the slower kernels that then read its split sums cost."""
     tiles = ((rows + 255) // 256) * ((n + 255) // 256)
     if 2 * tiles > clusters or k < 4096:
         return 1
