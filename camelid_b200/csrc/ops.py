@@ -66,6 +66,7 @@ _SIGNATURES = {
                                          c_int, c_float, c_int, c_float, c_float, ctypes.c_ulonglong, c_void_p, c_void_p],
     ("sampling", "cml_decode_fed_run"): [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    ("sampling", "cml_draws_at"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     ("sampling", "cml_sample_rows"): [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_void_p,
                                       c_void_p, c_void_p, c_void_p],
     ("random_fill", "cml_random_fill"): [c_void_p, c_int, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_ulonglong,
@@ -595,6 +596,16 @@ def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: flo
     _check(_fn("sampling", "cml_sample_rows")(_p(logits), logits.stride(0), rows, vocab, float(temperature),
                                              int(top_k or 0), float(top_p if top_p is not None else 1.0),
                                              float(min_p or 0.0), _p(draws), _p(out), _p(err), _stream()), "sample_rows")
+
+
+def draws_at(positions: torch.Tensor, seed: torch.Tensor, draws: torch.Tensor):
+    """draws[r] = the draw of the stream of ``seed`` (int64 [1] on the device) for a history of
+    positions[r] + 1 tokens: what ``sampling.options.unit_draw`` gives on the host."""
+    _dev(positions, seed, draws)
+    rows = draws.numel()
+    assert positions.dtype == torch.int32 and positions.numel() >= rows and seed.dtype == torch.int64
+    assert draws.dtype == torch.float32
+    _check(_fn("sampling", "cml_draws_at")(_p(positions), _p(seed), _p(draws), rows, _stream()), "draws_at")
 
 
 class NativeDecodeLoop:

@@ -318,6 +318,29 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SamplePa
     if (threadIdx.x == 0) out[blockIdx.x] = (int)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull));
 }
 
+// The draws of a step on the device: row r of a one-token step feeds the token at position
+// positions[r], so the history its next token is drawn for has positions[r] + 1 tokens, and the
+// draw is the reference's stream at that place: the top 24 bits of
+// splitmix64(seed + (length + 1) * golden) / 2^24 (src/inference.rs:6160-6180). The seed is read
+// from device memory, so one captured graph serves every seed.
+__global__ void draws_at_kernel(const int* __restrict__ positions, const unsigned long long* __restrict__ seed,
+                                float* __restrict__ draws, int rows) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    const unsigned long long length = (unsigned long long)(positions[r] + 1);
+    unsigned long long z = *seed + (length + 1ull) * 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z = z ^ (z >> 31);
+    draws[r] = (float)(z >> 40) / (float)(1u << 24);
+}
+
+extern "C" int cml_draws_at(const int* positions, const unsigned long long* seed, float* draws, int rows, void* stream) {
+    if (rows <= 0) return 0;
+    draws_at_kernel<<<(rows + 127) / 128, 128, 0, (cudaStream_t)stream>>>(positions, seed, draws, rows);
+    return cml_launch_status();
+}
+
 // draws[r] in [0, 1) is computed by the host from the seed and the length of the history.
 extern "C" int cml_sample_rows(const float* logits, int ld, int rows, int vocab, float temperature, int top_k,
                                float top_p, float min_p, const float* draws, int* out, int* err, void* stream) {

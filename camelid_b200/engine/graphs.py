@@ -54,6 +54,9 @@ class DecodeGraph:
         self.next_tokens = None
         self.launches = 0
         self._table_key = [None] * _RING
+        if feed and feed is not True:              # a sampling step: the seed lives on the device, any seed replays
+            self.seed = torch.zeros(1, dtype=torch.int64, device=dev)
+            self.draws = torch.zeros(n_seqs, dtype=torch.float32, device=dev)
 
     @property
     def cache(self):
@@ -90,8 +93,13 @@ class DecodeGraph:
 
     def _forward(self):
         logits = self.model.run(self.ctx)
-        if self.feed:
+        if self.feed is True:
             ops.argmax_rows(logits, self.ctx.tokens, self.model.logit_error_word())
+        elif self.feed:          # ("sample", temperature, top_k, top_p, min_p): the draw from the seed and the position
+            _kind, temperature, top_k, top_p, min_p = self.feed
+            ops.draws_at(self.ctx.row_pos, self.seed, self.draws)
+            ops.sample_rows(logits, temperature, top_k, top_p, min_p, self.draws, self.ctx.tokens,
+                            self.model.logit_error_word())
         return logits
 
     def capture(self):
@@ -138,11 +146,15 @@ class DecodeGraph:
         return loop.run(self.graph.raw_cuda_graph_exec(), tokens, starts, slots, history_lens, max_steps, stop_ids,
                         temperature, top_k, top_p, min_p, seed, self.launches)
 
-    def run_fed(self, slots: list, starts: list, tokens: list, steps: int):
-        """``steps`` greedy steps of a graph captured with ``feed``, queued at once by the C++ loop:
-        the device feeds itself, the host sends positions and reads the chosen tokens. Returns
-        the tokens [steps, sequences] as a numpy array."""
+    def run_fed(self, slots: list, starts: list, tokens: list, steps: int, seed: int = 0):
+        """``steps`` steps of a graph captured with ``feed`` (greedy, or sampling with the draws
+        made on the device from ``seed`` and each row's position), queued at once by the C++
+        loop: the device feeds itself, the host sends positions and reads the chosen tokens.
+        Returns the tokens [steps, sequences] as a numpy array."""
         assert self.feed
+        if self.feed is not True:
+            signed = int(seed) & ((1 << 64) - 1)
+            self.seed.fill_(signed - (1 << 64) if signed >= (1 << 63) else signed)
         i = self.fill(slots, starts, tokens)
         self.send(i, with_tokens=True)                  # block tables and the static arrays
         if self.graph is None:

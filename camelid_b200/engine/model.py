@@ -290,10 +290,12 @@ class DecoderModel:
             self._logit_err = torch.zeros(1, dtype=torch.int32, device=self.device)
         return self._logit_err
 
-    def decode_fed(self, cache: SequenceCache, slots: list, tokens: list, steps: int):
-        """Exactly ``steps`` greedy one-token steps of these sequences with the chosen token fed
-        back on the device: all steps are queued at once and the host waits once at the end.
-        Returns the tokens [steps][sequence] (numpy); the cache's lengths have moved by ``steps``."""
+    def decode_fed(self, cache: SequenceCache, slots: list, tokens: list, steps: int, sampling=None):
+        """Exactly ``steps`` one-token steps of these sequences with the chosen token fed back on the
+        device: all steps are queued at once and the host waits once at the end. ``sampling``
+        (``SamplingOptions`` without penalties or bias; None or temperature 0: greedy): the draws are
+        made on the device from the seed and each row's position, the same numbers the host would
+        draw. Returns the tokens [steps][sequence] (numpy); the cache's lengths have moved by ``steps``."""
         if not self.use_graphs:
             raise StepError("decoding with the token fed back on the device needs a model whose parts can run in a captured graph")
         if not self.loaded:
@@ -306,8 +308,15 @@ class DecoderModel:
         book = cache.book
         book.check_extend([(s, steps) for s in slots])
         starts = [book.extend(s, steps) for s in slots]
-        graph = self.decode_graph(cache, slots, feed=True)
-        out = graph.run_fed(slots, starts, [int(t) for t in tokens], steps)
+        feed, seed = True, 0
+        if sampling is not None and not sampling.greedy:
+            if sampling.adjusts:
+                raise StepError("penalties and biases need each request's history on the host: not in decode_fed")
+            feed = ("sample", float(sampling.temperature), int(sampling.top_k or 0),
+                    float(sampling.top_p if sampling.top_p is not None else 1.0), float(sampling.min_p or 0.0))
+            seed = int(sampling.seed or 0)
+        graph = self.decode_graph(cache, slots, feed=feed)
+        out = graph.run_fed(slots, starts, [int(t) for t in tokens], steps, seed)
         for s in slots:
             book.commit(s, steps)
         self.last_h2d_bytes = graph._fed.h2d_bytes_per_step
@@ -367,6 +376,7 @@ class DecoderModel:
         if self._logit_err is not None and int(self._logit_err.item()) != 0:
             self._logit_err.zero_()
             from ..errors import SamplingError
-            raise SamplingError("the logits of a greedy step contain a non-finite value")
+            raise SamplingError("the logits of a step that chose its tokens on the device contain a non-finite value "
+                                "(or its softmax sum was not a positive number)")
         from ..parts import linear
         linear.check_errors()

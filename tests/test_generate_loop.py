@@ -133,9 +133,9 @@ class FedModel(FakeModel):
         self.runs = []
 
     def decode_natively(self, *a, **k):
-        raise AssertionError("a greedy batch must take the fed loop")
+        raise AssertionError("a batch without penalties must take the fed loop")
 
-    def decode_fed(self, cache, slots, tokens, steps):
+    def decode_fed(self, cache, slots, tokens, steps, sampling=None):
         import numpy as np
         cache.book.check_extend([(s, steps) for s in slots])
         for s in slots:

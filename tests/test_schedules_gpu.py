@@ -199,3 +199,29 @@ def test_a_layout_seen_again_replays_a_captured_step(cuda, model_folders, name, 
     assert ((37, 5, 64), 6, (2,)) in graphs and ((9, 9, 9), 0, (1,)) in graphs, list(graphs)
     lm.model.check_device_errors()
     cache.book.audit()
+
+
+def test_sampled_generation_fed_on_the_device(cuda, model_folders):
+    """Temperature sampling (with top-k and top-p) also decodes with the token fed back on the
+    device: the draw of each step is made there from the seed and the row's position, the same
+    number the host makes, so the tokens are those of the loop that reads every token back, for two
+    seeds through one captured graph, and a request's tokens do not depend on its batch."""
+    import camelid_b200
+    from camelid_b200 import KernelOptions
+    name = "tiny_a"
+    prompts = [tokens(50 + i, n, CONFIGS[name]["vocab_size"]) for i, n in enumerate([5, 11, 1, 30])]
+    fed = camelid_b200.load(model_folders[name], dtype="float32")
+    unfed = camelid_b200.load(model_folders[name], dtype="float32", options=KernelOptions(feed_on_device=False))
+    runs = []
+    real = fed.model.decode_fed
+    fed.model.decode_fed = lambda *a, **k: (runs.append(a[3]), real(*a, **k))[1]
+    for kw in (dict(temperature=0.8, seed=1234), dict(temperature=1.3, top_k=40, top_p=0.9, seed=2 ** 63 + 11),
+               dict(temperature=0.7, min_p=0.05, seed=0)):
+        a = fed.generate(prompts, max_tokens=30, stop_token_ids=(), **kw)
+        b = unfed.generate(prompts, max_tokens=30, stop_token_ids=(), **kw)
+        assert a == b, kw
+        assert fed.generate(prompts[::-1], max_tokens=30, stop_token_ids=(), **kw) == a[::-1]
+    assert runs and all(r == 29 for r in runs)
+    cfg, w = pl.read_model(model_folders[name])
+    want = pl.generate(cfg, w, prompts[:2], 12, temperature=0.8, seed=1234, dtype=torch.float64)
+    assert fed.generate(prompts[:2], max_tokens=12, temperature=0.8, seed=1234, stop_token_ids=()) == want
