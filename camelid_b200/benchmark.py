@@ -291,19 +291,24 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
     rng = np.random.default_rng(shape["seed"])
     elem = 2 if dtype == "bfloat16" else 4
     flop_peak = (pk["bf16_tflops"] if dtype == "bfloat16" else FP32_TFLOPS) * 1e12
-    if prefill:
+    def timed_prefill():
+        if not prefill:
+            return {"value": None, "tokens": prefill_tokens, "ms": None, "frac": None}
         pre = measure_prefill(lm, cfg, prefill_tokens, rng)
         pre["frac"] = prefill_flops(cfg, prefill_tokens) / (pre["ms"] / 1e3) / flop_peak
-    else:
-        pre = {"value": None, "tokens": prefill_tokens, "ms": None, "frac": None}
+        return pre
     if not decode:
-        return {"prefill": pre, "dtype": dtype, "config": {"model": shape["name"], "layers": cfg["num_hidden_layers"]}}
+        return {"prefill": timed_prefill(), "dtype": dtype,
+                "config": {"model": shape["name"], "layers": cfg["num_hidden_layers"]}}
+    # The decode steps are timed first: seconds of dense prefill products put the GPU under its power cap,
+    # and the steps right behind them would be timed at the clocks that leaves.
     prompts = _prompts(rng, batch, prompt_range, cfg["vocab_size"]) if prompt_range else None
+    dec = measure_decode_device(lm, cfg, batch, prompt_tokens, decode_steps, warmup, rng, prompts=prompts)
+    pre = timed_prefill()
     pre_batch = None
     if prompts is not None and prefill:
         pre_batch = measure_prefill_batch(lm, cfg, prompts)
         pre_batch["frac"] = pre_batch.pop("flops") / (pre_batch["ms"] / 1e3) / flop_peak
-    dec = measure_decode_device(lm, cfg, batch, prompt_tokens, decode_steps, warmup, rng, prompts=prompts)
     roof = _roofline(cfg, batch, dec, elem, pk)
     e2e_steps = max(decode_steps, 128)
     rec = {
