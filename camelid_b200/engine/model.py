@@ -361,6 +361,8 @@ class DecoderModel:
             self.blocks[e.layer].forward(ctx, h)
         logits = torch.empty((ctx.n_want, self.vocab_size), dtype=torch.float32, device=self.device)
         if ctx.n_want:
+            if not self.final_norm.handles_pending:          # a norm from outside reads a settled stream
+                ctx.settle(h)
             x = self.final_norm.forward(ctx, h, rows_index=ctx.want_rows, n_rows=ctx.n_want, name="final_normed")
             self.head.forward(ctx, x, logits)
         ctx.pending = None

@@ -20,7 +20,7 @@ def _register_toys():
     from camelid_b200.cache import StateSpec
     from camelid_b200.config import LlamaConfig, ScheduleEntry, llama_plan, register_architecture
     from camelid_b200.config.plan import LayerSpec, PartSpec
-    from camelid_b200.parts import Part, TensorSpec, register_part
+    from camelid_b200.parts import Part, TensorSpec, build_part, register_part
 
     @register_part("mixer", "toy_running_sum")
     class RunningSum(Part):
@@ -146,6 +146,68 @@ def _register_toys():
         def load(self, tensors, device, dtype):
             self.inv_freq = (1.0 / (torch.arange(self.rotary_dim // 2, dtype=torch.float32) + 2.0)).to(device)
 
+    @register_part("norm", "toy_layernorm")
+    class ToyLayerNorm(Part):
+        """(x - mean) / sqrt(var + eps) * w: a norm from outside that knows nothing of pending sums
+        or of rows' scales (plain torch, so the model steps eagerly)."""
+
+        def __init__(self, params, prefix=""):
+            super().__init__(params, prefix)
+            self.hidden, self.eps = params["hidden_size"], params["eps"]
+
+        def tensor_specs(self):
+            return {self.prefix + "weight": TensorSpec((self.hidden,), "norm")}
+
+        def load(self, tensors, device, dtype):
+            self.w = tensors[self.prefix + "weight"].to(device=device, dtype=torch.float32)
+
+        def forward(self, ctx, h, rows_index=None, n_rows=None, name="normed", allow_row_scale=False):
+            x = h if rows_index is None else h[rows_index.long()[:n_rows]]
+            y = (x - x.mean(-1, keepdim=True)) / torch.sqrt(x.var(-1, unbiased=False, keepdim=True) + self.eps) * self.w
+            return y.to(ctx.dtype)
+
+    @register_part("block", "toy_parallel")
+    class ParallelBlock(Part):
+        """out = x + mixer(norm(x)) + ffn(norm(x)): both branches read the same normed rows."""
+
+        def __init__(self, layer_spec):
+            super().__init__({}, "")
+            self.norm = build_part("norm", layer_spec.norm1)
+            self.mixer = build_part("mixer", layer_spec.mixer)
+            self.ffn = build_part("ffn", layer_spec.ffn)
+
+        def tensor_specs(self):
+            return {**self.norm.tensor_specs(), **self.mixer.tensor_specs(), **self.ffn.tensor_specs()}
+
+        def load(self, tensors, device, dtype):
+            for part in (self.norm, self.mixer, self.ffn):
+                part.load(tensors, device, dtype)
+
+        @property
+        def graph_safe(self):
+            return self.norm.graph_safe and self.mixer.graph_safe and self.ffn.graph_safe
+
+        def cache_spec(self):
+            return self.mixer.cache_spec()
+
+        def query_tile_sizes(self):
+            return self.mixer.query_tile_sizes()
+
+        def forward(self, ctx, h):
+            ctx.settle(h)                       # what the layer before left pending
+            x = self.norm.forward(ctx, h).clone()          # the norm's buffer is reused by the next norm
+            self.mixer.forward(ctx, x, h)
+            ctx.settle(h)
+            self.ffn.forward(ctx, x, h)
+
+    def layernorm_parallel_plan(cfg):
+        base = llama_plan(cfg)
+        layers = list(base.layers)
+        ln = PartSpec("toy_layernorm", {"hidden_size": cfg.hidden_size, "eps": cfg.rms_norm_eps}, "model.layers.1.input_layernorm.")
+        layers[1] = dataclasses.replace(layers[1], arrangement="toy_parallel", norm1=ln)
+        final = PartSpec("toy_layernorm", {"hidden_size": cfg.hidden_size, "eps": cfg.rms_norm_eps}, "model.norm.")
+        return dataclasses.replace(base, layers=tuple(layers), final_norm=final)
+
     def routed_plan(cfg):
         base = llama_plan(cfg)
         layers = list(base.layers)
@@ -163,6 +225,7 @@ def _register_toys():
         return dataclasses.replace(base, layers=tuple(layers))
 
     register_architecture("ToyRoutedForCausalLM", LlamaConfig.from_dict, routed_plan)
+    register_architecture("ToyParallelForCausalLM", LlamaConfig.from_dict, layernorm_parallel_plan)
     register_architecture("ToyHarmonicForCausalLM", LlamaConfig.from_dict, harmonic_plan)
     register_architecture("ToyStateForCausalLM", LlamaConfig.from_dict, toy_plan)
     register_architecture("ToyDeviceSumForCausalLM", LlamaConfig.from_dict, device_sum_plan)
@@ -401,3 +464,41 @@ def test_graph_safe_mixer_from_outside_finds_its_state_by_slot(cuda, dtype):
         for i, tok in enumerate(gen):
             row = ref[len(prompt) - 1 + i]
             assert float(row.max() - row[tok]) <= (1e-4 if dtype == "float32" else 3e-2) * scale, (i, tok)
+
+
+@pytest.mark.parametrize("over", [{}, WIDE], ids=["head16", "head64"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_and_block_arrangement_of_their_own(cuda, dtype, over):
+    """A norm (mean-subtracting) and a block arrangement (attention and feed-forward in parallel on
+    the same normed rows) registered from outside, the norm also as the model's final norm: layer 0
+    is the library's own block and leaves its split sums pending, which the outside block and norm
+    never hear of."""
+    _register_toys()
+    cfg, model, w = _model("ToyParallelForCausalLM", dtype, seed=8, **over)
+    assert "model.layers.1.post_attention_layernorm.weight" not in w      # the arrangement decides which parts exist
+
+    def layernorm(x, weight):
+        return (x - x.mean(-1, keepdim=True)) / torch.sqrt(x.var(-1, unbiased=False, keepdim=True) + cfg["rms_norm_eps"]) * weight.double()
+
+    def plain(ids):
+        ids = torch.as_tensor(ids)
+        pos = torch.arange(len(ids))
+        fr = pl.rope_frequencies(cfg)
+        h = pl.embedding(ids, w["model.embed_tokens.weight"], torch.float64)
+        h, _ = pl.decoder_layer(h, w, 0, cfg, pos, fr)
+        p = "model.layers.1."
+        n = layernorm(h, w[p + "input_layernorm.weight"])
+        if dtype == "bfloat16":
+            n = n.to(torch.bfloat16).double()
+        a, _kv = pl.attention_block(n, w, p, cfg, pos, fr)
+        f = pl.swiglu(n, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+        h = h + a + f
+        n = layernorm(h, w["model.norm.weight"])
+        if dtype == "bfloat16":
+            n = n.to(torch.bfloat16).double()
+        return n @ pl.output_weight(cfg, w).double().T
+
+    seqs = [tokens(13, 70, 256), tokens(14, 33, 256), tokens(15, 66, 256)]
+    got = _drive(model, seqs, cut=[64, 3])
+    for i in range(3):
+        assert_close(got[i], plain(seqs[i]), dtype, f"layer norm and parallel block, request {i}")
