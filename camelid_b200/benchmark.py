@@ -442,9 +442,11 @@ def ablate_prefill(tokens: int = 2048, dtype: str = "bfloat16", layers: int | No
     place, with programmatic dependent launch overlapping its neighbours."""
     from . import api
     from .csrc import ops
+    from .options import KernelOptions
     shape = SHAPES[config_index]
     cfg = config_for(config_index, layers)
-    lm = api.from_random(cfg, seed=shape["seed"], dtype=dtype)
+    # every step launched eagerly: a captured step would replay the kernels it was captured with
+    lm = api.from_random(cfg, seed=shape["seed"], dtype=dtype, options=KernelOptions(capture_repeated_steps=False))
     rng = np.random.default_rng(0)
 
     def timed():
