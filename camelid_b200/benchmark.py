@@ -456,7 +456,8 @@ def ablate_prefill(tokens: int = 2048, dtype: str = "bfloat16", layers: int | No
         return None
 
     out = {"full": timed()}
-    for name in ("attn_prefill_tc", "attn_paged_mma", "rope_kv_write", "rmsnorm", "embed_gather"):
+    for name in ("attn_prefill_tc", "attn_paged_mma", "attn_paged_simt", "gemm_tn_simt", "rope_kv_write", "rmsnorm",
+                 "embed_gather"):
         real = getattr(ops, name)
         setattr(ops, name, noop)
         out["without " + name] = timed()

@@ -11,6 +11,7 @@
 // stream); SwiGLU, where output column j takes weight rows gate(j) and up(j) of a packed
 // [2*N, K] matrix interleaved in groups of `group` rows and stores silu(g) * u.
 #include "common.cuh"
+#include <cuda.h>
 
 #define GEMM_BM 64
 #define GEMM_BN 64
@@ -110,6 +111,10 @@ gemm_tn_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, i
 #define GB_N 128
 #define GB_K 16
 #define GB_LD (GB_M + 4)
+// Columns of the weight tile are kept with their 16-byte pieces permuted (piece p of the second half of every
+// 32 columns at p ^ 4), so that the eight lanes of a quarter warp, which read pieces {0..3, 8..11} (+4 for the
+// second group), touch eight different sets of four banks.
+__device__ __forceinline__ int gb_wcol(int c) { return c ^ (((c >> 5) & 1) << 4); }
 template <int EPI>
 __global__ void __launch_bounds__(256, 2)
 gemm_tn_f32_big_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw, float* __restrict__ C,
@@ -125,6 +130,8 @@ gemm_tn_f32_big_kernel(const float* __restrict__ A, int lda, const float* __rest
     const int cg = (tx >> 2) * 32 + (tx & 3) * 4;
     // the two 16-byte pieces of each operand tile this thread fetches per step
     const int lrow0 = tid >> 2, lrow1 = lrow0 + 64, lkq = (tid & 3) * 4;
+    const int wcol0 = gb_wcol(lrow0), wcol1 = gb_wcol(lrow1);
+    const int cg0 = gb_wcol(cg), cg1 = gb_wcol(cg + 16);
     const float* a0p = A + (size_t)min(m0 + lrow0, M - 1) * lda + lkq;
     const float* a1p = A + (size_t)min(m0 + lrow1, M - 1) * lda + lkq;
     const float* w0p = W + (size_t)min(n0 + lrow0, n_wrows - 1) * ldw + lkq;
@@ -146,8 +153,8 @@ gemm_tn_f32_big_kernel(const float* __restrict__ A, int lda, const float* __rest
     auto stash = [&](int buf, const float4& ra0, const float4& ra1, const float4& rw0, const float4& rw1) {
         As[buf][lkq + 0][lrow0] = ra0.x; As[buf][lkq + 1][lrow0] = ra0.y; As[buf][lkq + 2][lrow0] = ra0.z; As[buf][lkq + 3][lrow0] = ra0.w;
         As[buf][lkq + 0][lrow1] = ra1.x; As[buf][lkq + 1][lrow1] = ra1.y; As[buf][lkq + 2][lrow1] = ra1.z; As[buf][lkq + 3][lrow1] = ra1.w;
-        Ws[buf][lkq + 0][lrow0] = rw0.x; Ws[buf][lkq + 1][lrow0] = rw0.y; Ws[buf][lkq + 2][lrow0] = rw0.z; Ws[buf][lkq + 3][lrow0] = rw0.w;
-        Ws[buf][lkq + 0][lrow1] = rw1.x; Ws[buf][lkq + 1][lrow1] = rw1.y; Ws[buf][lkq + 2][lrow1] = rw1.z; Ws[buf][lkq + 3][lrow1] = rw1.w;
+        Ws[buf][lkq + 0][wcol0] = rw0.x; Ws[buf][lkq + 1][wcol0] = rw0.y; Ws[buf][lkq + 2][wcol0] = rw0.z; Ws[buf][lkq + 3][wcol0] = rw0.w;
+        Ws[buf][lkq + 0][wcol1] = rw1.x; Ws[buf][lkq + 1][wcol1] = rw1.y; Ws[buf][lkq + 2][wcol1] = rw1.z; Ws[buf][lkq + 3][wcol1] = rw1.w;
     };
     float4 ra0, ra1, rw0, rw1;
     fetch(0, ra0, ra1, rw0, rw1);
@@ -161,8 +168,8 @@ gemm_tn_f32_big_kernel(const float* __restrict__ A, int lda, const float* __rest
         for (int k = 0; k < GB_K; ++k) {
             const float4 av0 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 8]);
             const float4 av1 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 8 + 4]);
-            const float4 bv0 = *reinterpret_cast<const float4*>(&Ws[buf][k][cg]);
-            const float4 bv1 = *reinterpret_cast<const float4*>(&Ws[buf][k][cg + 16]);
+            const float4 bv0 = *reinterpret_cast<const float4*>(&Ws[buf][k][cg0]);
+            const float4 bv1 = *reinterpret_cast<const float4*>(&Ws[buf][k][cg1]);
             const float av[8] = {av0.x, av0.y, av0.z, av0.w, av1.x, av1.y, av1.z, av1.w};
             const float bv[8] = {bv0.x, bv0.y, bv0.z, bv0.w, bv1.x, bv1.y, bv1.z, bv1.w};
 #pragma unroll
@@ -307,182 +314,335 @@ gemv_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ 
     }
 }
 
-// Few rows in float, the form that streams weights: a block owns 32 consecutive weight rows and a
-// range of K; its activations (MB rows of that range) are staged in shared memory once and every
-// warp walks COLS weight rows at a time, so an activation read from shared memory serves COLS
-// dot products and each lane keeps 2 * COLS 16-byte weight loads in flight. The first weight
-// loads are issued before the wait on the previous kernel (weights do not depend on it). Where a
-// product has too few 32-row tiles for the SMs, K is split over gridDim.y: every block leaves
-// its sums in `scratch`, and the block that arrives last at the tile's ticket adds them in split
-// order and runs the epilogue. The order of summation is fixed by N and K alone: lanes take
-// their k's in ascending order, the lanes are summed in a fixed tree, the splits in index order.
-// SwiGLU needs interleave groups of 16, so that a tile of 32 packed rows is 16 gate rows and the
-// 16 up rows of the same outputs.
+// Few rows in float, the form that streams weights: a block owns tiles of 32 consecutive weight rows; every
+// warp walks COLS weight rows at a time against the MB rows of the step, so an activation read from shared
+// memory serves COLS dot products. Lanes take their k's in ascending order and are summed in a fixed tree.
+// SwiGLU needs interleave groups of 16, so that a tile of 32 packed rows is 16 gate rows and the 16 up rows
+// of the same outputs.
 #define GV_WARPS 8
-#define GV_ROWS 32          // weight rows per block
-#define GV_AHEAD 2          // steps of 128 columns a lane has weight loads in flight for
-template <int MB, int EPI>
-__global__ void __launch_bounds__(GV_WARPS * 32, 2)
-gemv_f32_stream_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw, float* __restrict__ C,
-                       int ldc, int M, int n_wrows, int K, int kc, float* __restrict__ scratch, int* __restrict__ tickets) {
-    constexpr int COLS = GV_ROWS / GV_WARPS;            // 4 weight rows per warp
-    extern __shared__ __align__(16) float a_s[];        // [MB][kc]
-    __shared__ int s_last;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int tile = blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
-    const int m0 = blockIdx.z * MB;
-    const int k_begin = split * kc, k_end = min(K, k_begin + kc);
-    const int steps = (k_end - k_begin + 127) / 128;
-    const float* wp[COLS];
-#pragma unroll
-    for (int c = 0; c < COLS; ++c) wp[c] = W + (size_t)min(tile * GV_ROWS + warp * COLS + c, n_wrows - 1) * ldw;
-    float acc[MB][COLS];
-#pragma unroll
-    for (int m = 0; m < MB; ++m)
-#pragma unroll
-        for (int c = 0; c < COLS; ++c) acc[m][c] = 0.f;
+#define GV_ROWS 32          // weight rows per tile
+// The weights come by TMA (cp.async.bulk.tensor into a ring of shared-memory stages, completion on
+// mbarriers), not by loads into registers: what a block
+// has on its way from HBM is the ring (RG_STAGES stages of 32 weight rows x 128 columns, 16 KB each, two
+// blocks per SM), not what its lanes can hold. A stage also carries the MB activation rows of its 128
+// columns, so a block can work on any range of K. The work of a product, tiles x steps of 128
+// columns, is dealt out evenly: block b takes the steps [b T / G, (b + 1) T / G) of the T steps
+// in tile order, so a tile's K may be shared by two or more blocks, which leave their sums in
+// `scratch` (slot tile + block) and count themselves at the tile's ticket; the block that arrives
+// last adds the slots in block order (ascending k) and runs the epilogue. The order of summation
+// is fixed by N, K and the number of blocks (twice the SMs of the device, or T if that is less),
+// not by the number of rows: every group of 8 rows is dealt out the same way.
+// Warps 0-7 compute (4 weight rows each), warp 8 issues the copies: the weights of the first
+// stages before the wait on the previous kernel, their activations after it. Every wait on a
+// barrier is bounded: a wait that runs out sets *err, the blocks's warps see the flag, let the
+// copies in flight land and leave.
+#define RG_STAGES 5
+#define RG_KS 128
+#define RG_WAIT_CYCLES 2000000000ll
+__device__ __forceinline__ uint32_t rg_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool rg_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool rg_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (rg_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (rg_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > RG_WAIT_CYCLES) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void rg_tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
 
-    // weights of the first GV_AHEAD steps: on their way before the previous kernel has finished
-    float4 w[GV_AHEAD][COLS];
-#pragma unroll
-    for (int u = 0; u < GV_AHEAD; ++u)
-#pragma unroll
-        for (int c = 0; c < COLS; ++c) w[u][c] = __ldg(reinterpret_cast<const float4*>(wp[c] + min(k_begin + u * 128 + lane * 4, K - 4)));
-    pdl_wait();
-    pdl_launch_dependents();
-    for (int i = threadIdx.x; i < MB * (kc / 4); i += blockDim.x) {
-        const int m = i / (kc / 4), k4 = (i - m * (kc / 4)) * 4;
-        const int k = min(k_begin + k4, K - 4);
-        *reinterpret_cast<float4*>(a_s + (size_t)m * kc + k4) =
-            *reinterpret_cast<const float4*>(A + (size_t)min(m0 + m, M - 1) * lda + k);
+struct RgShape {
+    int M, n_wrows, K;
+    int tiles, steps;            // 32-row tiles of the weights; steps of 128 columns in K
+    int blocks;                  // blocks per group of MB rows
+};
+// first step of block b of the group: floor(b * T / G)
+__device__ __forceinline__ int rg_first_step(const RgShape& sh, int b) {
+    return (int)(((long)b * ((long)sh.tiles * sh.steps)) / sh.blocks);
+}
+// the block whose range holds step q: the largest b with first_step(b) <= q
+__device__ __forceinline__ int rg_block_of(const RgShape& sh, int q) {
+    const long T = (long)sh.tiles * sh.steps;
+    int b = (int)min((long)sh.blocks - 1, (((long)q + 1) * sh.blocks - 1) / T);
+    while (b > 0 && rg_first_step(sh, b) > q) --b;
+    while (b + 1 < sh.blocks && rg_first_step(sh, b + 1) <= q) ++b;
+    return b;
+}
+
+template <int MB, int EPI>
+__global__ void __launch_bounds__((GV_WARPS + 1) * 32, 2)
+gemv_f32_ring_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapA, float* __restrict__ C,
+                     int ldc, RgShape sh, float* __restrict__ scratch, int* __restrict__ tickets, int* err) {
+    constexpr int COLS = GV_ROWS / GV_WARPS;
+    constexpr int STAGE_FLOATS = (GV_ROWS + MB) * RG_KS;
+    extern __shared__ __align__(128) float ring[];               // [RG_STAGES][GV_ROWS + MB][RG_KS]
+    __shared__ float sums[MB * GV_ROWS];
+    __shared__ __align__(8) uint64_t bars[2 * RG_STAGES];
+    __shared__ int s_last;
+    __shared__ int s_abort;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int b = blockIdx.x, group = blockIdx.y;
+    const int m0 = group * MB;
+    const int q_lo = rg_first_step(sh, b), q_hi = rg_first_step(sh, b + 1);
+    const uint32_t full0 = rg_smem_u32(bars), empty0 = full0 + 8u * RG_STAGES;
+    volatile int* abort_flag = &s_abort;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < RG_STAGES; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full0 + 8u * s), "r"(1));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty0 + 8u * s), "r"(GV_WARPS));
+        }
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    pdl_launch_dependents();
 
-    for (int st = 0; st < steps; st += GV_AHEAD) {
+    if (warp == GV_WARPS) {
+        // producer: stage (q - q_lo) % RG_STAGES holds step q
+        const uint32_t ring_u32 = rg_smem_u32(ring);
+        auto issue = [&](int q, bool weights, bool acts) {
+            if (lane != 0) return;
+            const int tile = q / sh.steps, ks = q - tile * sh.steps;
+            const int s = (q - q_lo) % RG_STAGES;
+            const uint32_t dst = ring_u32 + (uint32_t)s * STAGE_FLOATS * 4u, bar = full0 + 8u * s;
+            if (weights) {
+                // parts of a box beyond the matrix arrive as zeros and count as bytes all the same
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)STAGE_FLOATS * 4u) : "memory");
+                rg_tma_load_2d(dst, &mapW, bar, ks * RG_KS, tile * GV_ROWS);
+            }
+            if (acts) rg_tma_load_2d(dst + (uint32_t)GV_ROWS * RG_KS * 4u, &mapA, bar, ks * RG_KS, m0);
+        };
+        const int q_pre = min(q_hi, q_lo + RG_STAGES);
+        for (int q = q_lo; q < q_pre; ++q) issue(q, true, false);
+        pdl_wait();
+        for (int q = q_lo; q < q_pre; ++q) issue(q, false, true);
+        bool ok = true;
+        int q = q_pre;
+        for (; q < q_hi; ++q) {
+            const int i = q - q_lo;
+            ok = rg_wait(empty0 + 8u * (uint32_t)(i % RG_STAGES), (uint32_t)((i / RG_STAGES) - 1) & 1u, abort_flag);
+            if (!ok) break;
+            issue(q, true, true);
+        }
+        // The warp stays until what it issued has landed (the block's shared memory must outlive its copies).
+        for (int j = max(q_lo, q - RG_STAGES); j < q; ++j) {
+            const int i = j - q_lo;
+            const long long t0 = clock64();
+            while (!rg_try_wait(full0 + 8u * (uint32_t)(i % RG_STAGES), (uint32_t)(i / RG_STAGES) & 1u) &&
+                   clock64() - t0 < (*abort_flag ? 20000000ll : RG_WAIT_CYCLES)) {}
+        }
+        if (*abort_flag && lane == 0) atomicExch(err, 8);
+        return;
+    }
+
+    // consumers
+    pdl_wait();
+    const int tid = threadIdx.x;                                   // 0 .. 255
+    int q = q_lo;
+    while (q < q_hi) {
+        const int tile = q / sh.steps;
+        const int tile_q0 = tile * sh.steps;
+        const int q_end = min(q_hi, tile_q0 + sh.steps);
+        float acc[MB][COLS];
 #pragma unroll
-        for (int u = 0; u < GV_AHEAD; ++u) {
-            const int kl = (st + u) * 128 + lane * 4;
-            const bool live = k_begin + kl < k_end;      // past the range the clamped load does not count
-            const int ka = min(kl, kc - 4);
+        for (int m = 0; m < MB; ++m)
 #pragma unroll
-            for (int m = 0; m < MB; ++m) {
-                const float4 a4 = live ? *reinterpret_cast<const float4*>(a_s + (size_t)m * kc + ka) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c = 0; c < COLS; ++c) acc[m][c] = 0.f;
+        bool ok = true;
+        for (; q < q_end; ++q) {
+            const int i = q - q_lo;
+            const int s = i % RG_STAGES;
+            ok = rg_wait(full0 + 8u * (uint32_t)s, (uint32_t)(i / RG_STAGES) & 1u, abort_flag);
+            if (!ok) break;
+            const float* st = ring + (size_t)s * STAGE_FLOATS;
+            {
+                float4 w4[COLS];
 #pragma unroll
-                for (int c = 0; c < COLS; ++c) {
-                    acc[m][c] = fmaf(a4.x, w[u][c].x, acc[m][c]); acc[m][c] = fmaf(a4.y, w[u][c].y, acc[m][c]);
-                    acc[m][c] = fmaf(a4.z, w[u][c].z, acc[m][c]); acc[m][c] = fmaf(a4.w, w[u][c].w, acc[m][c]);
+                for (int c = 0; c < COLS; ++c) w4[c] = *reinterpret_cast<const float4*>(st + (warp * COLS + c) * RG_KS + lane * 4);
+#pragma unroll
+                for (int m = 0; m < MB; ++m) {
+                    const float4 a4 = *reinterpret_cast<const float4*>(st + (GV_ROWS + m) * RG_KS + lane * 4);
+#pragma unroll
+                    for (int c = 0; c < COLS; ++c) {
+                        acc[m][c] = fmaf(a4.x, w4[c].x, acc[m][c]); acc[m][c] = fmaf(a4.y, w4[c].y, acc[m][c]);
+                        acc[m][c] = fmaf(a4.z, w4[c].z, acc[m][c]); acc[m][c] = fmaf(a4.w, w4[c].w, acc[m][c]);
+                    }
                 }
             }
-            // this slot's next weights, GV_AHEAD steps on (clamped to a valid address at the end)
-            if (st + GV_AHEAD + u < steps) {
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8u * (uint32_t)s) : "memory");
+        }
+        if (!ok) q = q_hi;                                         // no more steps; the barriers below are still kept
 #pragma unroll
-                for (int c = 0; c < COLS; ++c)
-                    w[u][c] = __ldg(reinterpret_cast<const float4*>(wp[c] + min(k_begin + (st + GV_AHEAD + u) * 128 + lane * 4, K - 4)));
+        for (int m = 0; m < MB; ++m)
+#pragma unroll
+            for (int c = 0; c < COLS; ++c) {
+                const float v = warp_sum(acc[m][c]);
+                if (lane == 0) sums[m * GV_ROWS + warp * COLS + c] = v;
+            }
+        {   // one answer for all eight warps: has any of them, or the producer, given up?
+            uint32_t stop;
+            asm volatile(
+                "{\n\t.reg .pred p, q;\n\t"
+                "setp.ne.u32 q, %1, 0;\n\t"
+                "bar.red.or.pred p, 1, 256, q;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(stop) : "r"((uint32_t)(!ok || *abort_flag)) : "memory");
+            if (stop) {
+                if (tid == 0) atomicExch(err, 8);
+                break;
             }
         }
-    }
-    // this block's sums of its 32 weight rows, [MB][32], into shared memory (the staging area is free now)
-    __syncthreads();
-    float* sums = a_s;
-#pragma unroll
-    for (int m = 0; m < MB; ++m)
-#pragma unroll
-        for (int c = 0; c < COLS; ++c) {
-            const float v = warp_sum(acc[m][c]);
-            if (lane == 0) sums[m * GV_ROWS + warp * COLS + c] = v;
-        }
-    __syncthreads();
-    if (n_splits > 1) {
-        float* mine = scratch + (((size_t)blockIdx.z * gridDim.x + tile) * n_splits + split) * (MB * GV_ROWS);
-        for (int i = threadIdx.x; i < MB * GV_ROWS; i += blockDim.x) mine[i] = sums[i];
-        __threadfence();
-        __syncthreads();
-        int* ticket = tickets + blockIdx.z * gridDim.x + tile;
-        if (threadIdx.x == 0) {
-            const int t = atomicAdd(ticket, 1);
-            s_last = (t == n_splits - 1);
-            if (s_last) *ticket = 0;                     // left zero for the next launch
-        }
-        __syncthreads();
-        if (!s_last) return;
-        __threadfence();
-        const float* all = scratch + ((size_t)blockIdx.z * gridDim.x + tile) * n_splits * (MB * GV_ROWS);
-        for (int i = threadIdx.x; i < MB * GV_ROWS; i += blockDim.x) {
-            float v = 0.f;
-            for (int sp = 0; sp < n_splits; ++sp) v += __ldcg(all + (size_t)sp * (MB * GV_ROWS) + i);
-            sums[i] = v;
-        }
-        __syncthreads();
-    }
-    if (EPI == EPI_SWIGLU) {
-        for (int i = threadIdx.x; i < MB * (GV_ROWS / 2); i += blockDim.x) {
-            const int m = i / (GV_ROWS / 2), j = i - m * (GV_ROWS / 2);
-            const int n = tile * (GV_ROWS / 2) + j;
-            if (m0 + m < M && 2 * n < n_wrows) {
-                const float g = sums[m * GV_ROWS + j], u = sums[m * GV_ROWS + GV_ROWS / 2 + j];
-                C[(size_t)(m0 + m) * ldc + n] = (g / (1.0f + expf(-g))) * u;
+        const int t_in = tile % sh.tiles;                          // tile within the group
+        const int b_first = rg_block_of(sh, tile_q0), b_last = rg_block_of(sh, tile_q0 + sh.steps - 1);
+        bool mine = true;                                          // does this block run the tile's epilogue?
+        if (b_last > b_first) {
+            const size_t slots = (size_t)sh.tiles + sh.blocks;
+            float* slot = scratch + ((size_t)group * slots + t_in + b) * (MB * GV_ROWS);
+            for (int i = tid; i < MB * GV_ROWS; i += 256) slot[i] = sums[i];
+            __threadfence();
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            int* ticket = tickets + (size_t)group * sh.tiles + t_in;
+            if (tid == 0) {
+                const int t = atomicAdd(ticket, 1);
+                s_last = (t == b_last - b_first);
+                if (s_last) *ticket = 0;                           // left zero for the next launch
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            mine = s_last != 0;
+            if (mine) {
+                __threadfence();
+                const float* all = scratch + ((size_t)group * slots + t_in) * (MB * GV_ROWS);
+                for (int i = tid; i < MB * GV_ROWS; i += 256) {
+                    float v = 0.f;
+                    for (int bb = b_first; bb <= b_last; ++bb) v += __ldcg(all + (size_t)bb * (MB * GV_ROWS) + i);
+                    sums[i] = v;
+                }
+                asm volatile("bar.sync 1, 256;" ::: "memory");
             }
         }
-    } else {
-        for (int i = threadIdx.x; i < MB * GV_ROWS; i += blockDim.x) {
-            const int m = i / GV_ROWS, j = i - m * GV_ROWS;
-            const int n = tile * GV_ROWS + j;
-            if (m0 + m < M && n < n_wrows) {
-                float* o = C + (size_t)(m0 + m) * ldc + n;
-                if (EPI == EPI_ADD_F32) *o += sums[i];
-                else *o = sums[i];
+        if (mine) {
+            if (EPI == EPI_SWIGLU) {
+                for (int i = tid; i < MB * (GV_ROWS / 2); i += 256) {
+                    const int m = i / (GV_ROWS / 2), j = i - m * (GV_ROWS / 2);
+                    const int n = t_in * (GV_ROWS / 2) + j;
+                    if (m0 + m < sh.M && 2 * n < sh.n_wrows) {
+                        const float g = sums[m * GV_ROWS + j], u = sums[m * GV_ROWS + GV_ROWS / 2 + j];
+                        C[(size_t)(m0 + m) * ldc + n] = (g / (1.0f + expf(-g))) * u;
+                    }
+                }
+            } else {
+                for (int i = tid; i < MB * GV_ROWS; i += 256) {
+                    const int m = i / GV_ROWS, j = i - m * GV_ROWS;
+                    const int n = t_in * GV_ROWS + j;
+                    if (m0 + m < sh.M && n < sh.n_wrows) {
+                        float* o = C + (size_t)(m0 + m) * ldc + n;
+                        if (EPI == EPI_ADD_F32) *o += sums[i];
+                        else *o = sums[i];
+                    }
+                }
             }
         }
+        asm volatile("bar.sync 1, 256;" ::: "memory");             // sums is free for the next tile
     }
 }
 
 // Scratch the streaming form needs: tickets (ints, kept zero) in a first part of fixed size, which products of
-// every shape share, then the splits' sums. K is split only where there are fewer than 3 * SMs tiles, and a
-// step has at most 4 groups of 8 rows; a K beyond 2,048 columns is split whatever the tiles (an output head
-// over a wide model). GV_TICKETS tickets cover half a million weight rows at four groups; more are refused.
+// every shape share, then one slot of MB x 32 sums per (tile + block) of each group of 8 rows. A step has at
+// most 4 groups; GV_TICKETS tickets cover half a million weight rows at four groups; more are refused.
 #define GV_TICKETS 65536
-static int gemv_stream_splits(int n_wrows, int K) {
-    const int tiles = (n_wrows + GV_ROWS - 1) / GV_ROWS;
-    int splits = (3 * cml_sm_count() + tiles - 1) / tiles;          // about three blocks per SM
-    splits = max(1, min(splits, K / 512));                          // a range of at least 512 columns
-    splits = max(splits, (K + 2047) / 2048);                        // and of at most 2,048 (shared memory)
-    return splits;
+static RgShape rg_shape(int M, int n_wrows, int K) {
+    RgShape sh;
+    sh.M = M; sh.n_wrows = n_wrows; sh.K = K;
+    sh.tiles = (n_wrows + GV_ROWS - 1) / GV_ROWS;
+    sh.steps = (K + RG_KS - 1) / RG_KS;
+    const long T = (long)sh.tiles * sh.steps;
+    sh.blocks = (int)min((long)2 * cml_sm_count(), T);       // two blocks per SM: all of its shared memory as rings
+    return sh;
 }
 
 extern "C" long cml_gemv_f32_scratch_bytes(int M, int N, int K, int epilogue) {
     const int n_wrows = epilogue == EPI_SWIGLU ? 2 * N : N;
-    const int tiles = (n_wrows + GV_ROWS - 1) / GV_ROWS, groups = (M + 7) / 8;
-    const int splits = gemv_stream_splits(n_wrows, K);
-    return (long)GV_TICKETS * sizeof(int) + (splits > 1 ? (long)tiles * groups * splits * 8 * GV_ROWS * sizeof(float) : 0);
+    const int groups = (M + 7) / 8;
+    const RgShape sh = rg_shape(M, n_wrows, K);
+    return (long)GV_TICKETS * sizeof(int) + (long)groups * ((long)sh.tiles + sh.blocks) * 8 * GV_ROWS * (long)sizeof(float);
 }
 
-static int launch_gemv_f32_stream(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
-                                  int epilogue, void* scratch, cudaStream_t s) {
+typedef CUresult (*RgEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static RgEncodeFn rg_encode_fn() {
+    static RgEncodeFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (RgEncodeFn)p;
+    }
+    return fn;
+}
+// A map over a row-major float matrix [rows, K] (row stride ld elements): boxes of 128 columns by box_rows
+// rows, rows as they lie (no swizzle); what a box holds beyond the matrix reads as zero.
+static int rg_make_map(CUtensorMap* map, const void* base, long rows, long K, long ld, int box_rows) {
+    RgEncodeFn fn = rg_encode_fn();
+    if (!fn) return CML_ERR_BAD_SIZE;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+    cuuint32_t box[2] = {RG_KS, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : CML_ERR_BAD_SIZE;
+}
+
+static int launch_gemv_f32_ring(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
+                                int epilogue, void* scratch, int* err, cudaStream_t s) {
     constexpr int MB = 8;
     const int n_wrows = epilogue == EPI_SWIGLU ? 2 * N : N;
-    const int tiles = (n_wrows + GV_ROWS - 1) / GV_ROWS, groups = (M + MB - 1) / MB;
-    const int splits = gemv_stream_splits(n_wrows, K);
-    const int kc = ((K + splits - 1) / splits + 127) / 128 * 128;
-    const int n_splits = (K + kc - 1) / kc;
-    const size_t smem = (size_t)max(MB * kc, MB * GV_ROWS) * sizeof(float);
-    if (n_splits > 1 && (long)tiles * groups > GV_TICKETS) return CML_ERR_BAD_SIZE;
+    const int groups = (M + MB - 1) / MB;
+    const RgShape sh = rg_shape(M, n_wrows, K);
+    if ((long)sh.tiles * groups > GV_TICKETS || (long)sh.tiles * sh.steps > 0x7fffffffL) return CML_ERR_BAD_SIZE;
+    CUtensorMap mw, ma;
+    int rc = rg_make_map(&mw, W, n_wrows, K, ldw, GV_ROWS);
+    if (rc) return rc;
+    rc = rg_make_map(&ma, A, M, K, lda, MB);
+    if (rc) return rc;
+    const size_t smem = (size_t)RG_STAGES * (GV_ROWS + MB) * RG_KS * sizeof(float);
     int* tickets = (int*)scratch;
     float* sums = (float*)((char*)scratch + (size_t)GV_TICKETS * sizeof(int));
-    dim3 grid(tiles, n_splits, groups);
+    dim3 grid(sh.blocks, groups);
     cudaError_t e;
-#define CML_GEMVS(E)                                                                                                   \
-    e = cml_allow_smem<gemv_f32_stream_kernel<MB, E>>(smem);                                                           \
-    if (e != cudaSuccess) return (int)e;                                                                               \
-    launch_pdl(gemv_f32_stream_kernel<MB, E>, grid, dim3(GV_WARPS * 32), smem, s, (const float*)A, lda, (const float*)W, \
-               ldw, (float*)C, ldc, M, n_wrows, K, kc, sums, tickets)
+#define CML_GEMVR(E)                                                                                                    \
+    e = cml_allow_smem<gemv_f32_ring_kernel<MB, E>>(smem);                                                              \
+    if (e != cudaSuccess) return (int)e;                                                                                \
+    launch_pdl(gemv_f32_ring_kernel<MB, E>, grid, dim3((GV_WARPS + 1) * 32), smem, s, mw, ma, (float*)C, ldc, sh, sums, \
+               tickets, err)
     switch (epilogue) {
         case EPI_STORE:
-        case EPI_STORE_F32: CML_GEMVS(EPI_STORE_F32); break;
-        case EPI_ADD_F32: CML_GEMVS(EPI_ADD_F32); break;
-        case EPI_SWIGLU: CML_GEMVS(EPI_SWIGLU); break;
+        case EPI_STORE_F32: CML_GEMVR(EPI_STORE_F32); break;
+        case EPI_ADD_F32: CML_GEMVR(EPI_ADD_F32); break;
+        case EPI_SWIGLU: CML_GEMVR(EPI_SWIGLU); break;
         default: return CML_ERR_BAD_SIZE;
     }
-#undef CML_GEMVS
+#undef CML_GEMVR
     return cml_launch_status();
 }
 
@@ -527,17 +687,18 @@ static int launch_gemm(const void* A, int lda, const void* W, int ldw, void* C, 
 
 // A: [M, K] (row stride lda), W: [N, K] (or [2N, K] for SwiGLU; row stride ldw), C: [M, N] (ldc).
 // `scratch` (may be null): device memory of at least cml_gemv_f32_scratch_bytes(M, N, K, epilogue) bytes whose
-// first part (the tickets) is zero before the first call and left zero; with it, float products of at most 32 rows
-// whose sizes allow 16-byte loads take the streaming form.
+// first part (the tickets) is zero before the first call and left zero; with it and `err` (set to 8 if a bounded
+// wait of that form runs out), float products of at most 32 rows whose sizes allow 16-byte loads take the
+// streaming form.
 extern "C" int cml_gemm_tn_simt(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
-                                int dtype, int epilogue, int group, void* scratch, void* stream) {
+                                int dtype, int epilogue, int group, void* scratch, int* err, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == CML_DTYPE_F32 && M <= 32 && scratch != nullptr && K >= 128 && (K & 3) == 0 && (lda & 3) == 0 &&
+    if (dtype == CML_DTYPE_F32 && M <= 32 && scratch != nullptr && err != nullptr && K >= 128 && (K & 3) == 0 && (lda & 3) == 0 &&
         (ldw & 3) == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0 &&
         (epilogue != EPI_SWIGLU || (group == GV_ROWS / 2 && N % (GV_ROWS / 2) == 0)))
-        return launch_gemv_f32_stream(A, lda, W, ldw, C, ldc, M, N, K, epilogue, scratch, s);
+        return launch_gemv_f32_ring(A, lda, W, ldw, C, ldc, M, N, K, epilogue, scratch, err, s);
     if (dtype == CML_DTYPE_F32 && M <= 32) return launch_gemv_f32(A, lda, W, ldw, C, ldc, M, N, K, epilogue, group, s);
     if (dtype == CML_DTYPE_F32 && M >= 64 && (K & 3) == 0 && (lda & 3) == 0 && (ldw & 3) == 0 &&
         (((uintptr_t)A | (uintptr_t)W) & 15) == 0 && (epilogue != EPI_SWIGLU || (group == 16 && N % 16 == 0)))

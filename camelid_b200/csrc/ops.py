@@ -54,7 +54,7 @@ _SIGNATURES = {
                                               c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     ("gemm_simt", "cml_gemm_tn_simt"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                        c_int, c_int, c_void_p, c_void_p],
+                                        c_int, c_int, c_void_p, c_void_p, c_void_p],
     ("gemm_simt", "cml_gemv_f32_scratch_bytes"): [c_int, c_int, c_int, c_int],
     ("sampling", "cml_argmax_rows"): [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     ("sampling", "cml_adjust_logits"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_float,
@@ -525,9 +525,11 @@ def attn_prefill_tc(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_
         _stream()), "attn_prefill_tc")
 
 
-def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, group: int = 0):
+def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, group: int = 0, err=None):
     """c[M, N] (op)= a[M, K] @ w[N, K]^T with float accumulation on the CUDA cores.
-    EPI_SWIGLU reads w as packed [2N, K] gate/up rows interleaved in groups of ``group``."""
+    EPI_SWIGLU reads w as packed [2N, K] gate/up rows interleaved in groups of ``group``.
+    ``err`` (int32[1]): set to 8 by the form that streams float weights through shared memory if one
+    of its bounded waits runs out; by default this module's own word (``simt_error_word``)."""
     _dev(a, w, c)
     M, K = a.shape
     N = c.shape[1]
@@ -539,17 +541,30 @@ def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
         assert w.shape[0] == N
         assert c.dtype == (a.dtype if epilogue == EPI_STORE else torch.float32)
     scratch = None
+    if err is None:
+        err = simt_error_word(a.device)
     if a.dtype == torch.float32 and M <= 32:      # the streaming form for few float rows: tickets and split sums
         f = _fn("gemm_simt", "cml_gemv_f32_scratch_bytes")
         f.restype = c_long
         scratch = zeroed_scratch(a.device, "gemv_f32", int(f(M, N, K, epilogue)))
     _check(_fn("gemm_simt", "cml_gemm_tn_simt")(_p(a), a.stride(0), _p(w), w.stride(0), _p(c), c.stride(0), M, N, K,
-                                                dtype_code(a.dtype), epilogue, group, _p(scratch), _stream()),
+                                                dtype_code(a.dtype), epilogue, group, _p(scratch), _p(err), _stream()),
            "gemm_tn_simt")
 
 
 _scratch: dict = {}
 _retired: list = []
+_simt_err: dict = {}
+
+
+def simt_error_word(device) -> torch.Tensor:
+    """The error word ``gemm_tn_simt`` hands its kernels when the caller gives none."""
+    key = torch.device(device)
+    e = _simt_err.get(key)
+    if e is None:
+        e = torch.zeros(1, dtype=torch.int32, device=device)
+        _simt_err[key] = e
+    return e
 
 
 def zeroed_scratch(device, name: str, n_bytes: int) -> torch.Tensor:

@@ -117,7 +117,7 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
             else:
                 ops.gemm_tc(x, w, out, epi, bn, 1, err)
             return
-    ops.gemm_tn_simt(x, w, out, epilogue, group)
+    ops.gemm_tn_simt(x, w, out, epilogue, group, _err_word(x.device))
 
 
 def _pair_splits(rows: int, n: int, k: int, clusters: int) -> int:

@@ -111,6 +111,7 @@ def test_gemv_float_streaming_form(cuda, M, N, K):
         ops.gemm_tn_simt(a, packed, act, ops.EPI_SWIGLU, 16)
         gate, up = ref[:, :inter], ref[:, inter:]
         assert rel_err(act.cpu(), (gate / (1 + torch.exp(-gate))) * up) <= 2e-6
+    assert int(ops.simt_error_word(cuda).item()) == 0
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
