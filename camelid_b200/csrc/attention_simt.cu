@@ -13,8 +13,10 @@
 // Work split: one block handles `rows_per_tile` consecutive new tokens of one sequence,
 // `heads_per_cta` query heads of one kv head, and one contiguous range of key pages
 // (`n_splits` ranges; partial results are merged by attn_combine_kernel). One warp owns one
-// (token, head) pair; the block shares each key/value page through shared memory, two pages
-// deep: the next page is fetched while the warps work on this one.
+// token and 1, 2 or 4 of its heads (a key or value read from shared memory then serves all of
+// them; a decode step, with few pairs, gives every head its own warp); the block shares each
+// key/value page through shared memory, two pages deep: the next page is fetched while the warps
+// work on this one.
 #include "attention_common.cuh"
 
 __device__ __forceinline__ void cp_async16_f(float* dst, const float* src) {
@@ -48,7 +50,7 @@ __device__ __forceinline__ void attn_stage_page(float* Ks, float* Vs, const T* k
     }
 }
 
-template <typename T, int NACC>
+template <typename T, int NACC, int R>
 __global__ void attn_paged_simt_kernel(AttnParams p) {
     extern __shared__ __align__(16) float smem[];
     pdl_wait();
@@ -59,8 +61,8 @@ __global__ void attn_paged_simt_kernel(AttnParams p) {
     const int n_warps = blockDim.x >> 5;
     const int stage_floats = 2 * CML_PAGE * hd;          // keys, then values
     const int n_stages = p.n_stages;                     // 2, or 1 where two pages of this head size do not fit
-    float* Qs = smem + n_stages * stage_floats;          // [warps][hd]
-    float* Ps = Qs + n_warps * hd;             // [warps][PAGE]
+    float* Qs = smem + n_stages * stage_floats;          // [warps][R][hd]
+    float* Ps = Qs + n_warps * R * hd;                   // [warps][PAGE][R]
 
     const int tile = blockIdx.x;
     const int seq = p.tile_seq[tile];
@@ -73,10 +75,11 @@ __global__ void attn_paged_simt_kernel(AttnParams p) {
     const int row0 = p.seq_row0[seq];
     const int group = p.n_heads / p.n_kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r_local = warp / p.heads_per_cta;
-    const int hg = chunk * p.heads_per_cta + (warp - r_local * p.heads_per_cta);
-    const bool valid = (r_local < p.rows_per_tile) && (q0 + r_local < n_new) && (hg < group);
-    const int head = kvh * group + hg;
+    const int warps_per_row = p.heads_per_cta / R;       // a warp owns R heads of one token
+    const int r_local = warp / warps_per_row;
+    const int hg0 = chunk * p.heads_per_cta + (warp - r_local * warps_per_row) * R;
+    const bool valid = (r_local < p.rows_per_tile) && (q0 + r_local < n_new) && (hg0 < group);
+    const int head0 = kvh * group + hg0;
     const int row = row0 + q0 + r_local;
     const int pos = start + q0 + r_local;
     const int rows_in_tile = min(p.rows_per_tile, n_new - q0);
@@ -90,13 +93,22 @@ __global__ void attn_paged_simt_kernel(AttnParams p) {
     const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
 
     const T* q = (const T*)p.q;
-    if (valid)
-        for (int d = lane; d < hd; d += 32) Qs[warp * hd + d] = to_f32(q[(size_t)row * p.q_stride + head * hd + d]);
-
-    float m = -CUDART_INF_F, l = 0.f;
-    float acc[NACC];
+    if (valid) {
 #pragma unroll
-    for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
+        for (int rr = 0; rr < R; ++rr)                                // a head beyond the group: zeros, never stored
+            for (int d = lane; d < hd; d += 32)
+                Qs[(warp * R + rr) * hd + d] = hg0 + rr < group ? to_f32(q[(size_t)row * p.q_stride + (head0 + rr) * hd + d]) : 0.f;
+    }
+
+    float m[R], l[R];
+    float acc[R][NACC];
+#pragma unroll
+    for (int rr = 0; rr < R; ++rr) {
+        m[rr] = -CUDART_INF_F;
+        l[rr] = 0.f;
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) acc[rr][i] = 0.f;
+    }
 
     const T* kp = (const T*)p.k_pages;
     const T* vp = (const T*)p.v_pages;
@@ -128,80 +140,109 @@ __global__ void attn_paged_simt_kernel(AttnParams p) {
             __syncthreads();
         }
         if (valid) {
+            // A lane takes two keys of the page; a key's chunk, once read, serves the R heads of the warp.
             const int k0 = b * CML_PAGE + lane, k1 = k0 + 32;
-            const float4* q4 = reinterpret_cast<const float4*>(Qs + warp * hd);
+            const float4* q4 = reinterpret_cast<const float4*>(Qs + (size_t)warp * R * hd);
             const float4* ka = reinterpret_cast<const float4*>(Ks) + (size_t)lane * chunks;
             const float4* kb = reinterpret_cast<const float4*>(Ks) + (size_t)(lane + 32) * chunks;
             const int x0 = lane & mask, x1 = (lane + 32) & mask;
-            float s0 = 0.f, s1 = 0.f;
+            float s0[R], s1[R];
+#pragma unroll
+            for (int rr = 0; rr < R; ++rr) s0[rr] = 0.f, s1[rr] = 0.f;
             for (int c = 0; c < chunks; ++c) {
-                const float4 qq = q4[c];
                 const float4 a = ka[c ^ x0], bb = kb[c ^ x1];
-                s0 = fmaf(qq.x, a.x, s0); s0 = fmaf(qq.y, a.y, s0); s0 = fmaf(qq.z, a.z, s0); s0 = fmaf(qq.w, a.w, s0);
-                s1 = fmaf(qq.x, bb.x, s1); s1 = fmaf(qq.y, bb.y, s1); s1 = fmaf(qq.z, bb.z, s1); s1 = fmaf(qq.w, bb.w, s1);
+#pragma unroll
+                for (int rr = 0; rr < R; ++rr) {
+                    const float4 qq = q4[rr * chunks + c];
+                    s0[rr] = fmaf(qq.x, a.x, s0[rr]); s0[rr] = fmaf(qq.y, a.y, s0[rr]); s0[rr] = fmaf(qq.z, a.z, s0[rr]); s0[rr] = fmaf(qq.w, a.w, s0[rr]);
+                    s1[rr] = fmaf(qq.x, bb.x, s1[rr]); s1[rr] = fmaf(qq.y, bb.y, s1[rr]); s1[rr] = fmaf(qq.z, bb.z, s1[rr]); s1[rr] = fmaf(qq.w, bb.w, s1[rr]);
+                }
             }
             const bool in0 = (k0 >= lo) && (k0 <= pos), in1 = (k1 >= lo) && (k1 <= pos);
-            s0 = in0 ? s0 * p.scale : -CUDART_INF_F;
-            s1 = in1 ? s1 * p.scale : -CUDART_INF_F;
-            const float bm = warp_max(fmaxf(s0, s1));
-            if (bm != -CUDART_INF_F) {                                  // a visible key in this page
-                const float mn = fmaxf(m, bm);
-                const float corr = (m == -CUDART_INF_F) ? 0.f : expf(m - mn);
-                const float p0 = in0 ? expf(s0 - mn) : 0.f;
-                const float p1 = in1 ? expf(s1 - mn) : 0.f;
-                l = l * corr + warp_sum(p0 + p1);
+            if (__any_sync(0xffffffffu, in0 || in1)) {                  // a visible key in this page (the same for every head)
+                float* pw = Ps + (size_t)warp * CML_PAGE * R;
 #pragma unroll
-                for (int i = 0; i < NACC; ++i) acc[i] *= corr;
-                float* pw = Ps + warp * CML_PAGE;
-                pw[lane] = p0;
-                pw[lane + 32] = p1;
+                for (int rr = 0; rr < R; ++rr) {
+                    const float t0 = in0 ? s0[rr] * p.scale : -CUDART_INF_F;
+                    const float t1 = in1 ? s1[rr] * p.scale : -CUDART_INF_F;
+                    const float bm = warp_max(fmaxf(t0, t1));
+                    const float mn = fmaxf(m[rr], bm);
+                    const float corr = (m[rr] == -CUDART_INF_F) ? 0.f : expf(m[rr] - mn);
+                    const float p0 = in0 ? expf(t0 - mn) : 0.f;
+                    const float p1 = in1 ? expf(t1 - mn) : 0.f;
+                    l[rr] = l[rr] * corr + warp_sum(p0 + p1);
+#pragma unroll
+                    for (int i = 0; i < NACC; ++i) acc[rr][i] *= corr;
+                    pw[lane * R + rr] = p0;
+                    pw[(lane + 32) * R + rr] = p1;
+                    m[rr] = mn;
+                }
                 __syncwarp();
                 const int jend = min(CML_PAGE, live_rows);
                 for (int j = 0; j < jend; ++j) {
-                    const float pj = pw[j];
+                    float pj[R];
+                    if (R == 4) {
+                        const float4 t = *reinterpret_cast<const float4*>(pw + j * 4);
+                        pj[0] = t.x; pj[1 % R] = t.y; pj[2 % R] = t.z; pj[3 % R] = t.w;
+                    } else if (R == 2) {
+                        const float2 t = *reinterpret_cast<const float2*>(pw + j * 2);
+                        pj[0] = t.x; pj[1 % R] = t.y;
+                    } else {
+                        pj[0] = pw[j];
+                    }
                     const float* vr = Vs + j * hd;
 #pragma unroll
                     for (int i = 0; i < NACC; ++i) {
                         const int d = lane + 32 * i;
-                        if (d < hd) acc[i] = fmaf(pj, vr[d], acc[i]);
+                        if (d < hd) {
+                            const float v = vr[d];
+#pragma unroll
+                            for (int rr = 0; rr < R; ++rr) acc[rr][i] = fmaf(pj[rr], v, acc[rr][i]);
+                        }
                     }
                 }
                 __syncwarp();
-                m = mn;
             }
         }
         __syncthreads();               // this stage is free for the page after the next
     }
     cp_async_wait_f<0>();
     if (!valid) return;
-    if (p.n_splits == 1) {
-        T* o = (T*)p.out + (size_t)row * p.out_stride + head * hd;
-        const float inv = 1.0f / l;
 #pragma unroll
-        for (int i = 0; i < NACC; ++i) {
-            const int d = lane + 32 * i;
-            if (d < hd) o[d] = from_f32<T>(acc[i] * inv);
-        }
-    } else {
-        float* o = p.partial + (((size_t)row * p.n_heads + head) * p.n_splits + split) * (hd + 2);
-        if (lane == 0) {
-            o[0] = m;
-            o[1] = l;
-        }
+    for (int rr = 0; rr < R; ++rr) {
+        if (hg0 + rr >= group) break;
+        const int head = head0 + rr;
+        if (p.n_splits == 1) {
+            T* o = (T*)p.out + (size_t)row * p.out_stride + head * hd;
+            const float inv = 1.0f / l[rr];
 #pragma unroll
-        for (int i = 0; i < NACC; ++i) {
-            const int d = lane + 32 * i;
-            if (d < hd) o[2 + d] = acc[i];
+            for (int i = 0; i < NACC; ++i) {
+                const int d = lane + 32 * i;
+                if (d < hd) o[d] = from_f32<T>(acc[rr][i] * inv);
+            }
+        } else {
+            float* o = p.partial + (((size_t)row * p.n_heads + head) * p.n_splits + split) * (hd + 2);
+            if (lane == 0) {
+                o[0] = m[rr];
+                o[1] = l[rr];
+            }
+#pragma unroll
+            for (int i = 0; i < NACC; ++i) {
+                const int d = lane + 32 * i;
+                if (d < hd) o[2 + d] = acc[rr][i];
+            }
         }
     }
 }
 
 template <typename T>
-static int launch_attn(const AttnParams& p_in, int n_tiles, int n_rows, cudaStream_t s) {
+static int launch_attn(const AttnParams& p_in, int heads_per_warp, int n_tiles, int n_rows, cudaStream_t s) {
     const int hd = p_in.head_dim;
-    const int warps = p_in.rows_per_tile * p_in.heads_per_cta;
+    const int R = heads_per_warp;
+    if ((R != 1 && R != 2 && R != 4) || p_in.heads_per_cta % R != 0) return CML_ERR_BAD_SIZE;
+    const int warps = p_in.rows_per_tile * (p_in.heads_per_cta / R);
     if (warps < 1 || warps > 32) return CML_ERR_BAD_SIZE;
-    const size_t rest = ((size_t)warps * hd + (size_t)warps * CML_PAGE) * sizeof(float);
+    const size_t rest = ((size_t)warps * R * hd + (size_t)warps * R * CML_PAGE) * sizeof(float);
     const size_t stage = (size_t)2 * CML_PAGE * hd * sizeof(float);
     AttnParams p = p_in;
     p.n_stages = 2 * stage + rest <= 200 * 1024 ? 2 : 1;
@@ -211,17 +252,24 @@ static int launch_attn(const AttnParams& p_in, int n_tiles, int n_rows, cudaStre
     dim3 grid(n_tiles, p.n_kv_heads * p.head_chunks, p.n_splits);
     dim3 block(warps * 32);
     cudaError_t e = cudaSuccess;
-#define CML_ATTN(N)                                                                                        \
+#define CML_ATTN(N, RR)                                                                                    \
     do {                                                                                                   \
-        e = cml_allow_smem<attn_paged_simt_kernel<T, N>>(smem);                                            \
+        e = cml_allow_smem<attn_paged_simt_kernel<T, N, RR>>(smem);                                        \
         if (e != cudaSuccess) return (int)e;                                                               \
-        launch_pdl(attn_paged_simt_kernel<T, N>, grid, block, smem, s, p);                                 \
+        launch_pdl(attn_paged_simt_kernel<T, N, RR>, grid, block, smem, s, p);                             \
     } while (0)
-    if (nacc <= 1) CML_ATTN(1);
-    else if (nacc <= 2) CML_ATTN(2);
-    else if (nacc <= 4) CML_ATTN(4);
-    else if (nacc <= 8) CML_ATTN(8);
-    else return CML_ERR_BAD_SIZE;
+#define CML_ATTN_N(RR)                                                                                     \
+    do {                                                                                                   \
+        if (nacc <= 1) CML_ATTN(1, RR);                                                                    \
+        else if (nacc <= 2) CML_ATTN(2, RR);                                                               \
+        else if (nacc <= 4) CML_ATTN(4, RR);                                                               \
+        else if (nacc <= 8) CML_ATTN(8, RR);                                                               \
+        else return CML_ERR_BAD_SIZE;                                                                      \
+    } while (0)
+    if (R == 4) CML_ATTN_N(4);
+    else if (R == 2) CML_ATTN_N(2);
+    else CML_ATTN_N(1);
+#undef CML_ATTN_N
 #undef CML_ATTN
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
@@ -234,12 +282,14 @@ static int launch_attn(const AttnParams& p_in, int n_tiles, int n_rows, cudaStre
 }
 
 // `partial` must hold n_rows * n_heads * n_splits * (head_dim + 2) floats when n_splits > 1.
+// A block has rows_per_tile * heads_per_cta / heads_per_warp warps (at most 32); heads_per_warp is 1, 2 or 4
+// and divides heads_per_cta.
 extern "C" int cml_attn_paged_simt(const void* q, int q_stride, void* out, int out_stride, int dtype,
                                    const void* k_pages, const void* v_pages, const int* block_table, int max_blocks,
                                    const int* tile_seq, const int* tile_q0, int n_tiles, const int* seq_row0,
                                    const int* seq_start, const int* seq_new, int n_rows, int n_heads, int n_kv_heads,
-                                   int head_dim, int rows_per_tile, int heads_per_cta, int head_chunks, int n_splits,
-                                   int window, float scale, float* partial, void* stream) {
+                                   int head_dim, int rows_per_tile, int heads_per_cta, int heads_per_warp, int head_chunks,
+                                   int n_splits, int window, float scale, float* partial, void* stream) {
     if (n_tiles <= 0 || n_rows <= 0) return 0;
     if (head_dim <= 0 || head_dim > 256 || (head_dim & 15) || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return CML_ERR_BAD_SIZE;
     if (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) return CML_ERR_BAD_ALIGN;
@@ -253,7 +303,7 @@ extern "C" int cml_attn_paged_simt(const void* q, int q_stride, void* out, int o
     p.rows_per_tile = rows_per_tile; p.heads_per_cta = heads_per_cta; p.head_chunks = head_chunks;
     p.n_splits = n_splits; p.window = window; p.scale = scale; p.partial = partial; p.tickets = nullptr; p.n_stages = 2;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == CML_DTYPE_F32) return launch_attn<float>(p, n_tiles, n_rows, s);
-    if (dtype == CML_DTYPE_BF16) return launch_attn<bf16>(p, n_tiles, n_rows, s);
+    if (dtype == CML_DTYPE_F32) return launch_attn<float>(p, heads_per_warp, n_tiles, n_rows, s);
+    if (dtype == CML_DTYPE_BF16) return launch_attn<bf16>(p, heads_per_warp, n_tiles, n_rows, s);
     return CML_ERR_BAD_DTYPE;
 }

@@ -41,7 +41,7 @@ _SIGNATURES = {
     ("rowwise", "cml_scale_rows"): [c_void_p, c_int, c_long, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
     ("attention_simt", "cml_attn_paged_simt"): [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                                 c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                                 c_void_p, c_void_p],
     ("attention_mma", "cml_attn_paged_mma"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -398,13 +398,23 @@ def scale_rows(x: torch.Tensor, row_scale: RowScale):
                                            row_scale.eps, _stream()), "scale_rows")
 
 
+def attn_heads_per_warp(heads_per_cta: int, decode: bool) -> int:
+    """Heads of one token that a warp of the float attention kernel owns: in prefill as many of
+    4, 2, 1 as divide the block's heads (a key read from shared memory serves them all); a decode
+    step has few (row, head) pairs and gives each its own warp."""
+    if decode:
+        return 1
+    return 4 if heads_per_cta % 4 == 0 else 2 if heads_per_cta % 2 == 0 else 1
+
+
 def attn_tiling(n_heads: int, n_kv_heads: int, decode: bool) -> tuple[int, int, int]:
     """(rows_per_tile, heads_per_cta, head_chunks) of the float attention kernel: at most 16
-    warps, one per (row, head) pair; the heads of a kv group are cut in chunks if above 16."""
+    warps, each with one token and ``attn_heads_per_warp`` of its heads; the heads of a kv group
+    are cut in chunks if above 16."""
     group = n_heads // n_kv_heads
     chunks = (group + 15) // 16
     hpc = (group + chunks - 1) // chunks
-    rows = 1 if decode else max(1, 16 // hpc)
+    rows = 1 if decode else max(1, 16 * attn_heads_per_warp(hpc, False) // hpc)
     return rows, hpc, chunks
 
 
@@ -414,9 +424,12 @@ def attn_partial_floats(n_rows: int, n_heads: int, head_dim: int, n_splits: int)
 
 def attn_paged_simt(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_tiles, seq_row0, seq_start, seq_new,
                     n_rows, n_heads, n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, n_splits,
-                    window, scale, partial):
+                    window, scale, partial, heads_per_warp=None):
     """Attention of packed query rows over the paged cache (float arithmetic). ``q`` may be a
-    column slice of a wider matrix (its row stride is used)."""
+    column slice of a wider matrix (its row stride is used). ``heads_per_warp``: by default what
+    ``attn_tiling`` assumed (one where a tile is a single row)."""
+    if heads_per_warp is None:
+        heads_per_warp = attn_heads_per_warp(heads_per_cta, rows_per_tile == 1)
     _dev(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, seq_row0, seq_start, seq_new, partial)
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == v_pages.dtype
     assert k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim) and k_pages.is_contiguous() and v_pages.is_contiguous()
@@ -426,8 +439,8 @@ def attn_paged_simt(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_
     _check(_fn("attention_simt", "cml_attn_paged_simt")(
         _p(q), q.stride(0), _p(out), out.stride(0), dtype_code(q.dtype), _p(k_pages), _p(v_pages), _p(block_table),
         block_table.shape[1], _p(tile_seq), _p(tile_q0), n_tiles, _p(seq_row0), _p(seq_start), _p(seq_new), n_rows,
-        n_heads, n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, n_splits, int(window or 0),
-        float(scale), _p(partial), _stream()), "attn_paged_simt", 2 if n_splits > 1 else 1)
+        n_heads, n_kv_heads, head_dim, rows_per_tile, heads_per_cta, heads_per_warp, head_chunks, n_splits,
+        int(window or 0), float(scale), _p(partial), _stream()), "attn_paged_simt", 2 if n_splits > 1 else 1)
 
 
 def attn_mma_tiling(n_heads: int, n_kv_heads: int, decode: bool) -> tuple[int, int, int]:
