@@ -371,9 +371,16 @@ struct RgShape {
     int M, n_wrows, K;
     int tiles, steps;            // 32-row tiles of the weights; steps of 128 columns in K
     int blocks;                  // blocks per group of MB rows
+    int splits;                  // 0: the steps dealt out evenly. Else block b owns range b % splits of the K of
+    int per;                     //    tile b / splits (`per` steps a range) and stores its sums as partial sums
+    long split_stride;           //    at C + range * split_stride: no tickets, the reader adds the ranges.
 };
 // first step of block b of the group: floor(b * T / G)
 __device__ __forceinline__ int rg_first_step(const RgShape& sh, int b) {
+    if (sh.splits > 0) {
+        const int tile = b / sh.splits, range = b - tile * sh.splits;
+        return tile * sh.steps + min(sh.steps, range * sh.per);
+    }
     return (int)(((long)b * ((long)sh.tiles * sh.steps)) / sh.blocks);
 }
 // the block whose range holds step q: the largest b with first_step(b) <= q
@@ -510,6 +517,16 @@ gemv_f32_ring_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_cons
             }
         }
         const int t_in = tile % sh.tiles;                          // tile within the group
+        if (sh.splits > 0) {                                       // this range's sums, as they are
+            float* part = C + (size_t)(b - tile * sh.splits) * sh.split_stride;
+            for (int i = tid; i < MB * GV_ROWS; i += 256) {
+                const int m = i / GV_ROWS, j = i - m * GV_ROWS;
+                const int n = t_in * GV_ROWS + j;
+                if (m0 + m < sh.M && n < sh.n_wrows) part[(size_t)(m0 + m) * ldc + n] = sums[i];
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            continue;
+        }
         const int b_first = rg_block_of(sh, tile_q0), b_last = rg_block_of(sh, tile_q0 + sh.steps - 1);
         bool mine = true;                                          // does this block run the tile's epilogue?
         if (b_last > b_first) {
@@ -574,6 +591,7 @@ static RgShape rg_shape(int M, int n_wrows, int K) {
     sh.steps = (K + RG_KS - 1) / RG_KS;
     const long T = (long)sh.tiles * sh.steps;
     sh.blocks = (int)min((long)2 * cml_sm_count(), T);       // two blocks per SM: all of its shared memory as rings
+    sh.splits = 0; sh.per = 0; sh.split_stride = 0;
     return sh;
 }
 
@@ -643,6 +661,42 @@ static int launch_gemv_f32_ring(const void* A, int lda, const void* W, int ldw, 
         default: return CML_ERR_BAD_SIZE;
     }
 #undef CML_GEMVR
+    return cml_launch_status();
+}
+
+// Ranges of K a product of at most 8 float rows is cut into when its sums are left as partial sums: about as
+// many blocks as the device holds at a time (two per SM), ranges of at least two steps of 128 columns; 0 where
+// the sizes do not suit the streaming form.
+extern "C" int cml_gemv_f32_partial_splits(int M, int N, int K, int lda, int ldw) {
+    if (M < 1 || M > 8 || N < 1 || K < 256 || (K & 3) || (lda & 3) || (ldw & 3)) return 0;
+    const int tiles = (N + GV_ROWS - 1) / GV_ROWS, steps = (K + RG_KS - 1) / RG_KS;
+    int splits = max(1, min(2 * cml_sm_count() / tiles, steps / 2));
+    const int per = (steps + splits - 1) / splits;
+    return (steps + per - 1) / per;                                    // no empty range
+}
+
+// part[r][m][n] (float, row stride ldc, ranges split_stride apart) = the sum of A[m][k] * W[n][k] over range r of K,
+// for r < splits = cml_gemv_f32_partial_splits(...). At most 8 rows.
+extern "C" int cml_gemv_f32_partial(const void* A, int lda, const void* W, int ldw, void* part, int ldc, long split_stride,
+                                    int splits, int M, int N, int K, int* err, void* stream) {
+    constexpr int MB = 8;
+    if (splits < 1 || splits != cml_gemv_f32_partial_splits(M, N, K, lda, ldw) || err == nullptr) return CML_ERR_BAD_SIZE;
+    if ((((uintptr_t)A | (uintptr_t)W) & 15) != 0) return CML_ERR_BAD_ALIGN;
+    RgShape sh = rg_shape(M, N, K);
+    sh.splits = splits;
+    sh.per = (sh.steps + splits - 1) / splits;
+    sh.split_stride = split_stride;
+    sh.blocks = sh.tiles * splits;
+    CUtensorMap mw, ma;
+    int rc = rg_make_map(&mw, W, N, K, ldw, GV_ROWS);
+    if (rc) return rc;
+    rc = rg_make_map(&ma, A, M, K, lda, MB);
+    if (rc) return rc;
+    const size_t smem = (size_t)RG_STAGES * (GV_ROWS + MB) * RG_KS * sizeof(float);
+    cudaError_t e = cml_allow_smem<gemv_f32_ring_kernel<MB, EPI_STORE_F32>>(smem);
+    if (e != cudaSuccess) return (int)e;
+    launch_pdl(gemv_f32_ring_kernel<MB, EPI_STORE_F32>, dim3(sh.blocks, 1), dim3((GV_WARPS + 1) * 32), smem,
+               (cudaStream_t)stream, mw, ma, (float*)part, ldc, sh, (float*)nullptr, (int*)nullptr, err);
     return cml_launch_status();
 }
 

@@ -56,6 +56,9 @@ _SIGNATURES = {
     ("gemm_simt", "cml_gemm_tn_simt"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_void_p, c_void_p, c_void_p],
     ("gemm_simt", "cml_gemv_f32_scratch_bytes"): [c_int, c_int, c_int, c_int],
+    ("gemm_simt", "cml_gemv_f32_partial_splits"): [c_int, c_int, c_int, c_int, c_int],
+    ("gemm_simt", "cml_gemv_f32_partial"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_long, c_int, c_int,
+                                            c_int, c_int, c_void_p, c_void_p],
     ("sampling", "cml_argmax_rows"): [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     ("sampling", "cml_adjust_logits"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_float,
                                         c_void_p],
@@ -563,6 +566,28 @@ def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
     _check(_fn("gemm_simt", "cml_gemm_tn_simt")(_p(a), a.stride(0), _p(w), w.stride(0), _p(c), c.stride(0), M, N, K,
                                                 dtype_code(a.dtype), epilogue, group, _p(scratch), _p(err), _stream()),
            "gemm_tn_simt")
+
+
+def gemv_f32_partial_splits(a: torch.Tensor, w: torch.Tensor) -> int:
+    """Ranges of K that ``gemv_f32_partial`` cuts a[M, K] @ w[N, K]^T into; 0 where it does not take
+    the product (more than 8 rows, not float, sizes that do not allow 16-byte copies)."""
+    if a.dtype != torch.float32 or w.dtype != torch.float32 or a.stride(1) != 1 or w.stride(1) != 1:
+        return 0
+    if (a.data_ptr() | w.data_ptr()) & 15:
+        return 0
+    return int(_fn("gemm_simt", "cml_gemv_f32_partial_splits")(a.shape[0], w.shape[0], a.shape[1], a.stride(0),
+                                                               w.stride(0)))
+
+
+def gemv_f32_partial(a: torch.Tensor, w: torch.Tensor, part: torch.Tensor, err: torch.Tensor):
+    """part[r] = a @ w^T over range r of K (float, at most 8 rows): the product's sums left as
+    partial sums for the kernel that reads them next, with no pass over them in between."""
+    _dev(a, w, part, err)
+    splits, M, N = part.shape
+    assert part.dtype == torch.float32 and part.stride(2) == 1 and a.shape[0] == M and w.shape[0] == N
+    _check(_fn("gemm_simt", "cml_gemv_f32_partial")(_p(a), a.stride(0), _p(w), w.stride(0), _p(part), part.stride(1),
+                                                    part.stride(0), splits, M, N, a.shape[1], _p(err), _stream()),
+           "gemv_f32_partial")
 
 
 _scratch: dict = {}

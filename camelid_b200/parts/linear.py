@@ -137,7 +137,15 @@ def partial_sums(ctx, x: torch.Tensor, w: torch.Tensor, name: str, row_scale=Non
     (``ops.RowScale``): what the rows of ``x`` still lack; applied if a result is returned."""
     rows = x.shape[0]
     if not ops.gemm_tc_usable(x, w):
-        return None
+        # float: a step of at most 8 rows leaves the K ranges of its streaming blocks as they are
+        splits = ops.gemv_f32_partial_splits(x, w) if rows <= 8 else 0
+        if splits < 2:
+            return None
+        if row_scale is not None:
+            ops.scale_rows(x, row_scale)
+        part = ctx.buffer(name, (splits, rows, w.shape[0]), torch.float32)
+        ops.gemv_f32_partial(x, w, part, _err_word(x.device))
+        return part
     n, k = w.shape
     sms = ops.sm_count(x.device)
     if rows <= _opt(ctx).decode_rows:
