@@ -43,6 +43,7 @@ _SIGNATURES = {
                                                 c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                                 c_void_p, c_void_p],
+    ("attention_simt", "cml_attn_simt_smem_bytes"): [c_int, c_int, c_int, c_int],
     ("attention_mma", "cml_attn_paged_mma"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
@@ -403,22 +404,33 @@ def scale_rows(x: torch.Tensor, row_scale: RowScale):
 
 def attn_heads_per_warp(heads_per_cta: int, decode: bool) -> int:
     """Heads of one token that a warp of the float attention kernel owns: in prefill as many of
-    4, 2, 1 as divide the block's heads (a key read from shared memory serves them all); a decode
-    step has few (row, head) pairs and gives each its own warp."""
+    4, 2, 1 as divide the block's heads (a key read from shared memory serves them all). 0 names
+    the decode kernel, whose four warps share every page by keys and all work on the block's 2 or
+    4 heads; a decode step on single heads gives each its own warp."""
     if decode:
-        return 1
+        return 0 if heads_per_cta in (2, 4) else 1
     return 4 if heads_per_cta % 4 == 0 else 2 if heads_per_cta % 2 == 0 else 1
 
 
 def attn_tiling(n_heads: int, n_kv_heads: int, decode: bool) -> tuple[int, int, int]:
-    """(rows_per_tile, heads_per_cta, head_chunks) of the float attention kernel: at most 16
-    warps, each with one token and ``attn_heads_per_warp`` of its heads; the heads of a kv group
-    are cut in chunks if above 16."""
+    """(rows_per_tile, heads_per_cta, head_chunks) of the float attention kernel. Prefill: at most
+    16 warps, each with one token and ``attn_heads_per_warp`` of its heads; the heads of a kv group
+    are cut in chunks if above 16. Decode: one token and 2 or 4 heads of a kv group per block."""
     group = n_heads // n_kv_heads
+    if decode:
+        hpc = 1 if group == 1 else 2 if group == 2 else 4
+        return 1, hpc, (group + hpc - 1) // hpc
     chunks = (group + 15) // 16
     hpc = (group + chunks - 1) // chunks
-    rows = 1 if decode else max(1, 16 * attn_heads_per_warp(hpc, False) // hpc)
+    rows = max(1, 16 * attn_heads_per_warp(hpc, False) // hpc)
     return rows, hpc, chunks
+
+
+def attn_simt_smem_bytes(head_dim: int, rows_per_tile: int, heads_per_cta: int, decode: bool) -> int:
+    """Shared memory of a block of the float attention kernel with this tiling."""
+    f = _fn("attention_simt", "cml_attn_simt_smem_bytes")
+    f.restype = c_long
+    return int(f(head_dim, rows_per_tile, heads_per_cta, attn_heads_per_warp(heads_per_cta, decode)))
 
 
 def attn_partial_floats(n_rows: int, n_heads: int, head_dim: int, n_splits: int) -> int:

@@ -136,8 +136,8 @@ class GroupedQueryAttention(Part):
         if tensor_cores:
             per_sm = 2 if self.head_dim <= 64 else 1          # blocks that run at the same time on an SM
         else:                                                 # the float kernel keeps two pages of keys and values
-            group = self.num_heads // self.num_kv_heads
-            smem = 4 * (4 * PAGE * self.head_dim + min(group, 16) * (self.head_dim + PAGE))
+            rows, hpc, _ = ops.attn_tiling(self.num_heads, self.num_kv_heads, True)
+            smem = ops.attn_simt_smem_bytes(self.head_dim, rows, hpc, True) + 1024
             per_sm = max(1, min(8, (227 * 1024) // smem))
         resident = per_sm * ops.sm_count(ctx.device)
         return max(1, min((keys + unit - 1) // unit, resident // ctas, 64))
