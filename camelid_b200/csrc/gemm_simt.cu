@@ -316,7 +316,8 @@ gemv_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ 
 
 // Few rows in float, the form that streams weights: a block owns tiles of 32 consecutive weight rows; every
 // warp walks COLS weight rows at a time against the MB rows of the step, so an activation read from shared
-// memory serves COLS dot products. Lanes take their k's in ascending order and are summed in a fixed tree.
+// memory serves COLS dot products. Lanes take their k's in ascending order and are summed in a fixed tree
+// (a butterfly that leaves sum i in lane i).
 // SwiGLU needs interleave groups of 16, so that a tile of 32 packed rows is 16 gate rows and the 16 up rows
 // of the same outputs.
 #define GV_WARPS 8
@@ -423,6 +424,10 @@ gemv_f32_ring_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_cons
     if (warp == GV_WARPS) {
         // producer: stage (q - q_lo) % RG_STAGES holds step q
         const uint32_t ring_u32 = rg_smem_u32(ring);
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&mapW) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&mapA) : "memory");
+        }
         auto issue = [&](int q, bool weights, bool acts) {
             if (lane != 0) return;
             const int tile = q / sh.steps, ks = q - tile * sh.steps;
@@ -496,13 +501,25 @@ gemv_f32_ring_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_cons
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8u * (uint32_t)s) : "memory");
         }
         if (!ok) q = q_hi;                                         // no more steps; the barriers below are still kept
+        {   // the warp's 32 sums over its lanes, 31 shuffles in all: lane i ends up with sum i = acc[i / 4][i % 4]
+            float v[MB * COLS];
 #pragma unroll
-        for (int m = 0; m < MB; ++m)
+            for (int m = 0; m < MB; ++m)
 #pragma unroll
-            for (int c = 0; c < COLS; ++c) {
-                const float v = warp_sum(acc[m][c]);
-                if (lane == 0) sums[m * GV_ROWS + warp * COLS + c] = v;
+                for (int c = 0; c < COLS; ++c) v[m * COLS + c] = acc[m][c];
+            static_assert(MB * COLS == 32, "one sum per lane");
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) {
+                const bool upper = (lane & off) != 0;          // keeps the upper half of what is left, sends the lower
+#pragma unroll
+                for (int i = 0; i < off; ++i) {
+                    const float send = upper ? v[i] : v[i + off];
+                    const float keep = upper ? v[i + off] : v[i];
+                    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
             }
+            sums[(lane / COLS) * GV_ROWS + warp * COLS + (lane % COLS)] = v[0];
+        }
         {   // one answer for all eight warps: has any of them, or the producer, given up?
             uint32_t stop;
             asm volatile(
