@@ -137,11 +137,13 @@ gemm_tn_f32_big_kernel(const float* __restrict__ A, int lda, const float* __rest
     const float* w0p = W + (size_t)min(n0 + lrow0, n_wrows - 1) * ldw + lkq;
     const float* w1p = W + (size_t)min(n0 + lrow1, n_wrows - 1) * ldw + lkq;
     const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-    float acc[8][8];
+    // a thread's 8 x 8 sums as pairs of neighbouring columns: one packed FMA (two IEEE float FMAs in one
+    // instruction, sm_100) per pair and k, half the instructions and register reads of single FMAs
+    float2 acc[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+        for (int j = 0; j < 4; ++j) acc[i][j] = make_float2(0.f, 0.f);
 
     auto fetch = [&](int k0, float4& ra0, float4& ra1, float4& rw0, float4& rw1) {
         const bool in = k0 + lkq < K;
@@ -171,11 +173,14 @@ gemm_tn_f32_big_kernel(const float* __restrict__ A, int lda, const float* __rest
             const float4 bv0 = *reinterpret_cast<const float4*>(&Ws[buf][k][cg0]);
             const float4 bv1 = *reinterpret_cast<const float4*>(&Ws[buf][k][cg1]);
             const float av[8] = {av0.x, av0.y, av0.z, av0.w, av1.x, av1.y, av1.z, av1.w};
-            const float bv[8] = {bv0.x, bv0.y, bv0.z, bv0.w, bv1.x, bv1.y, bv1.z, bv1.w};
+            const float2 bv[4] = {make_float2(bv0.x, bv0.y), make_float2(bv0.z, bv0.w), make_float2(bv1.x, bv1.y),
+                                  make_float2(bv1.z, bv1.w)};
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < 8; ++i) {
+                const float2 a2 = make_float2(av[i], av[i]);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) acc[i][j] = __ffma2_rn(a2, bv[j], acc[i][j]);
+            }
         }
         if (st + 1 < steps) {
             stash(buf ^ 1, ra0, ra1, rw0, rw1);      // the other buffer was last read a step ago, before the barrier below
@@ -193,8 +198,9 @@ gemm_tn_f32_big_kernel(const float* __restrict__ A, int lda, const float* __rest
             for (int j = 0; j < 4; ++j) {
                 const int c = out0 + j;
                 if (2 * c < n_wrows) {
-                    const float g = acc[i][j];
-                    C[(size_t)r * ldc + c] = (g / (1.0f + expf(-g))) * acc[i][j + 4];
+                    const float g = (j & 1) ? acc[i][j >> 1].y : acc[i][j >> 1].x;
+                    const float u = (j & 1) ? acc[i][2 + (j >> 1)].y : acc[i][2 + (j >> 1)].x;
+                    C[(size_t)r * ldc + c] = (g / (1.0f + expf(-g))) * u;
                 }
             }
         } else {
@@ -205,8 +211,9 @@ gemm_tn_f32_big_kernel(const float* __restrict__ A, int lda, const float* __rest
                     const int c = n0 + cg + 16 * h + j;
                     if (c >= n_wrows) continue;
                     float* o = C + (size_t)r * ldc + c;
-                    if (EPI == EPI_ADD_F32) *o += acc[i][4 * h + j];
-                    else *o = acc[i][4 * h + j];
+                    const float v = (j & 1) ? acc[i][2 * h + (j >> 1)].y : acc[i][2 * h + (j >> 1)].x;
+                    if (EPI == EPI_ADD_F32) *o += v;
+                    else *o = v;
                 }
         }
     }
