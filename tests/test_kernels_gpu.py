@@ -114,6 +114,31 @@ def test_gemv_float_streaming_form(cuda, M, N, K):
     assert int(ops.simt_error_word(cuda).item()) == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 3072, 2048), (8, 2048, 2048), (8, 2048, 8192), (5, 517, 260), (3, 33, 4100),
+                                   (8, 40, 256), (7, 100, 648)])
+def test_gemv_float_partial_sums(cuda, M, N, K):
+    """The streaming float product with its K ranges left as partial sums: their sum in range order is the
+    product; ranges do not overlap or leave a gap (a row of ones against weights that name their column)."""
+    from camelid_b200.csrc import ops
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g).to(cuda)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(cuda)
+    splits = ops.gemv_f32_partial_splits(a, w)
+    assert splits >= 1
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    part = torch.full((splits, M, N), float("nan"), device=cuda)
+    ops.gemv_f32_partial(a, w, part, err)
+    assert int(err.item()) == 0
+    assert rel_err(part.sum(0).cpu(), a.cpu().double() @ w.cpu().double().T) <= 2e-6
+    ones = torch.ones(M, K, device=cuda)
+    cols = torch.arange(K, dtype=torch.float32, device=cuda).repeat(N, 1).contiguous()
+    ops.gemv_f32_partial(ones, cols, part, err)
+    per = part[:, 0, 0].cpu().double()
+    assert (per > 0).all() or K < 256, per                   # no empty range
+    assert float(per.sum()) == K * (K - 1) / 2               # exact in float up to 2^24 per range
+    assert ops.gemv_f32_partial_splits(torch.randn(9, K, device=cuda), w) == 0       # more than 8 rows: not taken
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M,inter,K,group", [(3, 48, 40, 16), (66, 136, 72, 136), (9, 160, 64, 16), (200, 160, 64, 16),
                                              (129, 8192, 256, 16), (64, 16, 12, 16)])
@@ -219,6 +244,17 @@ def test_attention_decode_splits(cuda, dtype, n_splits):
     """One new row per sequence, keys split over several blocks (also more splits than pages)."""
     _attn_case(cuda, dtype, 8, 2, 64, starts=[0, 63, 64, 700], news=[1, 1, 1, 1], window=None, decode=True,
                n_splits=n_splits, spike=(3, 130))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_heads,n_kv,hd", [(3, 1, 16), (6, 1, 48), (5, 5, 32), (12, 2, 128), (2, 1, 256), (34, 1, 64)])
+def test_attention_decode_shapes(cuda, dtype, n_heads, n_kv, hd):
+    """Decode tiling of the float kernel at other groupings and head sizes: groups that do not fill a block's 2 or
+    4 heads (3, 6, 34 heads on one kv head), single heads (their own warp each), the largest head size (one
+    page deep)."""
+    _attn_case(cuda, dtype, n_heads, n_kv, hd, starts=[0, 5, 64, 130], news=[1, 1, 1, 1], window=None, decode=True,
+               n_splits=2, spike=(3, 70))
+    _attn_case(cuda, dtype, n_heads, n_kv, hd, starts=[17, 200], news=[1, 1], window=40, decode=True, n_splits=1)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
