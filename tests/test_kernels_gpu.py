@@ -111,6 +111,10 @@ def test_gemv_float_streaming_form(cuda, M, N, K):
         ops.gemm_tn_simt(a, packed, act, ops.EPI_SWIGLU, 16)
         gate, up = ref[:, :inter], ref[:, inter:]
         assert rel_err(act.cpu(), (gate / (1 + torch.exp(-gate))) * up) <= 2e-6
+    # rows of a wider matrix (a strided view whose rows still start on 16-byte boundaries)
+    wide = torch.randn(M, K + 8, generator=g).to(cuda)
+    ops.gemm_tn_simt(wide[:, 8:], w, c, ops.EPI_STORE_F32)
+    assert rel_err(c.cpu(), wide[:, 8:].cpu().double() @ w.cpu().double().T) <= 2e-6
     assert int(ops.simt_error_word(cuda).item()) == 0
 
 
