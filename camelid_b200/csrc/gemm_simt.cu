@@ -329,6 +329,8 @@ gemv_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ 
 // of the same outputs.
 #define GV_WARPS 8
 #define GV_ROWS 32          // weight rows per tile
+#define GV_MAX_ROWS 64      // steps of up to this many rows take this form, 8 rows a block: beyond it the weights' way
+                            // into the SMs, once per group of 8 rows, costs more than the tiles of the many-row form
 // The weights come by TMA (cp.async.bulk.tensor into a ring of shared-memory stages, completion on
 // mbarriers), not by loads into registers: what a block
 // has on its way from HBM is the ring (RG_STAGES stages of 32 weight rows x 128 columns, 16 KB each, two
@@ -606,7 +608,7 @@ gemv_f32_ring_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_cons
 
 // Scratch the streaming form needs: tickets (ints, kept zero) in a first part of fixed size, which products of
 // every shape share, then one slot of MB x 32 sums per (tile + block) of each group of 8 rows. A step has at
-// most 4 groups; GV_TICKETS tickets cover half a million weight rows at four groups; more are refused.
+// most 8 groups; GV_TICKETS tickets cover a quarter of a million weight rows at eight groups; more are refused.
 #define GV_TICKETS 65536
 static RgShape rg_shape(int M, int n_wrows, int K) {
     RgShape sh;
@@ -766,19 +768,19 @@ static int launch_gemm(const void* A, int lda, const void* W, int ldw, void* C, 
 // A: [M, K] (row stride lda), W: [N, K] (or [2N, K] for SwiGLU; row stride ldw), C: [M, N] (ldc).
 // `scratch` (may be null): device memory of at least cml_gemv_f32_scratch_bytes(M, N, K, epilogue) bytes whose
 // first part (the tickets) is zero before the first call and left zero; with it and `err` (set to 8 if a bounded
-// wait of that form runs out), float products of at most 32 rows whose sizes allow 16-byte loads take the
+// wait of that form runs out), float products of at most 64 rows whose sizes allow 16-byte loads take the
 // streaming form.
 extern "C" int cml_gemm_tn_simt(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
                                 int dtype, int epilogue, int group, void* scratch, int* err, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == CML_DTYPE_F32 && M <= 32 && scratch != nullptr && err != nullptr && K >= 128 && (K & 3) == 0 && (lda & 3) == 0 &&
+    if (dtype == CML_DTYPE_F32 && M <= GV_MAX_ROWS && scratch != nullptr && err != nullptr && K >= 128 && (K & 3) == 0 && (lda & 3) == 0 &&
         (ldw & 3) == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0 &&
         (epilogue != EPI_SWIGLU || (group == GV_ROWS / 2 && N % (GV_ROWS / 2) == 0)))
         return launch_gemv_f32_ring(A, lda, W, ldw, C, ldc, M, N, K, epilogue, scratch, err, s);
     if (dtype == CML_DTYPE_F32 && M <= 32) return launch_gemv_f32(A, lda, W, ldw, C, ldc, M, N, K, epilogue, group, s);
-    if (dtype == CML_DTYPE_F32 && M >= 64 && (K & 3) == 0 && (lda & 3) == 0 && (ldw & 3) == 0 &&
+    if (dtype == CML_DTYPE_F32 && M > GV_MAX_ROWS && (K & 3) == 0 && (lda & 3) == 0 && (ldw & 3) == 0 &&
         (((uintptr_t)A | (uintptr_t)W) & 15) == 0 && (epilogue != EPI_SWIGLU || (group == 16 && N % 16 == 0)))
         return launch_gemm_f32_big(A, lda, W, ldw, C, ldc, M, N, K, epilogue, s);
     if (dtype == CML_DTYPE_F32) return launch_gemm<float>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, group, s);

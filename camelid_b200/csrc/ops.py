@@ -571,7 +571,7 @@ def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
     scratch = None
     if err is None:
         err = simt_error_word(a.device)
-    if a.dtype == torch.float32 and M <= 32:      # the streaming form for few float rows: tickets and split sums
+    if a.dtype == torch.float32 and M <= 64:      # the streaming form for few float rows: tickets and split sums
         f = _fn("gemm_simt", "cml_gemv_f32_scratch_bytes")
         f.restype = c_long
         scratch = zeroed_scratch(a.device, "gemv_f32", int(f(M, N, K, epilogue)))

@@ -76,9 +76,9 @@ def test_gemm_simt_epilogues(cuda, dtype, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 3072, 2048), (8, 2048, 2048), (8, 2048, 8192), (5, 517, 132), (32, 100, 640),
-                                   (17, 33, 4100), (2, 128256, 256), (8, 40, 128)])
+                                   (17, 33, 4100), (2, 128256, 256), (8, 40, 128), (64, 96, 640), (41, 2048, 2048)])
 def test_gemv_float_streaming_form(cuda, M, N, K):
-    """Float products of at most 32 rows whose sizes allow 16-byte loads: tiles of 32 weight rows,
+    """Float products of at most 64 rows whose sizes allow 16-byte loads: tiles of 32 weight rows,
     K split over blocks where there are few tiles, the splits summed in index order by the
     block that comes last. Every epilogue; tickets are left zero, so a second call is as good; a row's
     value does not depend on the other rows of the step."""
