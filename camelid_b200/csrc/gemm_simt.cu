@@ -690,11 +690,11 @@ static int launch_gemv_f32_ring(const void* A, int lda, const void* W, int ldw, 
     return cml_launch_status();
 }
 
-// Ranges of K a product of at most 8 float rows is cut into when its sums are left as partial sums: about as
+// Ranges of K a product of at most 64 float rows is cut into when its sums are left as partial sums: about as
 // many blocks as the device holds at a time (two per SM), ranges of at least two steps of 128 columns; 0 where
 // the sizes do not suit the streaming form.
 extern "C" int cml_gemv_f32_partial_splits(int M, int N, int K, int lda, int ldw) {
-    if (M < 1 || M > 8 || N < 1 || K < 256 || (K & 3) || (lda & 3) || (ldw & 3)) return 0;
+    if (M < 1 || M > GV_MAX_ROWS || N < 1 || K < 256 || (K & 3) || (lda & 3) || (ldw & 3)) return 0;
     const int tiles = (N + GV_ROWS - 1) / GV_ROWS, steps = (K + RG_KS - 1) / RG_KS;
     int splits = max(1, min(2 * cml_sm_count() / tiles, steps / 2));
     const int per = (steps + splits - 1) / splits;
@@ -702,7 +702,7 @@ extern "C" int cml_gemv_f32_partial_splits(int M, int N, int K, int lda, int ldw
 }
 
 // part[r][m][n] (float, row stride ldc, ranges split_stride apart) = the sum of A[m][k] * W[n][k] over range r of K,
-// for r < splits = cml_gemv_f32_partial_splits(...). At most 8 rows.
+// for r < splits = cml_gemv_f32_partial_splits(...). At most 64 rows (groups of 8 on blocks of their own).
 extern "C" int cml_gemv_f32_partial(const void* A, int lda, const void* W, int ldw, void* part, int ldc, long split_stride,
                                     int splits, int M, int N, int K, int* err, void* stream) {
     constexpr int MB = 8;
@@ -721,7 +721,7 @@ extern "C" int cml_gemv_f32_partial(const void* A, int lda, const void* W, int l
     const size_t smem = (size_t)RG_STAGES * (GV_ROWS + MB) * RG_KS * sizeof(float);
     cudaError_t e = cml_allow_smem<gemv_f32_ring_kernel<MB, EPI_STORE_F32>>(smem);
     if (e != cudaSuccess) return (int)e;
-    launch_pdl(gemv_f32_ring_kernel<MB, EPI_STORE_F32>, dim3(sh.blocks, 1), dim3((GV_WARPS + 1) * 32), smem,
+    launch_pdl(gemv_f32_ring_kernel<MB, EPI_STORE_F32>, dim3(sh.blocks, (M + MB - 1) / MB), dim3((GV_WARPS + 1) * 32), smem,
                (cudaStream_t)stream, mw, ma, (float*)part, ldc, sh, (float*)nullptr, (int*)nullptr, err);
     return cml_launch_status();
 }

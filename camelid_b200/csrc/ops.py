@@ -582,7 +582,7 @@ def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
 
 def gemv_f32_partial_splits(a: torch.Tensor, w: torch.Tensor) -> int:
     """Ranges of K that ``gemv_f32_partial`` cuts a[M, K] @ w[N, K]^T into; 0 where it does not take
-    the product (more than 8 rows, not float, sizes that do not allow 16-byte copies)."""
+    the product (more than 64 rows, not float, sizes that do not allow 16-byte copies)."""
     if a.dtype != torch.float32 or w.dtype != torch.float32 or a.stride(1) != 1 or w.stride(1) != 1:
         return 0
     if (a.data_ptr() | w.data_ptr()) & 15:
@@ -592,7 +592,7 @@ def gemv_f32_partial_splits(a: torch.Tensor, w: torch.Tensor) -> int:
 
 
 def gemv_f32_partial(a: torch.Tensor, w: torch.Tensor, part: torch.Tensor, err: torch.Tensor):
-    """part[r] = a @ w^T over range r of K (float, at most 8 rows): the product's sums left as
+    """part[r] = a @ w^T over range r of K (float, at most 64 rows): the product's sums left as
     partial sums for the kernel that reads them next, with no pass over them in between."""
     _dev(a, w, part, err)
     splits, M, N = part.shape

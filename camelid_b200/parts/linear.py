@@ -137,8 +137,8 @@ def partial_sums(ctx, x: torch.Tensor, w: torch.Tensor, name: str, row_scale=Non
     (``ops.RowScale``): what the rows of ``x`` still lack; applied if a result is returned."""
     rows = x.shape[0]
     if not ops.gemm_tc_usable(x, w):
-        # float: a step of at most 8 rows leaves the K ranges of its streaming blocks as they are
-        splits = ops.gemv_f32_partial_splits(x, w) if rows <= 8 else 0
+        # float: a step of at most 64 rows leaves the K ranges of its streaming blocks as they are
+        splits = ops.gemv_f32_partial_splits(x, w) if rows <= 64 else 0
         if splits < 2:
             return None
         if row_scale is not None:

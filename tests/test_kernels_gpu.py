@@ -119,7 +119,7 @@ def test_gemv_float_streaming_form(cuda, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 3072, 2048), (8, 2048, 2048), (8, 2048, 8192), (5, 517, 260), (3, 33, 4100),
-                                   (8, 40, 256), (7, 100, 648)])
+                                   (8, 40, 256), (7, 100, 648), (64, 2048, 2048), (19, 96, 1024)])
 def test_gemv_float_partial_sums(cuda, M, N, K):
     """The streaming float product with its K ranges left as partial sums: their sum in range order is the
     product; ranges do not overlap or leave a gap (a row of ones against weights that name their column)."""
@@ -140,7 +140,7 @@ def test_gemv_float_partial_sums(cuda, M, N, K):
     per = part[:, 0, 0].cpu().double()
     assert (per > 0).all() or K < 256, per                   # no empty range
     assert float(per.sum()) == K * (K - 1) / 2               # exact in float up to 2^24 per range
-    assert ops.gemv_f32_partial_splits(torch.randn(9, K, device=cuda), w) == 0       # more than 8 rows: not taken
+    assert ops.gemv_f32_partial_splits(torch.randn(65, K, device=cuda), w) == 0      # more than 64 rows: not taken
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
