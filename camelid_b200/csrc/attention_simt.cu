@@ -288,12 +288,13 @@ __global__ void __launch_bounds__(128) attn_decode_simt_kernel(AttnParams p) {
     const int sb = b_first + split * per;
     const int se = min(b_last, sb + per);
 
-    float m[H], l[H];
+    float m[H], l_own[HL];                               // l_own: the sums of this lane's keys for its own heads
     float acc[H][NACC];
+#pragma unroll
+    for (int hl = 0; hl < HL; ++hl) l_own[hl] = 0.f;
 #pragma unroll
     for (int h = 0; h < H; ++h) {
         m[h] = -CUDART_INF_F;
-        l[h] = 0.f;
 #pragma unroll
         for (int i = 0; i < NACC; ++i) acc[h][i] = 0.f;
     }
@@ -309,11 +310,12 @@ __global__ void __launch_bounds__(128) attn_decode_simt_kernel(AttnParams p) {
     // Pages below the token's own were written by earlier steps: the first one (two, with two stages) is asked
     // for before the wait on the kernel that writes this step's key and value; the block table, positions and
     // lengths are the step's inputs, in place before its first kernel started.
-    bool early[2] = {false, false};
-    if (n_stages == 2) {
+    constexpr int MAX_STAGES = 2;
+    bool early[MAX_STAGES] = {false, false};
+    if (n_stages > 1) {
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            early[u] = sb + u < se && (sb + u + 1) * CML_PAGE <= pos;
+        for (int u = 0; u < MAX_STAGES; ++u) {
+            early[u] = u < n_stages && sb + u < se && (sb + u + 1) * CML_PAGE <= pos;
             if (early[u]) attn_stage_page<T>(smem + u * stage_floats, smem + u * stage_floats + CML_PAGE * hd, kp, vp, page_base(sb + u), hd, mask);
         }
     }
@@ -325,16 +327,18 @@ __global__ void __launch_bounds__(128) attn_decode_simt_kernel(AttnParams p) {
             Qs[h * qld + d] = hg0 + h < group ? to_f32(q[(size_t)row * p.q_stride + (head0 + h) * hd + d]) : 0.f;
         }
     }
-    if (n_stages == 2) {
+    if (n_stages > 1) {
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < MAX_STAGES; ++u) {
+            if (u >= n_stages) break;
             if (!early[u] && sb + u < se)
                 attn_stage_page<T>(smem + u * stage_floats, smem + u * stage_floats + CML_PAGE * hd, kp, vp, page_base(sb + u), hd, mask);
             cp_async_commit_f();                          // one group per page, empty ones included
         }
     }
+    int stage = 0;                                        // of page b
     for (int b = sb; b < se; ++b) {
-        float* Ks = smem + (n_stages == 2 ? ((b - sb) & 1) * stage_floats : 0);
+        float* Ks = smem + stage * stage_floats;
         float* Vs = Ks + CML_PAGE * hd;
         if (n_stages == 2) {
             cp_async_wait_f<1>();                         // all but the newest group: page b is here
@@ -371,44 +375,53 @@ __global__ void __launch_bounds__(128) attn_decode_simt_kernel(AttnParams p) {
             }
 #pragma unroll
             for (int hl = 0; hl < HL; ++hl) sc[hl] += sd[hl];
-            float t[HL], mn_own[HL], corr[H];
+            // The reference m[h] the exponentials are taken against follows the maximum lazily: it moves only
+            // when a score of the warp stands more than 5.5 above it (probabilities up to e^5.5 are harmless in
+            // float), which one vote finds out; the reductions over lanes, the rescaling of the sums and output rows
+            // then happen on the first page and rarely after. Numerator and denominator share the reference, so
+            // the result is the same. A lane sums the probabilities of its own keys; the lanes meet at the end.
+            float t[HL];
+            bool move = false;
 #pragma unroll
             for (int hl = 0; hl < HL; ++hl) {
                 t[hl] = in ? sc[hl] * p.scale : -CUDART_INF_F;
-                float bm = t[hl];                                    // maximum over the 16 keys of this half warp
+                const float mo = low ? m[hl] : m[HL + hl];
+                move = move || (in && (mo == -CUDART_INF_F || t[hl] > mo + 5.5f));
+            }
+            if (__any_sync(0xffffffffu, move)) {
 #pragma unroll
-                for (int o = 8; o >= 1; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
-                const float other = __shfl_xor_sync(0xffffffffu, bm, 16);
-                const float bm_lo = low ? bm : other, bm_hi = low ? other : bm;      // heads hl and HL + hl
-                const float mn_lo = fmaxf(m[hl], bm_lo), mn_hi = fmaxf(m[HL + hl], bm_hi);
-                // a half warp whose heads see no key here keeps -inf: corr is 0 * nothing, p is 0
-                corr[hl] = (m[hl] == -CUDART_INF_F) ? 0.f : expf(m[hl] - mn_lo);
-                corr[HL + hl] = (m[HL + hl] == -CUDART_INF_F) ? 0.f : expf(m[HL + hl] - mn_hi);
-                m[hl] = mn_lo;
-                m[HL + hl] = mn_hi;
-                mn_own[hl] = low ? mn_lo : mn_hi;
+                for (int hl = 0; hl < HL; ++hl) {
+                    float bm = t[hl];                                // maximum over the 16 keys of this half warp
+#pragma unroll
+                    for (int o = 8; o >= 1; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+                    const float other = __shfl_xor_sync(0xffffffffu, bm, 16);
+                    const float bm_lo = low ? bm : other, bm_hi = low ? other : bm;  // heads hl and HL + hl
+                    const float mn_lo = fmaxf(m[hl], bm_lo), mn_hi = fmaxf(m[HL + hl], bm_hi);
+                    const float c_lo = (m[hl] == -CUDART_INF_F) ? 0.f : expf(m[hl] - mn_lo);
+                    const float c_hi = (m[HL + hl] == -CUDART_INF_F) ? 0.f : expf(m[HL + hl] - mn_hi);
+                    m[hl] = mn_lo;
+                    m[HL + hl] = mn_hi;
+                    l_own[hl] *= low ? c_lo : c_hi;
+#pragma unroll
+                    for (int i = 0; i < NACC; ++i) {
+                        acc[hl][i] *= c_lo;
+                        acc[HL + hl][i] *= c_hi;
+                    }
+                }
             }
             float* pw = Ps + warp * 16 * H;
 #pragma unroll
             for (int hl = 0; hl < HL; ++hl) {
-                const float pr = in ? expf(t[hl] - mn_own[hl]) : 0.f;
+                const float pr = in ? expf(t[hl] - (low ? m[hl] : m[HL + hl])) : 0.f;
                 pw[(lane & 15) * H + (low ? 0 : HL) + hl] = pr;
-                float sum = pr;
-#pragma unroll
-                for (int o = 8; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-                const float other = __shfl_xor_sync(0xffffffffu, sum, 16);
-                l[hl] = l[hl] * corr[hl] + (low ? sum : other);
-                l[HL + hl] = l[HL + hl] * corr[HL + hl] + (low ? other : sum);
+                l_own[hl] += pr;
             }
-#pragma unroll
-            for (int h = 0; h < H; ++h)
-#pragma unroll
-                for (int i = 0; i < NACC; ++i) acc[h][i] *= corr[h];
             __syncwarp();
-            const int jend = min(16, kend - (b * CML_PAGE + 16 * warp));        // value rows past the end may hold anything
-#pragma unroll 8
+            // value rows past the end may hold anything: they are read (every load is unconditional, so that all
+            // of them can be in flight together) and replaced by zero
+            const int jend = kend - (b * CML_PAGE + 16 * warp);
+#pragma unroll
             for (int j = 0; j < 16; ++j) {
-                if (j >= jend) break;
                 float pj[H];
                 if (H == 4) {
                     const float4 v4 = *reinterpret_cast<const float4*>(pw + j * 4);
@@ -420,23 +433,34 @@ __global__ void __launch_bounds__(128) attn_decode_simt_kernel(AttnParams p) {
                 const float* vr = Vs + (16 * warp + j) * hd;
 #pragma unroll
                 for (int i = 0; i < NACC; ++i) {
-                    const int d = lane + 32 * i;
-                    if (d < hd) {
-                        const float v = vr[d];
+                    const int d = min(lane + 32 * i, hd - 1);        // a clamped lane's sums are never stored
+                    const float vv = vr[d];
+                    const float v = j < jend ? vv : 0.f;
 #pragma unroll
-                        for (int h = 0; h < H; ++h) acc[h][i] = fmaf(pj[h], v, acc[h][i]);
-                    }
+                    for (int h = 0; h < H; ++h) acc[h][i] = fmaf(pj[h], v, acc[h][i]);
                 }
             }
             __syncwarp();
         }
         __syncthreads();               // this stage is free for the page after the next
-        if (n_stages == 2) {
-            if (b + 2 < se) attn_stage_page<T>(Ks, Vs, kp, vp, page_base(b + 2), hd, mask);
+        if (n_stages > 1) {
+            if (b + n_stages < se) attn_stage_page<T>(Ks, Vs, kp, vp, page_base(b + n_stages), hd, mask);
             cp_async_commit_f();
+            stage = stage + 1 == n_stages ? 0 : stage + 1;
         }
     }
     cp_async_wait_f<0>();
+    // the lanes' sums over the 16 keys of a half warp, then every lane has those of all heads
+    float l[H];
+#pragma unroll
+    for (int hl = 0; hl < HL; ++hl) {
+        float sum = l_own[hl];
+#pragma unroll
+        for (int o = 8; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float other = __shfl_xor_sync(0xffffffffu, sum, 16);
+        l[hl] = low ? sum : other;
+        l[HL + hl] = low ? other : sum;
+    }
     // the four warps' ranges of keys into one, in warp order
 #pragma unroll
     for (int h = 0; h < H; ++h) {
@@ -478,6 +502,10 @@ __global__ void __launch_bounds__(128) attn_decode_simt_kernel(AttnParams p) {
     }
 }
 
+// Pages a block of the decode kernel keeps in shared memory: two, or one where two do not fit. (Three, with two
+// blocks an SM instead of three, were slower at batch 8: 1.65 against 1.60 ms a float decode step.)
+static int cml_attn_decode_stages(size_t stage, size_t rest) { return 2 * stage + rest <= 200 * 1024 ? 2 : 1; }
+
 template <typename T>
 static int launch_attn(const AttnParams& p_in, int heads_per_warp, int n_tiles, int n_rows, cudaStream_t s) {
     const int hd = p_in.head_dim;
@@ -490,7 +518,7 @@ static int launch_attn(const AttnParams& p_in, int heads_per_warp, int n_tiles, 
         const size_t rest = ((size_t)H * (hd + 4) + 64 * H + (size_t)4 * H * (2 + hd)) * sizeof(float);
         const size_t stage = (size_t)2 * CML_PAGE * hd * sizeof(float);
         AttnParams p = p_in;
-        p.n_stages = 2 * stage + rest <= 200 * 1024 ? 2 : 1;
+        p.n_stages = cml_attn_decode_stages(stage, rest);
         const size_t smem = p.n_stages * stage + rest;
         if (smem > 227 * 1024) return CML_ERR_BAD_SIZE;
         const int nacc = (hd + 31) / 32;
@@ -576,6 +604,7 @@ extern "C" long cml_attn_simt_smem_bytes(int head_dim, int rows_per_tile, int he
         rest = ((size_t)heads_per_cta * (head_dim + 4) + 64 * heads_per_cta + (size_t)4 * heads_per_cta * (2 + head_dim)) * sizeof(float);
     else
         rest = (size_t)rows_per_tile * heads_per_cta * (head_dim + CML_PAGE) * sizeof(float);
+    if (heads_per_warp == 0) return (long)(cml_attn_decode_stages(stage, rest) * stage + rest);
     return (long)((2 * stage + rest <= 200 * 1024 ? 2 : 1) * stage + rest);
 }
 extern "C" int cml_attn_paged_simt(const void* q, int q_stride, void* out, int out_stride, int dtype,
