@@ -3,9 +3,11 @@
 // This is the matrix product of the true 32-bit path (plain FMA, no reduced-precision
 // tensor mode) and the one that takes every shape the tensor-core kernel refuses. It stands
 // where the reference runs q8_gemv / q8_gemm_batched (src/cuda_resident.rs:230, :1494) with
-// their fused residual add (:304-307). Each output element sums k = 0..K-1 in order, in
-// chunks of 16, whatever M is and wherever the element lies in its tile: the value of a
-// row does not depend on which other rows are in the batch.
+// their fused residual add (:304-307). In the tiled forms each output element sums
+// k = 0..K-1 in order wherever it lies in its tile; in the streaming form for few rows the
+// order is fixed by N, K and the device's block count. Either way the value of a row does
+// not depend on which other rows are in the step, only on which form the step's row count
+// selects (up to 64 rows: streaming; more: tiles).
 //
 // Epilogues: store in the input type; store float; add into a float matrix (the residual
 // stream); SwiGLU, where output column j takes weight rows gate(j) and up(j) of a packed
