@@ -45,24 +45,39 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int ld, int
     // parts of whole groups of four columns, so that aligned rows are read 16 bytes at a time
     const int per = ((vocab + gridDim.x - 1) / gridDim.x + 3) & ~3;
     const int begin = min(vocab, blockIdx.x * per), end = min(vocab, begin + per);
-    unsigned long long best = 0ull;
+    // A thread walks its columns in ascending order, so "strictly larger" keeps the lowest index among equals;
+    // the 64-bit word is made once, at the end.
+    float bv = -CUDART_INF_F;
+    int bi = -1;
     bool bad = false;
     auto take = [&](float v, int i) {
-        if (!isfinite(v)) bad = true;
-        const unsigned long long key = composite_key(v, i);
-        best = key > best ? key : best;
+        bad = bad || !(fabsf(v) < CUDART_INF_F);              // infinite or not a number
+        if (v > bv || bi < 0) {
+            bv = v;
+            bi = i;
+        }
     };
     if ((((uintptr_t)r) & 15) == 0) {
         const int end4 = begin + ((end - begin) & ~3);
-        for (int i = begin + 4 * threadIdx.x; i < end4; i += 4 * blockDim.x) {
-            const float4 v = *reinterpret_cast<const float4*>(r + i);
-            take(v.x, i); take(v.y, i + 1); take(v.z, i + 2); take(v.w, i + 3);
+        // four loads of 16 bytes in flight per thread (unconditional, of a clamped place), then their values
+        for (int i0 = begin + 4 * threadIdx.x; i0 < end4; i0 += 16 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const float4*>(r + min(i0 + u * 4 * (int)blockDim.x, end4 - 4));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * 4 * (int)blockDim.x;
+                if (i < end4) {
+                    take(v[u].x, i); take(v[u].y, i + 1); take(v[u].z, i + 2); take(v[u].w, i + 3);
+                }
+            }
         }
         for (int i = end4 + threadIdx.x; i < end; i += blockDim.x) take(r[i], i);
     } else {
         for (int i = begin + threadIdx.x; i < end; i += blockDim.x) take(r[i], i);
     }
     if (bad) atomicOr(err, SAMPLE_ERR_NONFINITE);
+    unsigned long long best = bi >= 0 ? composite_key(bv + 0.0f, bi) : 0ull;      // -0 as +0: equal, the lower index wins
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -86,12 +101,17 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int ld, int
     }
 }
 
+// Blocks per row: enough for two a multiprocessor over all rows and for at most two rounds of four 16-byte loads
+// a thread (8,192 columns a block), none with less than 2,048 columns.
+static int argmax_blocks(int rows, int vocab) {
+    return max(1, min(min(64, vocab / 2048), max((2 * cml_sm_count() + rows - 1) / rows, (vocab + 8191) / 8192)));
+}
+
 extern "C" int cml_argmax_rows(const float* logits, int ld, int rows, int vocab, int* out, int* err,
                                unsigned long long* scratch, void* stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0 || rows > 65535) return CML_ERR_BAD_SIZE;
-    // enough blocks for two a multiprocessor over all rows, none with less than 2,048 columns
-    const int blocks = max(1, min(min(64, vocab / 2048), (2 * cml_sm_count() + rows - 1) / rows));
+    const int blocks = argmax_blocks(rows, vocab);
     launch_pdl(argmax_rows_kernel, dim3(blocks, rows), dim3(256), 0, (cudaStream_t)stream, logits, ld, vocab, out, err, scratch);
     return cml_launch_status();
 }
@@ -421,7 +441,7 @@ extern "C" int cml_argmax_rows_static(const float* logits, int ld, int rows, int
         refuse(msg, msg_len, "cml_argmax_rows_static: clearing the scratch words failed");
         return (int)e;
     }
-    const int blocks = max(1, min(min(64, vocab / 2048), (2 * cml_sm_count() + rows - 1) / rows));
+    const int blocks = argmax_blocks(rows, vocab);
     argmax_rows_kernel<<<dim3(blocks, rows), 256, 0, s>>>(logits, ld, vocab, out, err, words);
     e = cudaGetLastError();
     if (e != cudaSuccess) refuse(msg, msg_len, "cml_argmax_rows_static: the kernel launch failed");
