@@ -9,8 +9,10 @@
 // p >= min_p * p_max and renormalises; top_p keeps the shortest prefix whose cumulative
 // probability reaches top_p and renormalises; the token is the first whose cumulative
 // probability exceeds the draw. The reference sorts; here every stage is a selection in the
-// same total order, found by descending the bits of a 64-bit key (orderable logit bits,
-// then inverted index) with per-digit histograms of weight, so no sort is needed. Sums are
+// same total order: in two passes over the row where that settles it (bins of the distance
+// from the maximum locate the crossing, the one bin's keys are sorted and walked), else by
+// descending the bits of a 64-bit key (orderable logit bits, then inverted index) with
+// per-digit histograms of weight. Sums are
 // kept in double; the reference's sequential float sums can differ from them in the last
 // bits, which moves a decision only when the draw or top_p lies on a boundary.
 #include "common.cuh"
@@ -216,6 +218,227 @@ __device__ void select_by_mass(const float* row, int vocab, unsigned long long f
     *out_cum = before + w;
 }
 
+// ------------------------------------------------------------------------------------
+// The same selection in two passes over the row instead of eight, for the usual case. The order of the
+// candidates is by value descending, so by x = max / T - value / T ascending. A first pass counts the
+// candidates and adds their weights (in float: only to find the place) into 2,048 bins of x; the bin in which
+// the cumulative weight reaches the target is found from those. A second pass adds, in double, the weights of
+// all candidates ordered before that bin and collects the bin's own keys, which are then sorted and walked
+// exactly as the selection above walks them. If the exact sums put the crossing into a neighbouring bin, that
+// bin is taken and the second pass repeated. A bin with more keys than the list holds is divided into 2,048
+// bins of its own (twice at most: then its keys are equal values, and the selection above, which orders equal
+// values by index digit by digit, takes over).
+#define FS_BINS 2048
+#define FS_CAP 2048
+struct FastShared {
+    unsigned int cnt[FS_BINS];
+    float mass[FS_BINS];
+    unsigned long long list[FS_CAP];
+    float lp[FS_CAP];
+    double dred[33];
+    unsigned int ured[33];
+    unsigned int n_list;
+    int bin;
+    int status;              // 0: walk again with `bin`; 1: found; 2: divide the bin; 3: give up (fall back)
+    unsigned long long key;
+    double cum;
+};
+
+__device__ __forceinline__ float value_of_key(unsigned long long key) {
+    const unsigned int u = (unsigned int)(key >> 32);
+    return __uint_as_float((u & 0x80000000u) ? (u & 0x7FFFFFFFu) : ~u);
+}
+
+// Returns true and the choice if the fast way settled it, false if the caller has to run select_by_mass.
+// `xof(v)` is the place of a value in the order (smaller first, monotone in v), `weight(v, i)` as above.
+template <typename XFn, typename WeightFn>
+__device__ bool select_fast(const float* row, int vocab, unsigned long long floor_key, double target, int strict,
+                            XFn xof, float x_max, WeightFn weight, FastShared* fs, unsigned long long* out_key,
+                            double* out_cum) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float lo = 0.f, inv_w = 64.0f;                       // bins of 1/64 from 0; the last one takes all beyond
+    bool open_end = true;
+    for (int level = 0; level < 3; ++level) {
+        // pass 1: counts and approximate weights of the candidates per bin of [lo, ...)
+        for (int b = threadIdx.x; b < FS_BINS; b += blockDim.x) fs->cnt[b] = 0u, fs->mass[b] = 0.f;
+        __syncthreads();
+        auto bin_of = [&](float v) {                     // -1: ordered before the range; FS_BINS: after it
+            const float r = (xof(v) - lo) * inv_w;
+            if (r < 0.f) return -1;
+            if (r >= (float)FS_BINS) return open_end ? FS_BINS - 1 : FS_BINS;
+            return (int)r;
+        };
+        double head = 0.0;                               // approximate weight ordered before the range
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float v = row[i];
+            if (composite_key(v, i) < floor_key) continue;
+            const int b = bin_of(v);
+            if (b < 0) head += (double)weight(v, i);
+            else if (b < FS_BINS) {
+                atomicAdd(&fs->cnt[b], 1u);
+                atomicAdd(&fs->mass[b], weight(v, i));
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) head += __shfl_xor_sync(0xffffffffu, head, o);
+        if (lane == 0) fs->dred[warp] = head;
+        __syncthreads();
+        if (warp == 0) {
+            // a lane sums 64 consecutive bins; the lane in which the cumulative weight reaches the target walks its own
+            double acc0 = 0.0;
+            for (int w = 0; w < nw; ++w) acc0 += fs->dred[w];
+            constexpr int PER = FS_BINS / 32;
+            double mine = 0.0;
+            int my_last = -1;
+            for (int b = lane * PER; b < (lane + 1) * PER; ++b) {
+                if (fs->cnt[b] == 0u) continue;
+                my_last = b;
+                mine += (double)fs->mass[b];
+            }
+            double incl = mine;                          // inclusive sum over lanes
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const double t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            const double upto = acc0 + incl;             // weight up to the end of this lane's bins
+            const bool reach = my_last >= 0 && (strict ? (upto > target) : (upto >= target));
+            const unsigned int who = __ballot_sync(0xffffffffu, reach);
+            int last = my_last;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
+            int chosen = -1;
+            if (who != 0u && lane == __ffs(who) - 1) {
+                double acc = upto - mine;
+                for (int b = lane * PER; b < (lane + 1) * PER; ++b) {
+                    if (fs->cnt[b] == 0u) continue;
+                    const double inc = acc + (double)fs->mass[b];
+                    if (strict ? (inc > target) : (inc >= target)) { chosen = b; break; }
+                    acc = inc;
+                }
+                if (chosen < 0) chosen = my_last;        // rounding between the two sums: the lane's last bin
+                fs->bin = chosen;
+                fs->status = 0;
+            }
+            if (who == 0u && lane == 0) {
+                fs->bin = last;                          // never reached: the last bin with candidates
+                fs->status = last < 0 ? 3 : 0;           // no candidate in the range at all: not ours
+            }
+        }
+        __syncthreads();
+        if (fs->status == 3) return false;
+        // pass 2, repeated while the exact sums move the crossing to a neighbouring bin
+        for (int tries = 0; tries < 6; ++tries) {
+            const int bsel = fs->bin;
+            if (threadIdx.x == 0) fs->n_list = 0u;
+            __syncthreads();
+            double before = 0.0;
+            unsigned int after = 0u;
+            for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+                const float v = row[i];
+                const unsigned long long key = composite_key(v, i);
+                if (key < floor_key) continue;
+                const int b = bin_of(v);
+                if (b < bsel) before += (double)weight(v, i);
+                else if (b == bsel) {
+                    const unsigned int slot = atomicAdd(&fs->n_list, 1u);
+                    if (slot < FS_CAP) fs->list[slot] = key;
+                } else ++after;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                before += __shfl_xor_sync(0xffffffffu, before, o);
+                after += __shfl_xor_sync(0xffffffffu, after, o);
+            }
+            if (lane == 0) fs->dred[warp] = before, fs->ured[warp] = after;
+            __syncthreads();
+            const unsigned int n = fs->n_list;
+            if (n > FS_CAP) {                            // too many for the list: divide this bin
+                if (threadIdx.x == 0) fs->status = 2;
+                __syncthreads();
+                break;
+            }
+            // sort the bin's keys, largest first (bitonic over the next power of two, padded with zeros)
+            unsigned int m = 1u;
+            while (m < n) m <<= 1;
+            for (unsigned int i = n + threadIdx.x; i < m; i += blockDim.x) fs->list[i] = 0ull;
+            __syncthreads();
+            for (unsigned int k = 2; k <= m; k <<= 1) {
+                for (unsigned int j = k >> 1; j > 0; j >>= 1) {
+                    for (unsigned int i = threadIdx.x; i < m; i += blockDim.x) {
+                        const unsigned int l = i ^ j;
+                        if (l > i) {
+                            const unsigned long long a = fs->list[i], c = fs->list[l];
+                            const bool desc = (i & k) == 0;
+                            if (desc ? (a < c) : (a > c)) { fs->list[i] = c; fs->list[l] = a; }
+                        }
+                    }
+                    __syncthreads();
+                }
+            }
+            for (unsigned int i = threadIdx.x; i < n; i += blockDim.x) {
+                const unsigned long long key = fs->list[i];
+                fs->lp[i] = weight(value_of_key(key), (int)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull)));
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                double cum = 0.0;
+                unsigned int more = 0u;
+                for (int w = 0; w < nw; ++w) cum += fs->dred[w], more += fs->ured[w];
+                int st = -1;
+                if (strict ? (cum > target) : (cum >= target)) {
+                    // the crossing lies before this bin: the nearest bin with candidates before it, if any
+                    int b = bsel - 1;
+                    while (b >= 0 && fs->cnt[b] == 0u) --b;
+                    if (b >= 0) { fs->bin = b; st = 0; }
+                    else if (lo > 0.f) st = 3;               // before a divided bin's range: not ours to settle
+                }
+                if (st < 0) {
+                    unsigned int i = 0;
+                    for (; i < n; ++i) {
+                        cum += (double)fs->lp[i];
+                        if (strict ? (cum > target) : (cum >= target)) break;
+                    }
+                    if (i < n) { fs->key = fs->list[i]; fs->cum = cum; st = 1; }
+                    else if (more > 0u) {
+                        int b = bsel + 1;
+                        while (b < FS_BINS && fs->cnt[b] == 0u) ++b;
+                        if (b < FS_BINS) { fs->bin = b; st = 0; }
+                        else st = 3;                         // candidates after the range: not ours to settle
+                    } else if (n > 0u) { fs->key = fs->list[n - 1]; fs->cum = cum; st = 1; }   // never reached: the last candidate
+                    else st = 3;
+                }
+                fs->status = st;
+            }
+            __syncthreads();
+            if (fs->status != 0) break;
+            if (tries == 5) {
+                if (threadIdx.x == 0) fs->status = 3;
+                __syncthreads();
+            }
+        }
+        const int st = fs->status;
+        if (st == 1) {
+            *out_key = fs->key;
+            *out_cum = fs->cum;
+            __syncthreads();
+            return true;
+        }
+        if (st != 2) return false;
+        // divide the chosen bin: its range of x in FS_BINS bins (the open last bin up to the largest x of the row)
+        const int bsel = fs->bin;
+        const float blo = lo + (float)bsel / inv_w;
+        const float bhi = (open_end && bsel == FS_BINS - 1) ? x_max : lo + (float)(bsel + 1) / inv_w;
+        __syncthreads();
+        if (!(bhi > blo)) return false;
+        lo = blo;
+        inv_w = (float)FS_BINS / (bhi - blo);
+        open_end = false;
+        if (!isfinite(inv_w)) return false;
+    }
+    return false;
+}
+
 struct SampleParams {
     float temperature;
     int top_k;          // 0: off
@@ -223,44 +446,60 @@ struct SampleParams {
     float min_p;        // <= 0: off
 };
 
-__global__ void __launch_bounds__(SAMPLE_THREADS)
+__global__ void __launch_bounds__(SAMPLE_THREADS, 1)
 sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SampleParams sp,
                    const float* __restrict__ draws, int* __restrict__ out, int* __restrict__ err) {
     __shared__ SelectShared sh;
+    __shared__ FastShared fs;
     __shared__ float red[33];
+    __shared__ float red2[33];
     __shared__ double dred[33];
     __shared__ unsigned long long kred[33];
     const float* row = logits + (size_t)blockIdx.x * ld;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
 
-    // maximum logit and finiteness
-    float mx = -CUDART_INF_F;
+    // maximum and minimum logit and finiteness
+    float mx = -CUDART_INF_F, mn = CUDART_INF_F;
     bool bad = false;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
         const float v = row[i];
         if (!isfinite(v)) bad = true;
         mx = fmaxf(mx, v);
+        mn = fminf(mn, v);
     }
     mx = warp_max(mx);
-    if (lane == 0) red[warp] = mx;
+    mn = -warp_max(-mn);
+    if (lane == 0) red[warp] = mx, red2[warp] = mn;
     if (bad) atomicOr(err, SAMPLE_ERR_NONFINITE);
     __syncthreads();
     if (warp == 0) {
         float t = lane < nw ? red[lane] : -CUDART_INF_F;
+        float u = lane < nw ? red2[lane] : CUDART_INF_F;
         t = warp_max(t);
-        if (lane == 0) red[32] = t;
+        u = -warp_max(-u);
+        if (lane == 0) red[32] = t, red2[32] = u;
     }
     __syncthreads();
     mx = red[32];
+    mn = red2[32];
     const float T = sp.temperature;
     const float max_scaled = mx / T;
+    // the place of a value in the order, as a distance from the maximum (what the exponential is taken of)
+    auto xof = [=](float v) { return max_scaled - v / T; };
+    const float x_max = max_scaled - mn / T;
+    if (red[32] != red[32] || !isfinite(x_max)) {          // not a number, or infinite: the error is set; no choice
+        if (threadIdx.x == 0) out[blockIdx.x] = 0;
+        return;
+    }
 
     unsigned long long floor_key = 0ull;
     unsigned long long key;
     double cum;
     // top_k: the k-th candidate in order becomes the floor
     if (sp.top_k > 0 && sp.top_k < vocab) {
-        select_by_mass(row, vocab, 0ull, (double)sp.top_k, 0, [](float, int) { return 1.0f; }, &sh, &key, &cum);
+        auto one = [](float, int) { return 1.0f; };
+        if (!select_fast(row, vocab, 0ull, (double)sp.top_k, 0, xof, x_max, one, &fs, &key, &cum))
+            select_by_mass(row, vocab, 0ull, (double)sp.top_k, 0, one, &sh, &key, &cum);
         floor_key = key;
         __syncthreads();
     }
@@ -327,14 +566,16 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SamplePa
     // top_p: shortest prefix whose cumulative probability reaches top_p
     if (sp.top_p < 1.0f) {
         auto p1 = [=](float v, int) { return raw_weight(v, 0) / total / renorm; };
-        select_by_mass(row, vocab, floor_key, (double)sp.top_p, 0, p1, &sh, &key, &cum);
+        if (!select_fast(row, vocab, floor_key, (double)sp.top_p, 0, xof, x_max, p1, &fs, &key, &cum))
+            select_by_mass(row, vocab, floor_key, (double)sp.top_p, 0, p1, &sh, &key, &cum);
         floor_key = key;
         renorm2 = (float)cum;
         __syncthreads();
     }
     // the draw
     auto p2 = [=](float v, int) { return raw_weight(v, 0) / total / renorm / renorm2; };
-    select_by_mass(row, vocab, floor_key, (double)draws[blockIdx.x], 1, p2, &sh, &key, &cum);
+    if (!select_fast(row, vocab, floor_key, (double)draws[blockIdx.x], 1, xof, x_max, p2, &fs, &key, &cum))
+        select_by_mass(row, vocab, floor_key, (double)draws[blockIdx.x], 1, p2, &sh, &key, &cum);
     if (threadIdx.x == 0) out[blockIdx.x] = (int)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull));
 }
 

@@ -95,3 +95,71 @@ def test_large_vocabulary_frequencies(cuda):
             counts[t] = counts.get(t, 0) + 1
     freq = np.array([counts[5], counts[70000], counts[128255]]) / 512
     assert np.abs(freq - p).max() < 0.07 and sum(counts.values()) == 512
+
+
+def _seed_with_draw(lo, hi, position):
+    """A seed whose draw at ``position`` lies in [lo, hi)."""
+    for seed in range(1, 200000):
+        if lo <= float(pl.unit_draw(seed, position)) < hi:
+            return seed
+    raise AssertionError("no seed found")
+
+
+def _interval_of(row, token, temperature, top_k=None, top_p=None, min_p=None):
+    """The stretch of the cumulative distribution that belongs to ``token`` when the sampler's steps
+    (src/inference.rs:5991-6091) are done in float64: candidates by logit descending and index ascending, top_k,
+    softmax of logit / T, min_p, top_p prefix, each renormalised. None if the token is no candidate."""
+    v = row.astype(np.float64)
+    order = np.lexsort((np.arange(v.shape[0]), -v))
+    if top_k is not None:
+        order = order[:min(top_k, order.shape[0])]
+    w = np.exp((v[order] - v[order].max()) / temperature)
+    prob = w / w.sum()
+    if min_p is not None and min_p > 0.0:
+        keep = prob >= min_p * prob.max()
+        order, prob = order[keep], prob[keep] / prob[keep].sum()
+    if top_p is not None and top_p < 1.0:
+        n = int(np.searchsorted(np.cumsum(prob), top_p, side="left")) + 1
+        order, prob = order[:n], prob[:n] / prob[:n].sum()
+    where = np.nonzero(order == token)[0]
+    if where.size == 0:
+        return None
+    cum = np.cumsum(prob)
+    i = int(where[0])
+    return float(cum[i] - prob[i]), float(cum[i]) if i + 1 < order.shape[0] else 2.0
+
+
+@pytest.mark.parametrize("case", ["top", "tail", "cold top-k", "nucleus", "all filters", "ties"])
+def test_sampler_at_a_large_vocabulary(cuda, case):
+    """The two-pass selection at a vocabulary of 50,000: the draw must lie in the chosen token's own stretch of
+    the cumulative distribution, computed in float64 (the plain sampler adds 50,000 float32 terms one by one
+    and drifts by more than a token's width out in the tail, so token-for-token equality is asked only at the
+    small vocabulary above). Draws that land among the few heavy tokens and far out in the crowded tail (where
+    a bin holds more keys than the kernel's list and is divided), a low temperature with top-k (the k-th value
+    lies beyond the binned range), and thousands of equal logits with the draw among them (equal values are
+    ordered by index: the digit-by-digit selection takes over; a token's stretch there is 3e-5 wide, the
+    slack 2e-6)."""
+    rng = np.random.default_rng(7)
+    vocab = 50000
+    logits = (rng.normal(size=(4, vocab)) * 2.5).astype(np.float32)
+    logits[1] *= 2.5
+    if case == "top":
+        opts, want_draw = dict(temperature=0.8), (0.0, 0.001)
+    elif case == "tail":
+        opts, want_draw = dict(temperature=30.0), (0.9995, 1.0)
+    elif case == "cold top-k":
+        opts, want_draw = dict(temperature=0.05, top_k=300), (0.5, 0.6)
+    elif case == "nucleus":
+        opts, want_draw = dict(temperature=1.0, top_p=0.95), (0.93, 0.97)
+    elif case == "all filters":
+        opts, want_draw = dict(temperature=1.2, top_k=1000, top_p=0.9, min_p=0.001), (0.0, 1.0)
+    else:
+        logits[:, 100:30000] = 1.5                     # 29,900 equal values above most of the rest
+        opts, want_draw = dict(temperature=2.0), (0.4, 0.6)
+    seed = _seed_with_draw(*want_draw, 0)
+    got = _sample(cuda, logits, [[]] * 4, seed=seed, **opts)
+    draw = float(pl.unit_draw(seed, 0))
+    for r in range(4):
+        span = _interval_of(logits[r], got[r], **opts)
+        assert span is not None, (r, got[r], "not a candidate")
+        assert span[0] - 2e-6 <= draw < span[1] + 2e-6, (r, got[r], span, draw)
