@@ -218,6 +218,27 @@ __device__ void select_by_mass(const float* row, int vocab, unsigned long long f
     *out_cum = before + w;
 }
 
+// Every element of a row to `f(value, index)`, a thread's elements in ascending index order. Rows that
+// start on a 16-byte boundary are read 16 bytes at a time, two such loads in flight per thread (a scan with
+// one 4-byte load at a time is bound by the loads' round trips: 125 of them for 128k columns).
+template <typename F>
+__device__ __forceinline__ void for_each_in_row(const float* __restrict__ row, int vocab, F f) {
+    if ((((uintptr_t)row) & 15) == 0) {
+        const int n4 = vocab >> 2;
+        const float4* r4 = reinterpret_cast<const float4*>(row);
+        for (int g0 = threadIdx.x; g0 < n4; g0 += 2 * blockDim.x) {
+            const int g1 = g0 + blockDim.x;
+            const float4 a = r4[g0];
+            const float4 b = r4[min(g1, n4 - 1)];
+            f(a.x, 4 * g0); f(a.y, 4 * g0 + 1); f(a.z, 4 * g0 + 2); f(a.w, 4 * g0 + 3);
+            if (g1 < n4) { f(b.x, 4 * g1); f(b.y, 4 * g1 + 1); f(b.z, 4 * g1 + 2); f(b.w, 4 * g1 + 3); }
+        }
+        for (int i = 4 * n4 + threadIdx.x; i < vocab; i += blockDim.x) f(row[i], i);
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) f(row[i], i);
+    }
+}
+
 // ------------------------------------------------------------------------------------
 // The same selection in two passes over the row instead of eight, for the usual case. The order of the
 // candidates is by value descending, so by x = max / T - value / T ascending. A first pass counts the
@@ -250,11 +271,12 @@ __device__ __forceinline__ float value_of_key(unsigned long long key) {
 }
 
 // Returns true and the choice if the fast way settled it, false if the caller has to run select_by_mass.
-// `xof(v)` is the place of a value in the order (smaller first, monotone in v), `weight(v, i)` as above.
-template <typename XFn, typename WeightFn>
+// `xof(v)` is the place of a value in the order (smaller first, monotone in v), `weight(v, i)` as above,
+// `approx(x)` a cheap estimate of the weight of a value at place x, good enough to find the bin.
+template <typename XFn, typename WeightFn, typename ApproxFn>
 __device__ bool select_fast(const float* row, int vocab, unsigned long long floor_key, double target, int strict,
-                            XFn xof, float x_max, WeightFn weight, FastShared* fs, unsigned long long* out_key,
-                            double* out_cum) {
+                            XFn xof, float x_max, WeightFn weight, ApproxFn approx, FastShared* fs,
+                            unsigned long long* out_key, double* out_cum) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     float lo = 0.f, inv_w = 64.0f;                       // bins of 1/64 from 0; the last one takes all beyond
     bool open_end = true;
@@ -262,23 +284,25 @@ __device__ bool select_fast(const float* row, int vocab, unsigned long long floo
         // pass 1: counts and approximate weights of the candidates per bin of [lo, ...)
         for (int b = threadIdx.x; b < FS_BINS; b += blockDim.x) fs->cnt[b] = 0u, fs->mass[b] = 0.f;
         __syncthreads();
-        auto bin_of = [&](float v) {                     // -1: ordered before the range; FS_BINS: after it
-            const float r = (xof(v) - lo) * inv_w;
+        auto bin_at = [&](float x) {                     // -1: ordered before the range; FS_BINS: after it
+            const float r = (x - lo) * inv_w;
             if (r < 0.f) return -1;
             if (r >= (float)FS_BINS) return open_end ? FS_BINS - 1 : FS_BINS;
             return (int)r;
         };
-        double head = 0.0;                               // approximate weight ordered before the range
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-            const float v = row[i];
-            if (composite_key(v, i) < floor_key) continue;
-            const int b = bin_of(v);
+        auto bin_of = [&](float v) { return bin_at(xof(v)); };
+        const bool has_floor = floor_key != 0ull;
+        double head = 0.0;                               // weight ordered before the range
+        for_each_in_row(row, vocab, [&](float v, int i) {
+            if (has_floor && composite_key(v, i) < floor_key) return;
+            const float x = xof(v);
+            const int b = bin_at(x);
             if (b < 0) head += (double)weight(v, i);
             else if (b < FS_BINS) {
                 atomicAdd(&fs->cnt[b], 1u);
-                atomicAdd(&fs->mass[b], weight(v, i));
+                atomicAdd(&fs->mass[b], approx(x));
             }
-        }
+        });
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) head += __shfl_xor_sync(0xffffffffu, head, o);
         if (lane == 0) fs->dred[warp] = head;
@@ -334,17 +358,15 @@ __device__ bool select_fast(const float* row, int vocab, unsigned long long floo
             __syncthreads();
             double before = 0.0;
             unsigned int after = 0u;
-            for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-                const float v = row[i];
-                const unsigned long long key = composite_key(v, i);
-                if (key < floor_key) continue;
+            for_each_in_row(row, vocab, [&](float v, int i) {
+                if (has_floor && composite_key(v, i) < floor_key) return;
                 const int b = bin_of(v);
                 if (b < bsel) before += (double)weight(v, i);
                 else if (b == bsel) {
                     const unsigned int slot = atomicAdd(&fs->n_list, 1u);
-                    if (slot < FS_CAP) fs->list[slot] = key;
+                    if (slot < FS_CAP) fs->list[slot] = composite_key(v, i);
                 } else ++after;
-            }
+            });
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
                 before += __shfl_xor_sync(0xffffffffu, before, o);
@@ -461,12 +483,11 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SamplePa
     // maximum and minimum logit and finiteness
     float mx = -CUDART_INF_F, mn = CUDART_INF_F;
     bool bad = false;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
+    for_each_in_row(row, vocab, [&](float v, int) {
         if (!isfinite(v)) bad = true;
         mx = fmaxf(mx, v);
         mn = fminf(mn, v);
-    }
+    });
     mx = warp_max(mx);
     mn = -warp_max(-mn);
     if (lane == 0) red[warp] = mx, red2[warp] = mn;
@@ -485,8 +506,11 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SamplePa
     const float T = sp.temperature;
     const float max_scaled = mx / T;
     // the place of a value in the order, as a distance from the maximum (what the exponential is taken of)
-    auto xof = [=](float v) { return max_scaled - v / T; };
-    const float x_max = max_scaled - mn / T;
+    const float inv_T = 1.0f / T, x_zero = mx * inv_T;
+    // monotone in v and never negative, which is all it has to be (the product rounded on its own: fused into the
+    // subtraction, the maximum's own place would come out as the product's rounding error, of either sign)
+    auto xof = [=](float v) { return fmaxf(x_zero - __fmul_rn(v, inv_T), 0.f); };
+    const float x_max = xof(mn);
     if (red[32] != red[32] || !isfinite(x_max)) {          // not a number, or infinite: the error is set; no choice
         if (threadIdx.x == 0) out[blockIdx.x] = 0;
         return;
@@ -498,7 +522,8 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SamplePa
     // top_k: the k-th candidate in order becomes the floor
     if (sp.top_k > 0 && sp.top_k < vocab) {
         auto one = [](float, int) { return 1.0f; };
-        if (!select_fast(row, vocab, 0ull, (double)sp.top_k, 0, xof, x_max, one, &fs, &key, &cum))
+        auto one_at = [](float) { return 1.0f; };
+        if (!select_fast(row, vocab, 0ull, (double)sp.top_k, 0, xof, x_max, one, one_at, &fs, &key, &cum))
             select_by_mass(row, vocab, 0ull, (double)sp.top_k, 0, one, &sh, &key, &cum);
         floor_key = key;
         __syncthreads();
@@ -506,10 +531,9 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SamplePa
     // softmax weights and their sum over the candidates
     auto raw_weight = [=](float v, int) { return expf(v / T - max_scaled); };
     double part = 0.0;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
+    for_each_in_row(row, vocab, [&](float v, int i) {
         if (composite_key(v, i) >= floor_key) part += (double)raw_weight(v, i);
-    }
+    });
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
     if (lane == 0) dred[warp] = part;
@@ -533,13 +557,12 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SamplePa
         const float thr = sp.min_p * pmax;
         unsigned long long kmin = ~0ull;
         double s = 0.0;
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-            const float v = row[i];
+        for_each_in_row(row, vocab, [&](float v, int i) {
             const unsigned long long ck = composite_key(v, i);
-            if (ck < floor_key) continue;
+            if (ck < floor_key) return;
             const float p = raw_weight(v, i) / total;
             if (p >= thr) { s += (double)p; kmin = ck < kmin ? ck : kmin; }
-        }
+        });
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             s += __shfl_xor_sync(0xffffffffu, s, o);
@@ -566,7 +589,9 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SamplePa
     // top_p: shortest prefix whose cumulative probability reaches top_p
     if (sp.top_p < 1.0f) {
         auto p1 = [=](float v, int) { return raw_weight(v, 0) / total / renorm; };
-        if (!select_fast(row, vocab, floor_key, (double)sp.top_p, 0, xof, x_max, p1, &fs, &key, &cum))
+        const float c1 = 1.0f / total / renorm;
+        auto a1 = [=](float x) { return __expf(-x) * c1; };
+        if (!select_fast(row, vocab, floor_key, (double)sp.top_p, 0, xof, x_max, p1, a1, &fs, &key, &cum))
             select_by_mass(row, vocab, floor_key, (double)sp.top_p, 0, p1, &sh, &key, &cum);
         floor_key = key;
         renorm2 = (float)cum;
@@ -574,7 +599,9 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SamplePa
     }
     // the draw
     auto p2 = [=](float v, int) { return raw_weight(v, 0) / total / renorm / renorm2; };
-    if (!select_fast(row, vocab, floor_key, (double)draws[blockIdx.x], 1, xof, x_max, p2, &fs, &key, &cum))
+    const float c2 = 1.0f / total / renorm / renorm2;
+    auto a2 = [=](float x) { return __expf(-x) * c2; };
+    if (!select_fast(row, vocab, floor_key, (double)draws[blockIdx.x], 1, xof, x_max, p2, a2, &fs, &key, &cum))
         select_by_mass(row, vocab, floor_key, (double)draws[blockIdx.x], 1, p2, &sh, &key, &cum);
     if (threadIdx.x == 0) out[blockIdx.x] = (int)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull));
 }
