@@ -1,5 +1,5 @@
 // Sampling on the device: greedy argmax and the reference's stochastic sampler
-// (temperature, top-k, min-p, top-p), one block per row of logits.
+// (temperature, top-k, min-p, top-p), a cluster of up to eight blocks per row of logits.
 //
 // Greedy follows greedy_sample (src/inference.rs:5890-5925; device twin argmax_f32 at
 // src/cuda_resident.rs:1847): strict '>', so the lowest index among equal maxima wins, and
@@ -16,9 +16,12 @@
 // kept in double; the reference's sequential float sums can differ from them in the last
 // bits, which moves a decision only when the draw or top_p lies on a boundary.
 #include "common.cuh"
+#include <cooperative_groups.h>
 #include <math_constants.h>
+namespace cg = cooperative_groups;
 
 #define SAMPLE_THREADS 1024
+#define SAMPLE_MAX_TEAM 8      // blocks that may share a row (a portable cluster)
 #define SAMPLE_ERR_NONFINITE 1
 #define SAMPLE_ERR_EMPTY 2
 
@@ -218,25 +221,69 @@ __device__ void select_by_mass(const float* row, int vocab, unsigned long long f
     *out_cum = before + w;
 }
 
-// Every element of a row to `f(value, index)`, a thread's elements in ascending index order. Rows that
-// start on a 16-byte boundary are read 16 bytes at a time, two such loads in flight per thread (a scan with
-// one 4-byte load at a time is bound by the loads' round trips: 125 of them for 128k columns).
+// The blocks that share a row of logits: a thread-block cluster (of one block where the row is short). Every
+// block scans its own slice of the row; what they find meets in the shared memory of block 0 (distributed shared
+// memory), between cluster barriers.
+struct Team {
+    int n, rank;
+    int begin, end;              // this block's slice of the row (begin a multiple of 4)
+    __device__ void sync() { cg::this_cluster().sync(); }
+    template <typename T> __device__ T* at0(T* p) { return cg::this_cluster().map_shared_rank(p, 0); }
+};
+
+// What a reduction over the team passes through block 0: one slot per block and place of use, written before a
+// cluster barrier and read after it by whoever needs the result (every block, or block 0 alone).
+struct TeamSlots {
+    double d[4][SAMPLE_MAX_TEAM];
+    float f[2][SAMPLE_MAX_TEAM];
+    unsigned int u[2][SAMPLE_MAX_TEAM];
+    unsigned long long k[1][SAMPLE_MAX_TEAM];
+};
+
+// Every element of this block's slice to `f(value, index)`, a thread's elements in ascending index order. Rows
+// that start on a 16-byte boundary are read 16 bytes at a time, two such loads in flight per thread (a scan with
+// one 4-byte load at a time is bound by the loads' round trips).
 template <typename F>
-__device__ __forceinline__ void for_each_in_row(const float* __restrict__ row, int vocab, F f) {
+__device__ __forceinline__ void for_each_in_slice(const float* __restrict__ row, const Team& tm, F f) {
+    const int begin = tm.begin, end = tm.end;
     if ((((uintptr_t)row) & 15) == 0) {
-        const int n4 = vocab >> 2;
+        const int g_begin = begin >> 2, g_end = end >> 2;          // whole groups of four within the slice
         const float4* r4 = reinterpret_cast<const float4*>(row);
-        for (int g0 = threadIdx.x; g0 < n4; g0 += 2 * blockDim.x) {
+        for (int g0 = g_begin + threadIdx.x; g0 < g_end; g0 += 2 * blockDim.x) {
             const int g1 = g0 + blockDim.x;
             const float4 a = r4[g0];
-            const float4 b = r4[min(g1, n4 - 1)];
+            const float4 b = r4[min(g1, g_end - 1)];
             f(a.x, 4 * g0); f(a.y, 4 * g0 + 1); f(a.z, 4 * g0 + 2); f(a.w, 4 * g0 + 3);
-            if (g1 < n4) { f(b.x, 4 * g1); f(b.y, 4 * g1 + 1); f(b.z, 4 * g1 + 2); f(b.w, 4 * g1 + 3); }
+            if (g1 < g_end) { f(b.x, 4 * g1); f(b.y, 4 * g1 + 1); f(b.z, 4 * g1 + 2); f(b.w, 4 * g1 + 3); }
         }
-        for (int i = 4 * n4 + threadIdx.x; i < vocab; i += blockDim.x) f(row[i], i);
+        for (int i = max(begin, 4 * g_end) + threadIdx.x; i < end; i += blockDim.x) f(row[i], i);
     } else {
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) f(row[i], i);
+        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) f(row[i], i);
     }
+}
+
+// Maximum over the block, in every thread. `scratch33`: 33 floats of shared memory.
+__device__ __forceinline__ float block_max(float v, float* scratch33) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch33[warp] = v;
+    __syncthreads();
+    return warp_max(lane < nw ? scratch33[lane] : -CUDART_INF_F);
+}
+
+// Sum over the block; the result is valid in thread 0.
+__device__ __forceinline__ double block_sum_double(double v, double* scratch33) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if (lane == 0) scratch33[warp] = v;
+    __syncthreads();
+    double t = 0.0;
+    if (threadIdx.x == 0)
+        for (int w = 0; w < nw; ++w) t += scratch33[w];
+    return t;
 }
 
 // ------------------------------------------------------------------------------------
@@ -274,16 +321,18 @@ __device__ __forceinline__ float value_of_key(unsigned long long key) {
 // `xof(v)` is the place of a value in the order (smaller first, monotone in v), `weight(v, i)` as above,
 // `approx(x)` a cheap estimate of the weight of a value at place x, good enough to find the bin.
 template <typename XFn, typename WeightFn, typename ApproxFn>
-__device__ bool select_fast(const float* row, int vocab, unsigned long long floor_key, double target, int strict,
-                            XFn xof, float x_max, WeightFn weight, ApproxFn approx, FastShared* fs,
+__device__ bool select_fast(const float* row, Team& tm, unsigned long long floor_key, double target, int strict,
+                            XFn xof, float x_max, WeightFn weight, ApproxFn approx, FastShared* fs, TeamSlots* ts,
                             unsigned long long* out_key, double* out_cum) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    FastShared* fs0 = tm.at0(fs);                        // block 0's: the merged bins, the list, the verdicts
+    TeamSlots* ts0 = tm.at0(ts);
     float lo = 0.f, inv_w = 64.0f;                       // bins of 1/64 from 0; the last one takes all beyond
     bool open_end = true;
     for (int level = 0; level < 3; ++level) {
-        // pass 1: counts and approximate weights of the candidates per bin of [lo, ...)
+        // pass 1: counts and approximate weights of the candidates per bin of [lo, ...), block by block
         for (int b = threadIdx.x; b < FS_BINS; b += blockDim.x) fs->cnt[b] = 0u, fs->mass[b] = 0.f;
-        __syncthreads();
+        tm.sync();                                       // block 0's bins are clear before anyone adds to them
         auto bin_at = [&](float x) {                     // -1: ordered before the range; FS_BINS: after it
             const float r = (x - lo) * inv_w;
             if (r < 0.f) return -1;
@@ -293,7 +342,7 @@ __device__ bool select_fast(const float* row, int vocab, unsigned long long floo
         auto bin_of = [&](float v) { return bin_at(xof(v)); };
         const bool has_floor = floor_key != 0ull;
         double head = 0.0;                               // weight ordered before the range
-        for_each_in_row(row, vocab, [&](float v, int i) {
+        for_each_in_slice(row, tm, [&](float v, int i) {
             if (has_floor && composite_key(v, i) < floor_key) return;
             const float x = xof(v);
             const int b = bin_at(x);
@@ -303,14 +352,22 @@ __device__ bool select_fast(const float* row, int vocab, unsigned long long floo
                 atomicAdd(&fs->mass[b], approx(x));
             }
         });
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) head += __shfl_xor_sync(0xffffffffu, head, o);
-        if (lane == 0) fs->dred[warp] = head;
-        __syncthreads();
-        if (warp == 0) {
+        head = block_sum_double(head, fs->dred);
+        if (threadIdx.x == 0) ts0->d[0][tm.rank] = head;
+        if (tm.rank != 0) {                              // this block's bins into block 0's
+            for (int b = threadIdx.x; b < FS_BINS; b += blockDim.x) {
+                const unsigned int c = fs->cnt[b];
+                if (c != 0u) {
+                    atomicAdd(&fs0->cnt[b], c);
+                    atomicAdd(&fs0->mass[b], fs->mass[b]);
+                }
+            }
+        }
+        tm.sync();
+        if (tm.rank == 0 && warp == 0) {
             // a lane sums 64 consecutive bins; the lane in which the cumulative weight reaches the target walks its own
             double acc0 = 0.0;
-            for (int w = 0; w < nw; ++w) acc0 += fs->dred[w];
+            for (int r = 0; r < tm.n; ++r) acc0 += ts->d[0][r];
             constexpr int PER = FS_BINS / 32;
             double mine = 0.0;
             int my_last = -1;
@@ -331,9 +388,9 @@ __device__ bool select_fast(const float* row, int vocab, unsigned long long floo
             int last = my_last;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
-            int chosen = -1;
             if (who != 0u && lane == __ffs(who) - 1) {
                 double acc = upto - mine;
+                int chosen = -1;
                 for (int b = lane * PER; b < (lane + 1) * PER; ++b) {
                     if (fs->cnt[b] == 0u) continue;
                     const double inc = acc + (double)fs->mass[b];
@@ -348,110 +405,106 @@ __device__ bool select_fast(const float* row, int vocab, unsigned long long floo
                 fs->bin = last;                          // never reached: the last bin with candidates
                 fs->status = last < 0 ? 3 : 0;           // no candidate in the range at all: not ours
             }
+            if (lane == 0) fs->n_list = 0u;
         }
-        __syncthreads();
-        if (fs->status == 3) return false;
+        tm.sync();
+        if (fs0->status == 3) { tm.sync(); return false; }
         // pass 2, repeated while the exact sums move the crossing to a neighbouring bin
+        int st = 0;
         for (int tries = 0; tries < 6; ++tries) {
-            const int bsel = fs->bin;
-            if (threadIdx.x == 0) fs->n_list = 0u;
-            __syncthreads();
+            const int bsel = fs0->bin;
             double before = 0.0;
             unsigned int after = 0u;
-            for_each_in_row(row, vocab, [&](float v, int i) {
+            for_each_in_slice(row, tm, [&](float v, int i) {
                 if (has_floor && composite_key(v, i) < floor_key) return;
                 const int b = bin_of(v);
                 if (b < bsel) before += (double)weight(v, i);
                 else if (b == bsel) {
-                    const unsigned int slot = atomicAdd(&fs->n_list, 1u);
-                    if (slot < FS_CAP) fs->list[slot] = composite_key(v, i);
+                    const unsigned int slot = atomicAdd(&fs0->n_list, 1u);
+                    if (slot < FS_CAP) fs0->list[slot] = composite_key(v, i);
                 } else ++after;
             });
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                before += __shfl_xor_sync(0xffffffffu, before, o);
-                after += __shfl_xor_sync(0xffffffffu, after, o);
-            }
-            if (lane == 0) fs->dred[warp] = before, fs->ured[warp] = after;
-            __syncthreads();
-            const unsigned int n = fs->n_list;
-            if (n > FS_CAP) {                            // too many for the list: divide this bin
-                if (threadIdx.x == 0) fs->status = 2;
-                __syncthreads();
-                break;
-            }
-            // sort the bin's keys, largest first (bitonic over the next power of two, padded with zeros)
-            unsigned int m = 1u;
-            while (m < n) m <<= 1;
-            for (unsigned int i = n + threadIdx.x; i < m; i += blockDim.x) fs->list[i] = 0ull;
-            __syncthreads();
-            for (unsigned int k = 2; k <= m; k <<= 1) {
-                for (unsigned int j = k >> 1; j > 0; j >>= 1) {
-                    for (unsigned int i = threadIdx.x; i < m; i += blockDim.x) {
-                        const unsigned int l = i ^ j;
-                        if (l > i) {
-                            const unsigned long long a = fs->list[i], c = fs->list[l];
-                            const bool desc = (i & k) == 0;
-                            if (desc ? (a < c) : (a > c)) { fs->list[i] = c; fs->list[l] = a; }
+            before = block_sum_double(before, fs->dred);
+            const double more_d = block_sum_double((double)after, fs->dred);
+            if (threadIdx.x == 0) ts0->d[1][tm.rank] = before, ts0->u[0][tm.rank] = more_d > 0.0 ? 1u : 0u;
+            tm.sync();
+            if (tm.rank == 0) {
+                const unsigned int n = fs->n_list;
+                if (n > FS_CAP) {                        // too many for the list: divide this bin
+                    if (threadIdx.x == 0) fs->status = 2;
+                } else {
+                    // sort the bin's keys, largest first (bitonic over the next power of two, padded with zeros)
+                    unsigned int m = 1u;
+                    while (m < n) m <<= 1;
+                    for (unsigned int i = n + threadIdx.x; i < m; i += blockDim.x) fs->list[i] = 0ull;
+                    __syncthreads();
+                    for (unsigned int k = 2; k <= m; k <<= 1) {
+                        for (unsigned int j = k >> 1; j > 0; j >>= 1) {
+                            for (unsigned int i = threadIdx.x; i < m; i += blockDim.x) {
+                                const unsigned int l = i ^ j;
+                                if (l > i) {
+                                    const unsigned long long a = fs->list[i], c = fs->list[l];
+                                    const bool desc = (i & k) == 0;
+                                    if (desc ? (a < c) : (a > c)) { fs->list[i] = c; fs->list[l] = a; }
+                                }
+                            }
+                            __syncthreads();
                         }
                     }
-                    __syncthreads();
-                }
-            }
-            for (unsigned int i = threadIdx.x; i < n; i += blockDim.x) {
-                const unsigned long long key = fs->list[i];
-                fs->lp[i] = weight(value_of_key(key), (int)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull)));
-            }
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                double cum = 0.0;
-                unsigned int more = 0u;
-                for (int w = 0; w < nw; ++w) cum += fs->dred[w], more += fs->ured[w];
-                int st = -1;
-                if (strict ? (cum > target) : (cum >= target)) {
-                    // the crossing lies before this bin: the nearest bin with candidates before it, if any
-                    int b = bsel - 1;
-                    while (b >= 0 && fs->cnt[b] == 0u) --b;
-                    if (b >= 0) { fs->bin = b; st = 0; }
-                    else if (lo > 0.f) st = 3;               // before a divided bin's range: not ours to settle
-                }
-                if (st < 0) {
-                    unsigned int i = 0;
-                    for (; i < n; ++i) {
-                        cum += (double)fs->lp[i];
-                        if (strict ? (cum > target) : (cum >= target)) break;
+                    for (unsigned int i = threadIdx.x; i < n; i += blockDim.x) {
+                        const unsigned long long key = fs->list[i];
+                        fs->lp[i] = weight(value_of_key(key), (int)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull)));
                     }
-                    if (i < n) { fs->key = fs->list[i]; fs->cum = cum; st = 1; }
-                    else if (more > 0u) {
-                        int b = bsel + 1;
-                        while (b < FS_BINS && fs->cnt[b] == 0u) ++b;
-                        if (b < FS_BINS) { fs->bin = b; st = 0; }
-                        else st = 3;                         // candidates after the range: not ours to settle
-                    } else if (n > 0u) { fs->key = fs->list[n - 1]; fs->cum = cum; st = 1; }   // never reached: the last candidate
-                    else st = 3;
+                    __syncthreads();
+                    if (threadIdx.x == 0) {
+                        double cum = 0.0;
+                        unsigned int more = 0u;
+                        for (int r = 0; r < tm.n; ++r) cum += ts->d[1][r], more += ts->u[0][r];
+                        int v = -1;
+                        if (strict ? (cum > target) : (cum >= target)) {
+                            // the crossing lies before this bin: the nearest bin with candidates before it, if any
+                            int b = bsel - 1;
+                            while (b >= 0 && fs->cnt[b] == 0u) --b;
+                            if (b >= 0) { fs->bin = b; v = 0; }
+                            else if (lo > 0.f) v = 3;        // before a divided bin's range: not ours to settle
+                        }
+                        if (v < 0) {
+                            unsigned int i = 0;
+                            for (; i < n; ++i) {
+                                cum += (double)fs->lp[i];
+                                if (strict ? (cum > target) : (cum >= target)) break;
+                            }
+                            if (i < n) { fs->key = fs->list[i]; fs->cum = cum; v = 1; }
+                            else if (more > 0u) {
+                                int b = bsel + 1;
+                                while (b < FS_BINS && fs->cnt[b] == 0u) ++b;
+                                if (b < FS_BINS) { fs->bin = b; v = 0; }
+                                else v = 3;                  // candidates after the range: not ours to settle
+                            } else if (n > 0u) { fs->key = fs->list[n - 1]; fs->cum = cum; v = 1; }   // never reached: the last candidate
+                            else v = 3;
+                        }
+                        fs->status = v;
+                        fs->n_list = 0u;
+                    }
                 }
-                fs->status = st;
             }
-            __syncthreads();
-            if (fs->status != 0) break;
-            if (tries == 5) {
-                if (threadIdx.x == 0) fs->status = 3;
-                __syncthreads();
-            }
+            tm.sync();
+            st = fs0->status;
+            if (st != 0) break;
         }
-        const int st = fs->status;
+        if (st == 0) st = 3;                             // six tries and still moving: give up
         if (st == 1) {
-            *out_key = fs->key;
-            *out_cum = fs->cum;
-            __syncthreads();
+            *out_key = fs0->key;
+            *out_cum = fs0->cum;
+            tm.sync();
             return true;
         }
-        if (st != 2) return false;
+        if (st != 2) { tm.sync(); return false; }
         // divide the chosen bin: its range of x in FS_BINS bins (the open last bin up to the largest x of the row)
-        const int bsel = fs->bin;
+        const int bsel = fs0->bin;
         const float blo = lo + (float)bsel / inv_w;
         const float bhi = (open_end && bsel == FS_BINS - 1) ? x_max : lo + (float)(bsel + 1) / inv_w;
-        __syncthreads();
+        tm.sync();
         if (!(bhi > blo)) return false;
         lo = blo;
         inv_w = (float)FS_BINS / (bhi - blo);
@@ -473,36 +526,42 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SamplePa
                    const float* __restrict__ draws, int* __restrict__ out, int* __restrict__ err) {
     __shared__ SelectShared sh;
     __shared__ FastShared fs;
-    __shared__ float red[33];
-    __shared__ float red2[33];
-    __shared__ double dred[33];
-    __shared__ unsigned long long kred[33];
-    const float* row = logits + (size_t)blockIdx.x * ld;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __shared__ TeamSlots ts;
+    Team tm;
+    tm.n = (int)cg::this_cluster().num_blocks();
+    tm.rank = (int)cg::this_cluster().block_rank();
+    const int row_index = blockIdx.x / tm.n;
+    {   // slices of whole groups of four columns
+        const int per = (((vocab + tm.n - 1) / tm.n) + 3) & ~3;
+        tm.begin = min(vocab, tm.rank * per);
+        tm.end = min(vocab, tm.begin + per);
+    }
+    TeamSlots* ts0 = tm.at0(&ts);
+    const float* row = logits + (size_t)row_index * ld;
 
     // maximum and minimum logit and finiteness
     float mx = -CUDART_INF_F, mn = CUDART_INF_F;
     bool bad = false;
-    for_each_in_row(row, vocab, [&](float v, int) {
+    for_each_in_slice(row, tm, [&](float v, int) {
         if (!isfinite(v)) bad = true;
         mx = fmaxf(mx, v);
         mn = fminf(mn, v);
     });
-    mx = warp_max(mx);
-    mn = -warp_max(-mn);
-    if (lane == 0) red[warp] = mx, red2[warp] = mn;
     if (bad) atomicOr(err, SAMPLE_ERR_NONFINITE);
-    __syncthreads();
-    if (warp == 0) {
-        float t = lane < nw ? red[lane] : -CUDART_INF_F;
-        float u = lane < nw ? red2[lane] : CUDART_INF_F;
-        t = warp_max(t);
-        u = -warp_max(-u);
-        if (lane == 0) red[32] = t, red2[32] = u;
+    {
+        const float bmx = block_max(mx, fs.lp), bmn = -block_max(-mn, fs.lp);     // lp: free until a selection runs
+        if (threadIdx.x == 0) ts0->f[0][tm.rank] = bmx, ts0->f[1][tm.rank] = bmn, ts0->u[1][tm.rank] = 0u;
+        const int any_bad = __syncthreads_or(bad ? 1 : 0);
+        if (threadIdx.x == 0 && any_bad) ts0->u[1][tm.rank] = 1u;
     }
-    __syncthreads();
-    mx = red[32];
-    mn = red2[32];
+    tm.sync();
+    mx = -CUDART_INF_F, mn = CUDART_INF_F;
+    unsigned int team_bad = 0u;
+    for (int r = 0; r < tm.n; ++r) {
+        mx = fmaxf(mx, ts0->f[0][r]);
+        mn = fminf(mn, ts0->f[1][r]);
+        team_bad |= ts0->u[1][r];
+    }
     const float T = sp.temperature;
     const float max_scaled = mx / T;
     // the place of a value in the order, as a distance from the maximum (what the exponential is taken of)
@@ -511,42 +570,52 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SamplePa
     // subtraction, the maximum's own place would come out as the product's rounding error, of either sign)
     auto xof = [=](float v) { return fmaxf(x_zero - __fmul_rn(v, inv_T), 0.f); };
     const float x_max = xof(mn);
-    if (red[32] != red[32] || !isfinite(x_max)) {          // not a number, or infinite: the error is set; no choice
-        if (threadIdx.x == 0) out[blockIdx.x] = 0;
+    if (team_bad != 0u || !isfinite(x_max)) {              // not a number, or infinite: the error is set; no choice
+        if (tm.rank == 0 && threadIdx.x == 0) out[row_index] = 0;
+        tm.sync();                                         // nobody leaves while block 0's slots may still be read
         return;
     }
 
     unsigned long long floor_key = 0ull;
     unsigned long long key;
     double cum;
+    // The selection in the digits of the key, by block 0 alone over the whole row, where the fast one gives up.
+    auto select_slow = [&](unsigned long long floor, double target, int strict, auto weight) {
+        FastShared* fs0 = tm.at0(&fs);
+        if (tm.rank == 0) {
+            unsigned long long k;
+            double c;
+            select_by_mass(row, vocab, floor, target, strict, weight, &sh, &k, &c);
+            if (threadIdx.x == 0) fs.key = k, fs.cum = c;
+        }
+        tm.sync();
+        key = fs0->key;
+        cum = fs0->cum;
+        tm.sync();
+    };
     // top_k: the k-th candidate in order becomes the floor
     if (sp.top_k > 0 && sp.top_k < vocab) {
         auto one = [](float, int) { return 1.0f; };
         auto one_at = [](float) { return 1.0f; };
-        if (!select_fast(row, vocab, 0ull, (double)sp.top_k, 0, xof, x_max, one, one_at, &fs, &key, &cum))
-            select_by_mass(row, vocab, 0ull, (double)sp.top_k, 0, one, &sh, &key, &cum);
+        if (!select_fast(row, tm, 0ull, (double)sp.top_k, 0, xof, x_max, one, one_at, &fs, &ts, &key, &cum))
+            select_slow(0ull, (double)sp.top_k, 0, one);
         floor_key = key;
-        __syncthreads();
     }
     // softmax weights and their sum over the candidates
     auto raw_weight = [=](float v, int) { return expf(v / T - max_scaled); };
     double part = 0.0;
-    for_each_in_row(row, vocab, [&](float v, int i) {
+    for_each_in_slice(row, tm, [&](float v, int i) {
         if (composite_key(v, i) >= floor_key) part += (double)raw_weight(v, i);
     });
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-    if (lane == 0) dred[warp] = part;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        double t = 0.0;
-        for (int i = 0; i < nw; ++i) t += dred[i];
-        dred[32] = t;
-    }
-    __syncthreads();
-    const float total = (float)dred[32];
+    part = block_sum_double(part, fs.dred);
+    if (threadIdx.x == 0) ts0->d[2][tm.rank] = part;
+    tm.sync();
+    double total_d = 0.0;
+    for (int r = 0; r < tm.n; ++r) total_d += ts0->d[2][r];
+    const float total = (float)total_d;
     if (!(total > 0.f) || !isfinite(total)) {
-        if (threadIdx.x == 0) { atomicOr(err, SAMPLE_ERR_EMPTY); out[blockIdx.x] = 0; }
+        if (tm.rank == 0 && threadIdx.x == 0) { atomicOr(err, SAMPLE_ERR_EMPTY); out[row_index] = 0; }
+        tm.sync();
         return;
     }
     float renorm = 1.0f;                 // successive renormalisations: p = w / total / renorm...
@@ -557,53 +626,60 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SamplePa
         const float thr = sp.min_p * pmax;
         unsigned long long kmin = ~0ull;
         double s = 0.0;
-        for_each_in_row(row, vocab, [&](float v, int i) {
+        for_each_in_slice(row, tm, [&](float v, int i) {
             const unsigned long long ck = composite_key(v, i);
             if (ck < floor_key) return;
             const float p = raw_weight(v, i) / total;
             if (p >= thr) { s += (double)p; kmin = ck < kmin ? ck : kmin; }
         });
+        s = block_sum_double(s, fs.dred);
+        {   // the smallest key over the block
+            const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            s += __shfl_xor_sync(0xffffffffu, s, o);
-            const unsigned long long ok = __shfl_xor_sync(0xffffffffu, kmin, o);
-            kmin = ok < kmin ? ok : kmin;
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long ok = __shfl_xor_sync(0xffffffffu, kmin, o);
+                kmin = ok < kmin ? ok : kmin;
+            }
+            __syncthreads();
+            if (lane == 0) fs.list[warp] = kmin;          // list: free until a selection runs
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                for (int w = 1; w < nw; ++w) kmin = fs.list[w] < kmin ? fs.list[w] : kmin;
+                ts0->d[3][tm.rank] = s;
+                ts0->k[0][tm.rank] = kmin;
+            }
         }
-        __syncthreads();
-        if (lane == 0) dred[warp] = s, kred[warp] = kmin;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            double t = 0.0;
-            unsigned long long k = ~0ull;
-            for (int i = 0; i < nw; ++i) { t += dred[i]; k = kred[i] < k ? kred[i] : k; }
-            dred[32] = t;
-            kred[32] = k;
+        tm.sync();
+        double s_all = 0.0;
+        unsigned long long k_all = ~0ull;
+        for (int r = 0; r < tm.n; ++r) {
+            s_all += ts0->d[3][r];
+            k_all = ts0->k[0][r] < k_all ? ts0->k[0][r] : k_all;
         }
-        __syncthreads();
-        if (kred[32] != ~0ull && dred[32] > 0.0) {
-            floor_key = kred[32];
-            renorm = (float)dred[32];
+        if (k_all != ~0ull && s_all > 0.0) {
+            floor_key = k_all;
+            renorm = (float)s_all;
         }
-        __syncthreads();
     }
     // top_p: shortest prefix whose cumulative probability reaches top_p
     if (sp.top_p < 1.0f) {
         auto p1 = [=](float v, int) { return raw_weight(v, 0) / total / renorm; };
         const float c1 = 1.0f / total / renorm;
         auto a1 = [=](float x) { return __expf(-x) * c1; };
-        if (!select_fast(row, vocab, floor_key, (double)sp.top_p, 0, xof, x_max, p1, a1, &fs, &key, &cum))
-            select_by_mass(row, vocab, floor_key, (double)sp.top_p, 0, p1, &sh, &key, &cum);
+        if (!select_fast(row, tm, floor_key, (double)sp.top_p, 0, xof, x_max, p1, a1, &fs, &ts, &key, &cum))
+            select_slow(floor_key, (double)sp.top_p, 0, p1);
         floor_key = key;
         renorm2 = (float)cum;
-        __syncthreads();
     }
     // the draw
     auto p2 = [=](float v, int) { return raw_weight(v, 0) / total / renorm / renorm2; };
     const float c2 = 1.0f / total / renorm / renorm2;
     auto a2 = [=](float x) { return __expf(-x) * c2; };
-    if (!select_fast(row, vocab, floor_key, (double)draws[blockIdx.x], 1, xof, x_max, p2, a2, &fs, &key, &cum))
-        select_by_mass(row, vocab, floor_key, (double)draws[blockIdx.x], 1, p2, &sh, &key, &cum);
-    if (threadIdx.x == 0) out[blockIdx.x] = (int)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull));
+    const double draw = (double)draws[row_index];
+    if (!select_fast(row, tm, floor_key, draw, 1, xof, x_max, p2, a2, &fs, &ts, &key, &cum))
+        select_slow(floor_key, draw, 1, p2);
+    if (tm.rank == 0 && threadIdx.x == 0) out[row_index] = (int)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull));
+    tm.sync();                                             // block 0's shared memory stays until every block has read it
 }
 
 // The draws of a step on the device: row r of a one-token step feeds the token at position
@@ -639,7 +715,24 @@ extern "C" int cml_sample_rows(const float* logits, int ld, int rows, int vocab,
     sp.top_k = top_k;
     sp.top_p = top_p;
     sp.min_p = min_p;
-    sample_rows_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, ld, vocab, sp, draws, out, err);
+    // A row of 32k columns or more is shared by a cluster of up to 8 blocks, a shorter one by fewer; a block of
+    // 1,024 threads takes a multiprocessor to itself, so no more blocks than there are multiprocessors.
+    int team = vocab >= 32768 ? 8 : (vocab >= 8192 ? 4 : 1);
+    while (team > 1 && rows * team > cml_sm_count()) team >>= 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(rows * team));
+    cfg.blockDim = dim3(SAMPLE_THREADS);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)team;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, sample_rows_kernel, logits, ld, vocab, sp, draws, out, err);
+    if (le != cudaSuccess) return (int)le;
     return cml_launch_status();
 }
 
