@@ -61,6 +61,8 @@ _SIGNATURES = {
     ("gemm_simt", "cml_gemv_f32_partial"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_long, c_int, c_int,
                                             c_int, c_int, c_void_p, c_void_p],
     ("sampling", "cml_argmax_rows"): [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    ("sampling", "cml_adjust_dense"): [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    ("sampling", "cml_count_tokens"): [c_void_p, c_void_p, c_int, c_int, c_void_p],
     ("sampling", "cml_adjust_logits"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_float,
                                         c_void_p],
     ("sampling", "cml_decode_loop_size"): [],
@@ -661,6 +663,27 @@ def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: flo
     _check(_fn("sampling", "cml_sample_rows")(_p(logits), logits.stride(0), rows, vocab, float(temperature),
                                              int(top_k or 0), float(top_p if top_p is not None else 1.0),
                                              float(min_p or 0.0), _p(draws), _p(out), _p(err), _stream()), "sample_rows")
+
+
+def adjust_dense(logits: torch.Tensor, counts: torch.Tensor, bias: torch.Tensor, penalties: torch.Tensor):
+    """Bias and penalties from device-side state: ``counts`` int32 [rows, vocab] (how often a token
+    stands in the row's history), ``bias`` float32 [vocab], ``penalties`` float32 [3] = repeat,
+    presence, frequency. In place on ``logits`` (float32 [rows, vocab])."""
+    _dev(logits, counts, bias, penalties)
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and counts.dtype == torch.int32
+    assert counts.shape == (rows, vocab) and counts.is_contiguous() and bias.numel() == vocab and penalties.numel() == 3
+    assert bias.dtype == torch.float32 and penalties.dtype == torch.float32
+    _check(_fn("sampling", "cml_adjust_dense")(_p(logits), logits.stride(0), rows, vocab, _p(counts), _p(bias),
+                                              _p(penalties), _stream()), "adjust_dense")
+
+
+def count_tokens(tokens: torch.Tensor, counts: torch.Tensor):
+    """counts[r][tokens[r]] += 1 for the rows of ``counts`` (int32 [rows, vocab])."""
+    _dev(tokens, counts)
+    rows, vocab = counts.shape
+    assert tokens.dtype == torch.int32 and tokens.numel() >= rows and counts.dtype == torch.int32 and counts.is_contiguous()
+    _check(_fn("sampling", "cml_count_tokens")(_p(tokens), _p(counts), rows, vocab, _stream()), "count_tokens")
 
 
 def draws_at(positions: torch.Tensor, seed: torch.Tensor, draws: torch.Tensor):

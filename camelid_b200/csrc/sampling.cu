@@ -151,6 +151,49 @@ extern "C" int cml_adjust_logits(float* logits, int ld, int vocab, const int* en
     return cml_launch_status();
 }
 
+// The same adjustments from counts kept on the device, for steps that feed themselves: counts[r][t] is how often
+// token t stands in row r's history, bias[t] the sum of the biases listed for t (0 elsewhere: adding it changes
+// nothing), penalties = {repeat, presence, frequency} in device memory, so that one captured graph serves any
+// values. count_tokens adds the tokens a step has chosen to their rows' counts.
+__global__ void adjust_dense_kernel(float* __restrict__ logits, int ld, int vocab, const int* __restrict__ counts,
+                                    const float* __restrict__ bias, const float* __restrict__ penalties) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x, row = blockIdx.y;
+    if (t >= vocab) return;
+    const float repeat_penalty = penalties[0], presence_penalty = penalties[1], frequency_penalty = penalties[2];
+    const int count = counts[(size_t)row * vocab + t];
+    const float b = bias[t];
+    if (count == 0 && b == 0.f) return;
+    float v = logits[(size_t)row * ld + t] + b;
+    if (count > 0) {
+        if (repeat_penalty != 1.0f) v = v > 0.f ? v / repeat_penalty : v * repeat_penalty;
+        if (presence_penalty != 0.0f) v -= presence_penalty;
+        if (frequency_penalty != 0.0f) v -= frequency_penalty * (float)count;
+    }
+    logits[(size_t)row * ld + t] = v;
+}
+
+__global__ void count_tokens_kernel(const int* __restrict__ tokens, int* __restrict__ counts, int rows, int vocab) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    const int t = tokens[r];
+    if (t >= 0 && t < vocab) counts[(size_t)r * vocab + t] += 1;
+}
+
+extern "C" int cml_adjust_dense(float* logits, int ld, int rows, int vocab, const int* counts, const float* bias,
+                                const float* penalties, void* stream) {
+    if (rows <= 0 || vocab <= 0) return 0;
+    if (rows > 65535) return CML_ERR_BAD_SIZE;
+    adjust_dense_kernel<<<dim3((vocab + 255) / 256, rows), 256, 0, (cudaStream_t)stream>>>(logits, ld, vocab, counts, bias,
+                                                                                          penalties);
+    return cml_launch_status();
+}
+
+extern "C" int cml_count_tokens(const int* tokens, int* counts, int rows, int vocab, void* stream) {
+    if (rows <= 0) return 0;
+    count_tokens_kernel<<<(rows + 127) / 128, 128, 0, (cudaStream_t)stream>>>(tokens, counts, rows, vocab);
+    return cml_launch_status();
+}
+
 // ------------------------------------------------------------------------------------
 // Selection in the total order (key descending). The weight of element i is given by the
 // functor; elements with key < floor_key are not candidates. Finds the first candidate at

@@ -88,22 +88,30 @@ def run_batch(model, cache, sampler, prompts: list, budgets: list, requested: li
         # After the prompts, a model that steps through captured graphs and a sampler without
         # per-history adjustments hand the one-token steps to the C++ loop: many steps per call.
         native = (getattr(model, "use_graphs", False) and hasattr(model, "decode_natively")
-                  and getattr(sampler, "native_ok", False))
+                  and (getattr(sampler, "native_ok", False) or getattr(sampler, "fed_ok", False)))
         # Better still, the captured step picks the token itself (greedy, or sampled with a draw made
         # on the device from the seed and the row's position) and feeds it to the next step on the
         # device, so a run of steps is queued at once and read back at its end. Sequences do not depend on one another, so a sequence that meets a stop token
         # inside such a run just drops what it produced after it; with stop tokens the runs are
         # short, so that little is produced in vain.
+        # Penalties and biases ride along there: the histories' token counts go to the device when a run starts.
         fed = (native and hasattr(model, "decode_fed")
                and getattr(getattr(model, "options", None), "feed_on_device", False))
+        adjusts = bool(getattr(getattr(sampler, "options", None), "adjusts", False))
+        if adjusts and not fed:
+            native = False                                 # the C++ loop without feeding knows no adjustments
         first = True
         while live:
             if native and not first:
                 k = min(budgets[i] - len(results[i].tokens) for i in live)
                 if fed:
                     steps = min(k, FED_RUN_WITH_STOPS) if stop_ids else k
-                    out = model.decode_fed(cache, [slots[i] for i in live], [results[i].tokens[-1] for i in live], steps,
-                                           sampler.options)
+                    if adjusts:
+                        out = model.decode_fed(cache, [slots[i] for i in live], [results[i].tokens[-1] for i in live],
+                                               steps, sampler.options, histories=[histories[i] for i in live])
+                    else:
+                        out = model.decode_fed(cache, [slots[i] for i in live], [results[i].tokens[-1] for i in live],
+                                               steps, sampler.options)
                 else:
                     out, steps = model.decode_natively(cache, [slots[i] for i in live],
                                                        [results[i].tokens[-1] for i in live],

@@ -33,8 +33,8 @@ def bucket_width(blocks: int) -> int:
 
 
 class DecodeGraph:
-    def __init__(self, model, cache, n_seqs: int, widths: list, feed: bool):
-        self.model, self.n_seqs, self.widths, self.feed = model, n_seqs, list(widths), feed
+    def __init__(self, model, cache, n_seqs: int, widths: list, feed: bool, adjust: bool = False):
+        self.model, self.n_seqs, self.widths, self.feed, self.adjust = model, n_seqs, list(widths), feed, adjust
         self._cache = weakref.ref(cache)        # the model keeps its graphs per cache and drops them with it
         dev = model.device
         self.ctx = StepContext.static(cache=cache, workspace=Workspace(dev), dtype=model.dtype, device=dev,
@@ -57,6 +57,15 @@ class DecodeGraph:
         if feed and feed is not True:              # a sampling step: the seed lives on the device, any seed replays
             self.seed = torch.zeros(1, dtype=torch.int64, device=dev)
             self.draws = torch.zeros(n_seqs, dtype=torch.float32, device=dev)
+        if adjust:
+            # Bias and penalties inside a step that feeds itself: how often each token stands in a row's
+            # history is kept on the device (set from the histories when a run starts, the chosen tokens
+            # counted by the step), the bias as a dense row, the three penalties as numbers in device memory.
+            assert feed, "adjustments on the device belong to steps that pick their own token"
+            self.counts = torch.zeros(n_seqs, model.vocab_size, dtype=torch.int32, device=dev)
+            self.bias = torch.zeros(model.vocab_size, dtype=torch.float32, device=dev)
+            self.penalties = torch.zeros(3, dtype=torch.float32, device=dev)
+            self.counts_host = torch.zeros(n_seqs, model.vocab_size, dtype=torch.int32).pin_memory()
 
     @property
     def cache(self):
@@ -93,6 +102,8 @@ class DecodeGraph:
 
     def _forward(self):
         logits = self.model.run(self.ctx)
+        if self.adjust:
+            ops.adjust_dense(logits, self.counts, self.bias, self.penalties)
         if self.feed is True:
             ops.argmax_rows(logits, self.ctx.tokens, self.model.logit_error_word())
         elif self.feed:          # ("sample", temperature, top_k, top_p, min_p): the draw from the seed and the position
@@ -100,6 +111,8 @@ class DecodeGraph:
             ops.draws_at(self.ctx.row_pos, self.seed, self.draws)
             ops.sample_rows(logits, temperature, top_k, top_p, min_p, self.draws, self.ctx.tokens,
                             self.model.logit_error_word())
+        if self.adjust:
+            ops.count_tokens(self.ctx.tokens, self.counts)
         return logits
 
     def capture(self):
@@ -146,11 +159,13 @@ class DecodeGraph:
         return loop.run(self.graph.raw_cuda_graph_exec(), tokens, starts, slots, history_lens, max_steps, stop_ids,
                         temperature, top_k, top_p, min_p, seed, self.launches)
 
-    def run_fed(self, slots: list, starts: list, tokens: list, steps: int, seed: int = 0):
+    def run_fed(self, slots: list, starts: list, tokens: list, steps: int, seed: int = 0, histories=None, options=None):
         """``steps`` steps of a graph captured with ``feed`` (greedy, or sampling with the draws
         made on the device from ``seed`` and each row's position), queued at once by the C++
         loop: the device feeds itself, the host sends positions and reads the chosen tokens.
-        Returns the tokens [steps, sequences] as a numpy array."""
+        A graph with adjustments needs ``histories`` (per sequence the tokens so far, the one fed
+        first included) and ``options`` (the penalties and the bias). Returns the tokens
+        [steps, sequences] as a numpy array."""
         assert self.feed
         if self.feed is not True:
             signed = int(seed) & ((1 << 64) - 1)
@@ -159,6 +174,8 @@ class DecodeGraph:
         self.send(i, with_tokens=True)                  # block tables and the static arrays
         if self.graph is None:
             self.capture()
+        if self.adjust:
+            self._set_adjustments(histories, options)
         if getattr(self, "_fed", None) is None:
             self._fed = ops.FedDecodeLoop(self.n_seqs, self.ctx.layout, self.ctx.meta_dev, self.host_np[i])
         out = []
@@ -170,6 +187,30 @@ class DecodeGraph:
                                      self.launches))
             done += k
         return np.concatenate(out) if len(out) > 1 else out[0]
+
+
+    def _set_adjustments(self, histories, options) -> None:
+        """Counts of each row's history, the dense bias and the penalties to the device (after the
+        capture, whose warm-up step counted a token of its own)."""
+        vocab = self.model.vocab_size
+        host = self.counts_host.numpy()
+        penalise = options.presence_penalty != 0.0 or options.frequency_penalty != 0.0 or options.repeat_penalty != 1.0
+        for r, hist in enumerate(histories):
+            if penalise:
+                h = np.asarray(hist, dtype=np.int64)
+                host[r] = np.bincount(h[(h >= 0) & (h < vocab)], minlength=vocab)
+            else:
+                host[r] = 0
+        self.counts.copy_(self.counts_host, non_blocking=True)
+        bias: dict = {}
+        for tok, b in options.logit_bias:
+            bias[tok] = bias.get(tok, 0.0) + b
+        dense = torch.zeros(vocab, dtype=torch.float32)
+        for tok, b in bias.items():
+            dense[tok] = b
+        self.bias.copy_(dense)
+        self.penalties.copy_(torch.tensor([options.repeat_penalty, options.presence_penalty, options.frequency_penalty],
+                                          dtype=torch.float32))
 
 
 class StepGraph:

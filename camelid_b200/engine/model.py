@@ -246,16 +246,16 @@ class DecoderModel:
         self.last_h2d_bytes = graph.load(host, slots, starts, news, row0)
         return graph.replay()
 
-    def decode_graph(self, cache: SequenceCache, slots: list, feed: bool = False):
+    def decode_graph(self, cache: SequenceCache, slots: list, feed: bool = False, adjust: bool = False):
         """The captured graph for one-token steps of these slots (made at its first use)."""
         from .graphs import DecodeGraph, bucket_width
         book = cache.book
         widths = [bucket_width(max(len(book.pages[g][s]) for s in slots)) for g in range(len(book.kv_specs))]
         graphs = self._graphs.setdefault(cache, {})
-        key = (len(slots), tuple(widths), feed)
+        key = (len(slots), tuple(widths), feed, adjust)
         graph = graphs.get(key)
         if graph is None:
-            graph = DecodeGraph(self, cache, len(slots), widths, feed)
+            graph = DecodeGraph(self, cache, len(slots), widths, feed, adjust)
             graphs[key] = graph
         return graph
 
@@ -290,12 +290,14 @@ class DecoderModel:
             self._logit_err = torch.zeros(1, dtype=torch.int32, device=self.device)
         return self._logit_err
 
-    def decode_fed(self, cache: SequenceCache, slots: list, tokens: list, steps: int, sampling=None):
+    def decode_fed(self, cache: SequenceCache, slots: list, tokens: list, steps: int, sampling=None, histories=None):
         """Exactly ``steps`` one-token steps of these sequences with the chosen token fed back on the
         device: all steps are queued at once and the host waits once at the end. ``sampling``
-        (``SamplingOptions`` without penalties or bias; None or temperature 0: greedy): the draws are
-        made on the device from the seed and each row's position, the same numbers the host would
-        draw. Returns the tokens [steps][sequence] (numpy); the cache's lengths have moved by ``steps``."""
+        (``SamplingOptions``; None or temperature 0: greedy): the draws are made on the device from the
+        seed and each row's position, the same numbers the host would draw. With penalties or a bias,
+        ``histories`` gives per sequence the tokens so far (the one fed first included): their counts
+        go to the device once and the steps count what they choose. Returns the tokens
+        [steps][sequence] (numpy); the cache's lengths have moved by ``steps``."""
         if not self.use_graphs:
             raise StepError("decoding with the token fed back on the device needs a model whose parts can run in a captured graph")
         if not self.loaded:
@@ -305,18 +307,19 @@ class DecoderModel:
                 raise StepError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
         if steps <= 0:
             raise StepError("decode_fed needs at least one step")
+        adjust = sampling is not None and sampling.adjusts
+        if adjust and (histories is None or len(histories) != len(slots)):
+            raise StepError("penalties and biases need each sequence's history: pass histories to decode_fed")
         book = cache.book
         book.check_extend([(s, steps) for s in slots])
         starts = [book.extend(s, steps) for s in slots]
         feed, seed = True, 0
         if sampling is not None and not sampling.greedy:
-            if sampling.adjusts:
-                raise StepError("penalties and biases need each request's history on the host: not in decode_fed")
             feed = ("sample", float(sampling.temperature), int(sampling.top_k or 0),
                     float(sampling.top_p if sampling.top_p is not None else 1.0), float(sampling.min_p or 0.0))
             seed = int(sampling.seed or 0)
-        graph = self.decode_graph(cache, slots, feed=feed)
-        out = graph.run_fed(slots, starts, [int(t) for t in tokens], steps, seed)
+        graph = self.decode_graph(cache, slots, feed=feed, adjust=adjust)
+        out = graph.run_fed(slots, starts, [int(t) for t in tokens], steps, seed, histories, sampling)
         for s in slots:
             book.commit(s, steps)
         self.last_h2d_bytes = graph._fed.h2d_bytes_per_step

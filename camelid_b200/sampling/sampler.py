@@ -4,6 +4,9 @@ Greedy is an argmax kernel. Otherwise the logits are adjusted in place (bias, re
 presence and frequency penalties over each request's history, prompt included, as
 src/main.rs:3714-3733 passes it) and the sampling kernel picks a token per row with the
 draw of that row's stream position. Only token ids and an error word come back to the host.
+This class is the step-by-step form (the histories' token counts are made on the host every
+step); the steps that feed themselves on the device keep those counts on the device
+(``engine/graphs.py``).
 """
 from __future__ import annotations
 
@@ -23,9 +26,15 @@ class Sampler:
 
     @property
     def native_ok(self) -> bool:
-        """Whether the C++ decode loop can sample for this sampler: everything but the
-        adjustments that need each request's history on the host (penalties, bias)."""
+        """Whether the C++ decode loop that samples between graph launches can serve this sampler:
+        everything but the adjustments (penalties, bias), which it does not know."""
         return not self.options.adjusts
+
+    @property
+    def fed_ok(self) -> bool:
+        """Whether steps that pick their own token on the device can serve this sampler: all of
+        them; adjustments ride along as token counts kept on the device."""
+        return True
 
     @property
     def error_word(self) -> torch.Tensor:

@@ -97,20 +97,40 @@ def test_command_line(cuda, model_folders, tmp_path):
         assert key in rec
 
 
-def test_penalties_take_the_python_loop_and_match_plain(cuda, model_folders):
-    """Penalties and bias need each request's history on the host, so these requests run the
-    Python loop instead of the C++ one; both must agree with the plain loop."""
+def test_penalties_and_bias_on_the_device_match_plain(cuda, model_folders):
+    """Penalties and bias ride along in the steps that feed themselves (token counts of each history kept on
+    the device, the chosen tokens counted by the step); with the feeding switched off the same requests run the
+    Python loop with the counts made on the host. Both must agree with the plain loop: greedy, sampled, with
+    stop tokens (short runs, the counts set again at every run) and with requests that end at different times."""
     import camelid_b200
+    from camelid_b200.options import KernelOptions
     name = "tiny_b"
-    lm = camelid_b200.load(model_folders[name], dtype="float32")
-    prompts = [tokens(80 + i, n, CONFIGS[name]["vocab_size"]) for i, n in enumerate([6, 13])]
+    vocab = CONFIGS[name]["vocab_size"]
+    prompts = [tokens(80 + i, n, vocab) for i, n in enumerate([6, 13, 40])]
     cfg, w = pl.read_model(model_folders[name])
-    opts = dict(repeat_penalty=1.3, presence_penalty=0.2, frequency_penalty=0.1, logit_bias=[(5, 2.0)])
-    want = pl.generate(cfg, w, prompts, 10, dtype=torch.float64, **opts)
-    got = lm.generate(prompts, max_tokens=10, stop_token_ids=(), **opts)
-    assert got == want
-    plain_loop = lm.generate(prompts, max_tokens=10, stop_token_ids=())          # the C++ loop
-    assert plain_loop == pl.generate(cfg, w, prompts, 10, dtype=torch.float64)
+    opts = dict(repeat_penalty=1.3, presence_penalty=0.2, frequency_penalty=0.1, logit_bias=[(5, 2.0), (7, -1.0), (5, 0.5)])
+    want = pl.generate(cfg, w, prompts, 40, dtype=torch.float64, **opts)
+    sampled = dict(opts, temperature=0.9, top_k=30, seed=11)
+    want_sampled = pl.generate(cfg, w, prompts, 24, dtype=torch.float64, **sampled)
+    for options in (None, KernelOptions(feed_on_device=False)):
+        lm = camelid_b200.load(model_folders[name], dtype="float32", options=options)
+        seen = []
+        real = lm.model.decode_fed if options is None else None
+        if real is not None:
+            def spy(*a, **k):
+                seen.append(k.get("histories") is not None)
+                return real(*a, **k)
+            lm.model.decode_fed = spy
+        assert lm.generate(prompts, max_tokens=40, stop_token_ids=(), **opts) == want
+        assert lm.generate(prompts, max_tokens=[24, 9, 17], stop_token_ids=(), **sampled) == [
+            want_sampled[0][:24], want_sampled[1][:9], want_sampled[2][:17]]
+        stop = want[0][20]                                  # a stop token in the middle of the first request
+        cut = [t[:t.index(stop) + 1] if stop in t else t for t in want]
+        assert lm.generate(prompts, max_tokens=40, stop_token_ids=(stop,), **opts) == cut
+        if real is not None:
+            assert seen and all(seen), "penalties must ride in the steps that feed themselves"
+        plain_loop = lm.generate(prompts, max_tokens=10, stop_token_ids=())
+        assert plain_loop == pl.generate(cfg, w, prompts, 10, dtype=torch.float64)
 
 
 def test_long_generation_crosses_pages_in_the_native_loop(cuda, model_folders):
