@@ -206,12 +206,14 @@ def _prefill_batch(lm, cache, prompts, chunk: int = 8):
     return slots, firsts
 
 
-def measure_decode_device(lm, cfg, batch: int, prompt_tokens, steps: int, warmup: int, rng, prompts=None) -> dict:
-    """K decode steps timed on the device, in the loop that ``generate`` runs for greedy requests
+def measure_decode_device(lm, cfg, batch: int, prompt_tokens, steps: int, warmup: int, rng, prompts=None,
+                          sampling=None) -> dict:
+    """K decode steps timed on the device, in the loop that ``generate`` runs
     (``DecoderModel.decode_fed``): the captured step graph picks each token and feeds it back on the
     device; per step the host sends the positions from pinned memory and reads the chosen tokens.
     CUDA events bracket exactly the K steps. ``prompt_tokens`` is one length or (lowest, highest);
-    ``prompts`` given wins over it."""
+    ``prompts`` given wins over it. ``sampling`` (``SamplingOptions``): None is greedy; with penalties
+    the prompts and what is generated are the histories."""
     from .csrc import ops
     if prompts is None:
         prompts = _prompts(rng, batch, prompt_tokens, cfg["vocab_size"])
@@ -219,12 +221,16 @@ def measure_decode_device(lm, cfg, batch: int, prompt_tokens, steps: int, warmup
     slots, firsts = _prefill_batch(lm, cache, prompts)
     model = lm.model
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    adjusts = sampling is not None and sampling.adjusts
     with ClockSampler() as clocks:
-        warm = model.decode_fed(cache, slots, firsts, warmup)
+        hist = [list(p) + [int(f)] for p, f in zip(prompts, firsts)] if adjusts else None
+        warm = model.decode_fed(cache, slots, firsts, warmup, sampling, histories=hist)
+        if adjusts:
+            hist = [h + [int(t) for t in warm[:, j]] for j, h in enumerate(hist)]
         torch.cuda.synchronize()
         launches0 = ops.launch_count()
         ev0.record()
-        model.decode_fed(cache, slots, warm[-1].tolist(), steps)
+        model.decode_fed(cache, slots, warm[-1].tolist(), steps, sampling, histories=hist)
         ev1.record()
         torch.cuda.synchronize()
     launches = ops.launch_count() - launches0
@@ -346,6 +352,14 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
             pts[f"decode_b{b}"] = d["value"]
             detail[f"decode_b{b}"] = {"value": d["value"], "ms_per_step": d["ms_per_step"], "bytes": r["bytes"],
                                       "frac": r["frac"]}
+        # the same steps with the stochastic sampler and its adjustments in the graph (not a key of `points`:
+        # those are the two the contract names)
+        from .sampling import SamplingOptions
+        so = SamplingOptions(temperature=0.8, top_k=40, top_p=0.9, seed=1, repeat_penalty=1.1, presence_penalty=0.1)
+        d = measure_decode_device(lm, cfg, batch, prompt_tokens, min(decode_steps, 64), min(warmup, 4), rng,
+                                  sampling=so.validate(cfg["vocab_size"]))
+        detail[f"decode_b{batch}_sampled"] = {"value": d["value"], "ms_per_step": d["ms_per_step"],
+                                             "sampling": "temperature 0.8, top-k 40, top-p 0.9, repeat 1.1, presence 0.1"}
         rec["points"] = pts
         rec["points_detail"] = detail
     if fp32 and dtype == "bfloat16":
