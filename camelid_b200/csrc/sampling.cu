@@ -22,6 +22,7 @@ namespace cg = cooperative_groups;
 
 #define SAMPLE_THREADS 1024
 #define SAMPLE_MAX_TEAM 8      // blocks that may share a row (a portable cluster)
+#define SAMPLE_LIST_WALK 512    // a top_k up to this is finished along its sorted list by one thread
 #define SAMPLE_ERR_NONFINITE 1
 #define SAMPLE_ERR_EMPTY 2
 
@@ -644,8 +645,89 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SamplePa
             select_slow(0ull, (double)sp.top_k, 0, one);
         floor_key = key;
     }
-    // softmax weights and their sum over the candidates
     auto raw_weight = [=](float v, int) { return expf(v / T - max_scaled); };
+    // A short list of candidates (top_k of a few hundred at most, the usual case): their keys are collected and
+    // sorted once, and the rest of the way (the sum, min_p, top_p, the draw) is walked along that list by one
+    // thread of block 0, with the same arithmetic as the passes over the row below.
+    if (floor_key != 0ull && sp.top_k > 0 && sp.top_k <= SAMPLE_LIST_WALK) {
+        FastShared* fs0 = tm.at0(&fs);
+        if (tm.rank == 0 && threadIdx.x == 0) fs.n_list = 0u;
+        tm.sync();
+        for_each_in_slice(row, tm, [&](float v, int i) {
+            const unsigned long long ck = composite_key(v, i);
+            if (ck >= floor_key) {
+                const unsigned int slot = atomicAdd(&fs0->n_list, 1u);
+                if (slot < FS_CAP) fs0->list[slot] = ck;
+            }
+        });
+        tm.sync();
+        if (tm.rank == 0) {
+            const unsigned int n = min(fs.n_list, (unsigned int)FS_CAP);      // top_k keys: the k largest
+            unsigned int m = 1u;
+            while (m < n) m <<= 1;
+            for (unsigned int i = n + threadIdx.x; i < m; i += blockDim.x) fs.list[i] = 0ull;
+            __syncthreads();
+            for (unsigned int k = 2; k <= m; k <<= 1) {
+                for (unsigned int j = k >> 1; j > 0; j >>= 1) {
+                    for (unsigned int i = threadIdx.x; i < m; i += blockDim.x) {
+                        const unsigned int l = i ^ j;
+                        if (l > i) {
+                            const unsigned long long a = fs.list[i], c = fs.list[l];
+                            const bool desc = (i & k) == 0;
+                            if (desc ? (a < c) : (a > c)) { fs.list[i] = c; fs.list[l] = a; }
+                        }
+                    }
+                    __syncthreads();
+                }
+            }
+            for (unsigned int i = threadIdx.x; i < n; i += blockDim.x) fs.lp[i] = raw_weight(value_of_key(fs.list[i]), 0);
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                double total_d = 0.0;
+                for (unsigned int i = 0; i < n; ++i) total_d += (double)fs.lp[i];
+                const float total = (float)total_d;
+                if (!(total > 0.f) || !isfinite(total)) {
+                    atomicOr(err, SAMPLE_ERR_EMPTY);
+                    out[row_index] = 0;
+                } else {
+                    unsigned int cand = n;                              // the candidates are list[0 .. cand)
+                    float renorm = 1.0f, renorm2 = 1.0f;
+                    if (sp.min_p > 0.f) {
+                        const float thr = sp.min_p * (1.0f / total);
+                        double sum = 0.0;
+                        unsigned int kept = 0;
+                        for (unsigned int i = 0; i < cand; ++i) {       // values descend, so do the probabilities
+                            const float pr = fs.lp[i] / total;
+                            if (pr >= thr) { sum += (double)pr; kept = i + 1; }
+                        }
+                        if (kept > 0 && sum > 0.0) { cand = kept; renorm = (float)sum; }
+                    }
+                    if (sp.top_p < 1.0f) {
+                        double c = 0.0;
+                        unsigned int i = 0;
+                        for (; i < cand; ++i) {
+                            c += (double)(fs.lp[i] / total / renorm);
+                            if (c >= (double)sp.top_p) break;
+                        }
+                        if (i < cand) cand = i + 1;                     // never reached: all of them, with their sum
+                        renorm2 = (float)c;
+                    }
+                    const double draw = (double)draws[row_index];
+                    double c = 0.0;
+                    unsigned int i = 0;
+                    for (; i < cand; ++i) {
+                        c += (double)(fs.lp[i] / total / renorm / renorm2);
+                        if (c > draw) break;
+                    }
+                    if (i >= cand) i = cand - 1;                        // never reached: the last candidate
+                    out[row_index] = (int)(0xFFFFFFFFu - (unsigned int)(fs.list[i] & 0xFFFFFFFFull));
+                }
+            }
+        }
+        tm.sync();
+        return;
+    }
+    // softmax weights and their sum over the candidates
     double part = 0.0;
     for_each_in_slice(row, tm, [&](float v, int i) {
         if (composite_key(v, i) >= floor_key) part += (double)raw_weight(v, i);
