@@ -233,6 +233,7 @@ class StepGraph:
         self.graph = None
         self.logits = None
         self.launches = 0
+        self.replays = 0
 
     def load(self, host_vec, slots, starts, news, row0) -> int:
         """The step's integers into the static buffer (one copy from pinned memory)."""
@@ -261,5 +262,6 @@ class StepGraph:
 
     def replay(self) -> torch.Tensor:
         self.graph.replay()
+        self.replays += 1
         ops.add_launches(self.launches)
         return self.logits.clone()          # the next replay writes the same buffer

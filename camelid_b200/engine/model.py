@@ -223,20 +223,34 @@ class DecoderModel:
         key = (tuple(int(a.size) for a in arrays), sum(len(w) for w in want), tuple(len(t[0]) for t in tables))
         graphs = self._step_graphs.setdefault(cache, {})
         graph = graphs.get(key)
+        seen = self._seen_layouts.setdefault(cache, {})         # how often each layout has come by
+        if len(seen) > 4096:
+            seen.clear()
+        seen[key] = seen.get(key, 0) + 1
         if graph is None:
-            seen = self._seen_layouts.setdefault(cache, {})
-            seen[key] = seen.get(key, 0) + 1
-            if seen[key] < 2:
-                if len(seen) > 4096:
-                    seen.clear()
+            # A capture costs tens to hundreds of milliseconds and saves a fraction of one per replay, less the
+            # longer the step: a layout is captured when it comes back (the third time for a long step), and only
+            # if there is room for it after dropping graphs of layouts that have come by less often than this
+            # one (the least recently used first). Layouts that take turns, more of them than the kept rows
+            # hold, have come by equally often: the first ones keep their graphs, the others run eagerly,
+            # instead of each being captured and dropped in turn for ever.
+            rows = sum(int(a.size) for a in arrays)
+            if seen[key] < (2 if rows <= 512 else 3) or rows > self.options.captured_step_rows:
                 return None
+            room = self.options.captured_step_rows - sum(g.rows for g in graphs.values())
+            drop = []
+            for k, g in graphs.items():                          # least recently used first
+                if room >= rows:
+                    break
+                if seen.get(k, 0) < seen[key]:
+                    drop.append(k)
+                    room += g.rows
+            if room < rows:
+                return None
+            for k in drop:
+                del graphs[k]
         layout, host, news, row0 = StepContext.host_arrays(slots, starts, arrays, want, tables, self.tile_sizes)
         if graph is None:
-            rows = sum(news)
-            if rows > self.options.captured_step_rows:
-                return None
-            while graphs and sum(g.rows for g in graphs.values()) + rows > self.options.captured_step_rows:
-                del graphs[next(iter(graphs))]                  # the oldest layout makes room
             graph = StepGraph(self, cache, layout)
             self.last_h2d_bytes = graph.load(host, slots, starts, news, row0)
             logits = graph.run_and_capture()

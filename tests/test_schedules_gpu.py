@@ -201,6 +201,50 @@ def test_a_layout_seen_again_replays_a_captured_step(cuda, model_folders, name, 
     cache.book.audit()
 
 
+def test_layouts_that_take_turns_do_not_evict_each_other_for_ever(cuda, model_folders):
+    """Three layouts of which only one fits the rows kept as captured steps, coming by in turn: the first to
+    come back is captured and stays, the others run eagerly every time (a capture costs far more than a replay
+    saves, so capturing and dropping them in turn would be the worst of both). A fourth layout that then comes
+    by more often than the kept one takes its place. Every step's logits are checked."""
+    import camelid_b200
+    from camelid_b200 import StepEntry
+    from camelid_b200.engine import graphs as graphs_mod
+    from camelid_b200.options import KernelOptions
+    name, dtype = "tiny_b", "float32"
+    lm = camelid_b200.load(model_folders[name], dtype=dtype, options=KernelOptions(captured_step_rows=128))
+    vocab = CONFIGS[name]["vocab_size"]
+    cache = lm.new_cache(256, max_slots=2)
+    captured = []
+    real = graphs_mod.StepGraph.run_and_capture
+
+    def counting(self):
+        captured.append(self.rows)
+        return real(self)
+
+    graphs_mod.StepGraph.run_and_capture = counting
+    try:
+        def run(n, seed):
+            ids = tokens(seed, n, vocab)
+            slot = cache.alloc_slot()
+            got = lm.step(cache, [StepEntry(slot, ids, [n - 1])]).cpu()
+            cache.free_slot(slot)
+            assert_close(got, oracle(model_folders[name], ids)[n - 1:], dtype, f"{n} tokens, seed {seed}")
+
+        for turn in range(5):
+            for n in (100, 90, 80):
+                run(n, 300 + 10 * turn + n)
+        assert captured == [100], captured
+        for again in range(8):
+            run(70, 500 + again)
+        assert captured == [100, 70], captured
+        kept = lm.model._step_graphs[cache]
+        assert [k[0] for k in kept] == [(70,)], list(kept)
+    finally:
+        graphs_mod.StepGraph.run_and_capture = real
+    lm.model.check_device_errors()
+    cache.book.audit()
+
+
 def test_sampled_generation_fed_on_the_device(cuda, model_folders):
     """Temperature sampling (with top-k and top-p) also decodes with the token fed back on the
     device: the draw of each step is made there from the seed and the row's position, the same
