@@ -260,6 +260,8 @@ class DecoderModel:
         self.last_h2d_bytes = graph.load(host, slots, starts, news, row0)
         return graph.replay()
 
+    MAX_DECODE_GRAPHS = 128     # per cache: batch sizes times block-table widths times the ways a step picks its token
+
     def decode_graph(self, cache: SequenceCache, slots: list, feed: bool = False, adjust: bool = False):
         """The captured graph for one-token steps of these slots (made at its first use)."""
         from .graphs import DecodeGraph, bucket_width
@@ -267,10 +269,12 @@ class DecoderModel:
         widths = [bucket_width(max(len(book.pages[g][s]) for s in slots)) for g in range(len(book.kv_specs))]
         graphs = self._graphs.setdefault(cache, {})
         key = (len(slots), tuple(widths), feed, adjust)
-        graph = graphs.get(key)
+        graph = graphs.pop(key, None)
         if graph is None:
             graph = DecodeGraph(self, cache, len(slots), widths, feed, adjust)
-            graphs[key] = graph
+            while len(graphs) >= self.MAX_DECODE_GRAPHS:        # each holds its own buffers: the least recently used goes
+                del graphs[next(iter(graphs))]
+        graphs[key] = graph                                     # most recently used last
         return graph
 
     def decode_natively(self, cache: SequenceCache, slots: list, tokens: list, history_lens: list, max_steps: int,
