@@ -30,8 +30,9 @@ class KernelOptions:
     # Greedy requests decode with the token fed back on the device.
     feed_on_device: bool = True
     # A step of several tokens per sequence whose layout (tokens per sequence, wanted places,
-    # block-table widths) was seen before replays a captured graph; this many rows of such
-    # layouts are kept at most (each keeps a workspace of its own), the oldest dropped first.
+    # block-table widths) has come back replays a captured graph; this many rows of such
+    # layouts are kept at most (each keeps a workspace of its own), and a kept one gives way
+    # only to a layout that has come by more often.
     capture_repeated_steps: bool = True
     captured_step_rows: int = 16384
 
