@@ -343,7 +343,8 @@ def sample(logits: np.ndarray, history, *, temperature=0.0, top_k=None, top_p=No
     if temperature == 0.0:
         return greedy(adjusted)
     T = np.float32(temperature)
-    order = sorted(range(adjusted.shape[0]), key=lambda i: (-float(adjusted[i]), i))
+    # the reference orders by total_cmp (src/inference.rs:6004-6006): +0.0 stands before -0.0, then the index
+    order = sorted(range(adjusted.shape[0]), key=lambda i: (-float(adjusted[i]), bool(np.signbit(adjusted[i])), i))
     if top_k is not None:
         order = order[:min(top_k, len(order))]
     scaled = np.array([np.float32(adjusted[i] / T) for i in order], dtype=np.float32)

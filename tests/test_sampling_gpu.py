@@ -110,7 +110,7 @@ def _interval_of(row, token, temperature, top_k=None, top_p=None, min_p=None):
     (src/inference.rs:5991-6091) are done in float64: candidates by logit descending and index ascending, top_k,
     softmax of logit / T, min_p, top_p prefix, each renormalised. None if the token is no candidate."""
     v = row.astype(np.float64)
-    order = np.lexsort((np.arange(v.shape[0]), -v))
+    order = np.lexsort((np.arange(v.shape[0]), np.signbit(row), -v))       # the reference's total order: +0.0 before -0.0
     if top_k is not None:
         order = order[:min(top_k, order.shape[0])]
     w = np.exp((v[order] - v[order].max()) / temperature)
