@@ -175,7 +175,14 @@ class DecodeGraph:
         if self.graph is None:
             self.capture()
         if self.adjust:
-            self._set_adjustments(histories, options)
+            # What the device holds after a run is what the next run of the same sequences starts from: the
+            # histories' counts are sent again only if this is not that next run (same slots in the same use,
+            # histories grown by exactly the run's steps, the run's last tokens fed, the same options).
+            book = self.cache.book
+            now = (tuple((s, book.generation[s]) for s in slots), tuple(len(h) for h in histories),
+                   tuple(int(t) for t in tokens), self._options_key(options))
+            if now != getattr(self, "_adjust_next", None):
+                self._set_adjustments(histories, options)
         if getattr(self, "_fed", None) is None:
             self._fed = ops.FedDecodeLoop(self.n_seqs, self.ctx.layout, self.ctx.meta_dev, self.host_np[i])
         out = []
@@ -186,8 +193,18 @@ class DecodeGraph:
             out.append(self._fed.run(self.graph.raw_cuda_graph_exec(), first, [s + done for s in starts], slots, k,
                                      self.launches))
             done += k
-        return np.concatenate(out) if len(out) > 1 else out[0]
+        result = np.concatenate(out) if len(out) > 1 else out[0]
+        if self.adjust:
+            book = self.cache.book
+            self._adjust_next = (tuple((s, book.generation[s]) for s in slots), tuple(len(h) + steps for h in histories),
+                                 tuple(int(t) for t in result[-1]), self._options_key(options))
+        return result
 
+
+    @staticmethod
+    def _options_key(options) -> tuple:
+        return (options.repeat_penalty, options.presence_penalty, options.frequency_penalty,
+                tuple((int(t), float(b)) for t, b in options.logit_bias))
 
     def _set_adjustments(self, histories, options) -> None:
         """Counts of each row's history, the dense bias and the penalties to the device (after the
