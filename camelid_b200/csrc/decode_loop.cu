@@ -17,7 +17,8 @@
 extern "C" int cml_argmax_rows(const float* logits, int ld, int rows, int vocab, int* out, int* err,
                                unsigned long long* scratch, void* stream);
 extern "C" int cml_sample_rows(const float* logits, int ld, int rows, int vocab, float temperature, int top_k,
-                               float top_p, float min_p, const float* draws, int* out, int* err, void* stream);
+                               float top_p, float min_p, const float* params_dev, const float* draws, int* out, int* err,
+                               void* stream);
 
 struct CmlDecodeLoop {
     int n;                    // sequences of the batch
@@ -98,7 +99,7 @@ extern "C" int cml_decode_loop_run(void* loop, void* graph_exec, void* stream, c
             for (int i = 0; i < n; ++i) L->draws_host[i] = unit_draw(seed, (uint64_t)(history_lens[i] + step));
             e = cudaMemcpyAsync(L->draws_dev, L->draws_host, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, s);
             if (e != cudaSuccess) return (int)e;
-            rc = cml_sample_rows(L->logits, L->ld, n, L->vocab, temperature, top_k, top_p, min_p, L->draws_dev,
+            rc = cml_sample_rows(L->logits, L->ld, n, L->vocab, temperature, top_k, top_p, min_p, nullptr, L->draws_dev,
                                  L->tokens_dev, L->err_dev, s);
         } else {
             rc = cml_argmax_rows(L->logits, L->ld, n, L->vocab, L->tokens_dev, L->err_dev, L->argmax_scratch, s);

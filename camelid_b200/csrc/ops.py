@@ -74,7 +74,7 @@ _SIGNATURES = {
                                         c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     ("sampling", "cml_draws_at"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     ("sampling", "cml_sample_rows"): [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_void_p,
-                                      c_void_p, c_void_p, c_void_p],
+                                      c_void_p, c_void_p, c_void_p, c_void_p],
     ("random_fill", "cml_random_fill"): [c_void_p, c_int, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_ulonglong,
                                          ctypes.c_double, ctypes.c_double, c_void_p],
 }
@@ -655,14 +655,18 @@ def adjust_logits(logits: torch.Tensor, entries: torch.Tensor, biases: torch.Ten
 
 
 def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float,
-                draws: torch.Tensor, out: torch.Tensor, err: torch.Tensor):
-    _dev(logits, draws, out, err)
+                draws: torch.Tensor, out: torch.Tensor, err: torch.Tensor, params=None):
+    """One token per row of ``logits`` by the reference's stochastic sampler. ``params`` (float32 [4] on the
+    device: temperature, top_k or 0, top_p or 1, min_p or 0), if given, is read by the kernel instead of
+    the four arguments, so that a captured launch serves any values."""
+    _dev(logits, draws, out, err, params)
     rows, vocab = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and draws.dtype == torch.float32
     assert draws.numel() >= rows and out.dtype == torch.int32 and out.numel() >= rows
     _check(_fn("sampling", "cml_sample_rows")(_p(logits), logits.stride(0), rows, vocab, float(temperature),
                                              int(top_k or 0), float(top_p if top_p is not None else 1.0),
-                                             float(min_p or 0.0), _p(draws), _p(out), _p(err), _stream()), "sample_rows")
+                                             float(min_p or 0.0), _p(params), _p(draws), _p(out), _p(err), _stream()),
+           "sample_rows")
 
 
 def adjust_dense(logits: torch.Tensor, counts: torch.Tensor, bias: torch.Tensor, penalties: torch.Tensor):

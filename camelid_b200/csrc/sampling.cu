@@ -566,8 +566,17 @@ struct SampleParams {
 };
 
 __global__ void __launch_bounds__(SAMPLE_THREADS, 1)
-sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SampleParams sp,
-                   const float* __restrict__ draws, int* __restrict__ out, int* __restrict__ err) {
+sample_rows_kernel(const float* __restrict__ logits, int ld, int vocab, SampleParams sp_launch,
+                   const float* __restrict__ params_dev, const float* __restrict__ draws, int* __restrict__ out,
+                   int* __restrict__ err) {
+    // temperature, top_k, top_p, min_p: from device memory where given (a captured graph then serves any of them)
+    SampleParams sp = sp_launch;
+    if (params_dev != nullptr) {
+        sp.temperature = params_dev[0];
+        sp.top_k = (int)params_dev[1];
+        sp.top_p = params_dev[2];
+        sp.min_p = params_dev[3];
+    }
     __shared__ SelectShared sh;
     __shared__ FastShared fs;
     __shared__ TeamSlots ts;
@@ -831,10 +840,13 @@ extern "C" int cml_draws_at(const int* positions, const unsigned long long* seed
 }
 
 // draws[r] in [0, 1) is computed by the host from the seed and the length of the history.
+// `params_dev` (may be null): four floats in device memory, temperature, top_k (0: off), top_p (1: off), min_p (0: off),
+// read by the kernel instead of the arguments.
 extern "C" int cml_sample_rows(const float* logits, int ld, int rows, int vocab, float temperature, int top_k,
-                               float top_p, float min_p, const float* draws, int* out, int* err, void* stream) {
+                               float top_p, float min_p, const float* params_dev, const float* draws, int* out, int* err,
+                               void* stream) {
     if (rows <= 0) return 0;
-    if (vocab <= 0 || !(temperature > 0.f)) return CML_ERR_BAD_SIZE;
+    if (vocab <= 0 || (params_dev == nullptr && !(temperature > 0.f))) return CML_ERR_BAD_SIZE;
     SampleParams sp;
     sp.temperature = temperature;
     sp.top_k = top_k;
@@ -856,7 +868,7 @@ extern "C" int cml_sample_rows(const float* logits, int ld, int rows, int vocab,
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t le = cudaLaunchKernelEx(&cfg, sample_rows_kernel, logits, ld, vocab, sp, draws, out, err);
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, sample_rows_kernel, logits, ld, vocab, sp, params_dev, draws, out, err);
     if (le != cudaSuccess) return (int)le;
     return cml_launch_status();
 }

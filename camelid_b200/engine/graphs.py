@@ -54,9 +54,10 @@ class DecodeGraph:
         self.next_tokens = None
         self.launches = 0
         self._table_key = [None] * _RING
-        if feed and feed is not True:              # a sampling step: the seed lives on the device, any seed replays
-            self.seed = torch.zeros(1, dtype=torch.int64, device=dev)
+        if feed and feed is not True:              # a sampling step: seed, temperature and filters live on the device,
+            self.seed = torch.zeros(1, dtype=torch.int64, device=dev)          # so one graph replays for any of them
             self.draws = torch.zeros(n_seqs, dtype=torch.float32, device=dev)
+            self.sample_params = torch.tensor([1.0, 0.0, 1.0, 0.0], dtype=torch.float32, device=dev)
         if adjust:
             # Bias and penalties inside a step that feeds itself: how often each token stands in a row's
             # history is kept on the device (set from the histories when a run starts, the chosen tokens
@@ -106,11 +107,10 @@ class DecodeGraph:
             ops.adjust_dense(logits, self.counts, self.bias, self.penalties)
         if self.feed is True:
             ops.argmax_rows(logits, self.ctx.tokens, self.model.logit_error_word())
-        elif self.feed:          # ("sample", temperature, top_k, top_p, min_p): the draw from the seed and the position
-            _kind, temperature, top_k, top_p, min_p = self.feed
+        elif self.feed:          # "sample": the draw from the seed and the position, the rest from sample_params
             ops.draws_at(self.ctx.row_pos, self.seed, self.draws)
-            ops.sample_rows(logits, temperature, top_k, top_p, min_p, self.draws, self.ctx.tokens,
-                            self.model.logit_error_word())
+            ops.sample_rows(logits, 1.0, 0, 1.0, 0.0, self.draws, self.ctx.tokens, self.model.logit_error_word(),
+                            params=self.sample_params)
         if self.adjust:
             ops.count_tokens(self.ctx.tokens, self.counts)
         return logits
@@ -170,6 +170,11 @@ class DecodeGraph:
         if self.feed is not True:
             signed = int(seed) & ((1 << 64) - 1)
             self.seed.fill_(signed - (1 << 64) if signed >= (1 << 63) else signed)
+            now = (float(options.temperature), float(options.top_k or 0),
+                   float(options.top_p if options.top_p is not None else 1.0), float(options.min_p or 0.0))
+            if now != getattr(self, "_sample_now", None):
+                self.sample_params.copy_(torch.tensor(now, dtype=torch.float32))
+                self._sample_now = now
         i = self.fill(slots, starts, tokens)
         self.send(i, with_tokens=True)                  # block tables and the static arrays
         if self.graph is None:

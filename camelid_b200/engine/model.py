@@ -333,8 +333,7 @@ class DecoderModel:
         starts = [book.extend(s, steps) for s in slots]
         feed, seed = True, 0
         if sampling is not None and not sampling.greedy:
-            feed = ("sample", float(sampling.temperature), int(sampling.top_k or 0),
-                    float(sampling.top_p if sampling.top_p is not None else 1.0), float(sampling.min_p or 0.0))
+            feed = "sample"              # temperature and filters reach the kernel through device memory
             seed = int(sampling.seed or 0)
         graph = self.decode_graph(cache, slots, feed=feed, adjust=adjust)
         out = graph.run_fed(slots, starts, [int(t) for t in tokens], steps, seed, histories, sampling)

@@ -248,8 +248,8 @@ def test_layouts_that_take_turns_do_not_evict_each_other_for_ever(cuda, model_fo
 def test_sampled_generation_fed_on_the_device(cuda, model_folders):
     """Temperature sampling (with top-k and top-p) also decodes with the token fed back on the
     device: the draw of each step is made there from the seed and the row's position, the same
-    number the host makes, so the tokens are those of the loop that reads every token back, for two
-    seeds through one captured graph, and a request's tokens do not depend on its batch."""
+    number the host makes, so the tokens are those of the loop that reads every token back, for three
+    seeds and settings through one captured graph per batch shape, and a request's tokens do not depend on its batch."""
     import camelid_b200
     from camelid_b200 import KernelOptions
     name = "tiny_a"
@@ -266,6 +266,9 @@ def test_sampled_generation_fed_on_the_device(cuda, model_folders):
         assert a == b, kw
         assert fed.generate(prompts[::-1], max_tokens=30, stop_token_ids=(), **kw) == a[::-1]
     assert runs and all(r == 29 for r in runs)
+    # temperature and the filters reach the kernel through device memory: the three settings shared their graphs
+    sampled = [k for g in fed.model._graphs.values() for k in g if k[2] == "sample"]
+    assert sampled and len(sampled) == len({k[:2] for k in sampled}), sampled
     cfg, w = pl.read_model(model_folders[name])
     want = pl.generate(cfg, w, prompts[:2], 12, temperature=0.8, seed=1234, dtype=torch.float64)
     assert fed.generate(prompts[:2], max_tokens=12, temperature=0.8, seed=1234, stop_token_ids=()) == want
