@@ -275,6 +275,15 @@ def measure_decode_e2e(lm, cfg, batch: int, prompt_tokens, steps: int, warmup: i
 FP32_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12        # plain FMA on every lane of 148 SMs at 1,965 MHz: nominal, 74.4
 
 
+SAMPLED = "temperature 0.8, top-k 40, top-p 0.9, repeat 1.1, presence 0.1"
+
+
+def _sampled_options(cfg):
+    from .sampling import SamplingOptions
+    return SamplingOptions(temperature=0.8, top_k=40, top_p=0.9, seed=1, repeat_penalty=1.1,
+                           presence_penalty=0.1).validate(cfg["vocab_size"])
+
+
 def _roofline(cfg, batch, dec, elem, pk) -> dict:
     bytes_step = decode_bytes(cfg, batch, dec["context"], elem)
     achieved = bytes_step / (dec["ms_per_step"] / 1e3) / 1e9
@@ -285,10 +294,12 @@ def _roofline(cfg, batch, dec, elem, pk) -> dict:
 def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warmup: int = 8, dtype: str = "bfloat16",
         layers: int | None = None, config_index: int = 2, points: bool = True, e2e: bool = True,
         prefill_tokens: int = 2048, prefill: bool = True, decode: bool = True, prompt_range=None,
-        fp32: bool = False, fp32_steps: int = 32) -> dict:
+        fp32: bool = False, fp32_steps: int = 32, sampled: bool = False) -> dict:
     """``prompt_range`` (lowest, highest): prompts of unequal lengths drawn uniformly between the
     two instead of ``prompt_tokens`` each; the record then also times their one prefill step.
-    ``fp32``: the same decode step and prefill again with a float32 model, as an ``fp32`` object."""
+    ``fp32``: the same decode step and prefill again with a float32 model, as an ``fp32`` object.
+    ``sampled``: the timed decode steps pick their tokens with the stochastic sampler and its
+    adjustments (``SAMPLED``) instead of the argmax; the record says so in ``config``."""
     from . import api
     shape = SHAPES[config_index]
     cfg = config_for(config_index, layers)
@@ -309,7 +320,8 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
     # The decode steps are timed first: seconds of dense prefill products put the GPU under its power cap,
     # and the steps right behind them would be timed at the clocks that leaves.
     prompts = _prompts(rng, batch, prompt_range, cfg["vocab_size"]) if prompt_range else None
-    dec = measure_decode_device(lm, cfg, batch, prompt_tokens, decode_steps, warmup, rng, prompts=prompts)
+    dec = measure_decode_device(lm, cfg, batch, prompt_tokens, decode_steps, warmup, rng, prompts=prompts,
+                                sampling=_sampled_options(cfg) if sampled else None)
     pre = timed_prefill()
     pre_batch = None
     if prompts is not None and prefill:
@@ -332,7 +344,8 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                    "tied": cfg["tie_word_embeddings"], "weights": f"random, seed {shape['seed']}",
                    "l2": "inputs larger than L2 (every step reads all weights)", "peaks": pk["source"],
-                   "e2e_steps": e2e_steps, "fp32_steps": fp32_steps if fp32 else 0},
+                   "e2e_steps": e2e_steps, "fp32_steps": fp32_steps if fp32 else 0,
+                   **({"sampling": SAMPLED} if sampled else {})},
         "prefill": {"value": pre["value"], "tokens": pre["tokens"], "ms": pre["ms"], "frac": pre["frac"]},
         "roofline": {k: roof[k] for k in ("bound", "achieved", "peak", "unit", "frac")},
         "clocks": dec["clocks"], "gpu_launches": dec["launches"],
@@ -354,12 +367,9 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
                                       "frac": r["frac"]}
         # the same steps with the stochastic sampler and its adjustments in the graph (not a key of `points`:
         # those are the two the contract names)
-        from .sampling import SamplingOptions
-        so = SamplingOptions(temperature=0.8, top_k=40, top_p=0.9, seed=1, repeat_penalty=1.1, presence_penalty=0.1)
         d = measure_decode_device(lm, cfg, batch, prompt_tokens, min(decode_steps, 64), min(warmup, 4), rng,
-                                  sampling=so.validate(cfg["vocab_size"]))
-        detail[f"decode_b{batch}_sampled"] = {"value": d["value"], "ms_per_step": d["ms_per_step"],
-                                             "sampling": "temperature 0.8, top-k 40, top-p 0.9, repeat 1.1, presence 0.1"}
+                                  sampling=_sampled_options(cfg))
+        detail[f"decode_b{batch}_sampled"] = {"value": d["value"], "ms_per_step": d["ms_per_step"], "sampling": SAMPLED}
         rec["points"] = pts
         rec["points_detail"] = detail
     if fp32 and dtype == "bfloat16":

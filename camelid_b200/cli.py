@@ -149,7 +149,7 @@ def cmd_bench(args) -> int:
     rec = benchmark.run(batch=args.batch, prompt_tokens=args.prompt_tokens, decode_steps=args.decode_steps,
                         warmup=args.warmup, dtype=args.dtype, layers=args.layers, config_index=args.config,
                         points=args.points, e2e=args.e2e, prefill=not args.no_prefill, decode=not args.no_decode,
-                        prefill_tokens=args.prefill_tokens, prompt_range=args.prompt_range)
+                        prefill_tokens=args.prefill_tokens, prompt_range=args.prompt_range, sampled=args.sampled)
     print(json.dumps(rec), flush=True)
     return 0
 
@@ -185,6 +185,8 @@ def main(argv=None) -> int:
     be.add_argument("--prefill-tokens", type=int, default=2048)
     be.add_argument("--points", action="store_true", help="also decode at batch 1 and 64")
     be.add_argument("--e2e", action="store_true", help="also time the loop through the Python entry point")
+    be.add_argument("--sampled", action="store_true",
+                    help="the timed decode steps sample (temperature, top-k, top-p, penalties) instead of taking the argmax")
     be.add_argument("--no-prefill", action="store_true")
     be.add_argument("--no-decode", action="store_true")
     be.add_argument("--ablate", action="store_true",
