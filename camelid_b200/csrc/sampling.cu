@@ -348,7 +348,6 @@ struct FastShared {
     unsigned long long list[FS_CAP];
     float lp[FS_CAP];
     double dred[33];
-    unsigned int ured[33];
     unsigned int n_list;
     int bin;
     int status;              // 0: walk again with `bin`; 1: found; 2: divide the bin; 3: give up (fall back)
